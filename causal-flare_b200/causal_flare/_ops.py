@@ -1,0 +1,156 @@
+"""Thin torch-side launch helpers over the C ABI: allocate outputs, fill argument structs, call."""
+
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import _lib
+
+
+def _prep(t, dtype):
+    if t is None:
+        return None
+    if t.dtype != dtype:
+        t = t.to(dtype)
+    return _lib.kernel_ready(t)
+
+
+def forward(Q, K, V, *, scale, Q_dec=None, K_dec=None, variant=_lib.SOFTMAX, power=2.0, block_size=1, mask=None,
+            state_in=None, want_state=False, want_lse=False, out_dtype=None, out_bhnd=False, path=_lib.PATH_AUTO,
+            want_y=True):
+    """Run flare_forward.  Q_dec / K_dec are None for the shared-weight default.
+
+    Returns (Y, state_out | None, lse_dec | None, lse_enc | None)."""
+    _lib.load()
+    dev = K.device
+    dt = K.dtype
+    _lib.dtype_code(dt)
+    B, N, H, Dk = K.shape
+    M, Dv = Q.shape[1], V.shape[-1]
+    q, k, v = _prep(Q, dt), _prep(K, dt), _prep(V, dt)
+    qd, kd = _prep(Q_dec, dt), _prep(K_dec, dt)
+    y = None
+    if want_y:
+        if out_bhnd:
+            y_store = torch.empty((B, H, N, Dv), device=dev, dtype=dt)
+            y = y_store.permute(0, 2, 1, 3)
+        else:
+            y_store = torch.empty((B, N, H, Dv), device=dev, dtype=dt)
+            y = y_store
+    st_out = None
+    if want_state:
+        st_out = {
+            "m": torch.empty((B, H, M), device=dev, dtype=torch.float32),
+            "d": torch.empty((B, H, M), device=dev, dtype=torch.float32),
+            "u": torch.empty((B, H, M, Dv), device=dev, dtype=torch.float32),
+        }
+    lse_dec = lse_enc = None
+    if want_lse:
+        lse_dec = torch.empty((B, H, N), device=dev, dtype=torch.float32)
+        if block_size > 1:
+            lse_enc = torch.empty((B, H, N // block_size, M), device=dev, dtype=torch.float32)
+    if mask is not None:
+        mask = mask.to(device=dev, dtype=torch.int32).contiguous()
+    if B > 0 and N > 0 or want_state:
+        args = _lib.make_fwd_args(q, k, v, qd, kd, y, scale=scale, variant=variant, power=power,
+                                  block_size=block_size, mask=mask, state_in=state_in, state_out=st_out,
+                                  lse_dec=lse_dec, lse_enc=lse_enc, path=path)
+        _lib.run_forward(args, dev)
+    out = None
+    if want_y:
+        out = y_store if out_dtype in (None, dt) else y_store.to(out_dtype)
+    return out, st_out, lse_dec, lse_enc
+
+
+def backward(Q, K, V, dY, *, scale, Q_dec=None, K_dec=None, variant=_lib.SOFTMAX, power=2.0, block_size=1,
+             dy_bhnd=False):
+    """Run flare_backward.  Returns fp32 dQ, input-dtype dK, dV, and dQ_dec / dK_dec (or None)."""
+    _lib.load()
+    dev = K.device
+    dt = K.dtype
+    B, N, H, Dk = K.shape
+    M, Dv = Q.shape[1], V.shape[-1]
+    q, k, v = _prep(Q, dt), _prep(K, dt), _prep(V, dt)
+    qd, kd = _prep(Q_dec, dt), _prep(K_dec, dt)
+    dy = dY.permute(0, 2, 1, 3) if dy_bhnd else dY
+    dy = _prep(dy, dt)
+    dq = torch.zeros((H, M, Dk), device=dev, dtype=torch.float32)
+    dk = torch.zeros((B, N, H, Dk), device=dev, dtype=dt)
+    dv = torch.zeros((B, N, H, Dv), device=dev, dtype=dt)
+    dqd = torch.zeros((B, N, H, Dk), device=dev, dtype=dt) if qd is not None else None
+    dkd = torch.zeros((H, M, Dk), device=dev, dtype=torch.float32) if kd is not None else None
+    if B > 0 and N > 0:
+        a = _lib.BwdArgs()
+        a.fwd = _lib.make_fwd_args(q, k, v, qd, kd, None, scale=scale, variant=variant, power=power,
+                                   block_size=block_size)
+        a.dy = dy.data_ptr()
+        a.dy_stride_b, a.dy_stride_n, a.dy_stride_h = dy.stride(0), dy.stride(1), dy.stride(2)
+        a.dq, a.dk, a.dv = dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
+        a.dq_dec, a.dk_dec = _lib.ptr(dqd), _lib.ptr(dkd)
+        _lib.run_backward(a, dev)
+    return dq, dk, dv, dqd, dkd
+
+
+def decode_step(Q, k, v, state, *, scale, q_dec=None, K_dec=None, mask=None):
+    """One token: k, v [B,H,D]; state updated in place.  Returns y [B,H,Dv] in k's dtype."""
+    lib = _lib.load()
+    dev = k.device
+    dt = k.dtype
+    B, H, Dk = k.shape
+    M, Dv = Q.shape[1], v.shape[-1]
+    q = _prep(Q, dt)
+    kd = _prep(K_dec, dt)
+    k = k if k.stride(-1) == 1 else k.contiguous()
+    v = v.to(dt) if v.dtype != dt else v
+    v = v if v.stride(-1) == 1 else v.contiguous()
+    if q_dec is not None:
+        q_dec = q_dec.to(dt) if q_dec.dtype != dt else q_dec
+        q_dec = q_dec if q_dec.stride(-1) == 1 else q_dec.contiguous()
+    y = torch.empty((B, H, Dv), device=dev, dtype=dt)
+    a = _lib.DecodeArgs()
+    a.q, a.k, a.v, a.q_dec, a.k_dec, a.y = q.data_ptr(), k.data_ptr(), v.data_ptr(), _lib.ptr(q_dec), _lib.ptr(kd), y.data_ptr()
+    if mask is not None:
+        mask = mask.to(device=dev, dtype=torch.int32).contiguous()
+    a.mask = _lib.ptr(mask)
+    a.state = _lib.state_struct(state)
+    a.B, a.H, a.M, a.Dk, a.Dv = B, H, M, Dk, Dv
+    a.q_stride_h, a.q_stride_m = q.stride(0), q.stride(1)
+    a.k_stride_b, a.k_stride_h = k.stride(0), k.stride(1)
+    a.v_stride_b, a.v_stride_h = v.stride(0), v.stride(1)
+    if q_dec is not None:
+        a.qd_stride_b, a.qd_stride_h = q_dec.stride(0), q_dec.stride(1)
+    if kd is not None:
+        a.kd_stride_h, a.kd_stride_m = kd.stride(0), kd.stride(1)
+    a.scale = float(scale)
+    a.dtype = _lib.dtype_code(dt)
+    rc = lib.flare_decode_step(C.byref(a), _lib.stream_handle(dev))
+    if rc == 2:
+        # shape outside the streaming kernel (value width not a power of two): general walk with N = 1
+        out, new_state, _, _ = forward(
+            Q, k[:, None], v[:, None], scale=scale, Q_dec=None if q_dec is None else q_dec[:, None], K_dec=K_dec,
+            mask=None if mask is None else mask.view(B, 1), state_in=state, want_state=True)
+        for key in ("m", "d", "u"):
+            state[key].copy_(new_state[key])
+        return out[:, 0]
+    _lib.check(rc, "flare_decode_step")
+    return y
+
+
+def merge_states(a, b_list):
+    """Fold the states in ``b_list`` (in order) into ``a``; returns a new state dict."""
+    lib = _lib.load()
+    dev = a["u"].device
+    B, H, M, Dv = a["u"].shape
+    a32 = {k: a[k].float().contiguous() for k in ("m", "d", "u")}
+    bm = torch.stack([b["m"].float() for b in b_list]).contiguous()
+    bd = torch.stack([b["d"].float() for b in b_list]).contiguous()
+    bu = torch.stack([b["u"].float() for b in b_list]).contiguous()
+    out = {k: torch.empty_like(a32[k]) for k in ("m", "d", "u")}
+    sa = _lib.state_struct(a32)
+    sb = _lib.State(bm.data_ptr(), bd.data_ptr(), bu.data_ptr())
+    so = _lib.state_struct(out)
+    rc = lib.flare_state_merge(C.byref(sa), C.byref(sb), C.byref(so), B * H, M, Dv, len(b_list), _lib.stream_handle(dev))
+    _lib.check(rc, "flare_state_merge")
+    return out

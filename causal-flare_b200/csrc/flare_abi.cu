@@ -1,0 +1,289 @@
+// extern "C" entry points of libflare_b200.so: argument validation, launch planning, dispatch.
+#include <stdio.h>
+#include <string.h>
+
+#include "bwd_exact.cuh"
+#include "decode_step.cuh"
+#include "flare_common.cuh"
+#include "state_ops.cuh"
+#include "walk_exact.cuh"
+
+namespace flare {
+
+static thread_local char g_cuda_error[512] = "";
+
+void set_cuda_error(cudaError_t e, const char* where) {
+  snprintf(g_cuda_error, sizeof(g_cuda_error), "%s: %s (%s)", where, cudaGetErrorName(e), cudaGetErrorString(e));
+}
+
+int sm_count() {
+  static int cached = 0;
+  if (cached > 0) return cached;
+  int dev = 0, n = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+      n <= 0) {
+    (void)cudaGetLastError();
+    return 148;  // B200; used only for planning when no device is visible
+  }
+  cached = n;
+  return n;
+}
+
+namespace {
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+bool mult8(int64_t x) { return (x % 8) == 0; }
+
+int check_forward(const flare_fwd_args_t* a) {
+  if (a == nullptr) return FLARE_ERR_BAD_POINTER;
+  if (a->B < 0 || a->N < 0 || a->H <= 0 || a->M <= 0 || a->Dk <= 0 || a->Dv <= 0) return FLARE_ERR_BAD_SHAPE;
+  if ((a->M % 16) || (a->Dk % 16) || (a->Dv % 16)) return FLARE_ERR_BAD_SHAPE;
+  if (a->dtype != FLARE_F32 && a->dtype != FLARE_BF16 && a->dtype != FLARE_F16) return FLARE_ERR_BAD_DTYPE;
+  if (a->variant != FLARE_SOFTMAX && a->variant != FLARE_STABLEMAX) return FLARE_ERR_BAD_CONFIG;
+  if (a->block_size < 1) return FLARE_ERR_BAD_CONFIG;
+  if (a->block_size > 1 && ((a->block_size % 16) || (a->N % a->block_size) || a->variant != FLARE_SOFTMAX ||
+                            a->mask != nullptr))
+    return FLARE_ERR_BAD_CONFIG;
+  if (a->B == 0 || a->N == 0) return FLARE_OK;
+  if (!a->q || !a->k || !a->v) return FLARE_ERR_BAD_POINTER;
+  if (!aligned16(a->q) || !aligned16(a->k) || !aligned16(a->v) || !aligned16(a->q_dec) || !aligned16(a->k_dec) ||
+      !aligned16(a->y))
+    return FLARE_ERR_BAD_POINTER;
+  if (!mult8(a->q_stride_h) || !mult8(a->q_stride_m) || !mult8(a->k_stride_b) || !mult8(a->k_stride_n) ||
+      !mult8(a->k_stride_h) || !mult8(a->v_stride_b) || !mult8(a->v_stride_n) || !mult8(a->v_stride_h))
+    return FLARE_ERR_BAD_POINTER;
+  if (a->q_dec && (!mult8(a->qd_stride_b) || !mult8(a->qd_stride_n) || !mult8(a->qd_stride_h))) return FLARE_ERR_BAD_POINTER;
+  if (a->k_dec && (!mult8(a->kd_stride_h) || !mult8(a->kd_stride_m))) return FLARE_ERR_BAD_POINTER;
+  if (a->y && (!mult8(a->y_stride_b) || !mult8(a->y_stride_n) || !mult8(a->y_stride_h))) return FLARE_ERR_BAD_POINTER;
+  const bool any_in = a->state_in.m || a->state_in.d || a->state_in.u;
+  if (any_in && !(a->state_in.m && a->state_in.d && a->state_in.u)) return FLARE_ERR_BAD_POINTER;
+  const bool any_out = a->state_out.m || a->state_out.d || a->state_out.u;
+  if (any_out && !(a->state_out.m && a->state_out.d && a->state_out.u)) return FLARE_ERR_BAD_POINTER;
+  if (!a->y && !any_out) return FLARE_ERR_BAD_POINTER;
+  if (a->M > 512) return FLARE_ERR_UNSUPPORTED;
+  return FLARE_OK;
+}
+
+struct FwdPlan {
+  int nseg;
+  int seg_len;
+  size_t state_floats;  // floats per state: 2M + M*Dv
+  size_t ws_bytes;
+};
+
+FwdPlan plan_forward(const flare_fwd_args_t* a) {
+  FwdPlan pl{1, a->N > 0 ? a->N : 1, 0, 0};
+  if (a->B == 0 || a->N == 0) return pl;
+  const int64_t lanes = (int64_t)a->B * a->H;
+  const int dd = walk_exact_dd(a->M, a->Dv);
+  const int dtiles = (a->Dv + 32 * dd - 1) / (32 * dd);
+  const int64_t ctas = lanes * dtiles;
+  const int64_t slots = 2LL * sm_count();
+  const int unit = a->block_size > 16 ? a->block_size : 16;
+  int nseg = 1;
+  if (ctas * 2 <= slots) {
+    nseg = (int)((slots + ctas - 1) / ctas);
+    const int max_seg = a->N / (4 * unit);
+    if (nseg > max_seg) nseg = max_seg;
+    if (nseg < 1) nseg = 1;
+  }
+  int seg_len = (a->N + nseg - 1) / nseg;
+  seg_len = (seg_len + unit - 1) / unit * unit;
+  nseg = (a->N + seg_len - 1) / seg_len;
+  pl.nseg = nseg;
+  pl.seg_len = seg_len;
+  pl.state_floats = (size_t)2 * a->M + (size_t)a->M * a->Dv;
+  pl.ws_bytes = nseg > 1 ? align_up((size_t)lanes * nseg * pl.state_floats * 4, 256) : 0;
+  return pl;
+}
+
+void fill_walk(WalkParams& w, const flare_fwd_args_t* a) {
+  memset(&w, 0, sizeof(w));
+  w.q = a->q; w.k = a->k; w.v = a->v; w.qd = a->q_dec; w.kd = a->k_dec;
+  w.y = a->y; w.mask = a->mask;
+  w.B = a->B; w.N = a->N; w.H = a->H; w.M = a->M; w.Dk = a->Dk; w.Dv = a->Dv;
+  w.q_stride_h = a->q_stride_h; w.q_stride_m = a->q_stride_m;
+  w.k_stride_b = a->k_stride_b; w.k_stride_n = a->k_stride_n; w.k_stride_h = a->k_stride_h;
+  w.v_stride_b = a->v_stride_b; w.v_stride_n = a->v_stride_n; w.v_stride_h = a->v_stride_h;
+  w.qd_stride_b = a->qd_stride_b; w.qd_stride_n = a->qd_stride_n; w.qd_stride_h = a->qd_stride_h;
+  w.kd_stride_h = a->kd_stride_h; w.kd_stride_m = a->kd_stride_m;
+  w.y_stride_b = a->y_stride_b; w.y_stride_n = a->y_stride_n; w.y_stride_h = a->y_stride_h;
+  w.scale = a->scale; w.power = a->power;
+  w.dtype = a->dtype; w.variant = a->variant; w.block_size = a->block_size;
+}
+
+int forward_exact(const flare_fwd_args_t* a, cudaStream_t stream) {
+  const FwdPlan pl = plan_forward(a);
+  if (pl.ws_bytes > 0 && (a->workspace == nullptr || a->workspace_bytes < pl.ws_bytes || !aligned16(a->workspace)))
+    return FLARE_ERR_WORKSPACE;
+  const int64_t lanes = (int64_t)a->B * a->H;
+  const bool have_out = a->state_out.u != nullptr;
+  WalkParams w;
+  fill_walk(w, a);
+  w.seg_len = pl.seg_len;
+  w.nseg_total = pl.nseg;
+  if (pl.nseg == 1) {
+    w.in_m = a->state_in.m; w.in_d = a->state_in.d; w.in_u = a->state_in.u;
+    w.in_lane_stride = 1; w.in_seg_stride = 0;
+    w.out_m = a->state_out.m; w.out_d = a->state_out.d; w.out_u = a->state_out.u;
+    w.out_lane_stride = 1; w.out_seg_stride = 0;
+    w.out_mode = have_out ? 2 : 0;
+    w.write_y = a->y != nullptr;
+    w.lse_dec = a->lse_dec; w.lse_enc = a->lse_enc;
+    return launch_walk_exact(w, 1, stream);
+  }
+  // segmented: (A) local state of every segment but the last, (B) exclusive scan with the carry-in,
+  // (C) walk every segment from its prefix state and emit the outputs.
+  float* seg_m = reinterpret_cast<float*>(a->workspace);
+  float* seg_d = seg_m + (size_t)lanes * pl.nseg * a->M;
+  float* seg_u = seg_d + (size_t)lanes * pl.nseg * a->M;
+  WalkParams wa = w;
+  wa.y = nullptr; wa.write_y = 0; wa.lse_dec = nullptr; wa.lse_enc = nullptr;
+  wa.out_m = seg_m; wa.out_d = seg_d; wa.out_u = seg_u;
+  wa.out_lane_stride = pl.nseg; wa.out_seg_stride = 1; wa.out_mode = 1;
+  int rc = launch_walk_exact(wa, pl.nseg - 1, stream);
+  if (rc != FLARE_OK) return rc;
+  FoldParams f;
+  memset(&f, 0, sizeof(f));
+  f.a_m = a->state_in.m; f.a_d = a->state_in.d; f.a_u = a->state_in.u;
+  f.s_m = seg_m; f.s_d = seg_d; f.s_u = seg_u;
+  f.lane_stride = pl.nseg; f.seg_stride = 1; f.count = pl.nseg; f.mode = 0;
+  f.lanes = lanes; f.M = a->M; f.Dv = a->Dv; f.stablemax = a->variant == FLARE_STABLEMAX;
+  rc = launch_fold(f, stream);
+  if (rc != FLARE_OK) return rc;
+  w.in_m = seg_m; w.in_d = seg_d; w.in_u = seg_u;
+  w.in_lane_stride = pl.nseg; w.in_seg_stride = 1;
+  w.out_m = a->state_out.m; w.out_d = a->state_out.d; w.out_u = a->state_out.u;
+  w.out_lane_stride = 1; w.out_seg_stride = 0;
+  w.out_mode = have_out ? 2 : 0;
+  w.write_y = a->y != nullptr;
+  w.lse_dec = a->lse_dec; w.lse_enc = a->lse_enc;
+  if (!w.write_y && !have_out) return FLARE_OK;
+  return launch_walk_exact(w, pl.nseg, stream);
+}
+
+}  // namespace
+}  // namespace flare
+
+using namespace flare;
+
+extern "C" {
+
+size_t flare_forward_workspace_bytes(const flare_fwd_args_t* args) {
+  if (check_forward(args) != FLARE_OK) return 0;
+  return plan_forward(args).ws_bytes;
+}
+
+int flare_forward(const flare_fwd_args_t* args, flare_stream_t stream) {
+  const int rc = check_forward(args);
+  if (rc != FLARE_OK) return rc;
+  if (args->B == 0 || args->N == 0) {
+    // empty sequence: the state passes through unchanged
+    if (args->state_out.u != nullptr && args->B > 0) {
+      FoldParams f;
+      memset(&f, 0, sizeof(f));
+      f.a_m = args->state_in.m; f.a_d = args->state_in.d; f.a_u = args->state_in.u;
+      f.count = 0; f.mode = 1;
+      f.o_m = args->state_out.m; f.o_d = args->state_out.d; f.o_u = args->state_out.u;
+      f.lanes = (int64_t)args->B * args->H; f.M = args->M; f.Dv = args->Dv;
+      f.stablemax = args->variant == FLARE_STABLEMAX;
+      f.count = 1; f.mode = 0;  // degenerate scan: writes `a` into slot 0 = the output state
+      f.s_m = f.o_m; f.s_d = f.o_d; f.s_u = f.o_u; f.lane_stride = 1; f.seg_stride = 0;
+      return launch_fold(f, stream);
+    }
+    return FLARE_OK;
+  }
+  return forward_exact(args, stream);
+}
+
+size_t flare_backward_workspace_bytes(const flare_bwd_args_t* args) {
+  if (args == nullptr || check_forward(&args->fwd) != FLARE_OK) return 0;
+  return bwd_exact_workspace_bytes(*args);
+}
+
+int flare_backward(const flare_bwd_args_t* args, flare_stream_t stream) {
+  if (args == nullptr) return FLARE_ERR_BAD_POINTER;
+  flare_fwd_args_t chk = args->fwd;
+  chk.y = const_cast<void*>(args->dy);  // reuse the forward validation for the shared fields
+  chk.y_stride_b = args->dy_stride_b; chk.y_stride_n = args->dy_stride_n; chk.y_stride_h = args->dy_stride_h;
+  chk.mask = nullptr;
+  chk.state_in = flare_state_t{nullptr, nullptr, nullptr};
+  chk.state_out = flare_state_t{nullptr, nullptr, nullptr};
+  const int rc = check_forward(&chk);
+  if (rc != FLARE_OK) return rc;
+  if (!args->dq || !args->dk || !args->dv || !args->dy) return FLARE_ERR_BAD_POINTER;
+  if ((args->fwd.q_dec != nullptr) != (args->dq_dec != nullptr)) return FLARE_ERR_BAD_POINTER;
+  if ((args->fwd.k_dec != nullptr) != (args->dk_dec != nullptr)) return FLARE_ERR_BAD_POINTER;
+  return bwd_exact(*args, stream);
+}
+
+int flare_decode_step(const flare_decode_args_t* a, flare_stream_t stream) {
+  if (a == nullptr) return FLARE_ERR_BAD_POINTER;
+  if (a->B < 0 || a->H <= 0 || a->M <= 0 || a->Dk <= 0 || a->Dv <= 0) return FLARE_ERR_BAD_SHAPE;
+  if ((a->M % 16) || (a->Dk % 16) || (a->Dv % 16)) return FLARE_ERR_BAD_SHAPE;
+  if (a->dtype != FLARE_F32 && a->dtype != FLARE_BF16 && a->dtype != FLARE_F16) return FLARE_ERR_BAD_DTYPE;
+  if (a->B == 0) return FLARE_OK;
+  if (!a->q || !a->k || !a->v || !a->y || !a->state.m || !a->state.d || !a->state.u) return FLARE_ERR_BAD_POINTER;
+  if (!aligned16(a->q) || !aligned16(a->k_dec) || !aligned16(a->y) || !aligned16(a->state.u)) return FLARE_ERR_BAD_POINTER;
+  if (!mult8(a->q_stride_h) || !mult8(a->q_stride_m)) return FLARE_ERR_BAD_POINTER;
+  if (a->k_dec && (!mult8(a->kd_stride_h) || !mult8(a->kd_stride_m))) return FLARE_ERR_BAD_POINTER;
+  if (!decode_step_supported(a->M, a->Dk, a->Dv)) return FLARE_ERR_UNSUPPORTED;
+  DecodeParams p;
+  memset(&p, 0, sizeof(p));
+  p.q = a->q; p.k = a->k; p.v = a->v; p.qd = a->q_dec; p.kd = a->k_dec; p.y = a->y; p.mask = a->mask;
+  p.m = a->state.m; p.d = a->state.d; p.u = a->state.u;
+  p.B = a->B; p.H = a->H; p.M = a->M; p.Dk = a->Dk; p.Dv = a->Dv;
+  p.q_stride_h = a->q_stride_h; p.q_stride_m = a->q_stride_m;
+  p.k_stride_b = a->k_stride_b; p.k_stride_h = a->k_stride_h;
+  p.v_stride_b = a->v_stride_b; p.v_stride_h = a->v_stride_h;
+  p.qd_stride_b = a->qd_stride_b; p.qd_stride_h = a->qd_stride_h;
+  p.kd_stride_h = a->kd_stride_h; p.kd_stride_m = a->kd_stride_m;
+  p.scale = a->scale; p.dtype = a->dtype;
+  return launch_decode_step(p, stream);
+}
+
+int flare_state_merge(const flare_state_t* a, const flare_state_t* b, const flare_state_t* out, int64_t lanes, int32_t M,
+                      int32_t Dv, int32_t count, flare_stream_t stream) {
+  if (!a || !b || !out || !b->m || !b->d || !b->u || !out->m || !out->d || !out->u) return FLARE_ERR_BAD_POINTER;
+  if (lanes < 0 || M <= 0 || Dv <= 0 || count < 1) return FLARE_ERR_BAD_SHAPE;
+  FoldParams f;
+  memset(&f, 0, sizeof(f));
+  f.a_m = a->m; f.a_d = a->d; f.a_u = a->u;
+  f.s_m = b->m; f.s_d = b->d; f.s_u = b->u;
+  f.lane_stride = 1; f.seg_stride = lanes; f.count = count; f.mode = 1;
+  f.o_m = out->m; f.o_d = out->d; f.o_u = out->u;
+  f.lanes = lanes; f.M = M; f.Dv = Dv;
+  return launch_fold(f, stream);
+}
+
+const char* flare_status_string(int status) {
+  switch (status) {
+    case FLARE_OK: return "ok";
+    case FLARE_ERR_BAD_SHAPE: return "bad shape: sizes must be positive and M, Dk, Dv multiples of 16";
+    case FLARE_ERR_UNSUPPORTED: return "shape not supported by the kernels";
+    case FLARE_ERR_BAD_POINTER: return "missing tensor, or pointer/stride not 16-byte aligned";
+    case FLARE_ERR_WORKSPACE: return "workspace missing or too small";
+    case FLARE_ERR_BAD_DTYPE: return "unsupported dtype";
+    case FLARE_ERR_BAD_CONFIG: return "invalid variant / block_size / mask combination";
+    case FLARE_ERR_CUDA: return "CUDA runtime error";
+    case FLARE_ERR_TOO_LARGE: return "request exceeds the fixed capacity of this entry point";
+    default: return "unknown status";
+  }
+}
+
+const char* flare_last_cuda_error(void) { return g_cuda_error; }
+
+int flare_abi_version(void) { return 1; }
+
+/* sizeof of the argument structs, so a foreign-language binding can verify its own layout */
+size_t flare_abi_sizeof(int which) {
+  switch (which) {
+    case 0: return sizeof(flare_fwd_args_t);
+    case 1: return sizeof(flare_bwd_args_t);
+    case 2: return sizeof(flare_decode_args_t);
+    case 3: return sizeof(flare_state_t);
+    default: return 0;
+  }
+}
+
+}  // extern "C"

@@ -1,0 +1,25 @@
+// Associative combination of online-softmax states (see state_ops.cu).
+#pragma once
+#include "flare_common.cuh"
+
+namespace flare {
+
+struct FoldParams {
+  // optional left operand (all null: the empty state); one state per lane
+  const float *a_m, *a_d, *a_u;
+  // `count` states per lane, state j of lane l at index l * lane_stride + j * seg_stride
+  float *s_m, *s_d, *s_u;
+  int64_t lane_stride, seg_stride;
+  int count;
+  // mode 0: s[j] <- a (+) s[0] (+) ... (+) s[j-1] in place (exclusive scan; s[count-1] is only written)
+  // mode 1: o <- a (+) s[0] (+) ... (+) s[count-1]
+  int mode;
+  float *o_m, *o_d, *o_u;
+  int64_t lanes;
+  int M, Dv;
+  int stablemax;  // the empty state has m = 0 instead of -inf
+};
+
+int launch_fold(const FoldParams& p, cudaStream_t stream);
+
+}  // namespace flare

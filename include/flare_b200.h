@@ -1,0 +1,167 @@
+/*
+ * flare_b200.h — C ABI of libflare_b200.so: Causal FLARE attention kernels for NVIDIA B200 (sm_100a).
+ *
+ * Every entry point takes plain device pointers and sizes, launches on the given CUDA stream and
+ * returns an int status (FLARE_OK == 0).  Nothing here allocates device memory unless stated; scratch
+ * is passed in by the caller (size from the matching *_workspace_bytes query).  No call synchronises.
+ *
+ * Tensor layouts are the public ones of the `causal_flare` Python package:
+ *   Q      [H, M, Dk]       latent queries, shared over the batch
+ *   K      [B, N, H, Dk]    token keys            V [B, N, H, Dv]   token values
+ *   Q_dec  [B, N, H, Dk]    optional decode-side queries (NULL: use K)
+ *   K_dec  [H, M, Dk]       optional decode-side keys    (NULL: use Q)
+ *   Y      [B, N, H, Dv]    output (any (b, n, h) strides, so [B, H, N, Dv] is expressible)
+ *   state  m, d [B, H, M] fp32 and u [B, H, M, Dv] fp32 (running max, denominator, numerator)
+ * The innermost dimension of every tensor is contiguous; the other strides are given in ELEMENTS.
+ * M, Dk and Dv must be multiples of 16.
+ */
+#ifndef FLARE_B200_H_
+#define FLARE_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* flare_stream_t; /* same handle type as cudaStream_t */
+
+enum flare_status {
+  FLARE_OK = 0,
+  FLARE_ERR_BAD_SHAPE = 1,      /* a dimension is zero/negative or not a multiple of 16 */
+  FLARE_ERR_UNSUPPORTED = 2,    /* shape outside what the kernels cover (e.g. M > 512) */
+  FLARE_ERR_BAD_POINTER = 3,    /* NULL where a tensor is required, or not 16-byte aligned */
+  FLARE_ERR_WORKSPACE = 4,      /* workspace missing or smaller than *_workspace_bytes says */
+  FLARE_ERR_BAD_DTYPE = 5,
+  FLARE_ERR_BAD_CONFIG = 6,     /* block_size does not divide N, bad variant, ... */
+  FLARE_ERR_CUDA = 7,           /* a CUDA runtime call failed; see flare_last_cuda_error() */
+  FLARE_ERR_TOO_LARGE = 8       /* request exceeds a fixed capacity of the entry point */
+};
+
+enum flare_dtype { FLARE_F32 = 0, FLARE_BF16 = 1, FLARE_F16 = 2 };
+
+/* Encoder weight of a token for a latent: exp(s) (softmax, tracked online with a running max) or
+ * the stablemax transform sigma(s) = (1+s)^p for s >= 0, (1-s)^-p for s < 0. */
+enum flare_variant { FLARE_SOFTMAX = 0, FLARE_STABLEMAX = 1 };
+
+/* Which implementation a call may use. AUTO picks the tensor-core path when the shape qualifies. */
+enum flare_path { FLARE_PATH_AUTO = 0, FLARE_PATH_EXACT = 1, FLARE_PATH_TENSOR = 2 };
+
+typedef struct flare_state {
+  float* m; /* [B, H, M]      running max per latent (ignored for stablemax) */
+  float* d; /* [B, H, M]      running denominator */
+  float* u; /* [B, H, M, Dv]  running un-normalised numerator */
+} flare_state_t;
+
+/*
+ * Forward problem.  Replaces the kernel launch sequences behind
+ *   flare_autoregressive_triton            causal_flare/autoregressive/training.py:4921 (forward :733-905)
+ *   flare_autoregressive_prefill_triton    causal_flare/autoregressive/inference.py:624-820
+ *   flare_recurrent_triton (forward)       causal_flare/autoregressive/recurrent.py:288-414
+ *   flare_autoregressive_stablemax_triton  causal_flare/autoregressive/stablemax_triton.py:1709-1978
+ *   flare_semi_autoregressive_trition      causal_flare/semi_autoregressive/training.py:1836-1961
+ */
+typedef struct flare_fwd_args {
+  const void* q;
+  const void* k;
+  const void* v;
+  const void* q_dec; /* NULL: weight sharing with k */
+  const void* k_dec; /* NULL: weight sharing with q */
+  void* y;           /* same dtype as the inputs; may be NULL when only the final state is wanted */
+  const int32_t* mask;      /* [B, N] int32, 0 = token leaves the state untouched and emits y = 0; may be NULL */
+  flare_state_t state_in;   /* all NULL: start from the empty state (m=-inf, d=0, u=0) */
+  flare_state_t state_out;  /* all NULL: final state not written */
+  float* lse_dec;           /* [B, H, N] log-sum-exp of the decode scores; may be NULL */
+  float* lse_enc;           /* [B, H, N/block_size, M] log normaliser after each block; semi-AR only; may be NULL */
+  void* workspace;
+  size_t workspace_bytes;
+  int32_t B, N, H, M, Dk, Dv;
+  int64_t q_stride_h, q_stride_m;
+  int64_t k_stride_b, k_stride_n, k_stride_h;
+  int64_t v_stride_b, v_stride_n, v_stride_h;
+  int64_t qd_stride_b, qd_stride_n, qd_stride_h;
+  int64_t kd_stride_h, kd_stride_m;
+  int64_t y_stride_b, y_stride_n, y_stride_h;
+  float scale;
+  float power;        /* stablemax exponent p */
+  int32_t dtype;      /* flare_dtype of q, k, v, q_dec, k_dec, y */
+  int32_t variant;    /* flare_variant */
+  int32_t block_size; /* 1: token-causal (autoregressive); > 1: block-causal (semi-autoregressive) */
+  int32_t path;       /* flare_path */
+} flare_fwd_args_t;
+
+size_t flare_forward_workspace_bytes(const flare_fwd_args_t* args);
+int flare_forward(const flare_fwd_args_t* args, flare_stream_t stream);
+
+/*
+ * Backward problem: gradients of <Y, dY>.  Replaces
+ *   _chunked_flare_lse_backward_impl       causal_flare/autoregressive/training.py:4369-4918
+ *   _recurrent_flare_backward_impl         causal_flare/autoregressive/recurrent.py:749-935
+ *   FLAREAutoregressiveStablemaxTriton.backward   causal_flare/autoregressive/stablemax_triton.py:1981-2420
+ *   _semi_autoregressive_backward_impl     causal_flare/semi_autoregressive/training.py:3768-3987
+ * Nothing but the inputs is needed from the forward: intermediates are recomputed.
+ * dq / dk_dec are fp32 [H, M, Dk] (summed over the batch); dk, dv, dq_dec have the input dtype and the
+ * input's shape, densely packed.  With weight sharing (q_dec/k_dec NULL) the decode-side gradients are
+ * folded into dk / dq and dq_dec / dk_dec must be NULL.
+ */
+typedef struct flare_bwd_args {
+  flare_fwd_args_t fwd; /* y, mask, state_*, lse_* are ignored */
+  const void* dy;       /* [B, N, H, Dv], input dtype */
+  int64_t dy_stride_b, dy_stride_n, dy_stride_h;
+  float* dq;            /* [H, M, Dk] fp32 */
+  void* dk;             /* [B, N, H, Dk] contiguous */
+  void* dv;             /* [B, N, H, Dv] contiguous */
+  void* dq_dec;         /* [B, N, H, Dk] contiguous or NULL */
+  float* dk_dec;        /* [H, M, Dk] fp32 or NULL */
+} flare_bwd_args_t;
+
+size_t flare_backward_workspace_bytes(const flare_bwd_args_t* args);
+int flare_backward(const flare_bwd_args_t* args, flare_stream_t stream);
+
+/*
+ * One decode token per (batch, head): updates (m, d, u) IN PLACE and writes y [B, H, Dv].
+ * Replaces flare_recurrent_step_kernel and its wrapper flare_autoregressive_decode_triton,
+ * causal_flare/autoregressive/inference.py:359-489, :492-621.
+ */
+typedef struct flare_decode_args {
+  const void* q;      /* [H, M, Dk] */
+  const void* k;      /* [B, H, Dk] */
+  const void* v;      /* [B, H, Dv] */
+  const void* q_dec;  /* [B, H, Dk] or NULL */
+  const void* k_dec;  /* [H, M, Dk] or NULL */
+  void* y;            /* [B, H, Dv], input dtype, contiguous */
+  const int32_t* mask; /* [B] or NULL */
+  flare_state_t state; /* updated in place; contiguous */
+  int32_t B, H, M, Dk, Dv;
+  int64_t q_stride_h, q_stride_m;
+  int64_t k_stride_b, k_stride_h;
+  int64_t v_stride_b, v_stride_h;
+  int64_t qd_stride_b, qd_stride_h;
+  int64_t kd_stride_h, kd_stride_m;
+  float scale;
+  int32_t dtype;
+} flare_decode_args_t;
+
+int flare_decode_step(const flare_decode_args_t* args, flare_stream_t stream);
+
+/*
+ * out = merge(a, b): the associative combination of two online-softmax states over `lanes` = B*H
+ * independent (batch, head) lanes; `out` may alias `a` or `b`.  Replaces _merge_flare_stats,
+ * causal_flare/autoregressive/inference.py:194-228.  With `count` > 1, `b` holds `count` states
+ * back to back (state j at offset j*lanes) which are folded in order into `a`.
+ */
+int flare_state_merge(const flare_state_t* a, const flare_state_t* b, const flare_state_t* out,
+                      int64_t lanes, int32_t M, int32_t Dv, int32_t count, flare_stream_t stream);
+
+const char* flare_status_string(int status);
+const char* flare_last_cuda_error(void);
+int flare_abi_version(void);
+/* sizeof(flare_fwd_args_t / flare_bwd_args_t / flare_decode_args_t / flare_state_t) for which = 0..3,
+ * so that a foreign-language binding can verify its struct layout at load time. */
+size_t flare_abi_sizeof(int which);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FLARE_B200_H_ */
