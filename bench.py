@@ -1,0 +1,340 @@
+"""Benchmark of the Causal FLARE hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--skip-decode]
+
+One JSON line on stdout (rank 0).  Metric: chunked causal prefill throughput in Mtok/s on the
+BASELINE "C2" workload (B=8, N=8192, H=16, M=128 latents, D=64, bf16 in / fp32 accumulate), one full
+workload per GPU (weak scaling: batch x head lanes are independent, no data-path collective).
+A step = one forward over the whole batch.  Extra keys: ``decode`` (C3: 512 single-token steps on a
+B=64, H=32, M=256, D=128 fp32 state, tok/s and achieved HBM GB/s), ``roofline``, ``cpu_baseline``,
+``e2e`` (host buffers, copies inside the timed region), ``clocks``, ``gpu_launches``.
+
+``--impl reference`` times the reference algorithm's CPU path (the oracle port of the reference's
+PyTorch loop) on the host cores, on a bounded sample of the same workload.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for _p in (ROOT, os.path.join(ROOT, "causal-flare_b200")):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+import torch  # noqa: E402
+
+C2 = dict(B=8, N=8192, H=16, M=128, Dk=64, Dv=64)
+C3 = dict(B=64, H=32, M=256, Dk=128, Dv=128, prefix=32768, steps=512)
+L2_BYTES = 126e6
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return dict(hbm_gbs=float(p["hbm_gbs"]), bf16_tflops=float(p["bf16_tflops"]), source="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.samples = []
+        self.proc = None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) >= 6:
+                self.samples.append(parts)
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        sm = [float(s[0]) for s in self.samples if s[0].replace(".", "").isdigit()]
+        mx = [float(s[1]) for s in self.samples if s[1].replace(".", "").isdigit()]
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        reasons = [n for i, n in enumerate(names) if any(s[2 + i].lower().startswith("active") for s in self.samples)]
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(self.samples)}
+
+
+def dist_setup(n_gpus: int):
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        import torch.distributed as dist
+
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    else:
+        torch.cuda.set_device(0)
+    return rank, world, local
+
+
+def barrier(world):
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+def max_over_ranks(x: float, world: int) -> float:
+    if world == 1:
+        return x
+    import torch.distributed as dist
+
+    t = torch.tensor([x], device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def device_inputs(cfg, seed, dtype=torch.bfloat16):
+    """N(0,1) inputs generated on the device from a seeded generator (values only matter statistically here;
+    the parity tests use the CPU-seeded generator shared with the oracle)."""
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    q = torch.randn(cfg["H"], cfg["M"], cfg["Dk"], generator=g, device="cuda").to(dtype)
+    k = torch.randn(cfg["B"], cfg["N"], cfg["H"], cfg["Dk"], generator=g, device="cuda").to(dtype)
+    v = torch.randn(cfg["B"], cfg["N"], cfg["H"], cfg["Dv"], generator=g, device="cuda").to(dtype)
+    return q, k, v
+
+
+def bench_prefill(args, rank, world):
+    import causal_flare as cf
+    from causal_flare import _lib
+
+    lib = _lib.load()
+    cfg = C2
+    q, k, v = device_inputs(cfg, seed=1234 + rank)
+    tokens = cfg["B"] * cfg["N"]
+    fn = lambda: cf.flare_autoregressive_triton(q, k, v)  # noqa: E731
+
+    ev_b = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    ev_e = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    for e in ev_b + ev_e:
+        e.record()  # materialise the handles
+    for _ in range(args.warmup):
+        fn()
+    barrier(world)
+    t0 = torch.cuda.Event(enable_timing=True)
+    t1 = torch.cuda.Event(enable_timing=True)
+    with ClockSampler(torch.cuda.current_device()) as clk:
+        t0.record()
+        for i in range(args.steps):
+            lib.flare_set_kernel_events(ev_b[i].cuda_event, ev_e[i].cuda_event)
+            y = fn()
+        t1.record()
+        lib.flare_set_kernel_events(None, None)
+        barrier(world)
+    launches = lib.flare_last_launch_count() * args.steps
+    ms = t0.elapsed_time(t1)
+    ms = max_over_ranks(ms, world)
+    kern_ms = statistics.mean(b.elapsed_time(e) for b, e in zip(ev_b, ev_e))
+    value = world * tokens * args.steps / (ms * 1e-3) / 1e6
+
+    # ---- end to end: pinned host buffers in, result back to the host, every step ---------------------
+    kh, vh = k.cpu().pin_memory(), v.cpu().pin_memory()
+    yh = torch.empty(y.shape, dtype=y.dtype).pin_memory()
+    kd, vd = torch.empty_like(k), torch.empty_like(v)
+
+    def e2e_step():
+        kd.copy_(kh, non_blocking=True)
+        vd.copy_(vh, non_blocking=True)
+        yy = cf.flare_autoregressive_triton(q, kd, vd)
+        yh.copy_(yy, non_blocking=True)
+
+    e2e_steps = max(2, min(args.steps, 5))
+    e2e_step()
+    barrier(world)
+    s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    s1.record()
+    barrier(world)
+    e2e_ms = max_over_ranks(s0.elapsed_time(s1), world)
+    e2e = {
+        "value": world * tokens * e2e_steps / (e2e_ms * 1e-3) / 1e6, "unit": "Mtok/s",
+        "h2d_bytes_per_step": kh.numel() * 2 + vh.numel() * 2, "d2h_bytes_per_step": yh.numel() * 2,
+        "steps": e2e_steps, "call": "causal_flare.flare_autoregressive_triton(q, k, v)",
+    }
+
+    pk = peaks()
+    alg_bytes = (k.numel() + v.numel() + y.numel()) * 2 + q.numel() * 2
+    alg_flops = 6.0 * cfg["M"] * cfg["Dk"] * cfg["B"] * cfg["N"] * cfg["H"]
+    achieved = alg_bytes / (kern_ms * 1e-3) / 1e9
+    roofline = {
+        "bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": achieved / pk["hbm_gbs"],
+        "traffic": None, "peak_source": pk["source"], "kernel_ms": kern_ms,
+        "kernel": "dominant forward kernel (CUDA events recorded around it inside flare_forward)",
+        "algorithmic_bytes": alg_bytes,
+        "tensor_frac": alg_flops / (kern_ms * 1e-3) / 1e12 / pk["bf16_tflops"],
+    }
+    return dict(value=value, ms_per_step=ms / args.steps, e2e=e2e, roofline=roofline, clocks=clk.summary(),
+                gpu_launches=launches, tokens_per_step=tokens)
+
+
+def bench_decode(args, rank, world):
+    import causal_flare as cf
+
+    c = C3
+    B, H, M, Dk, Dv = c["B"], c["H"], c["M"], c["Dk"], c["Dv"]
+    sc = Dk ** -0.5
+    g = torch.Generator(device="cuda").manual_seed(99 + rank)
+    q = torch.randn(H, M, Dk, generator=g, device="cuda").bfloat16()
+    # prefix prefill in batch slices (K+V of the full prefix would be 69 GB)
+    state = {"m": torch.empty(B, H, M, device="cuda"), "d": torch.empty(B, H, M, device="cuda"),
+             "u": torch.empty(B, H, M, Dv, device="cuda")}
+    sl = 4
+    prefix = args.decode_prefix
+    for b0 in range(0, B, sl):
+        kk = torch.randn(sl, prefix, H, Dk, generator=g, device="cuda").bfloat16()
+        vv = torch.randn(sl, prefix, H, Dv, generator=g, device="cuda").bfloat16()
+        _, st = cf.flare_autoregressive_prefill_triton(q, kk, vv, scale=sc)
+        for key in state:
+            state[key][b0:b0 + sl] = st[key]
+        del kk, vv, st
+    steps = c["steps"]
+    ks = torch.randn(steps, B, H, Dk, generator=g, device="cuda").bfloat16()
+    vs = torch.randn(steps, B, H, Dv, generator=g, device="cuda").bfloat16()
+    for i in range(8):
+        cf.flare_autoregressive_decode_triton(q, ks[i], vs[i], state, scale=sc)
+    barrier(world)
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for i in range(steps):
+        y, state = cf.flare_autoregressive_decode_triton(q, ks[i], vs[i], state, scale=sc)
+    t1.record()
+    barrier(world)
+    ms = max_over_ranks(t0.elapsed_time(t1), world)
+    assert torch.isfinite(y.float()).all()
+    step_bytes = 2 * B * H * M * Dv * 4 + 4 * B * H * M * 4 + H * M * Dk * 2 + B * H * (Dk + Dv) * 2 + B * H * Dv * 2
+    pk = peaks()
+    gbs = step_bytes * steps / (ms * 1e-3) / 1e9
+    return {
+        "workload": f"C3 decode B={B} H={H} M={M} D={Dk}, fp32 state after a {prefix}-token bf16 prefix, {steps} steps",
+        "tok_per_s": world * B * steps / (ms * 1e-3), "us_per_step": ms * 1e3 / steps, "hbm_gbs": gbs,
+        "hbm_frac": gbs / pk["hbm_gbs"], "bytes_per_step": step_bytes, "gpu_launches": steps,
+        "state_bytes": B * H * M * Dv * 4, "l2": "state 268 MB > 126 MB L2",
+    }
+
+
+def cpu_reference_sample(threads=None):
+    """The reference algorithm on the host: fp32 token recurrence over a bounded slice of C2."""
+    from oracle import flare_oracle as orc
+
+    if threads:
+        torch.set_num_threads(threads)
+    cfg = C2
+    Bs, Ns = 2, cfg["N"]
+    q, k, v = orc.make_inputs(Bs, Ns, cfg["H"], cfg["M"], cfg["Dk"], cfg["Dv"], seed0=0, dtype=torch.bfloat16)
+    orc.ar_forward(q, k[:, :16], v[:, :16], dtype=torch.float32)
+    t = time.perf_counter()
+    orc.ar_forward(q, k, v, dtype=torch.float32)
+    dt = time.perf_counter() - t
+    return dict(value=Bs * Ns / dt / 1e6, unit="Mtok/s", cores=torch.get_num_threads(), kind="port", seconds=dt,
+                sample=f"{Bs} of {cfg['B']} batch rows, all {Ns} tokens and {cfg['H']} heads, fp32 token recurrence "
+                       "(oracle port of the reference's PyTorch path)")
+
+
+def config_block(world):
+    c = C2
+    return {"workload": f"C2 chunked causal prefill forward B={c['B']} N={c['N']} H={c['H']} M={c['M']} D={c['Dk']} "
+                        "bf16 in / fp32 accumulate, one full workload per GPU", "global_batch": c["B"] * world,
+            "seq_len": c["N"], "parallelism": f"batch x head lanes, {world} GPU(s), no collective",
+            "l2": "K+V+Y = 403 MB per step > 126 MB L2 (no flush needed)"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--skip-decode", action="store_true")
+    ap.add_argument("--skip-cpu", action="store_true")
+    ap.add_argument("--decode-prefix", type=int, default=C3["prefix"])
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    if args.impl == "reference":
+        if int(os.environ.get("RANK", "0")) != 0:
+            return
+        steps = max(1, min(args.steps, 3))
+        for _ in range(min(args.warmup, 1)):
+            cpu_reference_sample()
+        runs = [cpu_reference_sample() for _ in range(steps)]
+        best = max(runs, key=lambda r: r["value"])
+        val = sum(r["value"] for r in runs) / len(runs)
+        line = {
+            "impl": "reference", "metric": "prefill throughput", "value": val, "unit": "Mtok/s", "n_gpus": args.gpus,
+            "steps": steps, "warmup": min(args.warmup, 1), "ms_per_step": 1e3 * sum(r["seconds"] for r in runs) / len(runs),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": config_block(1),
+            "cpu_baseline": dict(value=val, unit="Mtok/s", cores=best["cores"], kind="port", sample=best["sample"]),
+            "e2e": {"value": val, "unit": "Mtok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0,
+        }
+        print(json.dumps(line))
+        return
+
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU fallback)"
+    rank, world, _ = dist_setup(args.gpus)
+    pre = bench_prefill(args, rank, world)
+    dec = None if args.skip_decode else bench_decode(args, rank, world)
+    cpu = None
+    if rank == 0 and world == 1 and not args.skip_cpu:
+        cpu = cpu_reference_sample()
+        cpu.pop("seconds", None)
+    if rank == 0:
+        line = {
+            "metric": "prefill throughput", "value": pre["value"], "unit": "Mtok/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": pre["ms_per_step"], "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config_block(world),
+            "roofline": pre["roofline"], "cpu_baseline": cpu, "e2e": pre["e2e"], "gpu_launches": pre["gpu_launches"],
+            "clocks": pre["clocks"], "decode": dec,
+        }
+        print(json.dumps(line))
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -157,6 +157,13 @@ int flare_state_merge(const flare_state_t* a, const flare_state_t* b, const flar
 const char* flare_status_string(int status);
 const char* flare_last_cuda_error(void);
 int flare_abi_version(void);
+
+/* Measurement hooks (no counterpart in the reference; used by the benchmark).
+ * flare_set_kernel_events: two cudaEvent_t handles (or NULL, NULL to clear) that later flare_forward /
+ * flare_backward calls of this thread record immediately before and after their dominant kernel, on the
+ * stream they launch on.  flare_last_launch_count: kernels launched by this thread's last forward/backward. */
+void flare_set_kernel_events(void* begin_event, void* end_event);
+int flare_last_launch_count(void);
 /* sizeof(flare_fwd_args_t / flare_bwd_args_t / flare_decode_args_t / flare_state_t) for which = 0..3,
  * so that a foreign-language binding can verify its struct layout at load time. */
 size_t flare_abi_sizeof(int which);
