@@ -160,7 +160,9 @@ def flare_autoregressive_prefill_triton(Q, K, V, state=None, scale=1.0, input_pr
     if attention_mask is not None and attention_mask.shape != (B, T):
         raise ValueError(f"attention_mask must be [B, T]. Got {tuple(attention_mask.shape)}")
     _normalize_input_precision(input_precision)
-    Q_dec, K_dec, separate_Q_dec, separate_K_dec, _ = resolve_flare_causal_decode_inputs(Q, K, Q_dec, K_dec)
+    Q_dec, K_dec, separate_Q_dec, separate_K_dec, shared = resolve_flare_causal_decode_inputs(Q, K, Q_dec, K_dec)
+    if shared:
+        separate_Q_dec = separate_K_dec = False
     st = _canonicalize_flare_state(state, B, H, M, D_value, K.device)
     if T == 0:
         return torch.empty((B, 0, H, D_value), device=K.device, dtype=V.dtype), st

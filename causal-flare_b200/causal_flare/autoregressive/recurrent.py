@@ -32,7 +32,9 @@ class RecurrentFLARE(autograd.Function):
             )
         H, M, D = Q.size()
         scale = _resolve_attn_scale(scale, D)
-        Q_dec, K_dec, sep_q, sep_k, _ = resolve_flare_causal_decode_inputs(Q, K, Q_dec, K_dec)
+        Q_dec, K_dec, sep_q, sep_k, shared = resolve_flare_causal_decode_inputs(Q, K, Q_dec, K_dec)
+        if shared:
+            sep_q = sep_k = False
         if (M % 16) != 0 or (D % 16) != 0:
             raise ValueError(f"RecurrentFLARE requires M and D be multiples of 16. Got M={M}, D={D}")
         if block_t is not None and int(block_t) not in (1, 16, 32):

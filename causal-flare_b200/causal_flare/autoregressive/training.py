@@ -31,7 +31,11 @@ class AutoRegressiveFLARE(autograd.Function):
         )
         H, M, D_score = Q.shape
         D_value = V.size(3)
-        Q_dec, K_dec, separate_Q_dec, separate_K_dec, _ = resolve_flare_causal_decode_inputs(Q, K, Q_dec, K_dec)
+        Q_dec, K_dec, separate_Q_dec, separate_K_dec, shared = resolve_flare_causal_decode_inputs(Q, K, Q_dec, K_dec)
+        if shared:
+            # decode tensors that ARE the encode tensors (same objects) take the shared-weight path: one score
+            # matrix, decode-side gradients folded into dQ / dK, None returned for the aliased arguments
+            separate_Q_dec = separate_K_dec = False
         scale = _resolve_attn_scale(scale, D_score)
         _normalize_input_precision(input_precision)
         chunk_size = 64 if chunk_size is None else int(chunk_size)

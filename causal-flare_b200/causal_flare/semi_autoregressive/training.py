@@ -25,7 +25,9 @@ class SemiAutoRegressiveFLARE(autograd.Function):
             N=N, block_size=block_size, chunk_size=chunk_size, name="SemiAutoRegressiveFLARE")
         resolved_scale = _resolve_attn_scale(scale, D_score)
         _normalize_input_precision(input_precision)
-        Q_dec, K_dec, sep_q, sep_k, _ = resolve_flare_causal_decode_inputs(Q, K, Q_dec, K_dec)
+        Q_dec, K_dec, sep_q, sep_k, shared = resolve_flare_causal_decode_inputs(Q, K, Q_dec, K_dec)
+        if shared:
+            sep_q = sep_k = False
         if not K.is_cuda:
             raise RuntimeError("flare_semi_autoregressive requires CUDA tensors.")
         profile_data = {"forward": {}, "backward": {}} if profile else None

@@ -1,5 +1,947 @@
+// Exact (fp32, CUDA-core) backward of causal FLARE: softmax / stablemax encoders, token-causal or
+// block-causal read-out, shared or separate decode weights.  Nothing is saved by the forward; the
+// forward recurrence is replayed here.
+//
+// With e[t,m] the normalised encoder weight of token t at its read-out time (softmax exp(s - L_t),
+// stablemax sigma(s)/D_t) the read-out state obeys z_t = (1 - e_t) z_{t-1} + e_t v_t, hence
+//   p[t,m]   = <z_t[m,:], dY_t>                        g[t,:] = softmax_m(a[t,:])
+//   b_t[m,:] = g dY_t + (1 - e_{t+1}) b_{t+1}           c_t[m] = g p + (1 - e_{t+1}) c_{t+1}
+//   dV_t     = sum_m e b_t[m,:]
+//   dS_enc   = e * slope * (<b_t[m,:], v_t> - c_t[m])    slope = 1 | sigma'(s)/sigma(s)
+//   dS_dec   = g (p - sum_m g p)
+//   dK = scale dS Q,  dQ = scale sum_{b,t} dS^T k_t  (decode-side products go to dQ_dec / dK_dec when separate)
+// For block-causal read-out the state is read at block ends, so e, b, c are per block.
+//
+// Kernels: (1) replay: forward walk that stores e, g and the partial p of its Dv tile;
+// (2) reverse: reverse walk carrying (b, c), emits dV and the dS planes; (3) rows: dK / dQ_dec = dS Lat;
+// (4) latents: per-split partial dQ / dK_dec = dS^T Rows; (5) fixed-order sum of the partials
+// (deterministic: no atomics anywhere).
 #include "bwd_exact.cuh"
+
+#include <string.h>
+
+#include "walk_device.cuh"
+#include "walk_exact.cuh"
+
 namespace flare {
-size_t bwd_exact_workspace_bytes(const flare_bwd_args_t&) { return 0; }
-int bwd_exact(const flare_bwd_args_t&, cudaStream_t) { return FLARE_ERR_UNSUPPORTED; }
+
+using namespace walk;
+
+struct BwdParams {
+  const void *q, *k, *v, *qd, *kd, *dy;
+  int B, N, H, M, Dk, Dv;
+  int64_t q_stride_h, q_stride_m;
+  int64_t k_stride_b, k_stride_n, k_stride_h;
+  int64_t v_stride_b, v_stride_n, v_stride_h;
+  int64_t qd_stride_b, qd_stride_n, qd_stride_h;
+  int64_t kd_stride_h, kd_stride_m;
+  int64_t dy_stride_b, dy_stride_n, dy_stride_h;
+  float scale, power;
+  int dtype, variant, block_size;
+  // workspace planes, each [lanes][N][M] fp32
+  float* E;    // normalised encoder weight
+  float* G;    // decode softmax
+  float* W2;   // E * slope (stablemax), aliases E for softmax
+  float* P;    // [DT] planes: partial p of every Dv tile
+  float* dSe;  // [DT] planes: partial encode-score gradient (plane 0 also carries -c and, if shared, dS_dec)
+  float* dSd;  // decode-score gradient, null when the weights are shared
+  int DT;
+  int64_t plane;  // lanes * N * M
+  void* dv_out;   // [B, N, H, Dv] contiguous, input dtype
+};
+
+// defined once per MM_MAX in {2, 8, 16, 32, 64}, each in its own translation unit; stage 0 = replay, 1 = reverse
+template <int MM_MAX>
+int launch_bwd_mm(const BwdParams& p, int dd, dim3 grid, size_t smem1, size_t smem2, cudaStream_t stream, int stage);
+
+namespace {
+
+#ifdef FLARE_WALK_MM
+// --------------------------------------------------------------------------------------------------
+// (1) forward replay
+// --------------------------------------------------------------------------------------------------
+template <int MM_MAX, int DD>
+__global__ void __launch_bounds__(NT) bwd_replay_kernel(const BwdParams p) {
+  extern __shared__ __align__(16) float smem_raw[];
+  const int lane_id = blockIdx.x, dt = blockIdx.y;
+  const int b = lane_id / p.H, h = lane_id % p.H;
+  constexpr int dvt = 32 * DD;
+  const int dv0 = dt * dvt;
+  const int M = p.M, Dk = p.Dk, Dv = p.Dv, N = p.N;
+  const int mp = M + 4, ldk = Dk + 4;
+  float* base = smem_raw;
+  float* ks = base; base += BT * ldk;
+  float* qds = base; base += BT * ldk;
+  float* vs = base; base += BT * dvt;
+  float* dos = base; base += BT * dvt;
+  float* s_s = base; base += BT * mp;   // scores -> eta
+  float* a_s = base; base += BT * mp;   // decode softmax
+  float* g_s = base; base += BT * mp;   // gamma
+  float* r_s = base; base += BT * mp;   // 1 / d_t
+  float* m_run = base; base += mp;
+  float* d_run = base; base += mp;
+  float* dinv = base; base += mp;
+  int* valid = reinterpret_cast<int*>(base);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int mm = M / NW;
+  const bool shared_w = p.qd == nullptr && p.kd == nullptr;
+  const bool stablemax = p.variant == FLARE_STABLEMAX;
+  const int dtype = p.dtype;
+
+  float U[MM_MAX][DD];
+#pragma unroll
+  for (int mi = 0; mi < MM_MAX; ++mi)
+#pragma unroll
+    for (int j = 0; j < DD; ++j) U[mi][j] = 0.f;
+  for (int m = tid; m < M; m += NT) {
+    m_run[m] = stablemax ? 0.f : kNegInf;
+    d_run[m] = 0.f;
+  }
+  __syncthreads();
+
+  const int64_t k_off = (int64_t)b * p.k_stride_b + (int64_t)h * p.k_stride_h;
+  const int64_t v_off = (int64_t)b * p.v_stride_b + (int64_t)h * p.v_stride_h;
+  const int64_t qd_off = (int64_t)b * p.qd_stride_b + (int64_t)h * p.qd_stride_h;
+  const int64_t dy_off = (int64_t)b * p.dy_stride_b + (int64_t)h * p.dy_stride_h;
+  const int64_t q_off = (int64_t)h * p.q_stride_h;
+  const int64_t kd_off = (int64_t)h * p.kd_stride_h;
+  const int64_t row_base = (int64_t)lane_id * N;  // row index into the [lanes][N][M] planes
+  float* Ppart = p.P + (int64_t)dt * p.plane;
+
+  auto set_valid = [&](int t0) {
+    if (tid < BT) valid[tid] = (t0 + tid) < N;
+  };
+
+  // p[t, m] for the tokens of the staged tile: sum over this tile's value columns, then across lanes
+  auto emit_p = [&](int t0, int t, const float* rinv_row /* [mp] 1/d per latent */) {
+    float pp[MM_MAX];
+#pragma unroll
+    for (int mi = 0; mi < MM_MAX; ++mi) {
+      float acc = 0.f;
+#pragma unroll
+      for (int j = 0; j < DD; ++j) acc += U[mi][j] * dos[t * dvt + lane + 32 * j];
+      pp[mi] = acc;
+    }
+    warp_reduce_scatter<MM_MAX>(pp, lane);
+    constexpr int W = MM_MAX > 32 ? 32 : MM_MAX;
+    const int li = lane & (W - 1);
+#pragma unroll
+    for (int rep = 0; rep < (MM_MAX + 31) / 32; ++rep) {
+      const int mi = li + 32 * rep;
+      if (lane < W && mi < mm) {
+        const int m = warp * mm + mi;
+        Ppart[(row_base + t0 + t) * M + m] = pp[32 * rep] * rinv_row[m];
+      }
+    }
+  };
+
+  if (p.block_size <= 1) {
+    for (int t0 = 0; t0 < N; t0 += BT) {
+      __syncthreads();
+      set_valid(t0);
+      load_rows(ks, ldk, p.k, dtype, k_off, p.k_stride_n, t0, N, Dk, 0, Dk);
+      load_rows(vs, dvt, p.v, dtype, v_off, p.v_stride_n, t0, N, Dv, dv0, dvt);
+      load_rows(dos, dvt, p.dy, dtype, dy_off, p.dy_stride_n, t0, N, Dv, dv0, dvt);
+      if (p.qd != nullptr) load_rows(qds, ldk, p.qd, dtype, qd_off, p.qd_stride_n, t0, N, Dk, 0, Dk);
+      __syncthreads();
+      score_tile(s_s, mp, ks, ldk, p.q, dtype, q_off, p.q_stride_m, M, Dk, p.scale);
+      if (!shared_w)
+        score_tile(a_s, mp, p.qd ? qds : ks, ldk, p.kd ? p.kd : p.q, dtype, p.kd ? kd_off : q_off,
+                   p.kd ? p.kd_stride_m : p.q_stride_m, M, Dk, p.scale);
+      __syncthreads();
+      decode_softmax(a_s, shared_w ? s_s : a_s, mp, M, valid, nullptr, t0, N);
+      __syncthreads();
+      for (int m = tid; m < M; m += NT) {
+        float mr = m_run[m], dr = d_run[m];
+        for (int t = 0; t < BT; ++t) {
+          if (!valid[t]) continue;
+          const float s = s_s[t * mp + m];
+          float gam, eta;
+          if (stablemax) {
+            gam = 1.f;
+            eta = stablemax_sigma(s, p.power);
+            dr += eta;
+          } else {
+            const float mn = fmaxf(mr, s);
+            gam = (mr == kNegInf) ? 0.f : __expf(mr - mn);
+            eta = __expf(s - mn);
+            dr = dr * gam + eta;
+            mr = mn;
+          }
+          const float rinv = 1.0f / dr;
+          g_s[t * mp + m] = gam;
+          s_s[t * mp + m] = eta;
+          r_s[t * mp + m] = rinv;
+          if (dt == 0) {
+            const int64_t o = (row_base + t0 + t) * M + m;
+            const float e = eta * rinv;
+            p.E[o] = e;
+            p.G[o] = a_s[t * mp + m];
+            if (stablemax) p.W2[o] = e * stablemax_slope_ratio(s, p.power);
+          }
+        }
+        m_run[m] = mr;
+        d_run[m] = dr;
+      }
+      __syncthreads();
+#pragma unroll 1
+      for (int t = 0; t < BT; ++t) {
+        if (!valid[t]) continue;
+        float vv[DD];
+#pragma unroll
+        for (int j = 0; j < DD; ++j) vv[j] = vs[t * dvt + lane + 32 * j];
+#pragma unroll
+        for (int mi = 0; mi < MM_MAX; ++mi) {
+          if (mi < mm) {
+            const int m = warp * mm + mi;
+            const float gam = g_s[t * mp + m], eta = s_s[t * mp + m];
+#pragma unroll
+            for (int j = 0; j < DD; ++j) U[mi][j] = U[mi][j] * gam + eta * vv[j];
+          }
+        }
+        emit_p(t0, t, r_s + t * mp);
+      }
+    }
+  } else {
+    const int bs = p.block_size;
+    for (int blk0 = 0; blk0 < N; blk0 += bs) {
+      const int blk_end = blk0 + bs;
+      for (int t0 = blk0; t0 < blk_end; t0 += BT) {
+        __syncthreads();
+        set_valid(t0);
+        load_rows(ks, ldk, p.k, dtype, k_off, p.k_stride_n, t0, N, Dk, 0, Dk);
+        load_rows(vs, dvt, p.v, dtype, v_off, p.v_stride_n, t0, N, Dv, dv0, dvt);
+        __syncthreads();
+        score_tile(s_s, mp, ks, ldk, p.q, dtype, q_off, p.q_stride_m, M, Dk, p.scale);
+        __syncthreads();
+        for (int m = tid; m < M; m += NT) {
+          float mr = m_run[m], dr = d_run[m];
+          for (int t = 0; t < BT; ++t) {
+            const float s = s_s[t * mp + m];
+            const float mn = fmaxf(mr, s);
+            const float gam = (mr == kNegInf) ? 0.f : __expf(mr - mn);
+            const float eta = __expf(s - mn);
+            dr = dr * gam + eta;
+            mr = mn;
+            g_s[t * mp + m] = gam;
+            s_s[t * mp + m] = eta;
+          }
+          m_run[m] = mr;
+          d_run[m] = dr;
+        }
+        __syncthreads();
+#pragma unroll 1
+        for (int t = 0; t < BT; ++t) {
+          float vv[DD];
+#pragma unroll
+          for (int j = 0; j < DD; ++j) vv[j] = vs[t * dvt + lane + 32 * j];
+#pragma unroll
+          for (int mi = 0; mi < MM_MAX; ++mi) {
+            if (mi < mm) {
+              const int m = warp * mm + mi;
+              const float gam = g_s[t * mp + m], eta = s_s[t * mp + m];
+#pragma unroll
+              for (int j = 0; j < DD; ++j) U[mi][j] = U[mi][j] * gam + eta * vv[j];
+            }
+          }
+        }
+      }
+      __syncthreads();
+      for (int m = tid; m < M; m += NT) dinv[m] = 1.0f / d_run[m];
+      for (int t0 = blk0; t0 < blk_end; t0 += BT) {
+        __syncthreads();
+        set_valid(t0);
+        load_rows(ks, ldk, p.k, dtype, k_off, p.k_stride_n, t0, N, Dk, 0, Dk);
+        load_rows(dos, dvt, p.dy, dtype, dy_off, p.dy_stride_n, t0, N, Dv, dv0, dvt);
+        if (p.qd != nullptr) load_rows(qds, ldk, p.qd, dtype, qd_off, p.qd_stride_n, t0, N, Dk, 0, Dk);
+        __syncthreads();
+        score_tile(s_s, mp, ks, ldk, p.q, dtype, q_off, p.q_stride_m, M, Dk, p.scale);
+        if (!shared_w)
+          score_tile(a_s, mp, p.qd ? qds : ks, ldk, p.kd ? p.kd : p.q, dtype, p.kd ? kd_off : q_off,
+                     p.kd ? p.kd_stride_m : p.q_stride_m, M, Dk, p.scale);
+        __syncthreads();
+        decode_softmax(a_s, shared_w ? s_s : a_s, mp, M, valid, nullptr, t0, N);
+        __syncthreads();
+        if (dt == 0) {
+          for (int idx = tid; idx < BT * M; idx += NT) {
+            const int t = idx / M, m = idx % M;
+            const int64_t o = (row_base + t0 + t) * M + m;
+            p.E[o] = __expf(s_s[t * mp + m] - m_run[m]) * dinv[m];
+            p.G[o] = a_s[t * mp + m];
+          }
+        }
+#pragma unroll 1
+        for (int t = 0; t < BT; ++t) emit_p(t0, t, dinv);
+      }
+    }
+  }
+}
+
+// --------------------------------------------------------------------------------------------------
+// (2) reverse walk
+// --------------------------------------------------------------------------------------------------
+template <int MM_MAX, int DD>
+__global__ void __launch_bounds__(NT) bwd_reverse_kernel(const BwdParams p) {
+  extern __shared__ __align__(16) float smem_raw[];
+  const int lane_id = blockIdx.x, dt = blockIdx.y;
+  const int b = lane_id / p.H, h = lane_id % p.H;
+  constexpr int dvt = 32 * DD;
+  const int dv0 = dt * dvt;
+  const int M = p.M, Dv = p.Dv, N = p.N;
+  const int mp = M + 4;
+  const bool stablemax = p.variant == FLARE_STABLEMAX;
+  const bool shared_w = p.dSd == nullptr;
+  float* base = smem_raw;
+  float* vs = base; base += BT * dvt;
+  float* dos = base; base += BT * dvt;
+  float* e_s = base; base += BT * mp;
+  float* g_s = base; base += BT * mp;
+  float* p_s = base; base += BT * mp;   // p -> dS_dec
+  float* c_s = base; base += BT * mp;
+  float* bv_s = base; base += BT * mp;
+  float* w_s = stablemax ? base : e_s;
+  if (stablemax) base += BT * mp;
+  float* rho_in = base; base += mp;     // decay applied when stepping from the next tile / block into this one
+  float* c_run = base; base += mp;
+  float* esum = base; base += mp;
+  float* gp = base; base += BT;
+  float* dvpart = base; base += NW * BT * dvt;
+  int* valid = reinterpret_cast<int*>(base);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int mm = M / NW;
+  const int dtype = p.dtype;
+
+  float Bc[MM_MAX][DD];
+#pragma unroll
+  for (int mi = 0; mi < MM_MAX; ++mi)
+#pragma unroll
+    for (int j = 0; j < DD; ++j) Bc[mi][j] = 0.f;
+  for (int m = tid; m < M; m += NT) {
+    rho_in[m] = 0.f;
+    c_run[m] = 0.f;
+    esum[m] = 0.f;
+  }
+
+  const int64_t v_off = (int64_t)b * p.v_stride_b + (int64_t)h * p.v_stride_h;
+  const int64_t dy_off = (int64_t)b * p.dy_stride_b + (int64_t)h * p.dy_stride_h;
+  const int64_t row_base = (int64_t)lane_id * N;
+  float* dSe_part = p.dSe + (int64_t)dt * p.plane;
+
+  auto load_plane = [&](float* dst, const float* src, int t0, int parts) {
+    const int q4 = M / 4;
+    for (int idx = tid; idx < BT * q4; idx += NT) {
+      const int t = idx / q4, c = (idx % q4) * 4;
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (t0 + t < N) {
+        for (int part = 0; part < parts; ++part) {
+          const float4 x = *reinterpret_cast<const float4*>(src + (int64_t)part * p.plane + (row_base + t0 + t) * M + c);
+          acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w;
+        }
+      }
+      *reinterpret_cast<float4*>(dst + t * mp + c) = acc;
+    }
+  };
+  auto set_valid = [&](int t0) {
+    if (tid < BT) valid[tid] = (t0 + tid) < N;
+  };
+  auto compute_gp = [&]() {
+    for (int t = warp; t < BT; t += NW) {
+      float acc = 0.f;
+      for (int m = lane; m < M; m += 32) acc += g_s[t * mp + m] * p_s[t * mp + m];
+      acc = warp_sum(acc);
+      if (lane == 0) gp[t] = acc;
+    }
+  };
+  float dvacc[BT][DD];
+  auto zero_dv = [&]() {
+#pragma unroll
+    for (int t = 0; t < BT; ++t)
+#pragma unroll
+      for (int j = 0; j < DD; ++j) dvacc[t][j] = 0.f;
+  };
+  // <b[m,:], v_t> over this tile's value columns -> bv_s[t][m]
+  auto emit_bv = [&](int t) {
+    float pp[MM_MAX];
+#pragma unroll
+    for (int mi = 0; mi < MM_MAX; ++mi) {
+      float acc = 0.f;
+#pragma unroll
+      for (int j = 0; j < DD; ++j) acc += Bc[mi][j] * vs[t * dvt + lane + 32 * j];
+      pp[mi] = acc;
+    }
+    warp_reduce_scatter<MM_MAX>(pp, lane);
+    constexpr int W = MM_MAX > 32 ? 32 : MM_MAX;
+    const int li = lane & (W - 1);
+#pragma unroll
+    for (int rep = 0; rep < (MM_MAX + 31) / 32; ++rep) {
+      const int mi = li + 32 * rep;
+      if (lane < W && mi < mm) bv_s[t * mp + warp * mm + mi] = pp[32 * rep];
+    }
+  };
+  // dS planes and dV of the staged tile
+  auto finish_tile = [&](int t0, const float* c_of /* [BT][mp] or per-latent [mp] */, int c_ld) {
+#pragma unroll
+    for (int t = 0; t < BT; ++t)
+#pragma unroll
+      for (int j = 0; j < DD; ++j) dvpart[(warp * BT + t) * dvt + lane + 32 * j] = dvacc[t][j];
+    __syncthreads();
+    for (int idx = tid; idx < BT * M; idx += NT) {
+      const int t = idx / M, m = idx % M;
+      if (t0 + t >= N) continue;
+      const int64_t o = (row_base + t0 + t) * M + m;
+      float ds = w_s[t * mp + m] * (bv_s[t * mp + m] - (dt == 0 ? c_of[t * c_ld + m] : 0.f));
+      if (dt == 0) {
+        if (shared_w) ds += p_s[t * mp + m];
+        else p.dSd[o] = p_s[t * mp + m];
+      }
+      dSe_part[o] = ds;
+    }
+    const int q4 = dvt / 4;
+    for (int idx = tid; idx < BT * q4; idx += NT) {
+      const int t = idx / q4, c = (idx % q4) * 4;
+      if (t0 + t >= N || dv0 + c >= Dv) continue;
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int w = 0; w < NW; ++w) {
+        const float4 x = *reinterpret_cast<const float4*>(dvpart + (w * BT + t) * dvt + c);
+        acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w;
+      }
+      store4(p.dv_out, dtype, (((int64_t)b * N + t0 + t) * p.H + h) * Dv + dv0 + c, acc.x, acc.y, acc.z, acc.w);
+    }
+  };
+
+  if (p.block_size <= 1) {
+    const int last_tile = ((N - 1) / BT) * BT;
+    for (int t0 = last_tile; t0 >= 0; t0 -= BT) {
+      __syncthreads();
+      set_valid(t0);
+      load_rows(vs, dvt, p.v, dtype, v_off, p.v_stride_n, t0, N, Dv, dv0, dvt);
+      load_rows(dos, dvt, p.dy, dtype, dy_off, p.dy_stride_n, t0, N, Dv, dv0, dvt);
+      load_plane(e_s, p.E, t0, 1);
+      load_plane(g_s, p.G, t0, 1);
+      load_plane(p_s, p.P, t0, p.DT);
+      if (stablemax) load_plane(w_s, p.W2, t0, 1);
+      __syncthreads();
+      compute_gp();
+      // reverse scan of c per latent
+      for (int m = tid; m < M; m += NT) {
+        float c = c_run[m], rho = rho_in[m];
+        for (int t = BT - 1; t >= 0; --t) {
+          if (!valid[t]) continue;
+          c = g_s[t * mp + m] * p_s[t * mp + m] + rho * c;
+          c_s[t * mp + m] = c;
+          rho = 1.0f - e_s[t * mp + m];
+        }
+        c_run[m] = c;
+      }
+      __syncthreads();
+      for (int idx = tid; idx < BT * M; idx += NT) {
+        const int t = idx / M, m = idx % M;
+        p_s[t * mp + m] = g_s[t * mp + m] * (p_s[t * mp + m] - gp[t]);
+      }
+      zero_dv();
+#pragma unroll
+      for (int t = BT - 1; t >= 0; --t) {
+        if (!valid[t]) continue;
+        const bool next_in_tile = (t + 1 < BT) && valid[t + 1 < BT ? t + 1 : t];
+        float dd[DD];
+#pragma unroll
+        for (int j = 0; j < DD; ++j) dd[j] = dos[t * dvt + lane + 32 * j];
+#pragma unroll
+        for (int mi = 0; mi < MM_MAX; ++mi) {
+          if (mi < mm) {
+            const int m = warp * mm + mi;
+            const float rho = next_in_tile ? 1.0f - e_s[(t + 1 < BT ? t + 1 : t) * mp + m] : rho_in[m];
+            const float g = g_s[t * mp + m], e = e_s[t * mp + m];
+#pragma unroll
+            for (int j = 0; j < DD; ++j) {
+              Bc[mi][j] = Bc[mi][j] * rho + g * dd[j];
+              dvacc[t][j] += e * Bc[mi][j];
+            }
+          }
+        }
+        emit_bv(t);
+      }
+      __syncthreads();
+      for (int m = tid; m < M; m += NT) rho_in[m] = 1.0f - e_s[m];  // token 0 of this tile is always valid
+      finish_tile(t0, c_s, mp);
+    }
+  } else {
+    const int bs = p.block_size;
+    for (int blk0 = N - bs; blk0 >= 0; blk0 -= bs) {
+      const int blk_end = blk0 + bs;
+      // pass 1: fold the whole block into the carries
+      __syncthreads();
+      for (int m = tid; m < M; m += NT) {
+        c_run[m] *= rho_in[m];
+        esum[m] = 0.f;
+      }
+#pragma unroll
+      for (int mi = 0; mi < MM_MAX; ++mi) {
+        if (mi < mm) {
+          const float rho = rho_in[warp * mm + mi];
+#pragma unroll
+          for (int j = 0; j < DD; ++j) Bc[mi][j] *= rho;
+        }
+      }
+      for (int t0 = blk0; t0 < blk_end; t0 += BT) {
+        __syncthreads();
+        load_rows(dos, dvt, p.dy, dtype, dy_off, p.dy_stride_n, t0, N, Dv, dv0, dvt);
+        load_plane(e_s, p.E, t0, 1);
+        load_plane(g_s, p.G, t0, 1);
+        load_plane(p_s, p.P, t0, p.DT);
+        __syncthreads();
+        for (int m = tid; m < M; m += NT) {
+          float c = c_run[m], es = esum[m];
+          for (int t = 0; t < BT; ++t) {
+            c += g_s[t * mp + m] * p_s[t * mp + m];
+            es += e_s[t * mp + m];
+          }
+          c_run[m] = c;
+          esum[m] = es;
+        }
+#pragma unroll 1
+        for (int t = 0; t < BT; ++t) {
+          float dd[DD];
+#pragma unroll
+          for (int j = 0; j < DD; ++j) dd[j] = dos[t * dvt + lane + 32 * j];
+#pragma unroll
+          for (int mi = 0; mi < MM_MAX; ++mi) {
+            if (mi < mm) {
+              const float g = g_s[t * mp + warp * mm + mi];
+#pragma unroll
+              for (int j = 0; j < DD; ++j) Bc[mi][j] += g * dd[j];
+            }
+          }
+        }
+      }
+      // pass 2: gradients of every token of the block
+      for (int t0 = blk0; t0 < blk_end; t0 += BT) {
+        __syncthreads();
+        set_valid(t0);
+        load_rows(vs, dvt, p.v, dtype, v_off, p.v_stride_n, t0, N, Dv, dv0, dvt);
+        load_plane(e_s, p.E, t0, 1);
+        load_plane(g_s, p.G, t0, 1);
+        load_plane(p_s, p.P, t0, p.DT);
+        __syncthreads();
+        compute_gp();
+        __syncthreads();
+        for (int idx = tid; idx < BT * M; idx += NT) {
+          const int t = idx / M, m = idx % M;
+          p_s[t * mp + m] = g_s[t * mp + m] * (p_s[t * mp + m] - gp[t]);
+        }
+        zero_dv();
+#pragma unroll
+        for (int t = 0; t < BT; ++t) {
+#pragma unroll
+          for (int mi = 0; mi < MM_MAX; ++mi) {
+            if (mi < mm) {
+              const float e = e_s[t * mp + warp * mm + mi];
+#pragma unroll
+              for (int j = 0; j < DD; ++j) dvacc[t][j] += e * Bc[mi][j];
+            }
+          }
+          emit_bv(t);
+        }
+        __syncthreads();
+        finish_tile(t0, c_run, 0);
+      }
+      __syncthreads();
+      for (int m = tid; m < M; m += NT) rho_in[m] = 1.0f - esum[m];
+    }
+  }
+}
+
+#else
+// --------------------------------------------------------------------------------------------------
+// (3) token-row gradients: out[b, t, h, :] = scale * sum_src (sum_parts dS_src[t, :]) Lat_src[h]
+// --------------------------------------------------------------------------------------------------
+struct RowsParams {
+  const float* ds[2];
+  int parts[2];
+  const void* lat[2];
+  int64_t lat_stride_h[2], lat_stride_m[2];
+  int nsrc;
+  int64_t plane;
+  void* out;  // [B, N, H, Dk] contiguous
+  int B, N, H, M, Dk, dtype;
+  float scale;
+};
+
+constexpr int RT = 32;  // token rows per CTA
+
+__global__ void __launch_bounds__(NT) bwd_rows_kernel(const RowsParams p) {
+  extern __shared__ __align__(16) float smem_raw[];
+  const int lane_id = blockIdx.x, t0 = blockIdx.y * RT;
+  const int b = lane_id / p.H, h = lane_id % p.H;
+  const int M = p.M, Dk = p.Dk, N = p.N, mp = M + 4;
+  float* ds_s = smem_raw;  // [RT][mp]
+  const int tid = threadIdx.x;
+  const int c4n = Dk / 4;
+  // every thread owns a fixed column group and a set of rows
+  float4 acc[RT];  // row i of this thread is r0 + i * rows_per_pass; only the first nrow entries are used
+  const int rows_per_pass = NT / c4n > 0 ? NT / c4n : 1;
+  const int c4 = tid % c4n, r0 = tid / c4n;
+  const int nrow = (RT - r0 + rows_per_pass - 1) / rows_per_pass;
+#pragma unroll
+  for (int i = 0; i < RT; ++i) acc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int src = 0; src < p.nsrc; ++src) {
+    __syncthreads();
+    const int q4 = M / 4;
+    for (int idx = tid; idx < RT * q4; idx += NT) {
+      const int t = idx / q4, c = (idx % q4) * 4;
+      float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (t0 + t < N) {
+        for (int part = 0; part < p.parts[src]; ++part) {
+          const float4 x = *reinterpret_cast<const float4*>(p.ds[src] + (int64_t)part * p.plane +
+                                                            ((int64_t)lane_id * N + t0 + t) * M + c);
+          a.x += x.x; a.y += x.y; a.z += x.z; a.w += x.w;
+        }
+      }
+      *reinterpret_cast<float4*>(ds_s + t * mp + c) = a;
+    }
+    __syncthreads();
+    if (tid < c4n * rows_per_pass) {
+      const int64_t lat_off = (int64_t)h * p.lat_stride_h[src];
+      for (int m = 0; m < M; ++m) {
+        float l0, l1, l2, l3;
+        {
+          const int64_t o = lat_off + (int64_t)m * p.lat_stride_m[src] + c4 * 4;
+          l0 = load1(p.lat[src], p.dtype, o);
+          l1 = load1(p.lat[src], p.dtype, o + 1);
+          l2 = load1(p.lat[src], p.dtype, o + 2);
+          l3 = load1(p.lat[src], p.dtype, o + 3);
+        }
+#pragma unroll
+        for (int i = 0; i < RT; ++i) {
+          if (i < nrow) {
+            const float d = ds_s[(r0 + i * rows_per_pass) * mp + m];
+            acc[i].x += d * l0; acc[i].y += d * l1; acc[i].z += d * l2; acc[i].w += d * l3;
+          }
+        }
+      }
+    }
+  }
+  if (tid < c4n * rows_per_pass) {
+#pragma unroll
+    for (int i = 0; i < RT; ++i) {
+      const int t = t0 + r0 + i * rows_per_pass;
+      if (i < nrow && t < N)
+        store4(p.out, p.dtype, (((int64_t)b * N + t) * p.H + h) * Dk + c4 * 4, acc[i].x * p.scale, acc[i].y * p.scale,
+               acc[i].z * p.scale, acc[i].w * p.scale);
+    }
+  }
+}
+
+// --------------------------------------------------------------------------------------------------
+// (4) latent gradients: partial[split][h][m][dk] = scale * sum_src sum_{rows in split} dS_src[r, m] Rows_src[r, dk]
+// --------------------------------------------------------------------------------------------------
+struct LatParams {
+  const float* ds[2];
+  int parts[2];
+  const void* rows[2];
+  int64_t rows_stride_b[2], rows_stride_n[2], rows_stride_h[2];
+  int nsrc;
+  int64_t plane;
+  float* partial;  // [splits][H][M][Dk]
+  int B, N, H, M, Dk, dtype;
+  int rows_per_split, splits;
+  float scale;
+};
+
+constexpr int LM = 64;    // latents per CTA
+constexpr int LDK = 128;  // score columns per CTA
+
+__global__ void __launch_bounds__(NT) bwd_lat_kernel(const LatParams p) {
+  __shared__ __align__(16) float ds_s[BT][LM + 4];
+  __shared__ __align__(16) float rw_s[BT][LDK + 4];
+  const int mtiles = (p.M + LM - 1) / LM;
+  const int h = blockIdx.x / mtiles, m0 = (blockIdx.x % mtiles) * LM;
+  const int split = blockIdx.y, dk0 = blockIdx.z * LDK;
+  const int tid = threadIdx.x, tm = tid / 16, td = tid % 16;
+  const int M = p.M, Dk = p.Dk, N = p.N;
+  float acc[4][8];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
+  const int64_t total_rows = (int64_t)p.B * N;
+  const int64_t r_begin = (int64_t)split * p.rows_per_split;
+  const int64_t r_end = min(total_rows, r_begin + p.rows_per_split);
+  for (int src = 0; src < p.nsrc; ++src) {
+    for (int64_t r0 = r_begin; r0 < r_end; r0 += BT) {
+      __syncthreads();
+      for (int idx = tid; idx < BT * LM; idx += NT) {
+        const int t = idx / LM, mi = idx % LM;
+        const int64_t r = r0 + t;
+        float a = 0.f;
+        if (r < r_end && m0 + mi < M) {
+          const int64_t bb = r / N, tt = r % N;
+          const int64_t o = ((bb * p.H + h) * N + tt) * M + m0 + mi;
+          for (int part = 0; part < p.parts[src]; ++part) a += p.ds[src][(int64_t)part * p.plane + o];
+        }
+        ds_s[t][mi] = a;
+      }
+      for (int idx = tid; idx < BT * LDK; idx += NT) {
+        const int t = idx / LDK, di = idx % LDK;
+        const int64_t r = r0 + t;
+        float a = 0.f;
+        if (r < r_end && dk0 + di < Dk) {
+          const int64_t bb = r / N, tt = r % N;
+          a = load1(p.rows[src], p.dtype,
+                    bb * p.rows_stride_b[src] + tt * p.rows_stride_n[src] + (int64_t)h * p.rows_stride_h[src] + dk0 + di);
+        }
+        rw_s[t][di] = a;
+      }
+      __syncthreads();
+#pragma unroll
+      for (int t = 0; t < BT; ++t) {
+        float dsv[4], rv[8];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) dsv[i] = ds_s[t][tm * 4 + i];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) rv[j] = rw_s[t][td + 16 * j];
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[i][j] += dsv[i] * rv[j];
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int m = m0 + tm * 4 + i, dk = dk0 + td + 16 * j;
+      if (m < M && dk < Dk) p.partial[(((int64_t)split * p.H + h) * M + m) * Dk + dk] = acc[i][j] * p.scale;
+    }
+}
+
+// (5) out[i] = sum_split partial[split][i], fixed order
+__global__ void bwd_sum_splits_kernel(float* out, const float* partial, int64_t n, int splits) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  float acc = 0.f;
+  for (int s = 0; s < splits; ++s) acc += partial[(int64_t)s * n + i];
+  out[i] = acc;
+}
+
+size_t replay_smem(int M, int Dk, int dd) {
+  const int mp = M + 4, ldk = Dk + 4, dvt = 32 * dd;
+  return ((size_t)2 * BT * ldk + 2 * BT * dvt + (size_t)4 * BT * mp + 3 * mp) * 4 + BT * sizeof(int);
+}
+size_t reverse_smem(int M, int dd, bool stablemax) {
+  const int mp = M + 4, dvt = 32 * dd;
+  return ((size_t)2 * BT * dvt + (size_t)(stablemax ? 6 : 5) * BT * mp + 3 * mp + BT + (size_t)NW * BT * dvt) * 4 +
+         BT * sizeof(int);
+}
+
+struct BwdPlan {
+  int dd, DT, splits, rows_per_split;
+  int64_t plane;
+  size_t off_E, off_G, off_W2, off_P, off_dSe, off_dSd, off_part_q, off_part_kd, total;
+};
+
+BwdPlan plan_backward(const flare_bwd_args_t& a) {
+  const flare_fwd_args_t& f = a.fwd;
+  BwdPlan pl;
+  pl.dd = walk_exact_dd(f.M, f.Dv);
+  pl.DT = (f.Dv + 32 * pl.dd - 1) / (32 * pl.dd);
+  pl.plane = (int64_t)f.B * f.H * f.N * f.M;
+  const bool stablemax = f.variant == FLARE_STABLEMAX;
+  const bool shared_w = f.q_dec == nullptr && f.k_dec == nullptr;
+  const int64_t rows = (int64_t)f.B * f.N;
+  const int mt = (f.M + LM - 1) / LM, dkc = (f.Dk + LDK - 1) / LDK;
+  int64_t splits = (2LL * sm_count() + (int64_t)f.H * mt * dkc - 1) / ((int64_t)f.H * mt * dkc);
+  const int64_t max_splits = (rows + 255) / 256;
+  if (splits > max_splits) splits = max_splits;
+  if (splits < 1) splits = 1;
+  int64_t rps = (rows + splits - 1) / splits;
+  rps = (rps + BT - 1) / BT * BT;
+  splits = (rows + rps - 1) / rps;
+  pl.splits = (int)splits;
+  pl.rows_per_split = (int)rps;
+  size_t off = 0;
+  auto take = [&](size_t floats) {
+    const size_t o = off;
+    off += align_up(floats * 4, 256);
+    return o;
+  };
+  const size_t plane = (size_t)pl.plane;
+  pl.off_E = take(plane);
+  pl.off_G = take(plane);
+  pl.off_W2 = stablemax ? take(plane) : pl.off_E;
+  pl.off_P = take(plane * pl.DT);
+  pl.off_dSe = take(plane * pl.DT);
+  pl.off_dSd = shared_w ? 0 : take(plane);
+  const size_t lat = (size_t)f.H * f.M * f.Dk;
+  pl.off_part_q = take(lat * pl.splits);
+  pl.off_part_kd = f.k_dec ? take(lat * pl.splits) : 0;
+  pl.total = off;
+  return pl;
+}
+
+#endif
+
+}  // namespace
+
+#ifdef FLARE_WALK_MM
+template <int MM_MAX, int DD>
+static int launch_bwd_one(const BwdParams& p, dim3 grid, size_t smem1, size_t smem2, cudaStream_t stream, int stage) {
+  if (stage == 0) {
+    auto k1 = bwd_replay_kernel<MM_MAX, DD>;
+    FLARE_CUDA_CHECK(cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem1));
+    k1<<<grid, NT, smem1, stream>>>(p);
+  } else {
+    auto k2 = bwd_reverse_kernel<MM_MAX, DD>;
+    FLARE_CUDA_CHECK(cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2));
+    k2<<<grid, NT, smem2, stream>>>(p);
+  }
+  FLARE_CUDA_CHECK(cudaGetLastError());
+  return FLARE_OK;
+}
+
+template <>
+int launch_bwd_mm<FLARE_WALK_MM>(const BwdParams& p, int dd, dim3 grid, size_t smem1, size_t smem2, cudaStream_t stream,
+                                 int stage) {
+  constexpr int MM_MAX = FLARE_WALK_MM;
+  if (dd == 1) return launch_bwd_one<MM_MAX, 1>(p, grid, smem1, smem2, stream, stage);
+  if (dd == 2) {
+    if constexpr (MM_MAX * 2 <= 64) return launch_bwd_one<MM_MAX, 2>(p, grid, smem1, smem2, stream, stage);
+  }
+  if (dd == 4) {
+    if constexpr (MM_MAX * 4 <= 64) return launch_bwd_one<MM_MAX, 4>(p, grid, smem1, smem2, stream, stage);
+  }
+  return FLARE_ERR_UNSUPPORTED;
+}
+#else
+
+size_t bwd_exact_workspace_bytes(const flare_bwd_args_t& a) {
+  if (a.fwd.B == 0 || a.fwd.N == 0) return 0;
+  return plan_backward(a).total;
+}
+
+int bwd_exact(const flare_bwd_args_t& a, cudaStream_t stream) {
+  const flare_fwd_args_t& f = a.fwd;
+  if (f.B == 0 || f.N == 0) return FLARE_OK;
+  if (f.M > 512) return FLARE_ERR_UNSUPPORTED;
+  const BwdPlan pl = plan_backward(a);
+  if (f.workspace == nullptr || f.workspace_bytes < pl.total || (reinterpret_cast<uintptr_t>(f.workspace) & 15u))
+    return FLARE_ERR_WORKSPACE;
+  char* ws = reinterpret_cast<char*>(f.workspace);
+  const bool stablemax = f.variant == FLARE_STABLEMAX;
+  const bool shared_w = f.q_dec == nullptr && f.k_dec == nullptr;
+  BwdParams p;
+  memset(&p, 0, sizeof(p));
+  p.q = f.q; p.k = f.k; p.v = f.v; p.qd = f.q_dec; p.kd = f.k_dec; p.dy = a.dy;
+  p.B = f.B; p.N = f.N; p.H = f.H; p.M = f.M; p.Dk = f.Dk; p.Dv = f.Dv;
+  p.q_stride_h = f.q_stride_h; p.q_stride_m = f.q_stride_m;
+  p.k_stride_b = f.k_stride_b; p.k_stride_n = f.k_stride_n; p.k_stride_h = f.k_stride_h;
+  p.v_stride_b = f.v_stride_b; p.v_stride_n = f.v_stride_n; p.v_stride_h = f.v_stride_h;
+  p.qd_stride_b = f.qd_stride_b; p.qd_stride_n = f.qd_stride_n; p.qd_stride_h = f.qd_stride_h;
+  p.kd_stride_h = f.kd_stride_h; p.kd_stride_m = f.kd_stride_m;
+  p.dy_stride_b = a.dy_stride_b; p.dy_stride_n = a.dy_stride_n; p.dy_stride_h = a.dy_stride_h;
+  p.scale = f.scale; p.power = f.power; p.dtype = f.dtype; p.variant = f.variant; p.block_size = f.block_size;
+  p.E = reinterpret_cast<float*>(ws + pl.off_E);
+  p.G = reinterpret_cast<float*>(ws + pl.off_G);
+  p.W2 = reinterpret_cast<float*>(ws + pl.off_W2);
+  p.P = reinterpret_cast<float*>(ws + pl.off_P);
+  p.dSe = reinterpret_cast<float*>(ws + pl.off_dSe);
+  p.dSd = shared_w ? nullptr : reinterpret_cast<float*>(ws + pl.off_dSd);
+  p.DT = pl.DT; p.plane = pl.plane; p.dv_out = a.dv;
+
+  const int mm = f.M / NW;
+  const size_t smem1 = replay_smem(f.M, f.Dk, pl.dd), smem2 = reverse_smem(f.M, pl.dd, stablemax);
+  if (smem1 > 227 * 1024 || smem2 > 227 * 1024) return FLARE_ERR_UNSUPPORTED;
+  dim3 grid(f.B * f.H, pl.DT);
+  for (int stage = 0; stage < 2; ++stage) {
+    int rc;
+    if (mm <= 2) rc = launch_bwd_mm<2>(p, pl.dd, grid, smem1, smem2, stream, stage);
+    else if (mm <= 8) rc = launch_bwd_mm<8>(p, pl.dd, grid, smem1, smem2, stream, stage);
+    else if (mm <= 16) rc = launch_bwd_mm<16>(p, pl.dd, grid, smem1, smem2, stream, stage);
+    else if (mm <= 32) rc = launch_bwd_mm<32>(p, pl.dd, grid, smem1, smem2, stream, stage);
+    else rc = launch_bwd_mm<64>(p, pl.dd, grid, smem1, smem2, stream, stage);
+    if (rc != FLARE_OK) return rc;
+  }
+
+  // ---- dK (+ dQ_dec): products of the dS planes with the latent banks ------------------------------
+  const size_t rows_smem = (size_t)RT * (f.M + 4) * 4;
+  if (rows_smem > 48 * 1024)
+    FLARE_CUDA_CHECK(cudaFuncSetAttribute(bwd_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)rows_smem));
+  auto rows_launch = [&](RowsParams& r) -> int {
+    r.plane = pl.plane; r.B = f.B; r.N = f.N; r.H = f.H; r.M = f.M; r.Dk = f.Dk; r.dtype = f.dtype; r.scale = f.scale;
+    dim3 g(f.B * f.H, (f.N + RT - 1) / RT);
+    bwd_rows_kernel<<<g, NT, rows_smem, stream>>>(r);
+    FLARE_CUDA_CHECK(cudaGetLastError());
+    return FLARE_OK;
+  };
+  {
+    RowsParams r;
+    memset(&r, 0, sizeof(r));
+    r.out = a.dk;
+    r.ds[0] = p.dSe; r.parts[0] = pl.DT; r.lat[0] = f.q; r.lat_stride_h[0] = f.q_stride_h; r.lat_stride_m[0] = f.q_stride_m;
+    r.nsrc = 1;
+    if (!shared_w && f.q_dec == nullptr) {  // decode queries are the keys: their gradient lands on K
+      r.ds[1] = p.dSd; r.parts[1] = 1; r.lat[1] = f.k_dec; r.lat_stride_h[1] = f.kd_stride_h; r.lat_stride_m[1] = f.kd_stride_m;
+      r.nsrc = 2;
+    }
+    int rc = rows_launch(r);
+    if (rc != FLARE_OK) return rc;
+  }
+  if (f.q_dec != nullptr) {
+    RowsParams r;
+    memset(&r, 0, sizeof(r));
+    r.out = a.dq_dec;
+    r.ds[0] = p.dSd; r.parts[0] = 1;
+    r.lat[0] = f.k_dec ? f.k_dec : f.q;
+    r.lat_stride_h[0] = f.k_dec ? f.kd_stride_h : f.q_stride_h;
+    r.lat_stride_m[0] = f.k_dec ? f.kd_stride_m : f.q_stride_m;
+    r.nsrc = 1;
+    int rc = rows_launch(r);
+    if (rc != FLARE_OK) return rc;
+  }
+
+  // ---- dQ (+ dK_dec): split partial sums, then a fixed-order reduction -------------------------------
+  const int mt = (f.M + LM - 1) / LM, dkc = (f.Dk + LDK - 1) / LDK;
+  const int64_t lat_n = (int64_t)f.H * f.M * f.Dk;
+  auto lat_launch = [&](LatParams& l, float* partial, float* out) -> int {
+    l.plane = pl.plane; l.B = f.B; l.N = f.N; l.H = f.H; l.M = f.M; l.Dk = f.Dk; l.dtype = f.dtype; l.scale = f.scale;
+    l.rows_per_split = pl.rows_per_split; l.splits = pl.splits; l.partial = partial;
+    dim3 g(f.H * mt, pl.splits, dkc);
+    bwd_lat_kernel<<<g, NT, 0, stream>>>(l);
+    FLARE_CUDA_CHECK(cudaGetLastError());
+    bwd_sum_splits_kernel<<<(unsigned)((lat_n + 255) / 256), 256, 0, stream>>>(out, partial, lat_n, pl.splits);
+    FLARE_CUDA_CHECK(cudaGetLastError());
+    return FLARE_OK;
+  };
+  {
+    LatParams l;
+    memset(&l, 0, sizeof(l));
+    l.ds[0] = p.dSe; l.parts[0] = pl.DT; l.rows[0] = f.k;
+    l.rows_stride_b[0] = f.k_stride_b; l.rows_stride_n[0] = f.k_stride_n; l.rows_stride_h[0] = f.k_stride_h;
+    l.nsrc = 1;
+    if (!shared_w && f.k_dec == nullptr) {  // decode keys are the latent queries: their gradient lands on Q
+      l.ds[1] = p.dSd; l.parts[1] = 1; l.rows[1] = f.q_dec;
+      l.rows_stride_b[1] = f.qd_stride_b; l.rows_stride_n[1] = f.qd_stride_n; l.rows_stride_h[1] = f.qd_stride_h;
+      l.nsrc = 2;
+    }
+    int rc = lat_launch(l, reinterpret_cast<float*>(ws + pl.off_part_q), a.dq);
+    if (rc != FLARE_OK) return rc;
+  }
+  if (f.k_dec != nullptr) {
+    LatParams l;
+    memset(&l, 0, sizeof(l));
+    l.ds[0] = p.dSd; l.parts[0] = 1;
+    l.rows[0] = f.q_dec ? f.q_dec : f.k;
+    l.rows_stride_b[0] = f.q_dec ? f.qd_stride_b : f.k_stride_b;
+    l.rows_stride_n[0] = f.q_dec ? f.qd_stride_n : f.k_stride_n;
+    l.rows_stride_h[0] = f.q_dec ? f.qd_stride_h : f.k_stride_h;
+    l.nsrc = 1;
+    int rc = lat_launch(l, reinterpret_cast<float*>(ws + pl.off_part_kd), a.dk_dec);
+    if (rc != FLARE_OK) return rc;
+  }
+  return FLARE_OK;
+}
+#endif
+
 }  // namespace flare

@@ -215,12 +215,7 @@ int flare_forward(const flare_fwd_args_t* args, flare_stream_t stream) {
   return forward_exact(args, stream);
 }
 
-size_t flare_backward_workspace_bytes(const flare_bwd_args_t* args) {
-  if (args == nullptr || check_forward(&args->fwd) != FLARE_OK) return 0;
-  return bwd_exact_workspace_bytes(*args);
-}
-
-int flare_backward(const flare_bwd_args_t* args, flare_stream_t stream) {
+static int check_backward(const flare_bwd_args_t* args) {
   if (args == nullptr) return FLARE_ERR_BAD_POINTER;
   flare_fwd_args_t chk = args->fwd;
   chk.y = const_cast<void*>(args->dy);  // reuse the forward validation for the shared fields
@@ -230,9 +225,22 @@ int flare_backward(const flare_bwd_args_t* args, flare_stream_t stream) {
   chk.state_out = flare_state_t{nullptr, nullptr, nullptr};
   const int rc = check_forward(&chk);
   if (rc != FLARE_OK) return rc;
+  if (args->fwd.B == 0 || args->fwd.N == 0) return FLARE_OK;
   if (!args->dq || !args->dk || !args->dv || !args->dy) return FLARE_ERR_BAD_POINTER;
   if ((args->fwd.q_dec != nullptr) != (args->dq_dec != nullptr)) return FLARE_ERR_BAD_POINTER;
   if ((args->fwd.k_dec != nullptr) != (args->dk_dec != nullptr)) return FLARE_ERR_BAD_POINTER;
+  return FLARE_OK;
+}
+
+size_t flare_backward_workspace_bytes(const flare_bwd_args_t* args) {
+  if (check_backward(args) != FLARE_OK) return 0;
+  return bwd_exact_workspace_bytes(*args);
+}
+
+int flare_backward(const flare_bwd_args_t* args, flare_stream_t stream) {
+  const int rc = check_backward(args);
+  if (rc != FLARE_OK) return rc;
+  g_last_launches = 0;
   return bwd_exact(*args, stream);
 }
 
