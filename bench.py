@@ -179,6 +179,10 @@ def bench_prefill(args, rank, world):
         yh.copy_(yy, non_blocking=True)
 
     e2e_steps = max(2, min(args.steps, 5))
+    if args.skip_e2e:
+        e2e_steps = 0
+        return dict(value=value, ms_per_step=ms / args.steps, e2e=None, roofline=_roofline(cfg, q, k, v, y, kern_ms),
+                    clocks=clk.summary(), gpu_launches=launches, tokens_per_step=tokens)
     e2e_step()
     barrier(world)
     s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -194,19 +198,23 @@ def bench_prefill(args, rank, world):
         "steps": e2e_steps, "call": "causal_flare.flare_autoregressive_triton(q, k, v)",
     }
 
+    return dict(value=value, ms_per_step=ms / args.steps, e2e=e2e, roofline=_roofline(cfg, q, k, v, y, kern_ms),
+                clocks=clk.summary(), gpu_launches=launches, tokens_per_step=tokens)
+
+
+def _roofline(cfg, q, k, v, y, kern_ms):
+    """Algorithmic bytes of one forward = K + V read, Y written, Q read (bf16) over the dominant kernel's time."""
     pk = peaks()
     alg_bytes = (k.numel() + v.numel() + y.numel()) * 2 + q.numel() * 2
     alg_flops = 6.0 * cfg["M"] * cfg["Dk"] * cfg["B"] * cfg["N"] * cfg["H"]
     achieved = alg_bytes / (kern_ms * 1e-3) / 1e9
-    roofline = {
+    return {
         "bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": achieved / pk["hbm_gbs"],
         "traffic": None, "peak_source": pk["source"], "kernel_ms": kern_ms,
         "kernel": "dominant forward kernel (CUDA events recorded around it inside flare_forward)",
         "algorithmic_bytes": alg_bytes,
         "tensor_frac": alg_flops / (kern_ms * 1e-3) / 1e12 / pk["bf16_tflops"],
     }
-    return dict(value=value, ms_per_step=ms / args.steps, e2e=e2e, roofline=roofline, clocks=clk.summary(),
-                gpu_launches=launches, tokens_per_step=tokens)
 
 
 def bench_decode(args, rank, world):
@@ -229,10 +237,10 @@ def bench_decode(args, rank, world):
         for key in state:
             state[key][b0:b0 + sl] = st[key]
         del kk, vv, st
-    steps = c["steps"]
+    steps = args.decode_steps
     ks = torch.randn(steps, B, H, Dk, generator=g, device="cuda").bfloat16()
     vs = torch.randn(steps, B, H, Dv, generator=g, device="cuda").bfloat16()
-    for i in range(8):
+    for i in range(min(8, steps)):
         cf.flare_autoregressive_decode_triton(q, ks[i], vs[i], state, scale=sc)
     barrier(world)
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -289,6 +297,10 @@ def main():
     ap.add_argument("--skip-decode", action="store_true")
     ap.add_argument("--skip-cpu", action="store_true")
     ap.add_argument("--decode-prefix", type=int, default=C3["prefix"])
+    ap.add_argument("--decode-steps", type=int, default=C3["steps"])
+    ap.add_argument("--only", default="all", choices=["all", "prefill", "decode"],
+                    help="profiling aid: run one section only (the JSON line then lacks the other)")
+    ap.add_argument("--skip-e2e", action="store_true")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -315,8 +327,13 @@ def main():
 
     assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU fallback)"
     rank, world, _ = dist_setup(args.gpus)
+    if args.only == "decode":
+        dec = bench_decode(args, rank, world)
+        if rank == 0:
+            print(json.dumps({"metric": "decode throughput", "value": dec["tok_per_s"], "unit": "tok/s", "decode": dec}))
+        return
     pre = bench_prefill(args, rank, world)
-    dec = None if args.skip_decode else bench_decode(args, rank, world)
+    dec = None if (args.skip_decode or args.only == "prefill") else bench_decode(args, rank, world)
     cpu = None
     if rank == 0 and world == 1 and not args.skip_cpu:
         cpu = cpu_reference_sample()
