@@ -3,10 +3,22 @@
 from __future__ import annotations
 
 import ctypes as C
+import os
 
 import torch
 
 from . import _lib
+
+
+def default_path() -> int:
+    """Kernel path selector: FLARE_B200_PATH = auto (default) | exact | tensor."""
+    return {"auto": _lib.PATH_AUTO, "exact": _lib.PATH_EXACT, "tensor": _lib.PATH_TENSOR}[
+        os.environ.get("FLARE_B200_PATH", "auto").strip().lower()]
+
+
+def device_status(reset: bool = True) -> int:
+    """0 when every bounded wait inside the tensor-core kernels completed (synchronises the device)."""
+    return _lib.load().flare_device_status(1 if reset else 0)
 
 
 def _prep(t, dtype):
@@ -18,12 +30,14 @@ def _prep(t, dtype):
 
 
 def forward(Q, K, V, *, scale, Q_dec=None, K_dec=None, variant=_lib.SOFTMAX, power=2.0, block_size=1, mask=None,
-            state_in=None, want_state=False, want_lse=False, out_dtype=None, out_bhnd=False, path=_lib.PATH_AUTO,
+            state_in=None, want_state=False, want_lse=False, out_dtype=None, out_bhnd=False, path=None,
             want_y=True):
     """Run flare_forward.  Q_dec / K_dec are None for the shared-weight default.
 
     Returns (Y, state_out | None, lse_dec | None, lse_enc | None)."""
     _lib.load()
+    if path is None:
+        path = default_path()
     dev = K.device
     dt = K.dtype
     _lib.dtype_code(dt)

@@ -5,6 +5,7 @@
 #include "bwd_exact.cuh"
 #include "decode_step.cuh"
 #include "flare_common.cuh"
+#include "prefill_tc.cuh"
 #include "state_ops.cuh"
 #include "walk_exact.cuh"
 
@@ -79,6 +80,7 @@ int check_forward(const flare_fwd_args_t* a) {
 }
 
 struct FwdPlan {
+  bool use_tc;
   int nseg;
   int seg_len;
   size_t state_floats;  // floats per state: 2M + M*Dv
@@ -86,9 +88,28 @@ struct FwdPlan {
 };
 
 FwdPlan plan_forward(const flare_fwd_args_t* a) {
-  FwdPlan pl{1, a->N > 0 ? a->N : 1, 0, 0};
+  FwdPlan pl{false, 1, a->N > 0 ? a->N : 1, 0, 0};
   if (a->B == 0 || a->N == 0) return pl;
   const int64_t lanes = (int64_t)a->B * a->H;
+  pl.state_floats = (size_t)2 * a->M + (size_t)a->M * a->Dv;
+  if (a->path != FLARE_PATH_EXACT && prefill_tc_supported(a)) {
+    // tensor-core path: one CTA per SM walks a (lane, segment); split the sequence only when lanes are scarce
+    pl.use_tc = true;
+    int nseg = 1;
+    const int sms = sm_count();
+    if (lanes * 3 <= sms * 2) {
+      nseg = (int)((sms + lanes - 1) / lanes);
+      const int max_seg = a->N / 256;
+      if (nseg > max_seg) nseg = max_seg;
+      if (nseg < 1) nseg = 1;
+    }
+    int seg_len = (a->N + nseg - 1) / nseg;
+    seg_len = (seg_len + 127) / 128 * 128;
+    pl.nseg = (a->N + seg_len - 1) / seg_len;
+    pl.seg_len = seg_len;
+    pl.ws_bytes = pl.nseg > 1 ? align_up((size_t)lanes * pl.nseg * pl.state_floats * 4, 256) : 0;
+    return pl;
+  }
   const int dd = walk_exact_dd(a->M, a->Dv);
   const int dtiles = (a->Dv + 32 * dd - 1) / (32 * dd);
   const int64_t ctas = lanes * dtiles;
@@ -126,7 +147,22 @@ void fill_walk(WalkParams& w, const flare_fwd_args_t* a) {
   w.dtype = a->dtype; w.variant = a->variant; w.block_size = a->block_size;
 }
 
-int forward_exact(const flare_fwd_args_t* a, cudaStream_t stream) {
+int launch_walk(const flare_fwd_args_t* a, const FwdPlan& pl, const WalkParams& w, int nseg_grid, cudaStream_t stream) {
+  if (!pl.use_tc) return launch_walk_exact(w, nseg_grid, stream);
+  TcParams t;
+  memset(&t, 0, sizeof(t));
+  t.y = w.write_y ? w.y : nullptr;
+  t.y_stride_b = w.y_stride_b; t.y_stride_n = w.y_stride_n; t.y_stride_h = w.y_stride_h;
+  t.N = w.N; t.H = w.H; t.scale = w.scale; t.seg_len = w.seg_len;
+  t.in_m = w.in_m; t.in_d = w.in_d; t.in_u = w.in_u;
+  t.in_lane_stride = w.in_lane_stride; t.in_seg_stride = w.in_seg_stride;
+  t.out_m = w.out_m; t.out_d = w.out_d; t.out_u = w.out_u;
+  t.out_lane_stride = w.out_lane_stride; t.out_seg_stride = w.out_seg_stride;
+  t.out_mode = w.out_mode; t.nseg_total = w.nseg_total;
+  return launch_prefill_tc(a, t, nseg_grid, stream);
+}
+
+int forward_run(const flare_fwd_args_t* a, cudaStream_t stream) {
   const FwdPlan pl = plan_forward(a);
   if (pl.ws_bytes > 0 && (a->workspace == nullptr || a->workspace_bytes < pl.ws_bytes || !aligned16(a->workspace)))
     return FLARE_ERR_WORKSPACE;
@@ -146,7 +182,7 @@ int forward_exact(const flare_fwd_args_t* a, cudaStream_t stream) {
     w.lse_dec = a->lse_dec; w.lse_enc = a->lse_enc;
     g_last_launches = 1;
     DominantKernelTimer timer(stream);
-    return launch_walk_exact(w, 1, stream);
+    return launch_walk(a, pl, w, 1, stream);
   }
   // segmented: (A) local state of every segment but the last, (B) exclusive scan with the carry-in,
   // (C) walk every segment from its prefix state and emit the outputs.
@@ -157,7 +193,7 @@ int forward_exact(const flare_fwd_args_t* a, cudaStream_t stream) {
   wa.y = nullptr; wa.write_y = 0; wa.lse_dec = nullptr; wa.lse_enc = nullptr;
   wa.out_m = seg_m; wa.out_d = seg_d; wa.out_u = seg_u;
   wa.out_lane_stride = pl.nseg; wa.out_seg_stride = 1; wa.out_mode = 1;
-  int rc = launch_walk_exact(wa, pl.nseg - 1, stream);
+  int rc = launch_walk(a, pl, wa, pl.nseg - 1, stream);
   if (rc != FLARE_OK) return rc;
   FoldParams f;
   memset(&f, 0, sizeof(f));
@@ -178,7 +214,7 @@ int forward_exact(const flare_fwd_args_t* a, cudaStream_t stream) {
   if (!w.write_y && !have_out) return FLARE_OK;
   g_last_launches = 3;
   DominantKernelTimer timer(stream);
-  return launch_walk_exact(w, pl.nseg, stream);
+  return launch_walk(a, pl, w, pl.nseg, stream);
 }
 
 }  // namespace
@@ -212,7 +248,7 @@ int flare_forward(const flare_fwd_args_t* args, flare_stream_t stream) {
     }
     return FLARE_OK;
   }
-  return forward_exact(args, stream);
+  return forward_run(args, stream);
 }
 
 static int check_backward(const flare_bwd_args_t* args) {
@@ -308,6 +344,18 @@ void flare_set_kernel_events(void* begin_event, void* end_event) {
 }
 
 int flare_last_launch_count(void) { return g_last_launches; }
+
+int flare_forward_uses_tensor_path(const flare_fwd_args_t* args) {
+  if (check_forward(args) != FLARE_OK) return 0;
+  return plan_forward(args).use_tc ? 1 : 0;
+}
+
+int flare_device_status(int reset) {
+  int v = 0;
+  const int rc = prefill_tc_error_flag(&v, reset != 0);
+  if (rc != FLARE_OK) return -rc;
+  return v;
+}
 
 /* sizeof of the argument structs, so a foreign-language binding can verify its own layout */
 size_t flare_abi_sizeof(int which) {

@@ -1,0 +1,482 @@
+// Tensor-core (tcgen05 + TMEM + TMA) chunked causal prefill for the softmax encoder, bf16 operands, fp32
+// accumulation and statistics.  Shape class: M = 128 latents, Dk = Dv = 64, shared decode weights, no mask.
+//
+// One CTA owns a (batch, head, sequence segment) and walks its chunks of C = 128 tokens in order, carrying the
+// latent state on chip: U [128 latents x 64] fp32 in tensor memory, running max c and denominator d per latent
+// in registers of the thread that owns the latent (TMEM lane = thread).  Per chunk, with the frame c_m = running
+// max after the chunk and kappa = max_m c_m:
+//
+//   S^T = Q K_c^T                          MMA1  (128 x 128, k = 64)      latents on lanes, tokens on columns
+//   E[m,t]   = exp(s[m,t] - c_m)           one exp per element, thread m scans its row
+//   D[m,t]   = d_m + cumsum_t E[m,t]       (d_m already rescaled into the new frame)
+//   R[m,t]   = E[m,t] exp(c_m - kappa) / D[m,t]        = softmax-numerator / encoder denominator
+//   Y    = R^T U_bf16   ,  Den0 = R^T d    MMA3  (+ a 16-column MMA for the denominator column)
+//   W    = R^T E   (tokens x tokens)       MMA4  -> causal mask + bf16, written back to TMEM
+//   U   += E V_c                           MMA2
+//   Y   += tril(W) V_c                     MMA5  (A operand from TMEM)
+//   y_t  = Y[t,:] / (Den0[t] + rowsum tril(W)[t,:])
+//
+// Operands E, R (written by the latent threads row-wise) feed MMAs both K-major and MN-major from the same
+// 128-byte-swizzled buffers, so no transposition pass exists.  K_c / V_c tiles are TMA-staged and
+// double-buffered.  Warps 0-3: element-wise phases; warp 4: TMA producer and MMA issuer (one elected thread).
+#include "prefill_tc.cuh"
+
+#include <cuda.h>
+#include <string.h>
+
+#include "sm100_ptx.cuh"
+
+namespace flare {
+
+using namespace sm100;
+
+namespace {
+
+constexpr int C = 128;    // tokens per chunk
+constexpr int M = 128;    // latents
+constexpr int D = 64;     // Dk = Dv
+constexpr int NTHREADS = 160;
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+
+// shared memory map (bytes, every operand buffer 1024-aligned for the 128B swizzle)
+constexpr int OFF_Q = 0;                      // [128 m][64] bf16, K-major            16 KB
+constexpr int OFF_K = OFF_Q + 16384;          // 2 stages x [128 t][64] bf16          32 KB
+constexpr int OFF_V = OFF_K + 2 * 16384;      // 2 stages x [128 t][64] bf16          32 KB
+constexpr int OFF_E = OFF_V + 2 * 16384;      // [2 t-blocks][128 m][64 t] bf16       32 KB
+constexpr int OFF_R = OFF_E + 32768;          // [2 t-blocks][128 m][64 t] bf16       32 KB
+constexpr int OFF_U = OFF_R + 32768;          // [128 m][64 dv] bf16                  16 KB
+constexpr int OFF_B16 = OFF_U + 16384;        // [2 m-blocks][16 n][64 m] bf16         4 KB
+constexpr int OFF_MISC = OFF_B16 + 4096;      // barriers, tmem slot, reductions
+constexpr int SMEM_BYTES = OFF_MISC + 256 + 1024;  // + slack for manual 1024-byte alignment
+
+// tensor-memory columns
+constexpr uint32_t TM_S = 0, TM_W = 128, TM_U = 256, TM_Y = 320, TM_DEN = 384, TM_COLS = 512;
+
+struct Misc {
+  uint64_t full[2], empty[2], q_full, s_ready, kap_done, p1_done, w_ready, p2_done, y_ready;
+  uint32_t tmem_base;
+  int abort_flag;
+  float wmax[4];
+};
+
+__device__ int g_tc_error = 0;
+
+__device__ __forceinline__ uint32_t swz_chunk_off(int row, int chunk) { return row * 128 + ((chunk ^ (row & 7)) << 4); }
+
+}  // namespace
+
+__global__ void __launch_bounds__(NTHREADS, 1)
+prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                  const __grid_constant__ CUtensorMap tm_v, const TcParams p) {
+  extern __shared__ uint8_t smem_dyn[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
+  Misc* misc = reinterpret_cast<Misc*>(smem + OFF_MISC);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int lane_id = blockIdx.x, seg = blockIdx.y;
+  const int b = lane_id / p.H, h = lane_id % p.H;
+  const int seg_begin = seg * p.seg_len;
+  const int seg_end = min(p.N, seg_begin + p.seg_len);
+  const int nchunks = (seg_end - seg_begin + C - 1) / C;
+
+  if (tid == 0) {
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&misc->full[i], 1);
+      mbar_init(&misc->empty[i], 1);
+    }
+    mbar_init(&misc->q_full, 1);
+    mbar_init(&misc->s_ready, 1);
+    mbar_init(&misc->kap_done, 4);
+    mbar_init(&misc->p1_done, 128);
+    mbar_init(&misc->w_ready, 1);
+    mbar_init(&misc->p2_done, 128);
+    mbar_init(&misc->y_ready, 1);
+    misc->abort_flag = 0;
+    fence_barrier_init();
+  }
+  // zero the denominator operand tile once (rows 1..15 stay zero for the whole kernel)
+  for (int i = tid; i < 4096 / 16; i += NTHREADS) reinterpret_cast<uint4*>(smem + OFF_B16)[i] = make_uint4(0, 0, 0, 0);
+  if (warp == 4) {
+    tmem_alloc(&misc->tmem_base, TM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = misc->tmem_base;
+  bool ok = true;
+
+  if (warp == 4) {
+    // =========================== TMA producer + MMA issuer (one thread) ===========================
+    if (lane == 0) {
+      prefetch_tensormap(&tm_q);
+      prefetch_tensormap(&tm_k);
+      prefetch_tensormap(&tm_v);
+      mbar_arrive_expect_tx(&misc->q_full, 16384);
+      tma_load_3d(smem + OFF_Q, &tm_q, &misc->q_full, 0, 0, h);
+      auto produce = [&](int i) {
+        const int st = i & 1;
+        mbar_arrive_expect_tx(&misc->full[st], 32768);
+        tma_load_4d(smem + OFF_K + st * 16384, &tm_k, &misc->full[st], 0, h, seg_begin + i * C, b);
+        tma_load_4d(smem + OFF_V + st * 16384, &tm_v, &misc->full[st], 0, h, seg_begin + i * C, b);
+      };
+      int produced = 0;
+      for (; produced < 2 && produced < nchunks; ++produced) produce(produced);
+
+      const uint32_t q_addr = smem_u32(smem + OFF_Q), e_addr = smem_u32(smem + OFF_E), r_addr = smem_u32(smem + OFF_R);
+      const uint32_t u_addr = smem_u32(smem + OFF_U), b16_addr = smem_u32(smem + OFF_B16);
+      constexpr uint32_t ID_S = make_idesc_bf16(128, 128, 0, 0);   // Q (K-major) x K_c (K-major)
+      constexpr uint32_t ID_U = make_idesc_bf16(128, 64, 0, 1);    // E (K-major) x V (MN-major)
+      constexpr uint32_t ID_Y0 = make_idesc_bf16(128, 64, 1, 1);   // R (MN-major) x U_bf16 (MN-major)
+      constexpr uint32_t ID_DEN = make_idesc_bf16(128, 16, 1, 0);  // R (MN-major) x d tile (K-major)
+      constexpr uint32_t ID_W = make_idesc_bf16(128, 128, 1, 1);   // R (MN-major) x E (MN-major)
+      constexpr uint32_t ID_Y1 = make_idesc_bf16(128, 64, 0, 1);   // tril(W) (TMEM) x V (MN-major)
+
+      auto issue_scores = [&](int i) -> bool {
+        const int st = i & 1;
+        if (!mbar_wait(&misc->full[st], (i >> 1) & 1)) return false;
+        tc_fence_after_sync();
+        const uint32_t k_addr = smem_u32(smem + OFF_K + st * 16384);
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          mma_ss(tmem + TM_S, make_desc_sw128(q_addr + j * 32, 16, 1024), make_desc_sw128(k_addr + j * 32, 16, 1024), ID_S,
+                 j > 0);
+        tc_commit(&misc->s_ready);
+        return true;
+      };
+
+      ok = mbar_wait(&misc->q_full, 0);
+      if (ok && nchunks > 0) ok = issue_scores(0);
+      for (int i = 0; ok && i < nchunks; ++i) {
+        const int st = i & 1;
+        const uint32_t par = i & 1;
+        const uint32_t v_addr = smem_u32(smem + OFF_V + st * 16384);
+        if (!(ok = mbar_wait(&misc->p1_done, par))) break;
+        tc_fence_after_sync();
+        // W = R^T E  (k = latents, 8 steps of 16 rows = 2048 bytes)
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          mma_ss(tmem + TM_W, make_desc_sw128(r_addr + j * 2048, 16384, 1024), make_desc_sw128(e_addr + j * 2048, 16384, 1024),
+                 ID_W, j > 0);
+        tc_commit(&misc->w_ready);
+        // Y = R^T U_bf16, Den0 = R^T d
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          mma_ss(tmem + TM_Y, make_desc_sw128(r_addr + j * 2048, 16384, 1024), make_desc_sw128(u_addr + j * 2048, 1024, 1024),
+                 ID_Y0, j > 0);
+          mma_ss(tmem + TM_DEN, make_desc_sw128(r_addr + j * 2048, 16384, 1024),
+                 make_desc_sw128(b16_addr + (j >> 2) * 2048 + (j & 3) * 32, 16, 1024), ID_DEN, j > 0);
+        }
+        // U += E V_c  (k = tokens of the chunk)
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          mma_ss(tmem + TM_U, make_desc_sw128(e_addr + (j >> 2) * 16384 + (j & 3) * 32, 16, 1024),
+                 make_desc_sw128(v_addr + j * 2048, 1024, 1024), ID_U, 1);
+        // scores of the next chunk while the element-wise threads mask W
+        if (i + 1 < nchunks) {
+          if (!(ok = issue_scores(i + 1))) break;
+        }
+        if (!(ok = mbar_wait(&misc->p2_done, par))) break;
+        tc_fence_after_sync();
+        // Y += tril(W) V_c, A operand from tensor memory (bf16 pairs, 8 columns per k-step of 16)
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          mma_ts(tmem + TM_Y, tmem + TM_W + j * 8, make_desc_sw128(v_addr + j * 2048, 1024, 1024), ID_Y1, 1);
+        tc_commit(&misc->y_ready);
+        tc_commit(&misc->empty[st]);
+        // refill this stage with chunk i + 2 once the MMAs above have drained it
+        if (produced < nchunks) {
+          if (!(ok = mbar_wait(&misc->empty[st], (i >> 1) & 1))) break;
+          produce(produced++);
+        }
+      }
+      if (!ok) {
+        misc->abort_flag = 1;
+        atomicExch(&g_tc_error, 1);
+      }
+    }
+  } else {
+    // =========================== element-wise warps: thread = TMEM lane ===========================
+    const uint32_t tl = tmem + ((uint32_t)(warp * 32) << 16);  // this warp's lane quarter
+    const int m = tid;                                          // latent (phase 1) / token in chunk (phases 2, 3)
+    const float sc2 = p.scale * kLog2e;
+    const int64_t st_idx = (int64_t)lane_id * p.in_lane_stride + (int64_t)seg * p.in_seg_stride;
+    float c2 = p.in_m ? p.in_m[st_idx * M + m] * kLog2e : -INFINITY;  // running max, log2 units
+    float dsum = p.in_d ? p.in_d[st_idx * M + m] : 0.f;
+    {
+      // carry-in numerator -> tensor memory
+      uint32_t r[32];
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          r[i] = p.in_u ? __float_as_uint(p.in_u[(st_idx * M + m) * D + half * 32 + i]) : 0u;
+        tmem_st32(tl + TM_U + half * 32, r);
+      }
+      tmem_wait_st();
+    }
+    uint8_t* e_row = smem + OFF_E;
+    uint8_t* r_row = smem + OFF_R;
+
+    for (int i = 0; ok && i < nchunks; ++i) {
+      const uint32_t par = i & 1;
+      const int t0 = seg_begin + i * C;
+      const int nvalid = min(C, seg_end - t0);
+      // ------------------------------- phase 1: latent rows -------------------------------
+      if (!(ok = mbar_wait(&misc->s_ready, par))) break;
+      tc_fence_after_sync();
+      float cmax = -INFINITY;
+#pragma unroll 1
+      for (int j = 0; j < 4; ++j) {
+        uint32_t r[32];
+        tmem_ld32(tl + TM_S + j * 32, r);
+        tmem_wait_ld();
+#pragma unroll
+        for (int k = 0; k < 32; ++k)
+          if (j * 32 + k < nvalid) cmax = fmaxf(cmax, __uint_as_float(r[k]) * sc2);
+      }
+      const float c_new = fmaxf(c2, cmax);
+      const float alpha = ex2_approx(c2 - c_new);  // 0 when the old state is empty
+      // kappa = max over latents of the new frame (block-wide)
+      float wm = c_new;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) wm = fmaxf(wm, __shfl_xor_sync(0xffffffffu, wm, o));
+      if (lane == 0) {
+        misc->wmax[warp] = wm;
+        mbar_arrive(&misc->kap_done);
+      }
+      if (!(ok = mbar_wait(&misc->kap_done, par))) break;
+      const float kappa = fmaxf(fmaxf(misc->wmax[0], misc->wmax[1]), fmaxf(misc->wmax[2], misc->wmax[3]));
+      const float a_m = ex2_approx(c_new - kappa);
+      dsum *= alpha;
+      c2 = c_new;
+      // d (in the new frame) as the first row of the denominator operand tile
+      *reinterpret_cast<__nv_bfloat16*>(smem + OFF_B16 + (m >> 6) * 2048 + ((m & 63) >> 3) * 16 + (m & 7) * 2) =
+          __float2bfloat16_rn(dsum);
+      // state: rescale in tensor memory if needed, and publish a bf16 copy as an MMA operand
+      {
+        const bool need = __any_sync(0xffffffffu, alpha != 1.0f);
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          uint32_t r[32];
+          tmem_ld32(tl + TM_U + half * 32, r);
+          tmem_wait_ld();
+          if (need) {
+#pragma unroll
+            for (int k = 0; k < 32; ++k) r[k] = __float_as_uint(__uint_as_float(r[k]) * alpha);
+            tmem_st32(tl + TM_U + half * 32, r);
+          }
+#pragma unroll
+          for (int ch = 0; ch < 4; ++ch) {
+            uint4 v;
+            v.x = pack_bf16(__uint_as_float(r[ch * 8 + 0]), __uint_as_float(r[ch * 8 + 1]));
+            v.y = pack_bf16(__uint_as_float(r[ch * 8 + 2]), __uint_as_float(r[ch * 8 + 3]));
+            v.z = pack_bf16(__uint_as_float(r[ch * 8 + 4]), __uint_as_float(r[ch * 8 + 5]));
+            v.w = pack_bf16(__uint_as_float(r[ch * 8 + 6]), __uint_as_float(r[ch * 8 + 7]));
+            *reinterpret_cast<uint4*>(smem + OFF_U + swz_chunk_off(m, half * 4 + ch)) = v;
+          }
+        }
+        if (need) tmem_wait_st();
+      }
+      // E, D, R for the 128 tokens of the chunk
+#pragma unroll 1
+      for (int j = 0; j < 4; ++j) {
+        uint32_t r[32];
+        tmem_ld32(tl + TM_S + j * 32, r);
+        tmem_wait_ld();
+        uint32_t ep[16], rp[16];
+#pragma unroll
+        for (int k = 0; k < 32; k += 2) {
+          float e0 = (j * 32 + k < nvalid) ? ex2_approx(__uint_as_float(r[k]) * sc2 - c_new) : 0.f;
+          float e1 = (j * 32 + k + 1 < nvalid) ? ex2_approx(__uint_as_float(r[k + 1]) * sc2 - c_new) : 0.f;
+          dsum += e0;
+          const float r0 = e0 * a_m * rcp_approx(dsum);
+          dsum += e1;
+          const float r1 = e1 * a_m * rcp_approx(dsum);
+          ep[k >> 1] = pack_bf16(e0, e1);
+          rp[k >> 1] = pack_bf16(r0, r1);
+        }
+        // tokens [32 j, 32 j + 32) live in t-block j / 2, 16-byte chunks (j % 2) * 4 .. + 3 of row m
+        const int blk = j >> 1, ch0 = (j & 1) * 4;
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {
+          const uint32_t off = blk * 16384 + swz_chunk_off(m, ch0 + ch);
+          *reinterpret_cast<uint4*>(e_row + off) = make_uint4(ep[ch * 4], ep[ch * 4 + 1], ep[ch * 4 + 2], ep[ch * 4 + 3]);
+          *reinterpret_cast<uint4*>(r_row + off) = make_uint4(rp[ch * 4], rp[ch * 4 + 1], rp[ch * 4 + 2], rp[ch * 4 + 3]);
+        }
+      }
+      fence_proxy_async_smem();
+      tc_fence_before_sync();
+      mbar_arrive(&misc->p1_done);
+
+      // ------------------------------- phase 2: token rows of W -------------------------------
+      if (!(ok = mbar_wait(&misc->w_ready, par))) break;
+      tc_fence_after_sync();
+      float rowsum = 0.f;
+#pragma unroll 1
+      for (int j = 0; j < 4; ++j) {
+        uint32_t wp[16];
+        if (j <= warp) {
+          uint32_t r[32];
+          tmem_ld32(tl + TM_W + j * 32, r);
+          tmem_wait_ld();
+#pragma unroll
+          for (int k = 0; k < 32; k += 2) {
+            const float w0 = (j < warp || k <= lane) ? __uint_as_float(r[k]) : 0.f;
+            const float w1 = (j < warp || k + 1 <= lane) ? __uint_as_float(r[k + 1]) : 0.f;
+            const uint32_t pk = pack_bf16(w0, w1);
+            wp[k >> 1] = pk;
+            rowsum += __uint_as_float(pk << 16) + __uint_as_float(pk & 0xffff0000u);
+          }
+        } else {
+#pragma unroll
+          for (int k = 0; k < 16; ++k) wp[k] = 0u;
+        }
+        tmem_st16(tl + TM_W + j * 16, wp);
+      }
+      tmem_wait_st();
+      tc_fence_before_sync();
+      mbar_arrive(&misc->p2_done);
+
+      // ------------------------------- phase 3: normalise and store -------------------------------
+      if (!(ok = mbar_wait(&misc->y_ready, par))) break;
+      tc_fence_after_sync();
+      uint32_t den0;
+      tmem_ld1(tl + TM_DEN, den0);
+      tmem_wait_ld();
+      const float inv = 1.0f / (__uint_as_float(den0) + rowsum);
+      const int t = t0 + m;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t r[32];
+        tmem_ld32(tl + TM_Y + half * 32, r);
+        tmem_wait_ld();
+        if (p.y != nullptr && m < nvalid) {
+          uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.y) + (int64_t)b * p.y_stride_b +
+                                                (int64_t)t * p.y_stride_n + (int64_t)h * p.y_stride_h + half * 32);
+#pragma unroll
+          for (int ch = 0; ch < 4; ++ch) {
+            uint4 v;
+            v.x = pack_bf16(__uint_as_float(r[ch * 8 + 0]) * inv, __uint_as_float(r[ch * 8 + 1]) * inv);
+            v.y = pack_bf16(__uint_as_float(r[ch * 8 + 2]) * inv, __uint_as_float(r[ch * 8 + 3]) * inv);
+            v.z = pack_bf16(__uint_as_float(r[ch * 8 + 4]) * inv, __uint_as_float(r[ch * 8 + 5]) * inv);
+            v.w = pack_bf16(__uint_as_float(r[ch * 8 + 6]) * inv, __uint_as_float(r[ch * 8 + 7]) * inv);
+            dst[ch] = v;
+          }
+        }
+      }
+      tc_fence_before_sync();
+    }
+    if (!ok) {
+      misc->abort_flag = 1;
+      atomicExch(&g_tc_error, 1);
+    }
+    // carry-out state
+    if (ok && p.out_u != nullptr && (p.out_mode == 1 || (p.out_mode == 2 && seg == p.nseg_total - 1))) {
+      const int64_t so = (int64_t)lane_id * p.out_lane_stride + (int64_t)seg * p.out_seg_stride;
+      p.out_m[so * M + m] = c2 * kLn2;
+      p.out_d[so * M + m] = dsum;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t r[32];
+        tmem_ld32(tl + TM_U + half * 32, r);
+        tmem_wait_ld();
+        float4* dst = reinterpret_cast<float4*>(p.out_u + (so * M + m) * D + half * 32);
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          dst[k] = make_float4(__uint_as_float(r[4 * k]), __uint_as_float(r[4 * k + 1]), __uint_as_float(r[4 * k + 2]),
+                               __uint_as_float(r[4 * k + 3]));
+      }
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 4) tmem_dealloc(tmem, TM_COLS);
+}
+
+// -------------------------------------------------------------------------------------------------
+// host side
+// -------------------------------------------------------------------------------------------------
+namespace {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn) return fn;
+  void* ptr = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) != cudaSuccess ||
+      qres != cudaDriverEntryPointSuccess)
+    return nullptr;
+  fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  return fn;
+}
+
+// bf16 tensor with `rank` dims (innermost first), strides in elements for dims 1..rank-1
+bool make_map(CUtensorMap* map, const void* base, int rank, const uint64_t* dims, const int64_t* strides_elems,
+              const uint32_t* box) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t gdim[5], gstride[4];
+  cuuint32_t bx[5], estr[5];
+  for (int i = 0; i < rank; ++i) {
+    gdim[i] = dims[i];
+    bx[i] = box[i];
+    estr[i] = 1;
+  }
+  for (int i = 0; i + 1 < rank; ++i) gstride[i] = (cuuint64_t)strides_elems[i] * 2;
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank, const_cast<void*>(base), gdim, gstride, bx, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace
+
+bool prefill_tc_supported(const flare_fwd_args_t* a) {
+  return a->dtype == FLARE_BF16 && a->variant == FLARE_SOFTMAX && a->block_size == 1 && a->M == M && a->Dk == D &&
+         a->Dv == D && a->q_dec == nullptr && a->k_dec == nullptr && a->mask == nullptr && a->lse_dec == nullptr &&
+         a->q_stride_m == D && a->N >= 1;
+}
+
+int launch_prefill_tc(const flare_fwd_args_t* a, const TcParams& p, int nseg_grid, cudaStream_t stream) {
+  CUtensorMap tq, tk, tv;
+  {
+    const uint64_t dims[3] = {(uint64_t)D, (uint64_t)M, (uint64_t)a->H};
+    const int64_t str[2] = {a->q_stride_m, a->q_stride_h};
+    const uint32_t box[3] = {64, 128, 1};
+    if (!make_map(&tq, a->q, 3, dims, str, box)) return FLARE_ERR_CUDA;
+  }
+  {
+    const uint64_t dims[4] = {(uint64_t)D, (uint64_t)a->H, (uint64_t)a->N, (uint64_t)a->B};
+    const uint32_t box[4] = {64, 1, 128, 1};
+    const int64_t strk[3] = {a->k_stride_h, a->k_stride_n, a->k_stride_b};
+    const int64_t strv[3] = {a->v_stride_h, a->v_stride_n, a->v_stride_b};
+    if (!make_map(&tk, a->k, 4, dims, strk, box)) return FLARE_ERR_CUDA;
+    if (!make_map(&tv, a->v, 4, dims, strv, box)) return FLARE_ERR_CUDA;
+  }
+  static bool attr_set = false;
+  if (!attr_set) {
+    FLARE_CUDA_CHECK(cudaFuncSetAttribute(prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    attr_set = true;
+  }
+  dim3 grid(a->B * a->H, nseg_grid);
+  prefill_tc_kernel<<<grid, NTHREADS, SMEM_BYTES, stream>>>(tq, tk, tv, p);
+  FLARE_CUDA_CHECK(cudaGetLastError());
+  return FLARE_OK;
+}
+
+int prefill_tc_error_flag(int* host_value, bool reset) {
+  int v = 0;
+  FLARE_CUDA_CHECK(cudaMemcpyFromSymbol(&v, g_tc_error, sizeof(int)));
+  if (reset && v != 0) {
+    const int zero = 0;
+    FLARE_CUDA_CHECK(cudaMemcpyToSymbol(g_tc_error, &zero, sizeof(int)));
+  }
+  *host_value = v;
+  return FLARE_OK;
+}
+
+}  // namespace flare

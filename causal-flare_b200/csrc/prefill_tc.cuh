@@ -1,0 +1,28 @@
+// Tensor-core chunked prefill (see prefill_tc.cu).
+#pragma once
+#include "flare_common.cuh"
+
+namespace flare {
+
+struct TcParams {
+  void* y;  // bf16 [B, N, H, 64] (strided) or null
+  int64_t y_stride_b, y_stride_n, y_stride_h;
+  int N, H;
+  float scale;
+  int seg_len;
+  // carry-in / carry-out states, indexed lane * lane_stride + seg * seg_stride (in states)
+  const float *in_m, *in_d, *in_u;
+  int64_t in_lane_stride, in_seg_stride;
+  float *out_m, *out_d, *out_u;
+  int64_t out_lane_stride, out_seg_stride;
+  int out_mode;  // 0: none, 1: every segment, 2: last segment only
+  int nseg_total;
+};
+
+bool prefill_tc_supported(const flare_fwd_args_t* a);
+// launches segments 0 .. nseg_grid-1
+int launch_prefill_tc(const flare_fwd_args_t* a, const TcParams& p, int nseg_grid, cudaStream_t stream);
+// reads (and optionally clears) the device-side error flag of the tensor-core kernels; synchronises
+int prefill_tc_error_flag(int* host_value, bool reset);
+
+}  // namespace flare

@@ -164,6 +164,15 @@ int flare_abi_version(void);
  * stream they launch on.  flare_last_launch_count: kernels launched by this thread's last forward/backward. */
 void flare_set_kernel_events(void* begin_event, void* end_event);
 int flare_last_launch_count(void);
+
+/* 1 when flare_forward would take the tcgen05 tensor-core path for this problem (path AUTO or TENSOR and a
+ * supported shape: bf16, softmax encoder, M = 128, Dk = Dv = 64, shared decode weights, no mask), else 0. */
+int flare_forward_uses_tensor_path(const flare_fwd_args_t* args);
+
+/* Device-side health of the tensor-core kernels: synchronises the device and returns 0 when every bounded
+ * wait inside them completed, 1 when a kernel gave up on a wait (its outputs are then invalid), or a negative
+ * flare_status on a CUDA error.  reset != 0 clears the flag. */
+int flare_device_status(int reset);
 /* sizeof(flare_fwd_args_t / flare_bwd_args_t / flare_decode_args_t / flare_state_t) for which = 0..3,
  * so that a foreign-language binding can verify its struct layout at load time. */
 size_t flare_abi_sizeof(int which);

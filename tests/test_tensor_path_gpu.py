@@ -1,0 +1,85 @@
+"""GPU parity of the tcgen05 tensor-core prefill path (bf16, M=128, D=64) against the CPU oracle, the exact
+CUDA path, and size-independent properties at the full benchmark size."""
+import ctypes as C
+
+import pytest
+import torch
+
+import causal_flare as cf
+from causal_flare import _lib, _ops
+from oracle import flare_oracle as orc
+from util import assert_bf16_gate, assert_close, to_dev
+
+pytestmark = pytest.mark.gpu
+
+M, D = 128, 64
+
+
+def run(q, k, v, path, **kw):
+    out = _ops.forward(q, k, v, scale=kw.pop("scale", D ** -0.5), path=path, **kw)
+    assert _ops.device_status() == 0, "a tensor-core kernel gave up on a bounded wait"
+    return out
+
+
+def uses_tensor_path(q, k, v):
+    args = _lib.make_fwd_args(q, k, v, None, None, torch.empty_like(v), scale=1.0)
+    return _lib.load().flare_forward_uses_tensor_path(C.byref(args)) == 1
+
+
+@pytest.mark.parametrize("B, N, H", [(1, 128, 1), (1, 256, 1), (2, 300, 2), (1, 1000, 3)])
+def test_tensor_path_matches_oracle(B, N, H):
+    q, k, v = orc.make_inputs(B, N, H, M, D, seed0=3, dtype=torch.bfloat16)
+    ref = orc.ar_forward(q, k, v)
+    qc, kc, vc = to_dev(q, k, v)
+    assert uses_tensor_path(qc, kc, vc)
+    y, _, _, _ = run(qc, kc, vc, _lib.PATH_TENSOR)
+    assert_bf16_gate(y, ref, f"tensor path B={B} N={N} H={H}")
+
+
+def test_tensor_path_state_in_and_out():
+    q, k, v = orc.make_inputs(2, 400, 2, M, D, seed0=5, dtype=torch.bfloat16)
+    sc = D ** -0.5
+    _, st0 = orc.ar_forward(q, k[:, :144], v[:, :144], scale=sc, return_state=True)
+    ref, st_ref = orc.ar_forward(q, k, v, scale=sc, return_state=True)
+    qc, kc, vc = to_dev(q, k, v)
+    st_in = {a: b.float().cuda().contiguous() for a, b in st0.items()}
+    y, st, _, _ = run(qc, kc[:, 144:], vc[:, 144:], _lib.PATH_TENSOR, state_in=st_in, want_state=True, scale=sc)
+    assert_bf16_gate(y, ref[:, 144:], "carry-in y")
+    assert_close(st["m"], st_ref["m"], what="m", atol=1e-4, rtol=1e-4)
+    assert_close(st["d"], st_ref["d"], what="d", atol=1e-3, rtol=2e-3)
+    assert orc.rel_l2(st["u"].cpu(), st_ref["u"]) < 3e-3
+    # the public prefill API takes the same route and continues correctly into the decode kernel
+    y2, st2 = cf.flare_autoregressive_prefill_triton(qc, kc[:, :399], vc[:, :399], scale=sc)
+    y3, _ = cf.flare_autoregressive_decode_triton(qc, kc[:, 399], vc[:, 399], st2, scale=sc)
+    assert_bf16_gate(y3, ref[:, 399:], "decode after tensor-path prefill")
+
+
+def test_tensor_path_segmented_small_batch():
+    q, k, v = orc.make_inputs(1, 2048, 1, M, D, seed0=7, dtype=torch.bfloat16)
+    ref = orc.ar_forward(q, k, v)
+    y, _, _, _ = run(*to_dev(q, k, v), _lib.PATH_TENSOR)
+    assert_bf16_gate(y, ref, "segmented tensor path")
+
+
+def test_tensor_vs_exact_at_benchmark_size():
+    # C2: B=8, N=8192, H=16, M=128, D=64.  The exact path is itself checked against the oracle on small
+    # cases; here the two CUDA paths must agree at full size, and a prefix of one lane is checked on the CPU.
+    B, N, H = 8, 8192, 16
+    g = torch.Generator(device="cuda").manual_seed(0)
+    q = torch.randn(H, M, D, generator=g, device="cuda").bfloat16()
+    k = torch.randn(B, N, H, D, generator=g, device="cuda").bfloat16()
+    v = torch.randn(B, N, H, D, generator=g, device="cuda").bfloat16()
+    y_t, _, _, _ = run(q, k, v, _lib.PATH_TENSOR)
+    y_e, _, _, _ = run(q, k, v, _lib.PATH_EXACT)
+    assert torch.isfinite(y_t.float()).all()
+    assert_bf16_gate(y_t, y_e.float(), "tensor vs exact, C2")
+    ref = orc.ar_forward(q[3:4].cpu(), k[5:6, :512, 3:4].cpu(), v[5:6, :512, 3:4].cpu())
+    assert_bf16_gate(y_t[5:6, :512, 3:4], ref, "C2 lane prefix vs oracle")
+    # causality: changing the last quarter of the sequence must not change earlier outputs
+    k2, v2 = k.clone(), v.clone()
+    k2[:, 3 * N // 4:] = 0
+    v2[:, 3 * N // 4:] = 1
+    y2, _, _, _ = run(q, k2, v2, _lib.PATH_TENSOR)
+    assert torch.equal(y2[:, :3 * N // 4], y_t[:, :3 * N // 4])
+    y3, _, _, _ = run(q, k, v, _lib.PATH_TENSOR)
+    assert torch.equal(y3, y_t), "tensor path must be run-to-run deterministic"
