@@ -1,0 +1,65 @@
+"""Sequence parallelism over the GPUs of one node: every rank owns a contiguous span of tokens.
+
+The carried object of causal FLARE is the small associative state (m, d, u) per (batch, head), so a long
+sequence is split by (1) each rank summarising its span into a state, (2) one all-gather of those states,
+(3) each rank folding the states of the lower ranks into its carry-in, (4) each rank running its span from that
+carry-in.  Lanes (batch x head) need no communication at all; this module is only for the token axis.
+
+The reference has no multi-GPU code; the single-device math (prefill with ``state=``) is what this reproduces.
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+STATE_KEYS = ("m", "d", "u")
+
+
+def pack_state(state) -> torch.Tensor:
+    """[B, H, M, 2 + Dv] fp32: m, d and u side by side, so the exchange is one collective."""
+    return torch.cat([state["m"][..., None], state["d"][..., None], state["u"]], dim=-1).contiguous()
+
+
+def unpack_state(packed: torch.Tensor):
+    return {"m": packed[..., 0].contiguous(), "d": packed[..., 1].contiguous(), "u": packed[..., 2:].contiguous()}
+
+
+def exchange_states(local_state, group=None):
+    """All-gather the per-rank span states; returns the list of states ordered by rank."""
+    world = dist.get_world_size(group)
+    mine = pack_state(local_state)
+    gathered = [torch.empty_like(mine) for _ in range(world)]
+    dist.all_gather(gathered, mine, group=group)
+    return [unpack_state(g) for g in gathered]
+
+
+def prefix_state(states, rank: int, merge_fn, empty_state):
+    """Exclusive scan: the carry-in of ``rank`` is the in-order fold of the states of ranks < rank."""
+    if rank == 0:
+        return empty_state
+    return merge_fn(empty_state, states[:rank])
+
+
+def sequence_parallel_prefill(Q, K_local, V_local, *, scale, group=None):
+    """Causal FLARE over a sequence whose tokens are sharded across the ranks of ``group``.
+
+    K_local / V_local: this rank's span [B, N_local, H, D] (rank r holds tokens [r*N_local, (r+1)*N_local)).
+    Returns (Y_local, state_after_this_rank's_span).
+    """
+    from . import _ops
+    from .autoregressive.inference import _init_flare_recurrent_state
+
+    rank = dist.get_rank(group)
+    B, _, H, _ = K_local.shape
+    M, Dv = Q.shape[1], V_local.shape[-1]
+    # (1) span summary: final state only
+    _, local, _, _ = _ops.forward(Q, K_local, V_local, scale=scale, want_state=True, want_y=False)
+    # (2) one collective over NVLink
+    states = exchange_states(local, group)
+    # (3) fold lower ranks
+    empty = _init_flare_recurrent_state(B, H, M, Dv, K_local.device)
+    carry = prefix_state(states, rank, _ops.merge_states, empty)
+    # (4) the span itself, from the carry-in
+    Y, st, _, _ = _ops.forward(Q, K_local, V_local, scale=scale, state_in=carry, want_state=True)
+    return Y, st
