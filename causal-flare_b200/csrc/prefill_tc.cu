@@ -10,15 +10,19 @@
 //   E[m,t]   = exp(s[m,t] - c_m)           one exp per element, thread m scans its row
 //   D[m,t]   = d_m + cumsum_t E[m,t]       (d_m already rescaled into the new frame)
 //   R[m,t]   = E[m,t] exp(c_m - kappa) / D[m,t]        = softmax-numerator / encoder denominator
-//   Y    = R^T U_bf16   ,  Den0 = R^T d    MMA3  (+ a 16-column MMA for the denominator column)
 //   W    = R^T E   (tokens x tokens)       MMA4  -> causal mask + bf16, written back to TMEM
+//   Y    = R^T U_bf16   ,  Den0 = R^T d    MMA3  (+ a 16-column MMA for the denominator column)
 //   U   += E V_c                           MMA2
 //   Y   += tril(W) V_c                     MMA5  (A operand from TMEM)
 //   y_t  = Y[t,:] / (Den0[t] + rowsum tril(W)[t,:])
 //
 // Operands E, R (written by the latent threads row-wise) feed MMAs both K-major and MN-major from the same
-// 128-byte-swizzled buffers, so no transposition pass exists.  K_c / V_c tiles are TMA-staged and
-// double-buffered.  Warps 0-3: element-wise phases; warp 4: TMA producer and MMA issuer (one elected thread).
+// 128-byte-swizzled buffers, so no transposition pass exists.
+//
+// Warp roles (10 warps): 0-3 "latent group": scores -> E, R, state rescale (chunk i+1);  4-7 "token group":
+// causal mask of W, normalisation and store of Y (chunk i);  8: MMA issuer (one thread);  9: TMA producer (one
+// thread).  The three stages work on consecutive chunks concurrently: E/R operand buffers and the Y / Den
+// accumulators are double-buffered, K is single-buffered (free as soon as its score MMA has run), V has two stages.
 #include "prefill_tc.cuh"
 
 #include <cuda.h>
@@ -35,34 +39,49 @@ namespace {
 constexpr int C = 128;    // tokens per chunk
 constexpr int M = 128;    // latents
 constexpr int D = 64;     // Dk = Dv
-constexpr int NTHREADS = 160;
+constexpr int NTHREADS = 320;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 
 // shared memory map (bytes, every operand buffer 1024-aligned for the 128B swizzle)
-constexpr int OFF_Q = 0;                      // [128 m][64] bf16, K-major            16 KB
-constexpr int OFF_K = OFF_Q + 16384;          // 2 stages x [128 t][64] bf16          32 KB
-constexpr int OFF_V = OFF_K + 2 * 16384;      // 2 stages x [128 t][64] bf16          32 KB
-constexpr int OFF_E = OFF_V + 2 * 16384;      // [2 t-blocks][128 m][64 t] bf16       32 KB
-constexpr int OFF_R = OFF_E + 32768;          // [2 t-blocks][128 m][64 t] bf16       32 KB
-constexpr int OFF_U = OFF_R + 32768;          // [128 m][64 dv] bf16                  16 KB
-constexpr int OFF_B16 = OFF_U + 16384;        // [2 m-blocks][16 n][64 m] bf16         4 KB
+constexpr int OFF_Q = 0;                      // [128 m][64] bf16, K-major                 16 KB
+constexpr int OFF_K = OFF_Q + 16384;          // [128 t][64] bf16                          16 KB
+constexpr int OFF_V = OFF_K + 16384;          // 2 stages x [128 t][64] bf16               32 KB
+constexpr int OFF_E = OFF_V + 2 * 16384;      // 2 x [2 t-blocks][128 m][64 t] bf16        64 KB
+constexpr int OFF_R = OFF_E + 2 * 32768;      // 2 x [2 t-blocks][128 m][64 t] bf16        64 KB
+constexpr int OFF_U = OFF_R + 2 * 32768;      // [128 m][64 dv] bf16                       16 KB
+constexpr int OFF_B16 = OFF_U + 16384;        // [2 m-blocks][16 n][64 m] bf16              4 KB
 constexpr int OFF_MISC = OFF_B16 + 4096;      // barriers, tmem slot, reductions
-constexpr int SMEM_BYTES = OFF_MISC + 256 + 1024;  // + slack for manual 1024-byte alignment
+constexpr int SMEM_BYTES = OFF_MISC + 512 + 1024;  // + slack for manual 1024-byte alignment
 
 // tensor-memory columns
-constexpr uint32_t TM_S = 0, TM_W = 128, TM_U = 256, TM_Y = 320, TM_DEN = 384, TM_COLS = 512;
+constexpr uint32_t TM_S = 0, TM_W = 128, TM_U = 256, TM_Y = 320 /* 2 x 64 */, TM_DEN = 448 /* 2 x 16 */, TM_COLS = 512;
 
 struct Misc {
-  uint64_t full[2], empty[2], q_full, s_ready, kap_done, p1_done, w_ready, p2_done, y_ready;
+  uint64_t q_full, k_full, k_empty, v_full[2], v_empty[2];
+  uint64_t s_ready, s_free, kap_done, p1_done, u_done, w_ready, p2_done, y_ready;
   uint32_t tmem_base;
-  int abort_flag;
+  volatile int abort_flag;
   float wmax[4];
 };
 
 __device__ int g_tc_error = 0;
 
 __device__ __forceinline__ uint32_t swz_chunk_off(int row, int chunk) { return row * 128 + ((chunk ^ (row & 7)) << 4); }
+
+// bounded wait that also gives up as soon as another role of the CTA has given up
+__device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, Misc* misc) {
+  if (mbar_test_wait(bar, parity)) return true;
+  const uint64_t t0 = global_timer_ns();
+  uint32_t spins = 0;
+  while (true) {
+    if (mbar_test_wait(bar, parity)) return true;
+    if ((++spins & 31u) == 0) {
+      if (misc->abort_flag != 0 || global_timer_ns() - t0 > kWaitLimitNs) return false;
+      __nanosleep(32);
+    }
+  }
+}
 
 }  // namespace
 
@@ -80,14 +99,18 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   const int nchunks = (seg_end - seg_begin + C - 1) / C;
 
   if (tid == 0) {
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&misc->full[i], 1);
-      mbar_init(&misc->empty[i], 1);
-    }
     mbar_init(&misc->q_full, 1);
+    mbar_init(&misc->k_full, 1);
+    mbar_init(&misc->k_empty, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&misc->v_full[i], 1);
+      mbar_init(&misc->v_empty[i], 1);
+    }
     mbar_init(&misc->s_ready, 1);
+    mbar_init(&misc->s_free, 128);
     mbar_init(&misc->kap_done, 4);
     mbar_init(&misc->p1_done, 128);
+    mbar_init(&misc->u_done, 1);
     mbar_init(&misc->w_ready, 1);
     mbar_init(&misc->p2_done, 128);
     mbar_init(&misc->y_ready, 1);
@@ -96,7 +119,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   }
   // zero the denominator operand tile once (rows 1..15 stay zero for the whole kernel)
   for (int i = tid; i < 4096 / 16; i += NTHREADS) reinterpret_cast<uint4*>(smem + OFF_B16)[i] = make_uint4(0, 0, 0, 0);
-  if (warp == 4) {
+  if (warp == 8) {
     tmem_alloc(&misc->tmem_base, TM_COLS);
     tmem_relinquish();
   }
@@ -106,24 +129,31 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   const uint32_t tmem = misc->tmem_base;
   bool ok = true;
 
-  if (warp == 4) {
-    // =========================== TMA producer + MMA issuer (one thread) ===========================
+  if (warp == 9) {
+    // ======================================= TMA producer =======================================
     if (lane == 0) {
       prefetch_tensormap(&tm_q);
       prefetch_tensormap(&tm_k);
       prefetch_tensormap(&tm_v);
       mbar_arrive_expect_tx(&misc->q_full, 16384);
       tma_load_3d(smem + OFF_Q, &tm_q, &misc->q_full, 0, 0, h);
-      auto produce = [&](int i) {
+      for (int i = 0; ok && i < nchunks; ++i) {
+        const int t0 = seg_begin + i * C;
+        // K tile: free once the score MMA of the previous chunk has run
+        if (i > 0 && !(ok = wait_or_abort(&misc->k_empty, (i - 1) & 1, misc))) break;
+        mbar_arrive_expect_tx(&misc->k_full, 16384);
+        tma_load_4d(smem + OFF_K, &tm_k, &misc->k_full, 0, h, t0, b);
+        // V tile: stage i & 1, free once chunk i - 2 has been folded into Y
         const int st = i & 1;
-        mbar_arrive_expect_tx(&misc->full[st], 32768);
-        tma_load_4d(smem + OFF_K + st * 16384, &tm_k, &misc->full[st], 0, h, seg_begin + i * C, b);
-        tma_load_4d(smem + OFF_V + st * 16384, &tm_v, &misc->full[st], 0, h, seg_begin + i * C, b);
-      };
-      int produced = 0;
-      for (; produced < 2 && produced < nchunks; ++produced) produce(produced);
-
-      const uint32_t q_addr = smem_u32(smem + OFF_Q), e_addr = smem_u32(smem + OFF_E), r_addr = smem_u32(smem + OFF_R);
+        if (i >= 2 && !(ok = wait_or_abort(&misc->v_empty[st], ((i - 2) >> 1) & 1, misc))) break;
+        mbar_arrive_expect_tx(&misc->v_full[st], 16384);
+        tma_load_4d(smem + OFF_V + st * 16384, &tm_v, &misc->v_full[st], 0, h, t0, b);
+      }
+    }
+  } else if (warp == 8) {
+    // ======================================= MMA issuer =======================================
+    if (lane == 0) {
+      const uint32_t q_addr = smem_u32(smem + OFF_Q), k_addr = smem_u32(smem + OFF_K);
       const uint32_t u_addr = smem_u32(smem + OFF_U), b16_addr = smem_u32(smem + OFF_B16);
       constexpr uint32_t ID_S = make_idesc_bf16(128, 128, 0, 0);   // Q (K-major) x K_c (K-major)
       constexpr uint32_t ID_U = make_idesc_bf16(128, 64, 0, 1);    // E (K-major) x V (MN-major)
@@ -132,27 +162,45 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       constexpr uint32_t ID_W = make_idesc_bf16(128, 128, 1, 1);   // R (MN-major) x E (MN-major)
       constexpr uint32_t ID_Y1 = make_idesc_bf16(128, 64, 0, 1);   // tril(W) (TMEM) x V (MN-major)
 
-      auto issue_scores = [&](int i) -> bool {
-        const int st = i & 1;
-        if (!mbar_wait(&misc->full[st], (i >> 1) & 1)) return false;
+      auto issue_scores = [&](int i) -> bool {  // S^T of chunk i; K tile and the S columns must be free
+        if (!wait_or_abort(&misc->k_full, i & 1, misc)) return false;
         tc_fence_after_sync();
-        const uint32_t k_addr = smem_u32(smem + OFF_K + st * 16384);
 #pragma unroll
         for (int j = 0; j < 4; ++j)
           mma_ss(tmem + TM_S, make_desc_sw128(q_addr + j * 32, 16, 1024), make_desc_sw128(k_addr + j * 32, 16, 1024), ID_S,
                  j > 0);
         tc_commit(&misc->s_ready);
+        tc_commit(&misc->k_empty);
+        return true;
+      };
+      auto issue_tail = [&](int i) -> bool {  // Y += tril(W) V of chunk i, after the token group masked W
+        if (!wait_or_abort(&misc->p2_done, i & 1, misc)) return false;
+        tc_fence_after_sync();
+        const uint32_t v_addr = smem_u32(smem + OFF_V + (i & 1) * 16384);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          mma_ts(tmem + TM_Y + (i & 1) * 64, tmem + TM_W + j * 8, make_desc_sw128(v_addr + j * 2048, 1024, 1024), ID_Y1, 1);
+        tc_commit(&misc->y_ready);
+        tc_commit(&misc->v_empty[i & 1]);
         return true;
       };
 
-      ok = mbar_wait(&misc->q_full, 0);
+      ok = wait_or_abort(&misc->q_full, 0, misc);
       if (ok && nchunks > 0) ok = issue_scores(0);
       for (int i = 0; ok && i < nchunks; ++i) {
-        const int st = i & 1;
         const uint32_t par = i & 1;
-        const uint32_t v_addr = smem_u32(smem + OFF_V + st * 16384);
-        if (!(ok = mbar_wait(&misc->p1_done, par))) break;
+        if (i >= 1 && !(ok = issue_tail(i - 1))) break;
+        if (i + 1 < nchunks) {
+          // the latent group has read S of chunk i: the columns can take the next chunk's scores
+          if (!(ok = wait_or_abort(&misc->s_free, par, misc))) break;
+          if (!(ok = issue_scores(i + 1))) break;
+        }
+        if (!(ok = wait_or_abort(&misc->p1_done, par, misc))) break;
+        if (!(ok = wait_or_abort(&misc->v_full[i & 1], (i >> 1) & 1, misc))) break;
         tc_fence_after_sync();
+        const uint32_t e_addr = smem_u32(smem + OFF_E + (i & 1) * 32768);
+        const uint32_t r_addr = smem_u32(smem + OFF_R + (i & 1) * 32768);
+        const uint32_t v_addr = smem_u32(smem + OFF_V + (i & 1) * 16384);
         // W = R^T E  (k = latents, 8 steps of 16 rows = 2048 bytes)
 #pragma unroll
         for (int j = 0; j < 8; ++j)
@@ -162,9 +210,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         // Y = R^T U_bf16, Den0 = R^T d
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          mma_ss(tmem + TM_Y, make_desc_sw128(r_addr + j * 2048, 16384, 1024), make_desc_sw128(u_addr + j * 2048, 1024, 1024),
-                 ID_Y0, j > 0);
-          mma_ss(tmem + TM_DEN, make_desc_sw128(r_addr + j * 2048, 16384, 1024),
+          mma_ss(tmem + TM_Y + (i & 1) * 64, make_desc_sw128(r_addr + j * 2048, 16384, 1024),
+                 make_desc_sw128(u_addr + j * 2048, 1024, 1024), ID_Y0, j > 0);
+          mma_ss(tmem + TM_DEN + (i & 1) * 16, make_desc_sw128(r_addr + j * 2048, 16384, 1024),
                  make_desc_sw128(b16_addr + (j >> 2) * 2048 + (j & 3) * 32, 16, 1024), ID_DEN, j > 0);
         }
         // U += E V_c  (k = tokens of the chunk)
@@ -172,33 +220,14 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         for (int j = 0; j < 8; ++j)
           mma_ss(tmem + TM_U, make_desc_sw128(e_addr + (j >> 2) * 16384 + (j & 3) * 32, 16, 1024),
                  make_desc_sw128(v_addr + j * 2048, 1024, 1024), ID_U, 1);
-        // scores of the next chunk while the element-wise threads mask W
-        if (i + 1 < nchunks) {
-          if (!(ok = issue_scores(i + 1))) break;
-        }
-        if (!(ok = mbar_wait(&misc->p2_done, par))) break;
-        tc_fence_after_sync();
-        // Y += tril(W) V_c, A operand from tensor memory (bf16 pairs, 8 columns per k-step of 16)
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-          mma_ts(tmem + TM_Y, tmem + TM_W + j * 8, make_desc_sw128(v_addr + j * 2048, 1024, 1024), ID_Y1, 1);
-        tc_commit(&misc->y_ready);
-        tc_commit(&misc->empty[st]);
-        // refill this stage with chunk i + 2 once the MMAs above have drained it
-        if (produced < nchunks) {
-          if (!(ok = mbar_wait(&misc->empty[st], (i >> 1) & 1))) break;
-          produce(produced++);
-        }
+        tc_commit(&misc->u_done);
       }
-      if (!ok) {
-        misc->abort_flag = 1;
-        atomicExch(&g_tc_error, 1);
-      }
+      if (ok && nchunks > 0) ok = issue_tail(nchunks - 1);
     }
-  } else {
-    // =========================== element-wise warps: thread = TMEM lane ===========================
-    const uint32_t tl = tmem + ((uint32_t)(warp * 32) << 16);  // this warp's lane quarter
-    const int m = tid;                                          // latent (phase 1) / token in chunk (phases 2, 3)
+  } else if (warp < 4) {
+    // ============================ latent group: thread = latent = TMEM lane ============================
+    const uint32_t tl = tmem + ((uint32_t)(warp * 32) << 16);
+    const int m = tid;
     const float sc2 = p.scale * kLog2e;
     const int64_t st_idx = (int64_t)lane_id * p.in_lane_stride + (int64_t)seg * p.in_seg_stride;
     float c2 = p.in_m ? p.in_m[st_idx * M + m] * kLog2e : -INFINITY;  // running max, log2 units
@@ -215,16 +244,15 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       }
       tmem_wait_st();
     }
-    uint8_t* e_row = smem + OFF_E;
-    uint8_t* r_row = smem + OFF_R;
 
     for (int i = 0; ok && i < nchunks; ++i) {
       const uint32_t par = i & 1;
-      const int t0 = seg_begin + i * C;
-      const int nvalid = min(C, seg_end - t0);
-      // ------------------------------- phase 1: latent rows -------------------------------
-      if (!(ok = mbar_wait(&misc->s_ready, par))) break;
+      const int nvalid = min(C, seg_end - (seg_begin + i * C));
+      uint8_t* e_row = smem + OFF_E + (i & 1) * 32768;
+      uint8_t* r_row = smem + OFF_R + (i & 1) * 32768;
+      if (!(ok = wait_or_abort(&misc->s_ready, par, misc))) break;
       tc_fence_after_sync();
+      // pass 1: chunk maximum of this latent's row
       float cmax = -INFINITY;
 #pragma unroll 1
       for (int j = 0; j < 4; ++j) {
@@ -237,7 +265,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       }
       const float c_new = fmaxf(c2, cmax);
       const float alpha = ex2_approx(c2 - c_new);  // 0 when the old state is empty
-      // kappa = max over latents of the new frame (block-wide)
+      // kappa = max over latents of the new frame
       float wm = c_new;
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) wm = fmaxf(wm, __shfl_xor_sync(0xffffffffu, wm, o));
@@ -245,15 +273,46 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         misc->wmax[warp] = wm;
         mbar_arrive(&misc->kap_done);
       }
-      if (!(ok = mbar_wait(&misc->kap_done, par))) break;
+      if (!(ok = wait_or_abort(&misc->kap_done, par, misc))) break;
       const float kappa = fmaxf(fmaxf(misc->wmax[0], misc->wmax[1]), fmaxf(misc->wmax[2], misc->wmax[3]));
       const float a_m = ex2_approx(c_new - kappa);
       dsum *= alpha;
       c2 = c_new;
-      // d (in the new frame) as the first row of the denominator operand tile
+      const float d_carry = dsum;  // denominator of the carried state in the new frame
+      // pass 2: E, D, R for the 128 tokens of the chunk
+#pragma unroll 1
+      for (int j = 0; j < 4; ++j) {
+        uint32_t r[32];
+        tmem_ld32(tl + TM_S + j * 32, r);
+        tmem_wait_ld();
+        uint32_t ep[16], rp[16];
+#pragma unroll
+        for (int k = 0; k < 32; k += 2) {
+          const float e0 = (j * 32 + k < nvalid) ? ex2_approx(__uint_as_float(r[k]) * sc2 - c_new) : 0.f;
+          const float e1 = (j * 32 + k + 1 < nvalid) ? ex2_approx(__uint_as_float(r[k + 1]) * sc2 - c_new) : 0.f;
+          dsum += e0;
+          const float r0 = e0 * a_m * rcp_approx(dsum);
+          dsum += e1;
+          const float r1 = e1 * a_m * rcp_approx(dsum);
+          ep[k >> 1] = pack_bf16(e0, e1);
+          rp[k >> 1] = pack_bf16(r0, r1);
+        }
+        // tokens [32 j, 32 j + 32) live in t-block j / 2, 16-byte chunks (j % 2) * 4 .. + 3 of row m
+        const int blk = j >> 1, ch0 = (j & 1) * 4;
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {
+          const uint32_t off = blk * 16384 + swz_chunk_off(m, ch0 + ch);
+          *reinterpret_cast<uint4*>(e_row + off) = make_uint4(ep[ch * 4], ep[ch * 4 + 1], ep[ch * 4 + 2], ep[ch * 4 + 3]);
+          *reinterpret_cast<uint4*>(r_row + off) = make_uint4(rp[ch * 4], rp[ch * 4 + 1], rp[ch * 4 + 2], rp[ch * 4 + 3]);
+        }
+      }
+      tc_fence_before_sync();
+      mbar_arrive(&misc->s_free);  // the S columns may take the next chunk's scores
+      // state part: needs the numerator update of the previous chunk to have landed
+      if (i > 0 && !(ok = wait_or_abort(&misc->u_done, (i - 1) & 1, misc))) break;
+      tc_fence_after_sync();
       *reinterpret_cast<__nv_bfloat16*>(smem + OFF_B16 + (m >> 6) * 2048 + ((m & 63) >> 3) * 16 + (m & 7) * 2) =
-          __float2bfloat16_rn(dsum);
-      // state: rescale in tensor memory if needed, and publish a bf16 copy as an MMA operand
+          __float2bfloat16_rn(d_carry);
       {
         const bool need = __any_sync(0xffffffffu, alpha != 1.0f);
 #pragma unroll
@@ -278,52 +337,55 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         }
         if (need) tmem_wait_st();
       }
-      // E, D, R for the 128 tokens of the chunk
-#pragma unroll 1
-      for (int j = 0; j < 4; ++j) {
-        uint32_t r[32];
-        tmem_ld32(tl + TM_S + j * 32, r);
-        tmem_wait_ld();
-        uint32_t ep[16], rp[16];
-#pragma unroll
-        for (int k = 0; k < 32; k += 2) {
-          float e0 = (j * 32 + k < nvalid) ? ex2_approx(__uint_as_float(r[k]) * sc2 - c_new) : 0.f;
-          float e1 = (j * 32 + k + 1 < nvalid) ? ex2_approx(__uint_as_float(r[k + 1]) * sc2 - c_new) : 0.f;
-          dsum += e0;
-          const float r0 = e0 * a_m * rcp_approx(dsum);
-          dsum += e1;
-          const float r1 = e1 * a_m * rcp_approx(dsum);
-          ep[k >> 1] = pack_bf16(e0, e1);
-          rp[k >> 1] = pack_bf16(r0, r1);
-        }
-        // tokens [32 j, 32 j + 32) live in t-block j / 2, 16-byte chunks (j % 2) * 4 .. + 3 of row m
-        const int blk = j >> 1, ch0 = (j & 1) * 4;
-#pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {
-          const uint32_t off = blk * 16384 + swz_chunk_off(m, ch0 + ch);
-          *reinterpret_cast<uint4*>(e_row + off) = make_uint4(ep[ch * 4], ep[ch * 4 + 1], ep[ch * 4 + 2], ep[ch * 4 + 3]);
-          *reinterpret_cast<uint4*>(r_row + off) = make_uint4(rp[ch * 4], rp[ch * 4 + 1], rp[ch * 4 + 2], rp[ch * 4 + 3]);
-        }
-      }
       fence_proxy_async_smem();
       tc_fence_before_sync();
       mbar_arrive(&misc->p1_done);
-
-      // ------------------------------- phase 2: token rows of W -------------------------------
-      if (!(ok = mbar_wait(&misc->w_ready, par))) break;
+    }
+    // carry-out state
+    if (ok && p.out_u != nullptr && (p.out_mode == 1 || (p.out_mode == 2 && seg == p.nseg_total - 1))) {
+      if (nchunks > 0) ok = wait_or_abort(&misc->u_done, (nchunks - 1) & 1, misc);
+      tc_fence_after_sync();
+      if (ok) {
+        const int64_t so = (int64_t)lane_id * p.out_lane_stride + (int64_t)seg * p.out_seg_stride;
+        p.out_m[so * M + m] = c2 * kLn2;
+        p.out_d[so * M + m] = dsum;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          uint32_t r[32];
+          tmem_ld32(tl + TM_U + half * 32, r);
+          tmem_wait_ld();
+          float4* dst = reinterpret_cast<float4*>(p.out_u + (so * M + m) * D + half * 32);
+#pragma unroll
+          for (int k = 0; k < 8; ++k)
+            dst[k] = make_float4(__uint_as_float(r[4 * k]), __uint_as_float(r[4 * k + 1]), __uint_as_float(r[4 * k + 2]),
+                                 __uint_as_float(r[4 * k + 3]));
+        }
+      }
+    }
+  } else {
+    // ============================ token group: thread = token of the chunk = TMEM lane ============================
+    const int wq = warp - 4;  // lane quarter
+    const uint32_t tl = tmem + ((uint32_t)(wq * 32) << 16);
+    const int tt = wq * 32 + lane;  // token index inside the chunk
+    for (int i = 0; ok && i < nchunks; ++i) {
+      const uint32_t par = i & 1;
+      const int t0 = seg_begin + i * C;
+      const int nvalid = min(C, seg_end - t0);
+      // causal mask of W, bf16 pack, row sums
+      if (!(ok = wait_or_abort(&misc->w_ready, par, misc))) break;
       tc_fence_after_sync();
       float rowsum = 0.f;
 #pragma unroll 1
       for (int j = 0; j < 4; ++j) {
         uint32_t wp[16];
-        if (j <= warp) {
+        if (j <= wq) {
           uint32_t r[32];
           tmem_ld32(tl + TM_W + j * 32, r);
           tmem_wait_ld();
 #pragma unroll
           for (int k = 0; k < 32; k += 2) {
-            const float w0 = (j < warp || k <= lane) ? __uint_as_float(r[k]) : 0.f;
-            const float w1 = (j < warp || k + 1 <= lane) ? __uint_as_float(r[k + 1]) : 0.f;
+            const float w0 = (j < wq || k <= lane) ? __uint_as_float(r[k]) : 0.f;
+            const float w1 = (j < wq || k + 1 <= lane) ? __uint_as_float(r[k + 1]) : 0.f;
             const uint32_t pk = pack_bf16(w0, w1);
             wp[k >> 1] = pk;
             rowsum += __uint_as_float(pk << 16) + __uint_as_float(pk & 0xffff0000u);
@@ -338,22 +400,21 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       tc_fence_before_sync();
       mbar_arrive(&misc->p2_done);
 
-      // ------------------------------- phase 3: normalise and store -------------------------------
-      if (!(ok = mbar_wait(&misc->y_ready, par))) break;
+      // normalise and store
+      if (!(ok = wait_or_abort(&misc->y_ready, par, misc))) break;
       tc_fence_after_sync();
       uint32_t den0;
-      tmem_ld1(tl + TM_DEN, den0);
+      tmem_ld1(tl + TM_DEN + (i & 1) * 16, den0);
       tmem_wait_ld();
       const float inv = 1.0f / (__uint_as_float(den0) + rowsum);
-      const int t = t0 + m;
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
         uint32_t r[32];
-        tmem_ld32(tl + TM_Y + half * 32, r);
+        tmem_ld32(tl + TM_Y + (i & 1) * 64 + half * 32, r);
         tmem_wait_ld();
-        if (p.y != nullptr && m < nvalid) {
+        if (p.y != nullptr && tt < nvalid) {
           uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.y) + (int64_t)b * p.y_stride_b +
-                                                (int64_t)t * p.y_stride_n + (int64_t)h * p.y_stride_h + half * 32);
+                                                (int64_t)(t0 + tt) * p.y_stride_n + (int64_t)h * p.y_stride_h + half * 32);
 #pragma unroll
           for (int ch = 0; ch < 4; ++ch) {
             uint4 v;
@@ -367,32 +428,16 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       }
       tc_fence_before_sync();
     }
-    if (!ok) {
-      misc->abort_flag = 1;
-      atomicExch(&g_tc_error, 1);
-    }
-    // carry-out state
-    if (ok && p.out_u != nullptr && (p.out_mode == 1 || (p.out_mode == 2 && seg == p.nseg_total - 1))) {
-      const int64_t so = (int64_t)lane_id * p.out_lane_stride + (int64_t)seg * p.out_seg_stride;
-      p.out_m[so * M + m] = c2 * kLn2;
-      p.out_d[so * M + m] = dsum;
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        uint32_t r[32];
-        tmem_ld32(tl + TM_U + half * 32, r);
-        tmem_wait_ld();
-        float4* dst = reinterpret_cast<float4*>(p.out_u + (so * M + m) * D + half * 32);
-#pragma unroll
-        for (int k = 0; k < 8; ++k)
-          dst[k] = make_float4(__uint_as_float(r[4 * k]), __uint_as_float(r[4 * k + 1]), __uint_as_float(r[4 * k + 2]),
-                               __uint_as_float(r[4 * k + 3]));
-      }
-    }
+  }
+  if (!ok) {
+    misc->abort_flag = 1;
+    atomicExch(&g_tc_error, 1);
   }
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 4) tmem_dealloc(tmem, TM_COLS);
+  if (warp == 8) tmem_dealloc(tmem, TM_COLS);
 }
+
 
 // -------------------------------------------------------------------------------------------------
 // host side
