@@ -33,6 +33,7 @@ int sm_count() {
 // Optional CUDA events recorded around the dominant kernel of the next forward calls (benchmark hook).
 static thread_local cudaEvent_t g_ev_begin = nullptr, g_ev_end = nullptr;
 static thread_local int g_last_launches = 0;
+static thread_local long long* g_trace = nullptr;
 
 namespace {
 
@@ -159,6 +160,7 @@ int launch_walk(const flare_fwd_args_t* a, const FwdPlan& pl, const WalkParams& 
   t.out_m = w.out_m; t.out_d = w.out_d; t.out_u = w.out_u;
   t.out_lane_stride = w.out_lane_stride; t.out_seg_stride = w.out_seg_stride;
   t.out_mode = w.out_mode; t.nseg_total = w.nseg_total;
+  t.trace = g_trace;
   return launch_prefill_tc(a, t, nseg_grid, stream);
 }
 
@@ -344,6 +346,8 @@ void flare_set_kernel_events(void* begin_event, void* end_event) {
 }
 
 int flare_last_launch_count(void) { return g_last_launches; }
+
+void flare_set_trace_buffer(void* device_buffer) { g_trace = static_cast<long long*>(device_buffer); }
 
 int flare_forward_uses_tensor_path(const flare_fwd_args_t* args) {
   if (check_forward(args) != FLARE_OK) return 0;

@@ -62,10 +62,17 @@ struct Misc {
   uint64_t s_ready, s_free, kap_done, p1_done, u_done, w_ready, p2_done, y_ready;
   uint32_t tmem_base;
   volatile int abort_flag;
-  float wmax[4];
+  float wmax[2][4];
 };
 
 __device__ int g_tc_error = 0;
+
+// optional cycle trace of CTA (0, 0): [role][chunk < 16][slot < 8] clock64 stamps (diagnostic hook, null in normal use)
+#define TC_TRACE(role, chunk, slot)                                                                   \
+  do {                                                                                                \
+    if (p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && (chunk) < 16)                     \
+      p.trace[((role) * 16 + (chunk)) * 8 + (slot)] = clock64();                                      \
+  } while (0)
 
 __device__ __forceinline__ uint32_t swz_chunk_off(int row, int chunk) { return row * 128 + ((chunk ^ (row & 7)) << 4); }
 
@@ -73,13 +80,9 @@ __device__ __forceinline__ uint32_t swz_chunk_off(int row, int chunk) { return r
 __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, Misc* misc) {
   if (mbar_test_wait(bar, parity)) return true;
   const uint64_t t0 = global_timer_ns();
-  uint32_t spins = 0;
   while (true) {
-    if (mbar_test_wait(bar, parity)) return true;
-    if ((++spins & 31u) == 0) {
-      if (misc->abort_flag != 0 || global_timer_ns() - t0 > kWaitLimitNs) return false;
-      __nanosleep(32);
-    }
+    if (mbar_try_wait(bar, parity, 50000u)) return true;  // sleeps in hardware, wakes on completion
+    if (misc->abort_flag != 0 || global_timer_ns() - t0 > kWaitLimitNs) return false;
   }
 }
 
@@ -162,13 +165,20 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       constexpr uint32_t ID_W = make_idesc_bf16(128, 128, 1, 1);   // R (MN-major) x E (MN-major)
       constexpr uint32_t ID_Y1 = make_idesc_bf16(128, 64, 0, 1);   // tril(W) (TMEM) x V (MN-major)
 
+      // descriptors are built once; inside the loops only the start-address field (units of 16 bytes) advances
+      const uint64_t dq = make_desc_sw128(q_addr, 16, 1024), dk = make_desc_sw128(k_addr, 16, 1024);
+      const uint64_t du = make_desc_sw128(u_addr, 1024, 1024), db16 = make_desc_sw128(b16_addr, 16, 1024);
+      // second buffer of a double-buffered operand = first + its byte distance (in 16-byte units)
+      const uint64_t de_k0 = make_desc_sw128(smem_u32(smem + OFF_E), 16, 1024);
+      const uint64_t de_mn0 = make_desc_sw128(smem_u32(smem + OFF_E), 16384, 1024);
+      const uint64_t dr_mn0 = make_desc_sw128(smem_u32(smem + OFF_R), 16384, 1024);
+      const uint64_t dv_mn0 = make_desc_sw128(smem_u32(smem + OFF_V), 1024, 1024);
+
       auto issue_scores = [&](int i) -> bool {  // S^T of chunk i; K tile and the S columns must be free
         if (!wait_or_abort(&misc->k_full, i & 1, misc)) return false;
         tc_fence_after_sync();
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
-          mma_ss(tmem + TM_S, make_desc_sw128(q_addr + j * 32, 16, 1024), make_desc_sw128(k_addr + j * 32, 16, 1024), ID_S,
-                 j > 0);
+        for (int j = 0; j < 4; ++j) mma_ss(tmem + TM_S, dq + (j * 32 >> 4), dk + (j * 32 >> 4), ID_S, j > 0);
         tc_commit(&misc->s_ready);
         tc_commit(&misc->k_empty);
         return true;
@@ -176,10 +186,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       auto issue_tail = [&](int i) -> bool {  // Y += tril(W) V of chunk i, after the token group masked W
         if (!wait_or_abort(&misc->p2_done, i & 1, misc)) return false;
         tc_fence_after_sync();
-        const uint32_t v_addr = smem_u32(smem + OFF_V + (i & 1) * 16384);
+        const uint64_t dv = dv_mn0 + (uint64_t)((i & 1) * (16384 >> 4));
 #pragma unroll
-        for (int j = 0; j < 8; ++j)
-          mma_ts(tmem + TM_Y + (i & 1) * 64, tmem + TM_W + j * 8, make_desc_sw128(v_addr + j * 2048, 1024, 1024), ID_Y1, 1);
+        for (int j = 0; j < 8; ++j) mma_ts(tmem + TM_Y + (i & 1) * 64, tmem + TM_W + j * 8, dv + (j * 2048 >> 4), ID_Y1, 1);
         tc_commit(&misc->y_ready);
         tc_commit(&misc->v_empty[i & 1]);
         return true;
@@ -189,38 +198,41 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       if (ok && nchunks > 0) ok = issue_scores(0);
       for (int i = 0; ok && i < nchunks; ++i) {
         const uint32_t par = i & 1;
+        TC_TRACE(2, i, 0);
         if (i >= 1 && !(ok = issue_tail(i - 1))) break;
+        TC_TRACE(2, i, 1);
         if (i + 1 < nchunks) {
           // the latent group has read S of chunk i: the columns can take the next chunk's scores
           if (!(ok = wait_or_abort(&misc->s_free, par, misc))) break;
           if (!(ok = issue_scores(i + 1))) break;
         }
+        TC_TRACE(2, i, 2);
         if (!(ok = wait_or_abort(&misc->p1_done, par, misc))) break;
         if (!(ok = wait_or_abort(&misc->v_full[i & 1], (i >> 1) & 1, misc))) break;
         tc_fence_after_sync();
-        const uint32_t e_addr = smem_u32(smem + OFF_E + (i & 1) * 32768);
-        const uint32_t r_addr = smem_u32(smem + OFF_R + (i & 1) * 32768);
-        const uint32_t v_addr = smem_u32(smem + OFF_V + (i & 1) * 16384);
+        TC_TRACE(2, i, 3);
+        const uint64_t eoff = (uint64_t)((i & 1) * (32768 >> 4));
+        const uint64_t dek = de_k0 + eoff, dem = de_mn0 + eoff, drm = dr_mn0 + eoff;
+        const uint64_t dv = dv_mn0 + (uint64_t)((i & 1) * (16384 >> 4));
         // W = R^T E  (k = latents, 8 steps of 16 rows = 2048 bytes)
 #pragma unroll
-        for (int j = 0; j < 8; ++j)
-          mma_ss(tmem + TM_W, make_desc_sw128(r_addr + j * 2048, 16384, 1024), make_desc_sw128(e_addr + j * 2048, 16384, 1024),
-                 ID_W, j > 0);
+        for (int j = 0; j < 8; ++j) mma_ss(tmem + TM_W, drm + (j * 2048 >> 4), dem + (j * 2048 >> 4), ID_W, j > 0);
         tc_commit(&misc->w_ready);
+        TC_TRACE(2, i, 5);
         // Y = R^T U_bf16, Den0 = R^T d
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          mma_ss(tmem + TM_Y + (i & 1) * 64, make_desc_sw128(r_addr + j * 2048, 16384, 1024),
-                 make_desc_sw128(u_addr + j * 2048, 1024, 1024), ID_Y0, j > 0);
-          mma_ss(tmem + TM_DEN + (i & 1) * 16, make_desc_sw128(r_addr + j * 2048, 16384, 1024),
-                 make_desc_sw128(b16_addr + (j >> 2) * 2048 + (j & 3) * 32, 16, 1024), ID_DEN, j > 0);
+          mma_ss(tmem + TM_Y + (i & 1) * 64, drm + (j * 2048 >> 4), du + (j * 2048 >> 4), ID_Y0, j > 0);
+          mma_ss(tmem + TM_DEN + (i & 1) * 16, drm + (j * 2048 >> 4), db16 + (((j >> 2) * 2048 + (j & 3) * 32) >> 4), ID_DEN,
+                 j > 0);
         }
+        TC_TRACE(2, i, 6);
         // U += E V_c  (k = tokens of the chunk)
 #pragma unroll
         for (int j = 0; j < 8; ++j)
-          mma_ss(tmem + TM_U, make_desc_sw128(e_addr + (j >> 2) * 16384 + (j & 3) * 32, 16, 1024),
-                 make_desc_sw128(v_addr + j * 2048, 1024, 1024), ID_U, 1);
+          mma_ss(tmem + TM_U, dek + (((j >> 2) * 16384 + (j & 3) * 32) >> 4), dv + (j * 2048 >> 4), ID_U, 1);
         tc_commit(&misc->u_done);
+        TC_TRACE(2, i, 4);
       }
       if (ok && nchunks > 0) ok = issue_tail(nchunks - 1);
     }
@@ -252,50 +264,73 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       uint8_t* r_row = smem + OFF_R + (i & 1) * 32768;
       if (!(ok = wait_or_abort(&misc->s_ready, par, misc))) break;
       tc_fence_after_sync();
-      // pass 1: chunk maximum of this latent's row
-      float cmax = -INFINITY;
-#pragma unroll 1
-      for (int j = 0; j < 4; ++j) {
-        uint32_t r[32];
-        tmem_ld32(tl + TM_S + j * 32, r);
-        tmem_wait_ld();
+      if (tid == 0) TC_TRACE(0, i, 0);
+      // pass 1: chunk maximum of this latent's row; TMEM loads are double-buffered in registers so that the
+      // load of block j + 1 is in flight while block j is processed
+      uint32_t ra[32], rb[32];
+      float cm0 = -INFINITY, cm1 = -INFINITY, cm2 = -INFINITY, cm3 = -INFINITY;  // four independent max chains
+      constexpr bool full = false;  // tail masking is a compare + select per element
+      auto max_block = [&](const uint32_t(&r)[32], int j) {
 #pragma unroll
-        for (int k = 0; k < 32; ++k)
-          if (j * 32 + k < nvalid) cmax = fmaxf(cmax, __uint_as_float(r[k]) * sc2);
+        for (int k = 0; k < 32; k += 4) {
+          const int t = j * 32 + k;
+          cm0 = fmaxf(cm0, t < nvalid ? __uint_as_float(r[k]) * sc2 : -INFINITY);
+          cm1 = fmaxf(cm1, t + 1 < nvalid ? __uint_as_float(r[k + 1]) * sc2 : -INFINITY);
+          cm2 = fmaxf(cm2, t + 2 < nvalid ? __uint_as_float(r[k + 2]) * sc2 : -INFINITY);
+          cm3 = fmaxf(cm3, t + 3 < nvalid ? __uint_as_float(r[k + 3]) * sc2 : -INFINITY);
+        }
+      };
+      tmem_ld32(tl + TM_S, ra);
+#pragma unroll 1
+      for (int jj = 0; jj < 2; ++jj) {
+        tmem_wait_ld();
+        tmem_fence_regs(ra);
+        tmem_ld32(tl + TM_S + (2 * jj + 1) * 32, rb);
+        max_block(ra, 2 * jj);
+        tmem_wait_ld();
+        tmem_fence_regs(rb);
+        tmem_ld32(tl + TM_S + ((2 * jj + 2) & 3) * 32, ra);  // after the last block: block 0 again, for pass 2
+        max_block(rb, 2 * jj + 1);
       }
+      const float cmax = fmaxf(fmaxf(cm0, cm1), fmaxf(cm2, cm3));
       const float c_new = fmaxf(c2, cmax);
       const float alpha = ex2_approx(c2 - c_new);  // 0 when the old state is empty
-      // kappa = max over latents of the new frame
+      // kappa: common frame of the decode weights = max over latents of the running max.  Chunk 0 synchronises
+      // the four warps; later chunks use the value published during the previous chunk (one chunk stale, which
+      // only changes a per-token scale that cancels in y).
       float wm = c_new;
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) wm = fmaxf(wm, __shfl_xor_sync(0xffffffffu, wm, o));
-      if (lane == 0) {
-        misc->wmax[warp] = wm;
-        mbar_arrive(&misc->kap_done);
+      if (tid == 0) TC_TRACE(0, i, 1);
+      if (lane == 0) misc->wmax[i & 1][warp] = wm;
+      if (i == 0) {
+        if (lane == 0) mbar_arrive(&misc->kap_done);
+        if (!(ok = wait_or_abort(&misc->kap_done, 0, misc))) break;
       }
-      if (!(ok = wait_or_abort(&misc->kap_done, par, misc))) break;
-      const float kappa = fmaxf(fmaxf(misc->wmax[0], misc->wmax[1]), fmaxf(misc->wmax[2], misc->wmax[3]));
+      const float* wsrc = misc->wmax[i == 0 ? 0 : ((i - 1) & 1)];
+      const float kappa = fmaxf(fmaxf(wsrc[0], wsrc[1]), fmaxf(wsrc[2], wsrc[3]));
+      if (tid == 0) TC_TRACE(0, i, 2);
       const float a_m = ex2_approx(c_new - kappa);
       dsum *= alpha;
       c2 = c_new;
       const float d_carry = dsum;  // denominator of the carried state in the new frame
       // pass 2: E, D, R for the 128 tokens of the chunk
-#pragma unroll 1
-      for (int j = 0; j < 4; ++j) {
-        uint32_t r[32];
-        tmem_ld32(tl + TM_S + j * 32, r);
-        tmem_wait_ld();
+      auto er_block = [&](const uint32_t(&r)[32], int j) {
         uint32_t ep[16], rp[16];
 #pragma unroll
         for (int k = 0; k < 32; k += 2) {
-          const float e0 = (j * 32 + k < nvalid) ? ex2_approx(__uint_as_float(r[k]) * sc2 - c_new) : 0.f;
-          const float e1 = (j * 32 + k + 1 < nvalid) ? ex2_approx(__uint_as_float(r[k + 1]) * sc2 - c_new) : 0.f;
+          const float e0 = (full || j * 32 + k < nvalid) ? ex2_approx(__uint_as_float(r[k]) * sc2 - c_new) : 0.f;
+          const float e1 = (full || j * 32 + k + 1 < nvalid) ? ex2_approx(__uint_as_float(r[k + 1]) * sc2 - c_new) : 0.f;
           dsum += e0;
-          const float r0 = e0 * a_m * rcp_approx(dsum);
+          const float r0 = e0 * (a_m * rcp_fma(dsum));
           dsum += e1;
-          const float r1 = e1 * a_m * rcp_approx(dsum);
+          const float r1 = e1 * (a_m * rcp_fma(dsum));
           ep[k >> 1] = pack_bf16(e0, e1);
           rp[k >> 1] = pack_bf16(r0, r1);
+        }
+        if (tid == 0 && j == 0) {
+          asm volatile("" ::"r"(ep[15]), "r"(rp[15]), "r"(ep[0]), "r"(rp[7]) : "memory");
+          TC_TRACE(0, i, 6);
         }
         // tokens [32 j, 32 j + 32) live in t-block j / 2, 16-byte chunks (j % 2) * 4 .. + 3 of row m
         const int blk = j >> 1, ch0 = (j & 1) * 4;
@@ -305,12 +340,26 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           *reinterpret_cast<uint4*>(e_row + off) = make_uint4(ep[ch * 4], ep[ch * 4 + 1], ep[ch * 4 + 2], ep[ch * 4 + 3]);
           *reinterpret_cast<uint4*>(r_row + off) = make_uint4(rp[ch * 4], rp[ch * 4 + 1], rp[ch * 4 + 2], rp[ch * 4 + 3]);
         }
+        if (tid == 0 && j == 0) TC_TRACE(0, i, 7);
+      };
+#pragma unroll 1
+      for (int jj = 0; jj < 2; ++jj) {
+        tmem_wait_ld();
+        tmem_fence_regs(ra);
+        tmem_ld32(tl + TM_S + (2 * jj + 1) * 32, rb);
+        er_block(ra, 2 * jj);
+        tmem_wait_ld();
+        tmem_fence_regs(rb);
+        if (jj == 0) tmem_ld32(tl + TM_S + 2 * 32, ra);
+        er_block(rb, 2 * jj + 1);
       }
       tc_fence_before_sync();
       mbar_arrive(&misc->s_free);  // the S columns may take the next chunk's scores
+      if (tid == 0) TC_TRACE(0, i, 3);
       // state part: needs the numerator update of the previous chunk to have landed
       if (i > 0 && !(ok = wait_or_abort(&misc->u_done, (i - 1) & 1, misc))) break;
       tc_fence_after_sync();
+      if (tid == 0) TC_TRACE(0, i, 4);
       *reinterpret_cast<__nv_bfloat16*>(smem + OFF_B16 + (m >> 6) * 2048 + ((m & 63) >> 3) * 16 + (m & 7) * 2) =
           __float2bfloat16_rn(d_carry);
       {
@@ -340,6 +389,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       fence_proxy_async_smem();
       tc_fence_before_sync();
       mbar_arrive(&misc->p1_done);
+      if (tid == 0) TC_TRACE(0, i, 5);
     }
     // carry-out state
     if (ok && p.out_u != nullptr && (p.out_mode == 1 || (p.out_mode == 2 && seg == p.nseg_total - 1))) {
@@ -374,6 +424,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       // causal mask of W, bf16 pack, row sums
       if (!(ok = wait_or_abort(&misc->w_ready, par, misc))) break;
       tc_fence_after_sync();
+      if (tid == 128) TC_TRACE(1, i, 0);
       float rowsum = 0.f;
 #pragma unroll 1
       for (int j = 0; j < 4; ++j) {
@@ -399,10 +450,12 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       tmem_wait_st();
       tc_fence_before_sync();
       mbar_arrive(&misc->p2_done);
+      if (tid == 128) TC_TRACE(1, i, 1);
 
       // normalise and store
       if (!(ok = wait_or_abort(&misc->y_ready, par, misc))) break;
       tc_fence_after_sync();
+      if (tid == 128) TC_TRACE(1, i, 2);
       uint32_t den0;
       tmem_ld1(tl + TM_DEN + (i & 1) * 16, den0);
       tmem_wait_ld();
@@ -427,6 +480,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         }
       }
       tc_fence_before_sync();
+      if (tid == 128) TC_TRACE(1, i, 3);
     }
   }
   if (!ok) {

@@ -17,6 +17,7 @@ struct TcParams {
   int64_t out_lane_stride, out_seg_stride;
   int out_mode;  // 0: none, 1: every segment, 2: last segment only
   int nseg_total;
+  long long* trace;  // optional diagnostic cycle stamps of CTA (0, 0), see TC_TRACE; null in normal use
 };
 
 bool prefill_tc_supported(const flare_fwd_args_t* a);

@@ -36,24 +36,33 @@ __device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// Suspending wait: the warp sleeps in hardware until the phase completes or `hint_ns` elapse, so a waiting role
+// does not take issue slots from the working warps of its scheduler.  Returns whether the phase has completed.
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
 __device__ __forceinline__ uint64_t global_timer_ns() {
   uint64_t t;
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
   return t;
 }
-// Bounded wait: polls without blocking and gives up after kWaitLimitNs of wall time, far beyond any
+// Bounded wait: suspends in slices of 50 us and gives up after kWaitLimitNs of wall time, far beyond any
 // legitimate wait in these kernels.  Returns false when it gave up.
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
   if (mbar_test_wait(bar, parity)) return true;
   const uint64_t t0 = global_timer_ns();
-  uint32_t spins = 0;
   while (true) {
-    if (mbar_test_wait(bar, parity)) return true;
-    if ((++spins & 63u) == 0) {
-      if (global_timer_ns() - t0 > kWaitLimitNs) return false;
-      __nanosleep(64);
-    }
+    if (mbar_try_wait(bar, parity, 50000u)) return true;
+    if (global_timer_ns() - t0 > kWaitLimitNs) return false;
   }
 }
 
@@ -154,6 +163,17 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
       : "r"(taddr)
       : "memory");
 }
+// Zero-instruction dependency: values loaded by tcgen05.ld must not be consumed before tcgen05.wait::ld.  Placing
+// this after the wait makes the compiler treat the registers as redefined there, so no use can move above it.
+__device__ __forceinline__ void tmem_fence_regs(uint32_t (&r)[32]) {
+  asm volatile(""
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]),
+                 "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]), "+r"(r[16]),
+                 "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]), "+r"(r[24]),
+                 "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+               :
+               : "memory");
+}
 __device__ __forceinline__ void tmem_ld1(uint32_t taddr, uint32_t& r) {
   asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(r) : "r"(taddr) : "memory");
 }
@@ -185,6 +205,14 @@ __device__ __forceinline__ float rcp_approx(float x) {
   float y;
   asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+// 1 / x for normal positive x on the FMA pipe (keeps the special-function unit free for the exponentials):
+// exponent-flip seed (about 12 % off) and two Newton steps, relative error about 2e-4, enough for a bf16 operand.
+__device__ __forceinline__ float rcp_fma(float x) {
+  float r = __uint_as_float(0x7EF311C7u - __float_as_uint(x));
+  r = r * fmaf(-x, r, 2.0f);
+  r = r * fmaf(-x, r, 2.0f);
+  return r;
 }
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   uint32_t r;

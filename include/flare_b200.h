@@ -164,6 +164,9 @@ int flare_abi_version(void);
  * stream they launch on.  flare_last_launch_count: kernels launched by this thread's last forward/backward. */
 void flare_set_kernel_events(void* begin_event, void* end_event);
 int flare_last_launch_count(void);
+/* Diagnostic: device buffer of 3 x 16 x 8 int64 that the tensor-core prefill kernel fills with clock64 stamps of
+ * the phases of its first CTA (roles: latent group, token group, MMA issuer; first 16 chunks).  NULL disables. */
+void flare_set_trace_buffer(void* device_buffer);
 
 /* 1 when flare_forward would take the tcgen05 tensor-core path for this problem (path AUTO or TENSOR and a
  * supported shape: bf16, softmax encoder, M = 128, Dk = Dv = 64, shared decode weights, no mask), else 0. */
