@@ -19,9 +19,9 @@
 // Operands E, R (written by the latent threads row-wise) feed MMAs both K-major and MN-major from the same
 // 128-byte-swizzled buffers, so no transposition pass exists.
 //
-// Warp roles (10 warps): 0-3 "latent group": scores -> E, R, state rescale (chunk i+1);  4-7 "token group":
-// causal mask of W, normalisation and store of Y (chunk i);  8: MMA issuer (one thread);  9: TMA producer (one
-// thread).  The three stages work on consecutive chunks concurrently: E/R operand buffers and the Y / Den
+// Warp roles (14 warps): 0-7 "latent group" (two warps per lane quarter, each half of the chunk's tokens): scores ->
+// E, R, state rescale (chunk i+1);  8-11 "token group": causal mask of W, normalisation and store of Y (chunk i);
+// 12: MMA issuer (one thread);  13: TMA producer (one thread).  The three stages work on consecutive chunks concurrently: E/R operand buffers and the Y / Den
 // accumulators are double-buffered, K is single-buffered (free as soon as its score MMA has run), V has two stages.
 #include "prefill_tc.cuh"
 
@@ -39,7 +39,7 @@ namespace {
 constexpr int C = 128;    // tokens per chunk
 constexpr int M = 128;    // latents
 constexpr int D = 64;     // Dk = Dv
-constexpr int NTHREADS = 320;
+constexpr int NTHREADS = 448;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 
@@ -52,7 +52,7 @@ constexpr int OFF_R = OFF_E + 2 * 32768;      // 2 x [2 t-blocks][128 m][64 t] b
 constexpr int OFF_U = OFF_R + 2 * 32768;      // [128 m][64 dv] bf16                       16 KB
 constexpr int OFF_B16 = OFF_U + 16384;        // [2 m-blocks][16 n][64 m] bf16              4 KB
 constexpr int OFF_MISC = OFF_B16 + 4096;      // barriers, tmem slot, reductions
-constexpr int SMEM_BYTES = OFF_MISC + 512 + 1024;  // + slack for manual 1024-byte alignment
+constexpr int SMEM_BYTES = OFF_MISC + 4608 + 1024;  // + slack for manual 1024-byte alignment
 
 // tensor-memory columns
 constexpr uint32_t TM_S = 0, TM_W = 128, TM_U = 256, TM_Y = 320 /* 2 x 64 */, TM_DEN = 448 /* 2 x 16 */, TM_COLS = 512;
@@ -60,9 +60,11 @@ constexpr uint32_t TM_S = 0, TM_W = 128, TM_U = 256, TM_Y = 320 /* 2 x 64 */, TM
 struct Misc {
   uint64_t q_full, k_full, k_empty, v_full[2], v_empty[2];
   uint64_t s_ready, s_free, kap_done, p1_done, u_done, w_ready, p2_done, y_ready;
+  uint64_t pmax[4], psum[4];  // pair barriers of the two latent half-groups, one per lane quarter
   uint32_t tmem_base;
   volatile int abort_flag;
   float wmax[2][4];
+  float xmax[2][2][128], xsum[2][2][128];  // [chunk parity][half][latent]
 };
 
 __device__ int g_tc_error = 0;
@@ -110,9 +112,13 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       mbar_init(&misc->v_empty[i], 1);
     }
     mbar_init(&misc->s_ready, 1);
-    mbar_init(&misc->s_free, 128);
+    mbar_init(&misc->s_free, 256);
     mbar_init(&misc->kap_done, 4);
-    mbar_init(&misc->p1_done, 128);
+    mbar_init(&misc->p1_done, 256);
+    for (int i = 0; i < 4; ++i) {
+      mbar_init(&misc->pmax[i], 64);
+      mbar_init(&misc->psum[i], 64);
+    }
     mbar_init(&misc->u_done, 1);
     mbar_init(&misc->w_ready, 1);
     mbar_init(&misc->p2_done, 128);
@@ -122,7 +128,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   }
   // zero the denominator operand tile once (rows 1..15 stay zero for the whole kernel)
   for (int i = tid; i < 4096 / 16; i += NTHREADS) reinterpret_cast<uint4*>(smem + OFF_B16)[i] = make_uint4(0, 0, 0, 0);
-  if (warp == 8) {
+  if (warp == 12) {
     tmem_alloc(&misc->tmem_base, TM_COLS);
     tmem_relinquish();
   }
@@ -132,7 +138,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   const uint32_t tmem = misc->tmem_base;
   bool ok = true;
 
-  if (warp == 9) {
+  if (warp == 13) {
     // ======================================= TMA producer =======================================
     if (lane == 0) {
       prefetch_tensormap(&tm_q);
@@ -153,7 +159,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         tma_load_4d(smem + OFF_V + st * 16384, &tm_v, &misc->v_full[st], 0, h, t0, b);
       }
     }
-  } else if (warp == 8) {
+  } else if (warp == 12) {
     // ======================================= MMA issuer =======================================
     if (lane == 0) {
       const uint32_t q_addr = smem_u32(smem + OFF_Q), k_addr = smem_u32(smem + OFF_K);
@@ -236,153 +242,174 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       }
       if (ok && nchunks > 0) ok = issue_tail(nchunks - 1);
     }
-  } else if (warp < 4) {
-    // ============================ latent group: thread = latent = TMEM lane ============================
-    const uint32_t tl = tmem + ((uint32_t)(warp * 32) << 16);
-    const int m = tid;
+  } else if (warp < 8) {
+    // ===================== latent group: 8 warps, thread = (latent = TMEM lane, half of the chunk's tokens) =====================
+    // Warps q and q + 4 own the same 32 latents and split the 128 tokens of a chunk in halves, so that two warps
+    // per scheduler overlap the special-function, ALU and FMA pipes.  The halves exchange the row maximum and the
+    // row sum of E through shared memory.
+    const int hf = warp >> 2, q = warp & 3;
+    const uint32_t tl = tmem + ((uint32_t)(q * 32) << 16);
+    const int m = q * 32 + lane;
     const float sc2 = p.scale * kLog2e;
     const int64_t st_idx = (int64_t)lane_id * p.in_lane_stride + (int64_t)seg * p.in_seg_stride;
-    float c2 = p.in_m ? p.in_m[st_idx * M + m] * kLog2e : -INFINITY;  // running max, log2 units
+    float c2 = p.in_m ? p.in_m[st_idx * M + m] * kLog2e : -INFINITY;  // running max, log2 units (both halves keep a copy)
     float dsum = p.in_d ? p.in_d[st_idx * M + m] : 0.f;
     {
-      // carry-in numerator -> tensor memory
+      // carry-in numerator -> tensor memory, 32 value columns per half
       uint32_t r[32];
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
-#pragma unroll
-        for (int i = 0; i < 32; ++i)
-          r[i] = p.in_u ? __float_as_uint(p.in_u[(st_idx * M + m) * D + half * 32 + i]) : 0u;
-        tmem_st32(tl + TM_U + half * 32, r);
-      }
+      for (int i = 0; i < 32; ++i) r[i] = p.in_u ? __float_as_uint(p.in_u[(st_idx * M + m) * D + hf * 32 + i]) : 0u;
+      tmem_st32(tl + TM_U + hf * 32, r);
       tmem_wait_st();
     }
 
     for (int i = 0; ok && i < nchunks; ++i) {
       const uint32_t par = i & 1;
       const int nvalid = min(C, seg_end - (seg_begin + i * C));
-      uint8_t* e_row = smem + OFF_E + (i & 1) * 32768;
-      uint8_t* r_row = smem + OFF_R + (i & 1) * 32768;
+      const int tok0 = hf * 64;
+      uint8_t* e_row = smem + OFF_E + (i & 1) * 32768 + hf * 16384;  // t-block hf of the chunk's operand buffers
+      uint8_t* r_row = smem + OFF_R + (i & 1) * 32768 + hf * 16384;
       if (!(ok = wait_or_abort(&misc->s_ready, par, misc))) break;
       tc_fence_after_sync();
       if (tid == 0) TC_TRACE(0, i, 0);
-      // pass 1: chunk maximum of this latent's row; TMEM loads are double-buffered in registers so that the
-      // load of block j + 1 is in flight while block j is processed
+      // the 64 scores of this thread stay in registers for the whole chunk
       uint32_t ra[32], rb[32];
-      float cm0 = -INFINITY, cm1 = -INFINITY, cm2 = -INFINITY, cm3 = -INFINITY;  // four independent max chains
-      constexpr bool full = false;  // tail masking is a compare + select per element
-      auto max_block = [&](const uint32_t(&r)[32], int j) {
+      tmem_ld32(tl + TM_S + tok0, ra);
+      tmem_ld32(tl + TM_S + tok0 + 32, rb);
+      tmem_wait_ld();
+      tmem_fence_regs(ra);
+      tmem_fence_regs(rb);
+      tc_fence_before_sync();
+      mbar_arrive(&misc->s_free);  // the S columns may take the next chunk's scores
+      // row maximum over the valid tokens of this half
+      float cm0 = -INFINITY, cm1 = -INFINITY, cm2 = -INFINITY, cm3 = -INFINITY;
+      if (nvalid == C) {
 #pragma unroll
-        for (int k = 0; k < 32; k += 4) {
-          const int t = j * 32 + k;
-          cm0 = fmaxf(cm0, t < nvalid ? __uint_as_float(r[k]) * sc2 : -INFINITY);
-          cm1 = fmaxf(cm1, t + 1 < nvalid ? __uint_as_float(r[k + 1]) * sc2 : -INFINITY);
-          cm2 = fmaxf(cm2, t + 2 < nvalid ? __uint_as_float(r[k + 2]) * sc2 : -INFINITY);
-          cm3 = fmaxf(cm3, t + 3 < nvalid ? __uint_as_float(r[k + 3]) * sc2 : -INFINITY);
+        for (int k = 0; k < 32; k += 2) {
+          cm0 = fmaxf(cm0, __uint_as_float(ra[k]) * sc2);
+          cm1 = fmaxf(cm1, __uint_as_float(ra[k + 1]) * sc2);
+          cm2 = fmaxf(cm2, __uint_as_float(rb[k]) * sc2);
+          cm3 = fmaxf(cm3, __uint_as_float(rb[k + 1]) * sc2);
         }
-      };
-      tmem_ld32(tl + TM_S, ra);
-#pragma unroll 1
-      for (int jj = 0; jj < 2; ++jj) {
-        tmem_wait_ld();
-        tmem_fence_regs(ra);
-        tmem_ld32(tl + TM_S + (2 * jj + 1) * 32, rb);
-        max_block(ra, 2 * jj);
-        tmem_wait_ld();
-        tmem_fence_regs(rb);
-        tmem_ld32(tl + TM_S + ((2 * jj + 2) & 3) * 32, ra);  // after the last block: block 0 again, for pass 2
-        max_block(rb, 2 * jj + 1);
+      } else {
+#pragma unroll
+        for (int k = 0; k < 32; ++k) {
+          if (tok0 + k < nvalid) cm0 = fmaxf(cm0, __uint_as_float(ra[k]) * sc2);
+          if (tok0 + 32 + k < nvalid) cm2 = fmaxf(cm2, __uint_as_float(rb[k]) * sc2);
+        }
       }
-      const float cmax = fmaxf(fmaxf(cm0, cm1), fmaxf(cm2, cm3));
+      misc->xmax[par][hf][m] = fmaxf(fmaxf(cm0, cm1), fmaxf(cm2, cm3));
+      mbar_arrive(&misc->pmax[q]);
+      if (!(ok = wait_or_abort(&misc->pmax[q], par, misc))) break;
+      const float cmax = fmaxf(misc->xmax[par][0][m], misc->xmax[par][1][m]);
       const float c_new = fmaxf(c2, cmax);
       const float alpha = ex2_approx(c2 - c_new);  // 0 when the old state is empty
-      // kappa: common frame of the decode weights = max over latents of the running max.  Chunk 0 synchronises
-      // the four warps; later chunks use the value published during the previous chunk (one chunk stale, which
-      // only changes a per-token scale that cancels in y).
+      // kappa: common frame of the decode weights = max over latents of the running max.  Chunk 0 synchronises;
+      // later chunks use the value published during the previous chunk (one chunk stale, which only changes a
+      // per-token scale that cancels in y).
       float wm = c_new;
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) wm = fmaxf(wm, __shfl_xor_sync(0xffffffffu, wm, o));
-      if (tid == 0) TC_TRACE(0, i, 1);
-      if (lane == 0) misc->wmax[i & 1][warp] = wm;
+      if (hf == 0 && lane == 0) misc->wmax[par][q] = wm;
       if (i == 0) {
-        if (lane == 0) mbar_arrive(&misc->kap_done);
+        if (hf == 0 && lane == 0) mbar_arrive(&misc->kap_done);
         if (!(ok = wait_or_abort(&misc->kap_done, 0, misc))) break;
       }
       const float* wsrc = misc->wmax[i == 0 ? 0 : ((i - 1) & 1)];
       const float kappa = fmaxf(fmaxf(wsrc[0], wsrc[1]), fmaxf(wsrc[2], wsrc[3]));
-      if (tid == 0) TC_TRACE(0, i, 2);
+      if (tid == 0) TC_TRACE(0, i, 1);
       const float a_m = ex2_approx(c_new - kappa);
-      dsum *= alpha;
+      const float d_carry = dsum * alpha;  // denominator of the carried state in the new frame
       c2 = c_new;
-      const float d_carry = dsum;  // denominator of the carried state in the new frame
-      // pass 2: E, D, R for the 128 tokens of the chunk
-      auto er_block = [&](const uint32_t(&r)[32], int j) {
-        uint32_t ep[16], rp[16];
+      // phase a: E for the 64 tokens of this half (in place of the scores), their sum, E operand rows
+      float tot0 = 0.f, tot1 = 0.f;
+      if (nvalid == C) {
+#pragma unroll
+        for (int k = 0; k < 32; ++k) {
+          const float e0 = ex2_approx(__uint_as_float(ra[k]) * sc2 - c_new);
+          const float e1 = ex2_approx(__uint_as_float(rb[k]) * sc2 - c_new);
+          ra[k] = __float_as_uint(e0);
+          rb[k] = __float_as_uint(e1);
+          tot0 += e0;
+          tot1 += e1;
+        }
+      } else {
+#pragma unroll
+        for (int k = 0; k < 32; ++k) {
+          const float e0 = (tok0 + k < nvalid) ? ex2_approx(__uint_as_float(ra[k]) * sc2 - c_new) : 0.f;
+          const float e1 = (tok0 + 32 + k < nvalid) ? ex2_approx(__uint_as_float(rb[k]) * sc2 - c_new) : 0.f;
+          ra[k] = __float_as_uint(e0);
+          rb[k] = __float_as_uint(e1);
+          tot0 += e0;
+          tot1 += e1;
+        }
+      }
+      misc->xsum[par][hf][m] = tot0 + tot1;
+      mbar_arrive(&misc->psum[q]);
+#pragma unroll
+      for (int ch = 0; ch < 4; ++ch) {
+        *reinterpret_cast<uint4*>(e_row + swz_chunk_off(m, ch)) =
+            make_uint4(pack_bf16(__uint_as_float(ra[ch * 8 + 0]), __uint_as_float(ra[ch * 8 + 1])),
+                       pack_bf16(__uint_as_float(ra[ch * 8 + 2]), __uint_as_float(ra[ch * 8 + 3])),
+                       pack_bf16(__uint_as_float(ra[ch * 8 + 4]), __uint_as_float(ra[ch * 8 + 5])),
+                       pack_bf16(__uint_as_float(ra[ch * 8 + 6]), __uint_as_float(ra[ch * 8 + 7])));
+        *reinterpret_cast<uint4*>(e_row + swz_chunk_off(m, 4 + ch)) =
+            make_uint4(pack_bf16(__uint_as_float(rb[ch * 8 + 0]), __uint_as_float(rb[ch * 8 + 1])),
+                       pack_bf16(__uint_as_float(rb[ch * 8 + 2]), __uint_as_float(rb[ch * 8 + 3])),
+                       pack_bf16(__uint_as_float(rb[ch * 8 + 4]), __uint_as_float(rb[ch * 8 + 5])),
+                       pack_bf16(__uint_as_float(rb[ch * 8 + 6]), __uint_as_float(rb[ch * 8 + 7])));
+      }
+      if (!(ok = wait_or_abort(&misc->psum[q], par, misc))) break;
+      const float sum_lo = misc->xsum[par][0][m], sum_hi = misc->xsum[par][1][m];
+      dsum = d_carry + sum_lo + sum_hi;  // carried denominator after this chunk
+      if (tid == 0) TC_TRACE(0, i, 2);
+      // phase b: D = running denominator, R = E a_m / D, R operand rows
+      float run = d_carry + (hf ? sum_lo : 0.f);
+#pragma unroll
+      for (int blk = 0; blk < 2; ++blk) {
+        uint32_t rp[16];
 #pragma unroll
         for (int k = 0; k < 32; k += 2) {
-          const float e0 = (full || j * 32 + k < nvalid) ? ex2_approx(__uint_as_float(r[k]) * sc2 - c_new) : 0.f;
-          const float e1 = (full || j * 32 + k + 1 < nvalid) ? ex2_approx(__uint_as_float(r[k + 1]) * sc2 - c_new) : 0.f;
-          dsum += e0;
-          const float r0 = e0 * (a_m * rcp_fma(dsum));
-          dsum += e1;
-          const float r1 = e1 * (a_m * rcp_fma(dsum));
-          ep[k >> 1] = pack_bf16(e0, e1);
+          const float e0 = __uint_as_float(blk ? rb[k] : ra[k]);
+          const float e1 = __uint_as_float(blk ? rb[k + 1] : ra[k + 1]);
+          run += e0;
+          const float r0 = e0 * (a_m * rcp_approx(run));
+          run += e1;
+          const float r1 = e1 * (a_m * rcp_approx(run));
           rp[k >> 1] = pack_bf16(r0, r1);
         }
-        if (tid == 0 && j == 0) {
-          asm volatile("" ::"r"(ep[15]), "r"(rp[15]), "r"(ep[0]), "r"(rp[7]) : "memory");
-          TC_TRACE(0, i, 6);
-        }
-        // tokens [32 j, 32 j + 32) live in t-block j / 2, 16-byte chunks (j % 2) * 4 .. + 3 of row m
-        const int blk = j >> 1, ch0 = (j & 1) * 4;
 #pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {
-          const uint32_t off = blk * 16384 + swz_chunk_off(m, ch0 + ch);
-          *reinterpret_cast<uint4*>(e_row + off) = make_uint4(ep[ch * 4], ep[ch * 4 + 1], ep[ch * 4 + 2], ep[ch * 4 + 3]);
-          *reinterpret_cast<uint4*>(r_row + off) = make_uint4(rp[ch * 4], rp[ch * 4 + 1], rp[ch * 4 + 2], rp[ch * 4 + 3]);
-        }
-        if (tid == 0 && j == 0) TC_TRACE(0, i, 7);
-      };
-#pragma unroll 1
-      for (int jj = 0; jj < 2; ++jj) {
-        tmem_wait_ld();
-        tmem_fence_regs(ra);
-        tmem_ld32(tl + TM_S + (2 * jj + 1) * 32, rb);
-        er_block(ra, 2 * jj);
-        tmem_wait_ld();
-        tmem_fence_regs(rb);
-        if (jj == 0) tmem_ld32(tl + TM_S + 2 * 32, ra);
-        er_block(rb, 2 * jj + 1);
+        for (int ch = 0; ch < 4; ++ch)
+          *reinterpret_cast<uint4*>(r_row + swz_chunk_off(m, blk * 4 + ch)) =
+              make_uint4(rp[ch * 4], rp[ch * 4 + 1], rp[ch * 4 + 2], rp[ch * 4 + 3]);
       }
-      tc_fence_before_sync();
-      mbar_arrive(&misc->s_free);  // the S columns may take the next chunk's scores
       if (tid == 0) TC_TRACE(0, i, 3);
       // state part: needs the numerator update of the previous chunk to have landed
       if (i > 0 && !(ok = wait_or_abort(&misc->u_done, (i - 1) & 1, misc))) break;
       tc_fence_after_sync();
       if (tid == 0) TC_TRACE(0, i, 4);
-      *reinterpret_cast<__nv_bfloat16*>(smem + OFF_B16 + (m >> 6) * 2048 + ((m & 63) >> 3) * 16 + (m & 7) * 2) =
-          __float2bfloat16_rn(d_carry);
+      if (hf == 0)
+        *reinterpret_cast<__nv_bfloat16*>(smem + OFF_B16 + (m >> 6) * 2048 + ((m & 63) >> 3) * 16 + (m & 7) * 2) =
+            __float2bfloat16_rn(d_carry);
       {
         const bool need = __any_sync(0xffffffffu, alpha != 1.0f);
+        uint32_t r[32];
+        tmem_ld32(tl + TM_U + hf * 32, r);
+        tmem_wait_ld();
+        tmem_fence_regs(r);
+        if (need) {
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          uint32_t r[32];
-          tmem_ld32(tl + TM_U + half * 32, r);
-          tmem_wait_ld();
-          if (need) {
+          for (int k = 0; k < 32; ++k) r[k] = __float_as_uint(__uint_as_float(r[k]) * alpha);
+          tmem_st32(tl + TM_U + hf * 32, r);
+        }
 #pragma unroll
-            for (int k = 0; k < 32; ++k) r[k] = __float_as_uint(__uint_as_float(r[k]) * alpha);
-            tmem_st32(tl + TM_U + half * 32, r);
-          }
-#pragma unroll
-          for (int ch = 0; ch < 4; ++ch) {
-            uint4 v;
-            v.x = pack_bf16(__uint_as_float(r[ch * 8 + 0]), __uint_as_float(r[ch * 8 + 1]));
-            v.y = pack_bf16(__uint_as_float(r[ch * 8 + 2]), __uint_as_float(r[ch * 8 + 3]));
-            v.z = pack_bf16(__uint_as_float(r[ch * 8 + 4]), __uint_as_float(r[ch * 8 + 5]));
-            v.w = pack_bf16(__uint_as_float(r[ch * 8 + 6]), __uint_as_float(r[ch * 8 + 7]));
-            *reinterpret_cast<uint4*>(smem + OFF_U + swz_chunk_off(m, half * 4 + ch)) = v;
-          }
+        for (int ch = 0; ch < 4; ++ch) {
+          uint4 v;
+          v.x = pack_bf16(__uint_as_float(r[ch * 8 + 0]), __uint_as_float(r[ch * 8 + 1]));
+          v.y = pack_bf16(__uint_as_float(r[ch * 8 + 2]), __uint_as_float(r[ch * 8 + 3]));
+          v.z = pack_bf16(__uint_as_float(r[ch * 8 + 4]), __uint_as_float(r[ch * 8 + 5]));
+          v.w = pack_bf16(__uint_as_float(r[ch * 8 + 6]), __uint_as_float(r[ch * 8 + 7]));
+          *reinterpret_cast<uint4*>(smem + OFF_U + swz_chunk_off(m, hf * 4 + ch)) = v;
         }
         if (need) tmem_wait_st();
       }
@@ -397,24 +424,24 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       tc_fence_after_sync();
       if (ok) {
         const int64_t so = (int64_t)lane_id * p.out_lane_stride + (int64_t)seg * p.out_seg_stride;
-        p.out_m[so * M + m] = c2 * kLn2;
-        p.out_d[so * M + m] = dsum;
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          uint32_t r[32];
-          tmem_ld32(tl + TM_U + half * 32, r);
-          tmem_wait_ld();
-          float4* dst = reinterpret_cast<float4*>(p.out_u + (so * M + m) * D + half * 32);
-#pragma unroll
-          for (int k = 0; k < 8; ++k)
-            dst[k] = make_float4(__uint_as_float(r[4 * k]), __uint_as_float(r[4 * k + 1]), __uint_as_float(r[4 * k + 2]),
-                                 __uint_as_float(r[4 * k + 3]));
+        if (hf == 0) {
+          p.out_m[so * M + m] = c2 * kLn2;
+          p.out_d[so * M + m] = dsum;
         }
+        uint32_t r[32];
+        tmem_ld32(tl + TM_U + hf * 32, r);
+        tmem_wait_ld();
+        tmem_fence_regs(r);
+        float4* dst = reinterpret_cast<float4*>(p.out_u + (so * M + m) * D + hf * 32);
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          dst[k] = make_float4(__uint_as_float(r[4 * k]), __uint_as_float(r[4 * k + 1]), __uint_as_float(r[4 * k + 2]),
+                               __uint_as_float(r[4 * k + 3]));
       }
     }
   } else {
     // ============================ token group: thread = token of the chunk = TMEM lane ============================
-    const int wq = warp - 4;  // lane quarter
+    const int wq = warp - 8;  // lane quarter
     const uint32_t tl = tmem + ((uint32_t)(wq * 32) << 16);
     const int tt = wq * 32 + lane;  // token index inside the chunk
     for (int i = 0; ok && i < nchunks; ++i) {
@@ -424,7 +451,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       // causal mask of W, bf16 pack, row sums
       if (!(ok = wait_or_abort(&misc->w_ready, par, misc))) break;
       tc_fence_after_sync();
-      if (tid == 128) TC_TRACE(1, i, 0);
+      if (tid == 256) TC_TRACE(1, i, 0);
       float rowsum = 0.f;
 #pragma unroll 1
       for (int j = 0; j < 4; ++j) {
@@ -450,12 +477,12 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       tmem_wait_st();
       tc_fence_before_sync();
       mbar_arrive(&misc->p2_done);
-      if (tid == 128) TC_TRACE(1, i, 1);
+      if (tid == 256) TC_TRACE(1, i, 1);
 
       // normalise and store
       if (!(ok = wait_or_abort(&misc->y_ready, par, misc))) break;
       tc_fence_after_sync();
-      if (tid == 128) TC_TRACE(1, i, 2);
+      if (tid == 256) TC_TRACE(1, i, 2);
       uint32_t den0;
       tmem_ld1(tl + TM_DEN + (i & 1) * 16, den0);
       tmem_wait_ld();
@@ -480,7 +507,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         }
       }
       tc_fence_before_sync();
-      if (tid == 128) TC_TRACE(1, i, 3);
+      if (tid == 256) TC_TRACE(1, i, 3);
     }
   }
   if (!ok) {
@@ -489,7 +516,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   }
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 8) tmem_dealloc(tmem, TM_COLS);
+  if (warp == 12) tmem_dealloc(tmem, TM_COLS);
 }
 
 
