@@ -80,7 +80,10 @@ __device__ __forceinline__ uint32_t swz_chunk_off(int row, int chunk) { return r
 
 // bounded wait that also gives up as soon as another role of the CTA has given up
 __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, Misc* misc) {
-  if (mbar_test_wait(bar, parity)) return true;
+  // short waits (partner warp a few hundred cycles behind) are polled; longer ones suspend in hardware
+#pragma unroll 1
+  for (int spin = 0; spin < 24; ++spin)
+    if (mbar_test_wait(bar, parity)) return true;
   const uint64_t t0 = global_timer_ns();
   while (true) {
     if (mbar_try_wait(bar, parity, 50000u)) return true;  // sleeps in hardware, wakes on completion
@@ -283,14 +286,17 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       mbar_arrive(&misc->s_free);  // the S columns may take the next chunk's scores
       // row maximum over the valid tokens of this half
       float cm0 = -INFINITY, cm1 = -INFINITY, cm2 = -INFINITY, cm3 = -INFINITY;
-      if (nvalid == C) {
+      if (nvalid == C && sc2 >= 0.f) {
+        // the scale is monotone: take the maximum of the raw scores and scale once
 #pragma unroll
         for (int k = 0; k < 32; k += 2) {
-          cm0 = fmaxf(cm0, __uint_as_float(ra[k]) * sc2);
-          cm1 = fmaxf(cm1, __uint_as_float(ra[k + 1]) * sc2);
-          cm2 = fmaxf(cm2, __uint_as_float(rb[k]) * sc2);
-          cm3 = fmaxf(cm3, __uint_as_float(rb[k + 1]) * sc2);
+          cm0 = fmaxf(cm0, __uint_as_float(ra[k]));
+          cm1 = fmaxf(cm1, __uint_as_float(ra[k + 1]));
+          cm2 = fmaxf(cm2, __uint_as_float(rb[k]));
+          cm3 = fmaxf(cm3, __uint_as_float(rb[k + 1]));
         }
+        cm0 = fmaxf(fmaxf(cm0, cm1), fmaxf(cm2, cm3)) * sc2;
+        cm1 = cm2 = cm3 = cm0;
       } else {
 #pragma unroll
         for (int k = 0; k < 32; ++k) {
@@ -373,9 +379,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           const float e0 = __uint_as_float(blk ? rb[k] : ra[k]);
           const float e1 = __uint_as_float(blk ? rb[k + 1] : ra[k + 1]);
           run += e0;
-          const float r0 = e0 * (a_m * rcp_approx(run));
+          const float r0 = e0 * (a_m * rcp_approx(run));  // special-function unit
           run += e1;
-          const float r1 = e1 * (a_m * rcp_approx(run));
+          const float r1 = e1 * (a_m * rcp_fma(run));     // FMA pipe: the two units share the divisions
           rp[k >> 1] = pack_bf16(r0, r1);
         }
 #pragma unroll
