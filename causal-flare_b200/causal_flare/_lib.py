@@ -72,6 +72,7 @@ EXPORTS = (
     "flare_decode_step", "flare_state_merge", "flare_status_string", "flare_last_cuda_error",
     "flare_abi_version", "flare_abi_sizeof", "flare_set_kernel_events", "flare_last_launch_count",
     "flare_forward_uses_tensor_path", "flare_device_status", "flare_set_trace_buffer",
+    "flare_forward_noalloc", "flare_noalloc_scratch_capacity",
 )
 
 _lib = None
@@ -111,6 +112,9 @@ def load() -> C.CDLL:
     lib.flare_forward_uses_tensor_path.restype = C.c_int
     lib.flare_forward_uses_tensor_path.argtypes = [C.POINTER(FwdArgs)]
     lib.flare_device_status.restype = C.c_int
+    lib.flare_forward_noalloc.restype = C.c_int
+    lib.flare_forward_noalloc.argtypes = [C.POINTER(FwdArgs), C.c_void_p]
+    lib.flare_noalloc_scratch_capacity.restype = C.c_size_t
     lib.flare_set_trace_buffer.restype = None
     lib.flare_set_trace_buffer.argtypes = [C.c_void_p]
     lib.flare_device_status.argtypes = [C.c_int]

@@ -1,0 +1,56 @@
+// flare_forward_noalloc: the forward entry point for callers that must not allocate device memory.
+//
+// Who needs it: code that runs where cudaMalloc is off limits - a serving loop that has handed all device
+// memory to its own pool, a plugin called from inside another framework's allocator callback or from a
+// latency-critical path where an allocation (which may synchronise the device) is unacceptable, or a host
+// language binding that has no allocator to offer for the workspace.  flare_forward asks such callers for a
+// workspace whenever it splits a long sequence into segments (few (batch, head) lanes); this variant keeps that
+// workspace - the per-segment (m, d, u) states of the segment scan - in a fixed array inside the library.
+#include <string.h>
+
+#include "flare_common.cuh"
+
+// Capacity of the built-in scratch.  Every GPU that loads the library holds this much memory until exit.
+#define FLARE_NOALLOC_SCRATCH_BYTES (8u << 20)
+
+static __device__ __align__(256) unsigned char g_flare_noalloc_scratch[FLARE_NOALLOC_SCRATCH_BYTES];
+
+namespace {
+
+constexpr int kMaxDevices = 64;
+// Device address of the scratch array per device ordinal.  The array's name is only a host-side handle here;
+// the address a kernel can use must be asked for, once per device, while that device is current.
+void* g_scratch_ptr[kMaxDevices] = {};
+
+}  // namespace
+
+extern "C" {
+
+size_t flare_noalloc_scratch_capacity(void) { return FLARE_NOALLOC_SCRATCH_BYTES; }
+
+int flare_forward_noalloc(const flare_fwd_args_t* args, flare_stream_t stream) {
+  if (args == nullptr) return FLARE_ERR_BAD_POINTER;
+  int dev = 0;
+  FLARE_CUDA_CHECK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return FLARE_ERR_UNSUPPORTED;
+  if (g_scratch_ptr[dev] == nullptr) {
+    // first call on this device: resolve the device address of the scratch array (not a stream operation;
+    // make this first call before any stream capture)
+    void* ptr = nullptr;
+    FLARE_CUDA_CHECK(cudaGetSymbolAddress(&ptr, g_flare_noalloc_scratch));
+    if (ptr == nullptr) return FLARE_ERR_CUDA;
+    g_scratch_ptr[dev] = ptr;
+  }
+  flare_fwd_args_t a = *args;
+  a.workspace = nullptr;
+  a.workspace_bytes = 0;
+  const size_t need = flare_forward_workspace_bytes(&a);
+  if (need > FLARE_NOALLOC_SCRATCH_BYTES) return FLARE_ERR_TOO_LARGE;
+  // Nothing in the scratch has to start at zero: the segment pass writes every state slot before the scan and the
+  // output pass read it.  The contents of the previous call are simply overwritten.
+  a.workspace = g_scratch_ptr[dev];
+  a.workspace_bytes = FLARE_NOALLOC_SCRATCH_BYTES;
+  return flare_forward(&a, stream);
+}
+
+}  // extern "C"

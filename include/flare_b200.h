@@ -95,6 +95,21 @@ size_t flare_forward_workspace_bytes(const flare_fwd_args_t* args);
 int flare_forward(const flare_fwd_args_t* args, flare_stream_t stream);
 
 /*
+ * flare_forward for callers that cannot allocate device memory (no counterpart in the reference, whose wrappers
+ * always allocate their workspaces with torch).  Same arguments and results as flare_forward, except that
+ * args->workspace / workspace_bytes are ignored: the scratch for the segment-state scan lives in a fixed array
+ * inside the library, flare_noalloc_scratch_capacity() bytes (8 MiB) per GPU, held from library load to exit.
+ * Returns FLARE_ERR_TOO_LARGE, without launching anything, when the problem needs more scratch than that
+ * (flare_forward_workspace_bytes tells how much).  The call performs no cudaMalloc / cudaFree and calls no
+ * allocating library routine.  The first call on each device resolves the array's device address
+ * (cudaGetSymbolAddress); make that first call outside any stream capture.  All calls share the one array:
+ * two calls whose kernels may overlap on the GPU (different streams, or different host threads) race on it,
+ * so serialise them.  Nothing in the array needs clearing between calls.
+ */
+int flare_forward_noalloc(const flare_fwd_args_t* args, flare_stream_t stream);
+size_t flare_noalloc_scratch_capacity(void);
+
+/*
  * Backward problem: gradients of <Y, dY>.  Replaces
  *   _chunked_flare_lse_backward_impl       causal_flare/autoregressive/training.py:4369-4918
  *   _recurrent_flare_backward_impl         causal_flare/autoregressive/recurrent.py:749-935
