@@ -78,6 +78,13 @@ __device__ int g_tc_error = 0;
 
 __device__ __forceinline__ uint32_t swz_chunk_off(int row, int chunk) { return row * 128 + ((chunk ^ (row & 7)) << 4); }
 
+// One arrival per warp: 32 lanes arriving one by one are 32 serialised shared-memory atomics.  __syncwarp orders the
+// lanes' earlier writes before lane 0's releasing arrive.
+__device__ __forceinline__ void warp_arrive(uint64_t* bar, int lane) {
+  __syncwarp();
+  if (lane == 0) mbar_arrive(bar);
+}
+
 // bounded wait that also gives up as soon as another role of the CTA has given up
 __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, Misc* misc) {
   // short waits (partner warp a few hundred cycles behind) are polled; longer ones suspend in hardware
@@ -115,16 +122,16 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       mbar_init(&misc->v_empty[i], 1);
     }
     mbar_init(&misc->s_ready, 1);
-    mbar_init(&misc->s_free, 256);
+    mbar_init(&misc->s_free, 8);
     mbar_init(&misc->kap_done, 4);
-    mbar_init(&misc->p1_done, 256);
+    mbar_init(&misc->p1_done, 8);
     for (int i = 0; i < 4; ++i) {
-      mbar_init(&misc->pmax[i], 64);
-      mbar_init(&misc->psum[i], 64);
+      mbar_init(&misc->pmax[i], 2);
+      mbar_init(&misc->psum[i], 2);
     }
     mbar_init(&misc->u_done, 1);
     mbar_init(&misc->w_ready, 1);
-    mbar_init(&misc->p2_done, 128);
+    mbar_init(&misc->p2_done, 4);
     mbar_init(&misc->y_ready, 1);
     misc->abort_flag = 0;
     fence_barrier_init();
@@ -256,7 +263,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     const float sc2 = p.scale * kLog2e;
     const int64_t st_idx = (int64_t)lane_id * p.in_lane_stride + (int64_t)seg * p.in_seg_stride;
     float c2 = p.in_m ? p.in_m[st_idx * M + m] * kLog2e : -INFINITY;  // running max, log2 units (both halves keep a copy)
-    float dsum = p.in_d ? p.in_d[st_idx * M + m] : 0.f;
+    float dsum = p.in_d ? p.in_d[st_idx * M + m] : 0.f;  // denominator in frame c2, through the last finished chunk
+    float d_prev = 0.f;                                  // denominator before the chunk in flight, in its frame
     {
       // carry-in numerator -> tensor memory, 32 value columns per half
       uint32_t r[32];
@@ -283,7 +291,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       tmem_fence_regs(ra);
       tmem_fence_regs(rb);
       tc_fence_before_sync();
-      mbar_arrive(&misc->s_free);  // the S columns may take the next chunk's scores
+      warp_arrive(&misc->s_free, lane);  // the S columns may take the next chunk's scores
       // row maximum over the valid tokens of this half
       float cm0 = -INFINITY, cm1 = -INFINITY, cm2 = -INFINITY, cm3 = -INFINITY;
       if (nvalid == C && sc2 >= 0.f) {
@@ -305,10 +313,21 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         }
       }
       misc->xmax[par][hf][m] = fmaxf(fmaxf(cm0, cm1), fmaxf(cm2, cm3));
-      mbar_arrive(&misc->pmax[q]);
-      if (!(ok = wait_or_abort(&misc->pmax[q], par, misc))) break;
-      const float cmax = fmaxf(misc->xmax[par][0][m], misc->xmax[par][1][m]);
-      const float c_new = fmaxf(c2, cmax);
+      // Frame of this chunk.  Chunk 0 exchanges the two halves' maxima synchronously (the carried frame may be
+      // empty).  Later chunks use the running max through the PREVIOUS chunk, known without waiting; E may then
+      // exceed 1 by the growth of the max inside one chunk, which fp32 / bf16 hold easily, and the maxima published
+      // above enter the next chunk's frame.  The state is put into the exact running-max frame when it is written out.
+      float c_new;
+      if (i == 0) {
+        warp_arrive(&misc->pmax[q], lane);
+        if (!(ok = wait_or_abort(&misc->pmax[q], 0, misc))) break;
+        c_new = fmaxf(c2, fmaxf(misc->xmax[0][0][m], misc->xmax[0][1][m]));
+      } else {
+        // bookkeeping of chunk i - 1: both halves' sums and maxima are published once its psum phase completed
+        if (!(ok = wait_or_abort(&misc->psum[q], (i - 1) & 1, misc))) break;
+        dsum = d_prev + (misc->xsum[par ^ 1][0][m] + misc->xsum[par ^ 1][1][m]);
+        c_new = fmaxf(c2, fmaxf(misc->xmax[par ^ 1][0][m], misc->xmax[par ^ 1][1][m]));
+      }
       const float alpha = ex2_approx(c2 - c_new);  // 0 when the old state is empty
       // kappa: common frame of the decode weights = max over latents of the running max.  Chunk 0 synchronises;
       // later chunks use the value published during the previous chunk (one chunk stale, which only changes a
@@ -351,7 +370,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         }
       }
       misc->xsum[par][hf][m] = tot0 + tot1;
-      mbar_arrive(&misc->psum[q]);
+      warp_arrive(&misc->psum[q], lane);
 #pragma unroll
       for (int ch = 0; ch < 4; ++ch) {
         *reinterpret_cast<uint4*>(e_row + swz_chunk_off(m, ch)) =
@@ -365,12 +384,15 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                        pack_bf16(__uint_as_float(rb[ch * 8 + 4]), __uint_as_float(rb[ch * 8 + 5])),
                        pack_bf16(__uint_as_float(rb[ch * 8 + 6]), __uint_as_float(rb[ch * 8 + 7])));
       }
-      if (!(ok = wait_or_abort(&misc->psum[q], par, misc))) break;
-      const float sum_lo = misc->xsum[par][0][m], sum_hi = misc->xsum[par][1][m];
-      dsum = d_carry + sum_lo + sum_hi;  // carried denominator after this chunk
+      d_prev = d_carry;
+      // the upper half continues the lower half's running denominator; the lower half needs nothing from its partner
+      float run = d_carry;
+      if (hf) {
+        if (!(ok = wait_or_abort(&misc->psum[q], par, misc))) break;
+        run += misc->xsum[par][0][m];
+      }
       if (tid == 0) TC_TRACE(0, i, 2);
       // phase b: D = running denominator, R = E a_m / D, R operand rows
-      float run = d_carry + (hf ? sum_lo : 0.f);
 #pragma unroll
       for (int blk = 0; blk < 2; ++blk) {
         uint32_t rp[16];
@@ -421,18 +443,28 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       }
       fence_proxy_async_smem();
       tc_fence_before_sync();
-      mbar_arrive(&misc->p1_done);
+      warp_arrive(&misc->p1_done, lane);
       if (tid == 0) TC_TRACE(0, i, 5);
     }
     // carry-out state
     if (ok && p.out_u != nullptr && (p.out_mode == 1 || (p.out_mode == 2 && seg == p.nseg_total - 1))) {
-      if (nchunks > 0) ok = wait_or_abort(&misc->u_done, (nchunks - 1) & 1, misc);
+      float fin = 1.0f;  // factor from the last chunk's frame to the exact running-max frame
+      if (nchunks > 0) {
+        const int lp = (nchunks - 1) & 1;
+        ok = wait_or_abort(&misc->u_done, lp, misc) && wait_or_abort(&misc->psum[q], lp, misc);
+        if (ok) {
+          dsum = d_prev + (misc->xsum[lp][0][m] + misc->xsum[lp][1][m]);
+          const float c_true = fmaxf(c2, fmaxf(misc->xmax[lp][0][m], misc->xmax[lp][1][m]));
+          fin = ex2_approx(c2 - c_true);
+          c2 = c_true;
+        }
+      }
       tc_fence_after_sync();
       if (ok) {
         const int64_t so = (int64_t)lane_id * p.out_lane_stride + (int64_t)seg * p.out_seg_stride;
         if (hf == 0) {
           p.out_m[so * M + m] = c2 * kLn2;
-          p.out_d[so * M + m] = dsum;
+          p.out_d[so * M + m] = dsum * fin;
         }
         uint32_t r[32];
         tmem_ld32(tl + TM_U + hf * 32, r);
@@ -441,8 +473,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         float4* dst = reinterpret_cast<float4*>(p.out_u + (so * M + m) * D + hf * 32);
 #pragma unroll
         for (int k = 0; k < 8; ++k)
-          dst[k] = make_float4(__uint_as_float(r[4 * k]), __uint_as_float(r[4 * k + 1]), __uint_as_float(r[4 * k + 2]),
-                               __uint_as_float(r[4 * k + 3]));
+          dst[k] = make_float4(__uint_as_float(r[4 * k]) * fin, __uint_as_float(r[4 * k + 1]) * fin,
+                               __uint_as_float(r[4 * k + 2]) * fin, __uint_as_float(r[4 * k + 3]) * fin);
       }
     }
   } else {
@@ -482,7 +514,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       }
       tmem_wait_st();
       tc_fence_before_sync();
-      mbar_arrive(&misc->p2_done);
+      warp_arrive(&misc->p2_done, lane);
       if (tid == 256) TC_TRACE(1, i, 1);
 
       // normalise and store
