@@ -524,7 +524,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       uint32_t den0;
       tmem_ld1(tl + TM_DEN + (i & 1) * 16, den0);
       tmem_wait_ld();
-      const float inv = 1.0f / (__uint_as_float(den0) + rowsum);
+      const float den = __uint_as_float(den0) + rowsum;
+      // outside the numeric domain of this path (scores of a token more than ~80 nats below the running maxima):
+      // every weight underflowed.  Flag it; the exact path has no such limit.
+      if (tt < nvalid && !(den > 0.f && den < INFINITY)) atomicOr(&g_tc_error, 2);
+      const float inv = 1.0f / den;
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
         uint32_t r[32];
@@ -550,7 +554,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   }
   if (!ok) {
     misc->abort_flag = 1;
-    atomicExch(&g_tc_error, 1);
+    atomicOr(&g_tc_error, 1);
   }
   tc_fence_before_sync();
   __syncthreads();

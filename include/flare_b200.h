@@ -187,9 +187,11 @@ void flare_set_trace_buffer(void* device_buffer);
  * supported shape: bf16, softmax encoder, M = 128, Dk = Dv = 64, shared decode weights, no mask), else 0. */
 int flare_forward_uses_tensor_path(const flare_fwd_args_t* args);
 
-/* Device-side health of the tensor-core kernels: synchronises the device and returns 0 when every bounded
- * wait inside them completed, 1 when a kernel gave up on a wait (its outputs are then invalid), or a negative
- * flare_status on a CUDA error.  reset != 0 clears the flag. */
+/* Device-side health of the tensor-core kernels: synchronises the device and returns a bit set (0 = healthy), or a
+ * negative flare_status on a CUDA error.  Bit 0 (1): a kernel gave up on a bounded wait, its outputs are invalid.
+ * Bit 1 (2): some token's decode denominator underflowed or overflowed - the inputs are outside the numeric domain
+ * of the tensor path (scores spread over more than ~80 nats); rerun with path = FLARE_PATH_EXACT.
+ * reset != 0 clears the flags. */
 int flare_device_status(int reset);
 /* sizeof(flare_fwd_args_t / flare_bwd_args_t / flare_decode_args_t / flare_state_t) for which = 0..3,
  * so that a foreign-language binding can verify its struct layout at load time. */

@@ -83,3 +83,20 @@ def test_tensor_vs_exact_at_benchmark_size():
     assert torch.equal(y2[:, :3 * N // 4], y_t[:, :3 * N // 4])
     y3, _, _, _ = run(q, k, v, _lib.PATH_TENSOR)
     assert torch.equal(y3, y_t), "tensor path must be run-to-run deterministic"
+
+
+def test_sharp_scores_are_flagged_not_silently_wrong():
+    # scores with a standard deviation of ~64 nats: outside the tensor path's domain.  Either the result still
+    # meets the gate, or the device status reports the range problem; the exact path is right in any case.
+    q, k, v = orc.make_inputs(1, 512, 2, M, D, seed0=13, dtype=torch.bfloat16)
+    q, k = (q.float() * 8).bfloat16(), (k.float() * 8).bfloat16()
+    ref = orc.ar_forward(q, k, v)
+    qc, kc, vc = to_dev(q, k, v)
+    y_t, _, _, _ = _ops.forward(qc, kc, vc, scale=D ** -0.5, path=_lib.PATH_TENSOR)
+    status = _ops.device_status()
+    assert status in (0, 2)
+    if status == 0:
+        assert_bf16_gate(y_t, ref, "sharp scores, tensor path")
+    y_e, _, _, _ = _ops.forward(qc, kc, vc, scale=D ** -0.5, path=_lib.PATH_EXACT)
+    assert _ops.device_status() == 0
+    assert_bf16_gate(y_e, ref, "sharp scores, exact path")
