@@ -61,7 +61,7 @@ namespace {
 // (1) forward replay
 // --------------------------------------------------------------------------------------------------
 template <int MM_MAX, int DD>
-__global__ void __launch_bounds__(NT) bwd_replay_kernel(const BwdParams p) {
+__global__ void __launch_bounds__(NT, (MM_MAX * DD <= 32) ? 2 : 1) bwd_replay_kernel(const BwdParams p) {
   extern __shared__ __align__(16) float smem_raw[];
   const int lane_id = blockIdx.x, dt = blockIdx.y;
   const int b = lane_id / p.H, h = lane_id % p.H;
@@ -281,7 +281,7 @@ __global__ void __launch_bounds__(NT) bwd_replay_kernel(const BwdParams p) {
 // (2) reverse walk
 // --------------------------------------------------------------------------------------------------
 template <int MM_MAX, int DD>
-__global__ void __launch_bounds__(NT) bwd_reverse_kernel(const BwdParams p) {
+__global__ void __launch_bounds__(NT, (MM_MAX * DD <= 32) ? 2 : 1) bwd_reverse_kernel(const BwdParams p) {
   extern __shared__ __align__(16) float smem_raw[];
   const int lane_id = blockIdx.x, dt = blockIdx.y;
   const int b = lane_id / p.H, h = lane_id % p.H;

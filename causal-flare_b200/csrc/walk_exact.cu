@@ -19,7 +19,7 @@ namespace flare {
 using namespace walk;
 
 template <int MM_MAX, int DD>
-__global__ void __launch_bounds__(NT) walk_exact_kernel(const WalkParams p) {
+__global__ void __launch_bounds__(NT, (MM_MAX * DD <= 32) ? 2 : 1) walk_exact_kernel(const WalkParams p) {
   extern __shared__ __align__(16) float smem_raw[];
   const int lane_id = blockIdx.x;  // (b, h) lane
   const int seg = blockIdx.y;
