@@ -12,7 +12,7 @@ import os
 import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(os.path.dirname(_HERE), "libflare_b200.so")
+LIB_PATH = os.environ.get("FLARE_B200_LIB") or os.path.join(os.path.dirname(_HERE), "libflare_b200.so")
 
 F32, BF16, F16 = 0, 1, 2
 SOFTMAX, STABLEMAX = 0, 1

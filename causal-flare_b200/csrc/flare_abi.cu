@@ -154,7 +154,7 @@ int launch_walk(const flare_fwd_args_t* a, const FwdPlan& pl, const WalkParams& 
   memset(&t, 0, sizeof(t));
   t.y = w.write_y ? w.y : nullptr;
   t.y_stride_b = w.y_stride_b; t.y_stride_n = w.y_stride_n; t.y_stride_h = w.y_stride_h;
-  t.N = w.N; t.H = w.H; t.scale = w.scale; t.seg_len = w.seg_len;
+  t.N = w.N; t.H = w.H; t.M = w.M; t.scale = w.scale; t.seg_len = w.seg_len;
   t.in_m = w.in_m; t.in_d = w.in_d; t.in_u = w.in_u;
   t.in_lane_stride = w.in_lane_stride; t.in_seg_stride = w.in_seg_stride;
   t.out_m = w.out_m; t.out_d = w.out_d; t.out_u = w.out_u;

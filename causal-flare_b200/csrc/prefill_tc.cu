@@ -1,5 +1,6 @@
 // Tensor-core (tcgen05 + TMEM + TMA) chunked causal prefill for the softmax encoder, bf16 operands, fp32
-// accumulation and statistics.  Shape class: M = 128 latents, Dk = Dv = 64, shared decode weights, no mask.
+// accumulation and statistics.  Shape class: M <= 128 latents (multiple of 16, padded to 128 rows), Dk = Dv = 64, shared
+// decode weights, no mask.
 //
 // One CTA owns a (batch, head, sequence segment) and walks its chunks of C = 128 tokens in order, carrying the
 // latent state on chip: U [128 latents x 64] fp32 in tensor memory, running max c and denominator d per latent
@@ -100,6 +101,8 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, Mi
 
 }  // namespace
 
+// PADDED: fewer than 128 latents (rows padded); the full-width instance carries none of the padding predicates
+template <bool PADDED>
 __global__ void __launch_bounds__(NTHREADS, 1)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                   const __grid_constant__ CUtensorMap tm_v, const TcParams p) {
@@ -262,14 +265,19 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     const int m = q * 32 + lane;
     const float sc2 = p.scale * kLog2e;
     const int64_t st_idx = (int64_t)lane_id * p.in_lane_stride + (int64_t)seg * p.in_seg_stride;
-    float c2 = p.in_m ? p.in_m[st_idx * M + m] * kLog2e : -INFINITY;  // running max, log2 units (both halves keep a copy)
-    float dsum = p.in_d ? p.in_d[st_idx * M + m] : 0.f;  // denominator in frame c2, through the last finished chunk
+    // Fewer than 128 latents: the missing rows are padding (Q rows read as zero by the TMA).  A padding latent keeps
+    // a fixed frame 0 and a denominator of 1, its E is forced to zero, so it contributes nothing anywhere.
+    const bool live = !PADDED || m < p.M;
+    constexpr bool padded = PADDED;
+    float c2 = !live ? 0.f : (p.in_m ? p.in_m[st_idx * p.M + m] * kLog2e : -INFINITY);  // running max, log2 units
+    float dsum = !live ? 1.f : (p.in_d ? p.in_d[st_idx * p.M + m] : 0.f);  // denominator in frame c2
     float d_prev = 0.f;                                  // denominator before the chunk in flight, in its frame
     {
       // carry-in numerator -> tensor memory, 32 value columns per half
       uint32_t r[32];
 #pragma unroll
-      for (int i = 0; i < 32; ++i) r[i] = p.in_u ? __float_as_uint(p.in_u[(st_idx * M + m) * D + hf * 32 + i]) : 0u;
+      for (int i = 0; i < 32; ++i)
+        r[i] = (p.in_u && live) ? __float_as_uint(p.in_u[(st_idx * p.M + m) * D + hf * 32 + i]) : 0u;
       tmem_st32(tl + TM_U + hf * 32, r);
       tmem_wait_st();
     }
@@ -312,7 +320,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           if (tok0 + 32 + k < nvalid) cm2 = fmaxf(cm2, __uint_as_float(rb[k]) * sc2);
         }
       }
-      misc->xmax[par][hf][m] = fmaxf(fmaxf(cm0, cm1), fmaxf(cm2, cm3));
+      misc->xmax[par][hf][m] = live ? fmaxf(fmaxf(cm0, cm1), fmaxf(cm2, cm3)) : -INFINITY;
       // Frame of this chunk.  Chunk 0 exchanges the two halves' maxima synchronously (the carried frame may be
       // empty).  Later chunks use the running max through the PREVIOUS chunk, known without waiting; E may then
       // exceed 1 by the growth of the max inside one chunk, which fp32 / bf16 hold easily, and the maxima published
@@ -332,7 +340,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       // kappa: common frame of the decode weights = max over latents of the running max.  Chunk 0 synchronises;
       // later chunks use the value published during the previous chunk (one chunk stale, which only changes a
       // per-token scale that cancels in y).
-      float wm = c_new;
+      float wm = live ? c_new : -INFINITY;
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) wm = fmaxf(wm, __shfl_xor_sync(0xffffffffu, wm, o));
       if (hf == 0 && lane == 0) misc->wmax[par][q] = wm;
@@ -348,7 +356,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       c2 = c_new;
       // phase a: E for the 64 tokens of this half (in place of the scores), their sum, E operand rows
       float tot0 = 0.f, tot1 = 0.f;
-      if (nvalid == C) {
+      if (nvalid == C && !padded) {
 #pragma unroll
         for (int k = 0; k < 32; ++k) {
           const float e0 = ex2_approx(__uint_as_float(ra[k]) * sc2 - c_new);
@@ -361,8 +369,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       } else {
 #pragma unroll
         for (int k = 0; k < 32; ++k) {
-          const float e0 = (tok0 + k < nvalid) ? ex2_approx(__uint_as_float(ra[k]) * sc2 - c_new) : 0.f;
-          const float e1 = (tok0 + 32 + k < nvalid) ? ex2_approx(__uint_as_float(rb[k]) * sc2 - c_new) : 0.f;
+          const float e0 = (live && tok0 + k < nvalid) ? ex2_approx(__uint_as_float(ra[k]) * sc2 - c_new) : 0.f;
+          const float e1 = (live && tok0 + 32 + k < nvalid) ? ex2_approx(__uint_as_float(rb[k]) * sc2 - c_new) : 0.f;
           ra[k] = __float_as_uint(e0);
           rb[k] = __float_as_uint(e1);
           tot0 += e0;
@@ -462,18 +470,18 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       tc_fence_after_sync();
       if (ok) {
         const int64_t so = (int64_t)lane_id * p.out_lane_stride + (int64_t)seg * p.out_seg_stride;
-        if (hf == 0) {
-          p.out_m[so * M + m] = c2 * kLn2;
-          p.out_d[so * M + m] = dsum * fin;
+        if (hf == 0 && live) {
+          p.out_m[so * p.M + m] = c2 * kLn2;
+          p.out_d[so * p.M + m] = dsum * fin;
         }
         uint32_t r[32];
         tmem_ld32(tl + TM_U + hf * 32, r);
         tmem_wait_ld();
         tmem_fence_regs(r);
-        float4* dst = reinterpret_cast<float4*>(p.out_u + (so * M + m) * D + hf * 32);
+        float4* dst = reinterpret_cast<float4*>(p.out_u + (so * p.M + (live ? m : 0)) * D + hf * 32);
 #pragma unroll
         for (int k = 0; k < 8; ++k)
-          dst[k] = make_float4(__uint_as_float(r[4 * k]) * fin, __uint_as_float(r[4 * k + 1]) * fin,
+          if (live) dst[k] = make_float4(__uint_as_float(r[4 * k]) * fin, __uint_as_float(r[4 * k + 1]) * fin,
                                __uint_as_float(r[4 * k + 2]) * fin, __uint_as_float(r[4 * k + 3]) * fin);
       }
     }
@@ -604,7 +612,7 @@ bool make_map(CUtensorMap* map, const void* base, int rank, const uint64_t* dims
 }  // namespace
 
 bool prefill_tc_supported(const flare_fwd_args_t* a) {
-  return a->dtype == FLARE_BF16 && a->variant == FLARE_SOFTMAX && a->block_size == 1 && a->M == M && a->Dk == D &&
+  return a->dtype == FLARE_BF16 && a->variant == FLARE_SOFTMAX && a->block_size == 1 && a->M <= M && a->M >= 16 && (a->M % 16) == 0 && a->Dk == D &&
          a->Dv == D && a->q_dec == nullptr && a->k_dec == nullptr && a->mask == nullptr && a->lse_dec == nullptr &&
          a->q_stride_m == D && a->N >= 1;
 }
@@ -612,7 +620,7 @@ bool prefill_tc_supported(const flare_fwd_args_t* a) {
 int launch_prefill_tc(const flare_fwd_args_t* a, const TcParams& p, int nseg_grid, cudaStream_t stream) {
   CUtensorMap tq, tk, tv;
   {
-    const uint64_t dims[3] = {(uint64_t)D, (uint64_t)M, (uint64_t)a->H};
+    const uint64_t dims[3] = {(uint64_t)D, (uint64_t)a->M, (uint64_t)a->H};  // rows beyond M read as zero
     const int64_t str[2] = {a->q_stride_m, a->q_stride_h};
     const uint32_t box[3] = {64, 128, 1};
     if (!make_map(&tq, a->q, 3, dims, str, box)) return FLARE_ERR_CUDA;
@@ -627,11 +635,13 @@ int launch_prefill_tc(const flare_fwd_args_t* a, const TcParams& p, int nseg_gri
   }
   static bool attr_set = false;
   if (!attr_set) {
-    FLARE_CUDA_CHECK(cudaFuncSetAttribute(prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    FLARE_CUDA_CHECK(cudaFuncSetAttribute(prefill_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    FLARE_CUDA_CHECK(cudaFuncSetAttribute(prefill_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
     attr_set = true;
   }
   dim3 grid(a->B * a->H, nseg_grid);
-  prefill_tc_kernel<<<grid, NTHREADS, SMEM_BYTES, stream>>>(tq, tk, tv, p);
+  if (a->M == M) prefill_tc_kernel<false><<<grid, NTHREADS, SMEM_BYTES, stream>>>(tq, tk, tv, p);
+  else prefill_tc_kernel<true><<<grid, NTHREADS, SMEM_BYTES, stream>>>(tq, tk, tv, p);
   FLARE_CUDA_CHECK(cudaGetLastError());
   return FLARE_OK;
 }

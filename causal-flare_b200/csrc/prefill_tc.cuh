@@ -8,6 +8,7 @@ struct TcParams {
   void* y;  // bf16 [B, N, H, 64] (strided) or null
   int64_t y_stride_b, y_stride_n, y_stride_h;
   int N, H;
+  int M;  // latents, <= 128
   float scale;
   int seg_len;
   // carry-in / carry-out states, indexed lane * lane_stride + seg * seg_stride (in states)

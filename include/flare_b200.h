@@ -184,7 +184,8 @@ int flare_last_launch_count(void);
 void flare_set_trace_buffer(void* device_buffer);
 
 /* 1 when flare_forward would take the tcgen05 tensor-core path for this problem (path AUTO or TENSOR and a
- * supported shape: bf16, softmax encoder, M = 128, Dk = Dv = 64, shared decode weights, no mask), else 0. */
+ * supported shape: bf16, softmax encoder, M <= 128 (multiple of 16), Dk = Dv = 64, shared decode weights, no mask),
+ * else 0. */
 int flare_forward_uses_tensor_path(const flare_fwd_args_t* args);
 
 /* Device-side health of the tensor-core kernels: synchronises the device and returns a bit set (0 = healthy), or a

@@ -100,3 +100,18 @@ def test_sharp_scores_are_flagged_not_silently_wrong():
     y_e, _, _, _ = _ops.forward(qc, kc, vc, scale=D ** -0.5, path=_lib.PATH_EXACT)
     assert _ops.device_status() == 0
     assert_bf16_gate(y_e, ref, "sharp scores, exact path")
+
+
+@pytest.mark.parametrize("Ml", [16, 64, 96])
+def test_tensor_path_fewer_latents(Ml):
+    q, k, v = orc.make_inputs(2, 333, 2, Ml, D, seed0=19, dtype=torch.bfloat16)
+    sc = D ** -0.5
+    ref, st_ref = orc.ar_forward(q, k, v, scale=sc, return_state=True)
+    qc, kc, vc = to_dev(q, k, v)
+    assert uses_tensor_path(qc, kc, vc)
+    y, st, _, _ = run(qc, kc, vc, _lib.PATH_TENSOR, want_state=True, scale=sc)
+    assert_bf16_gate(y, ref, f"tensor path M={Ml}")
+    assert st["u"].shape == (2, 2, Ml, D)
+    assert_close(st["m"], st_ref["m"], what="m", atol=1e-4, rtol=1e-4)
+    assert_close(st["d"], st_ref["d"], what="d", atol=1e-3, rtol=3e-3)
+    assert orc.rel_l2(st["u"].cpu(), st_ref["u"]) < 3e-3
