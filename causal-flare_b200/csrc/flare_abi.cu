@@ -98,8 +98,9 @@ FwdPlan plan_forward(const flare_fwd_args_t* a) {
     pl.use_tc = true;
     int nseg = 1;
     const int sms = sm_count();
-    if (lanes * 3 <= sms * 2) {
-      nseg = (int)((sms + lanes - 1) / lanes);
+    const int64_t ctas = lanes * prefill_tc_ctas_per_lane(a);
+    if (ctas * 3 <= sms * 2) {
+      nseg = (int)((sms + ctas - 1) / ctas);
       const int max_seg = a->N / 256;
       if (nseg > max_seg) nseg = max_seg;
       if (nseg < 1) nseg = 1;
@@ -154,7 +155,8 @@ int launch_walk(const flare_fwd_args_t* a, const FwdPlan& pl, const WalkParams& 
   memset(&t, 0, sizeof(t));
   t.y = w.write_y ? w.y : nullptr;
   t.y_stride_b = w.y_stride_b; t.y_stride_n = w.y_stride_n; t.y_stride_h = w.y_stride_h;
-  t.N = w.N; t.H = w.H; t.M = w.M; t.scale = w.scale; t.seg_len = w.seg_len;
+  t.q = w.q; t.q_stride_h = w.q_stride_h; t.q_stride_m = w.q_stride_m;
+  t.N = w.N; t.H = w.H; t.M = w.M; t.Dv = w.Dv; t.scale = w.scale; t.seg_len = w.seg_len;
   t.in_m = w.in_m; t.in_d = w.in_d; t.in_u = w.in_u;
   t.in_lane_stride = w.in_lane_stride; t.in_seg_stride = w.in_seg_stride;
   t.out_m = w.out_m; t.out_d = w.out_d; t.out_u = w.out_u;

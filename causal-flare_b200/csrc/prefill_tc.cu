@@ -1,9 +1,10 @@
 // Tensor-core (tcgen05 + TMEM + TMA) chunked causal prefill for the softmax encoder, bf16 operands, fp32
-// accumulation and statistics.  Shape class: M <= 128 latents (multiple of 16, padded to 128 rows), Dk = Dv = 64, shared
-// decode weights, no mask.
+// accumulation and statistics.  Shape class: M <= 128 latents (multiple of 16, padded to 128 rows), Dk = Dv = 64 or 128,
+// shared decode weights, no mask.
 //
-// One CTA owns a (batch, head, sequence segment) and walks its chunks of C = 128 tokens in order, carrying the
-// latent state on chip: U [128 latents x 64] fp32 in tensor memory, running max c and denominator d per latent
+// One CTA owns a (batch, head, sequence segment, slice of 64 value columns) and walks its chunks of C = 128 tokens in
+// order, carrying the latent state on chip: U [128 latents x 64] fp32 in tensor memory, the latent bank Q as packed
+// bf16 in tensor memory (A operand of the score MMA), running max c and denominator d per latent
 // in registers of the thread that owns the latent (TMEM lane = thread).  Per chunk, with the frame c_m = running
 // max after the chunk and kappa = max_m c_m:
 //
@@ -39,28 +40,38 @@ namespace {
 
 constexpr int C = 128;    // tokens per chunk
 constexpr int M = 128;    // latents
-constexpr int D = 64;     // Dk = Dv
+constexpr int D = 64;     // value columns per CTA, and width of one 128-byte operand block
 constexpr int NTHREADS = 448;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 
 // shared memory map (bytes, every operand buffer 1024-aligned for the 128B swizzle)
-constexpr int OFF_Q = 0;                      // [128 m][64] bf16, K-major                 16 KB
-constexpr int OFF_K = OFF_Q + 16384;          // [128 t][64] bf16                          16 KB
-constexpr int OFF_V = OFF_K + 16384;          // 2 stages x [128 t][64] bf16               32 KB
-constexpr int OFF_E = OFF_V + 2 * 16384;      // 2 x [2 t-blocks][128 m][64 t] bf16        64 KB
-constexpr int OFF_R = OFF_E + 2 * 32768;      // 2 x [2 t-blocks][128 m][64 t] bf16        64 KB
-constexpr int OFF_U = OFF_R + 2 * 32768;      // [128 m][64 dv] bf16                       16 KB
-constexpr int OFF_B16 = OFF_U + 16384;        // [2 m-blocks][16 n][64 m] bf16              4 KB
-constexpr int OFF_MISC = OFF_B16 + 4096;      // barriers, tmem slot, reductions
-constexpr int SMEM_BYTES = OFF_MISC + 4608 + 1024;  // + slack for manual 1024-byte alignment
-
-// tensor-memory columns
-constexpr uint32_t TM_S = 0, TM_W = 128, TM_U = 256, TM_Y = 320 /* 2 x 64 */, TM_DEN = 448 /* 2 x 16 */, TM_COLS = 512;
+// DKB = Dk / 64 = number of 64-wide key blocks
+template <int DKB>
+struct Lay {
+  // Dk = 64: the latent bank stays in shared memory (TMA-loaded); Dk = 128 has no room for it there and keeps it in
+  // tensor memory as the A operand of the score MMA
+  static constexpr bool Q_SMEM = DKB == 1;
+  static constexpr int OFF_Q = 0;                          // [128 m][64] bf16, K-major                 16 KB or 0
+  static constexpr int OFF_K = Q_SMEM ? 16384 : 0;         // DKB x [128 t][64] bf16                    16 KB each
+  static constexpr int OFF_V = OFF_K + DKB * 16384;        // 2 stages x [128 t][64] bf16               32 KB
+  static constexpr int OFF_E = OFF_V + 2 * 16384;          // 2 x [2 t-blocks][128 m][64 t] bf16        64 KB
+  static constexpr int OFF_R = OFF_E + 2 * 32768;          // 2 x [2 t-blocks][128 m][64 t] bf16        64 KB
+  static constexpr int OFF_U = OFF_R + 2 * 32768;          // [128 m][64 dv] bf16                       16 KB
+  static constexpr int OFF_B16 = OFF_U + 16384;            // [2 m-blocks][16 n][64 m] bf16              4 KB
+  static constexpr int OFF_MISC = OFF_B16 + 4096;          // barriers, tmem slot, reductions
+  static constexpr int SMEM_BYTES = OFF_MISC + 4608 + 1024;  // + slack for manual 1024-byte alignment
+  // tensor-memory columns.  The Y / Den accumulators are double-buffered when the columns allow it (Dk = 64).
+  static constexpr int YB = DKB == 1 ? 2 : 1;
+  static constexpr uint32_t TM_S = 0, TM_W = 128, TM_U = 256, TM_Y = 320, TM_DEN = TM_Y + YB * 64,
+                            TM_Q = TM_DEN + YB * 16 /* Dk / 2 columns of packed bf16 (Dk = 128 only) */;
+  static_assert(TM_Q + (Q_SMEM ? 0 : DKB * 32) <= 512, "tensor memory columns");
+};
+constexpr uint32_t TM_COLS = 512;
 
 struct Misc {
   uint64_t q_full, k_full, k_empty, v_full[2], v_empty[2];
-  uint64_t s_ready, s_free, kap_done, p1_done, u_done, w_ready, p2_done, y_ready;
+  uint64_t s_ready, s_free, kap_done, p1_done, u_done, w_ready, p2_done, y_ready, y_free;
   uint64_t pmax[4], psum[4];  // pair barriers of the two latent half-groups, one per lane quarter
   uint32_t tmem_base;
   volatile int abort_flag;
@@ -99,25 +110,40 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, Mi
   }
 }
 
+// first value column of this CTA's slice (grid.z slices of D columns; a compile-time zero when there is one slice)
+template <int DKB>
+__device__ __forceinline__ int value_col0() {
+  return DKB == 1 ? 0 : (int)blockIdx.z * D;
+}
+
 }  // namespace
 
 // PADDED: fewer than 128 latents (rows padded); the full-width instance carries none of the padding predicates
-template <bool PADDED>
+template <bool PADDED, int DKB>
 __global__ void __launch_bounds__(NTHREADS, 1)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                   const __grid_constant__ CUtensorMap tm_v, const TcParams p) {
+  using L = Lay<DKB>;
+  constexpr int OFF_K = L::OFF_K, OFF_V = L::OFF_V, OFF_E = L::OFF_E, OFF_R = L::OFF_R, OFF_U = L::OFF_U,
+                OFF_B16 = L::OFF_B16, OFF_Q = L::OFF_Q, OFF_MISC = L::OFF_MISC, YB = L::YB;
+  constexpr bool Q_SMEM = L::Q_SMEM;
+  constexpr uint32_t TM_S = L::TM_S, TM_W = L::TM_W, TM_U = L::TM_U, TM_Y = L::TM_Y, TM_DEN = L::TM_DEN, TM_Q = L::TM_Q;
   extern __shared__ uint8_t smem_dyn[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
   Misc* misc = reinterpret_cast<Misc*>(smem + OFF_MISC);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int lane_id = blockIdx.x, seg = blockIdx.y;
+  // Dv = Dk.  This CTA's slice of the value columns starts at blockIdx.z * D (a compile-time zero when Dv = 64); the
+  // roles read it where they need it instead of keeping it in a register across their chunk loops, because the
+  // latent group runs at the register cap and an extra live value there cost 4 % of the kernel's time.
+  constexpr int DV = DKB * D;
   const int b = lane_id / p.H, h = lane_id % p.H;
   const int seg_begin = seg * p.seg_len;
   const int seg_end = min(p.N, seg_begin + p.seg_len);
   const int nchunks = (seg_end - seg_begin + C - 1) / C;
 
   if (tid == 0) {
-    mbar_init(&misc->q_full, 1);
+    mbar_init(&misc->q_full, Q_SMEM ? 1 : 8);
     mbar_init(&misc->k_full, 1);
     mbar_init(&misc->k_empty, 1);
     for (int i = 0; i < 2; ++i) {
@@ -136,6 +162,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     mbar_init(&misc->w_ready, 1);
     mbar_init(&misc->p2_done, 4);
     mbar_init(&misc->y_ready, 1);
+    mbar_init(&misc->y_free, 4);
     misc->abort_flag = 0;
     fence_barrier_init();
   }
@@ -154,30 +181,33 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   if (warp == 13) {
     // ======================================= TMA producer =======================================
     if (lane == 0) {
-      prefetch_tensormap(&tm_q);
       prefetch_tensormap(&tm_k);
       prefetch_tensormap(&tm_v);
-      mbar_arrive_expect_tx(&misc->q_full, 16384);
-      tma_load_3d(smem + OFF_Q, &tm_q, &misc->q_full, 0, 0, h);
+      if (Q_SMEM) {
+        mbar_arrive_expect_tx(&misc->q_full, 16384);
+        tma_load_3d(smem + OFF_Q, &tm_q, &misc->q_full, 0, 0, h);  // rows beyond M read as zero
+      }
+      const int vc0 = value_col0<DKB>();
       for (int i = 0; ok && i < nchunks; ++i) {
         const int t0 = seg_begin + i * C;
         // K tile: free once the score MMA of the previous chunk has run
         if (i > 0 && !(ok = wait_or_abort(&misc->k_empty, (i - 1) & 1, misc))) break;
-        mbar_arrive_expect_tx(&misc->k_full, 16384);
-        tma_load_4d(smem + OFF_K, &tm_k, &misc->k_full, 0, h, t0, b);
+        mbar_arrive_expect_tx(&misc->k_full, DKB * 16384);
+#pragma unroll
+        for (int kb = 0; kb < DKB; ++kb) tma_load_4d(smem + OFF_K + kb * 16384, &tm_k, &misc->k_full, kb * 64, h, t0, b);
         // V tile: stage i & 1, free once chunk i - 2 has been folded into Y
         const int st = i & 1;
         if (i >= 2 && !(ok = wait_or_abort(&misc->v_empty[st], ((i - 2) >> 1) & 1, misc))) break;
         mbar_arrive_expect_tx(&misc->v_full[st], 16384);
-        tma_load_4d(smem + OFF_V + st * 16384, &tm_v, &misc->v_full[st], 0, h, t0, b);
+        tma_load_4d(smem + OFF_V + st * 16384, &tm_v, &misc->v_full[st], vc0, h, t0, b);
       }
     }
   } else if (warp == 12) {
     // ======================================= MMA issuer =======================================
     if (lane == 0) {
-      const uint32_t q_addr = smem_u32(smem + OFF_Q), k_addr = smem_u32(smem + OFF_K);
+      const uint32_t k_addr = smem_u32(smem + OFF_K);
       const uint32_t u_addr = smem_u32(smem + OFF_U), b16_addr = smem_u32(smem + OFF_B16);
-      constexpr uint32_t ID_S = make_idesc_bf16(128, 128, 0, 0);   // Q (K-major) x K_c (K-major)
+      constexpr uint32_t ID_S = make_idesc_bf16(128, 128, 0, 0);   // Q (TMEM) x K_c (K-major)
       constexpr uint32_t ID_U = make_idesc_bf16(128, 64, 0, 1);    // E (K-major) x V (MN-major)
       constexpr uint32_t ID_Y0 = make_idesc_bf16(128, 64, 1, 1);   // R (MN-major) x U_bf16 (MN-major)
       constexpr uint32_t ID_DEN = make_idesc_bf16(128, 16, 1, 0);  // R (MN-major) x d tile (K-major)
@@ -185,7 +215,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       constexpr uint32_t ID_Y1 = make_idesc_bf16(128, 64, 0, 1);   // tril(W) (TMEM) x V (MN-major)
 
       // descriptors are built once; inside the loops only the start-address field (units of 16 bytes) advances
-      const uint64_t dq = make_desc_sw128(q_addr, 16, 1024), dk = make_desc_sw128(k_addr, 16, 1024);
+      const uint64_t dk = make_desc_sw128(k_addr, 16, 1024);
+      const uint64_t dq = make_desc_sw128(smem_u32(smem + OFF_Q), 16, 1024);
       const uint64_t du = make_desc_sw128(u_addr, 1024, 1024), db16 = make_desc_sw128(b16_addr, 16, 1024);
       // second buffer of a double-buffered operand = first + its byte distance (in 16-byte units)
       const uint64_t de_k0 = make_desc_sw128(smem_u32(smem + OFF_E), 16, 1024);
@@ -197,7 +228,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         if (!wait_or_abort(&misc->k_full, i & 1, misc)) return false;
         tc_fence_after_sync();
 #pragma unroll
-        for (int j = 0; j < 4; ++j) mma_ss(tmem + TM_S, dq + (j * 32 >> 4), dk + (j * 32 >> 4), ID_S, j > 0);
+        for (int j = 0; j < 4 * DKB; ++j) {
+          const uint64_t dkj = dk + (((j >> 2) * 16384 + (j & 3) * 32) >> 4);
+          if (Q_SMEM) mma_ss(tmem + TM_S, dq + (j * 32 >> 4), dkj, ID_S, j > 0);
+          else mma_ts(tmem + TM_S, tmem + TM_Q + j * 8, dkj, ID_S, j > 0);
+        }
         tc_commit(&misc->s_ready);
         tc_commit(&misc->k_empty);
         return true;
@@ -207,13 +242,15 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         tc_fence_after_sync();
         const uint64_t dv = dv_mn0 + (uint64_t)((i & 1) * (16384 >> 4));
 #pragma unroll
-        for (int j = 0; j < 8; ++j) mma_ts(tmem + TM_Y + (i & 1) * 64, tmem + TM_W + j * 8, dv + (j * 2048 >> 4), ID_Y1, 1);
+        for (int j = 0; j < 8; ++j)
+          mma_ts(tmem + TM_Y + (i & (YB - 1)) * 64, tmem + TM_W + j * 8, dv + (j * 2048 >> 4), ID_Y1, 1);
         tc_commit(&misc->y_ready);
         tc_commit(&misc->v_empty[i & 1]);
         return true;
       };
 
-      ok = wait_or_abort(&misc->q_full, 0, misc);
+      ok = wait_or_abort(&misc->q_full, 0, misc);  // the latent bank is in place
+      tc_fence_after_sync();
       if (ok && nchunks > 0) ok = issue_scores(0);
       for (int i = 0; ok && i < nchunks; ++i) {
         const uint32_t par = i & 1;
@@ -238,12 +275,16 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         for (int j = 0; j < 8; ++j) mma_ss(tmem + TM_W, drm + (j * 2048 >> 4), dem + (j * 2048 >> 4), ID_W, j > 0);
         tc_commit(&misc->w_ready);
         TC_TRACE(2, i, 5);
-        // Y = R^T U_bf16, Den0 = R^T d
+        // Y = R^T U_bf16, Den0 = R^T d.  Single-buffered accumulators: the token group must have read chunk i - 1.
+        if (YB == 1 && i >= 1) {
+          if (!(ok = wait_or_abort(&misc->y_free, (i - 1) & 1, misc))) break;
+          tc_fence_after_sync();
+        }
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          mma_ss(tmem + TM_Y + (i & 1) * 64, drm + (j * 2048 >> 4), du + (j * 2048 >> 4), ID_Y0, j > 0);
-          mma_ss(tmem + TM_DEN + (i & 1) * 16, drm + (j * 2048 >> 4), db16 + (((j >> 2) * 2048 + (j & 3) * 32) >> 4), ID_DEN,
-                 j > 0);
+          mma_ss(tmem + TM_Y + (i & (YB - 1)) * 64, drm + (j * 2048 >> 4), du + (j * 2048 >> 4), ID_Y0, j > 0);
+          mma_ss(tmem + TM_DEN + (i & (YB - 1)) * 16, drm + (j * 2048 >> 4),
+                 db16 + (((j >> 2) * 2048 + (j & 3) * 32) >> 4), ID_DEN, j > 0);
         }
         TC_TRACE(2, i, 6);
         // U += E V_c  (k = tokens of the chunk)
@@ -265,19 +306,36 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     const int m = q * 32 + lane;
     const float sc2 = p.scale * kLog2e;
     const int64_t st_idx = (int64_t)lane_id * p.in_lane_stride + (int64_t)seg * p.in_seg_stride;
-    // Fewer than 128 latents: the missing rows are padding (Q rows read as zero by the TMA).  A padding latent keeps
-    // a fixed frame 0 and a denominator of 1, its E is forced to zero, so it contributes nothing anywhere.
+    // Fewer than 128 latents: the missing rows are padding (zero rows of Q).  A padding latent gets the frame +inf,
+    // so its E = exp2(0 - inf) is exactly zero without any predicate in the element loops, and a denominator of 1.
     const bool live = !PADDED || m < p.M;
-    constexpr bool padded = PADDED;
     float c2 = !live ? 0.f : (p.in_m ? p.in_m[st_idx * p.M + m] * kLog2e : -INFINITY);  // running max, log2 units
     float dsum = !live ? 1.f : (p.in_d ? p.in_d[st_idx * p.M + m] : 0.f);  // denominator in frame c2
     float d_prev = 0.f;                                  // denominator before the chunk in flight, in its frame
+    if constexpr (!Q_SMEM) {
+      // latent bank row m -> tensor memory as packed bf16 (element k in column k / 2); each half-group thread
+      // writes half of the row.  Rows beyond M are zero.
+      uint32_t r[DKB * 16];
+      const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.q) +
+                                                        (int64_t)h * p.q_stride_h + (int64_t)(live ? m : 0) * p.q_stride_m +
+                                                        hf * (DKB * 32));
+#pragma unroll
+      for (int i = 0; i < DKB * 4; ++i) {
+        const uint4 x = live ? __ldg(src + i) : make_uint4(0, 0, 0, 0);
+        r[4 * i] = x.x; r[4 * i + 1] = x.y; r[4 * i + 2] = x.z; r[4 * i + 3] = x.w;
+      }
+      static_assert(Q_SMEM || DKB == 2, "store width");
+      tmem_st32(tl + TM_Q + hf * 32, r);
+      tmem_wait_st();
+      tc_fence_before_sync();
+      warp_arrive(&misc->q_full, lane);
+    }
     {
       // carry-in numerator -> tensor memory, 32 value columns per half
       uint32_t r[32];
 #pragma unroll
       for (int i = 0; i < 32; ++i)
-        r[i] = (p.in_u && live) ? __float_as_uint(p.in_u[(st_idx * p.M + m) * D + hf * 32 + i]) : 0u;
+        r[i] = (p.in_u && live) ? __float_as_uint(p.in_u[(st_idx * p.M + m) * DV + value_col0<DKB>() + hf * 32 + i]) : 0u;
       tmem_st32(tl + TM_U + hf * 32, r);
       tmem_wait_st();
     }
@@ -336,7 +394,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         dsum = d_prev + (misc->xsum[par ^ 1][0][m] + misc->xsum[par ^ 1][1][m]);
         c_new = fmaxf(c2, fmaxf(misc->xmax[par ^ 1][0][m], misc->xmax[par ^ 1][1][m]));
       }
-      const float alpha = ex2_approx(c2 - c_new);  // 0 when the old state is empty
+      float alpha = ex2_approx(c2 - c_new);  // 0 when the old state is empty
       // kappa: common frame of the decode weights = max over latents of the running max.  Chunk 0 synchronises;
       // later chunks use the value published during the previous chunk (one chunk stale, which only changes a
       // per-token scale that cancels in y).
@@ -351,12 +409,18 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       const float* wsrc = misc->wmax[i == 0 ? 0 : ((i - 1) & 1)];
       const float kappa = fmaxf(fmaxf(wsrc[0], wsrc[1]), fmaxf(wsrc[2], wsrc[3]));
       if (tid == 0) TC_TRACE(0, i, 1);
-      const float a_m = ex2_approx(c_new - kappa);
-      const float d_carry = dsum * alpha;  // denominator of the carried state in the new frame
+      float a_m = ex2_approx(c_new - kappa);
+      float d_carry = dsum * alpha;  // denominator of the carried state in the new frame
+      if (PADDED && !live) {
+        c_new = INFINITY;
+        alpha = 1.0f;
+        a_m = 0.f;
+        d_carry = 1.0f;
+      }
       c2 = c_new;
       // phase a: E for the 64 tokens of this half (in place of the scores), their sum, E operand rows
       float tot0 = 0.f, tot1 = 0.f;
-      if (nvalid == C && !padded) {
+      if (nvalid == C) {
 #pragma unroll
         for (int k = 0; k < 32; ++k) {
           const float e0 = ex2_approx(__uint_as_float(ra[k]) * sc2 - c_new);
@@ -369,8 +433,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       } else {
 #pragma unroll
         for (int k = 0; k < 32; ++k) {
-          const float e0 = (live && tok0 + k < nvalid) ? ex2_approx(__uint_as_float(ra[k]) * sc2 - c_new) : 0.f;
-          const float e1 = (live && tok0 + 32 + k < nvalid) ? ex2_approx(__uint_as_float(rb[k]) * sc2 - c_new) : 0.f;
+          const float e0 = (tok0 + k < nvalid) ? ex2_approx(__uint_as_float(ra[k]) * sc2 - c_new) : 0.f;
+          const float e1 = (tok0 + 32 + k < nvalid) ? ex2_approx(__uint_as_float(rb[k]) * sc2 - c_new) : 0.f;
           ra[k] = __float_as_uint(e0);
           rb[k] = __float_as_uint(e1);
           tot0 += e0;
@@ -470,7 +534,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       tc_fence_after_sync();
       if (ok) {
         const int64_t so = (int64_t)lane_id * p.out_lane_stride + (int64_t)seg * p.out_seg_stride;
-        if (hf == 0 && live) {
+        if (hf == 0 && live && blockIdx.z == 0) {
           p.out_m[so * p.M + m] = c2 * kLn2;
           p.out_d[so * p.M + m] = dsum * fin;
         }
@@ -478,7 +542,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         tmem_ld32(tl + TM_U + hf * 32, r);
         tmem_wait_ld();
         tmem_fence_regs(r);
-        float4* dst = reinterpret_cast<float4*>(p.out_u + (so * p.M + (live ? m : 0)) * D + hf * 32);
+        float4* dst = reinterpret_cast<float4*>(p.out_u + (so * p.M + (live ? m : 0)) * DV + value_col0<DKB>() + hf * 32);
 #pragma unroll
         for (int k = 0; k < 8; ++k)
           if (live) dst[k] = make_float4(__uint_as_float(r[4 * k]) * fin, __uint_as_float(r[4 * k + 1]) * fin,
@@ -490,6 +554,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     const int wq = warp - 8;  // lane quarter
     const uint32_t tl = tmem + ((uint32_t)(wq * 32) << 16);
     const int tt = wq * 32 + lane;  // token index inside the chunk
+    __nv_bfloat16* const y_lane = reinterpret_cast<__nv_bfloat16*>(p.y) + (int64_t)b * p.y_stride_b +
+                                  (int64_t)h * p.y_stride_h + value_col0<DKB>();
     for (int i = 0; ok && i < nchunks; ++i) {
       const uint32_t par = i & 1;
       const int t0 = seg_begin + i * C;
@@ -530,7 +596,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       tc_fence_after_sync();
       if (tid == 256) TC_TRACE(1, i, 2);
       uint32_t den0;
-      tmem_ld1(tl + TM_DEN + (i & 1) * 16, den0);
+      tmem_ld1(tl + TM_DEN + (i & (YB - 1)) * 16, den0);
       tmem_wait_ld();
       const float den = __uint_as_float(den0) + rowsum;
       // outside the numeric domain of this path (scores of a token more than ~80 nats below the running maxima):
@@ -540,11 +606,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
         uint32_t r[32];
-        tmem_ld32(tl + TM_Y + (i & 1) * 64 + half * 32, r);
+        tmem_ld32(tl + TM_Y + (i & (YB - 1)) * 64 + half * 32, r);
         tmem_wait_ld();
         if (p.y != nullptr && tt < nvalid) {
-          uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.y) + (int64_t)b * p.y_stride_b +
-                                                (int64_t)(t0 + tt) * p.y_stride_n + (int64_t)h * p.y_stride_h + half * 32);
+          uint4* dst = reinterpret_cast<uint4*>(y_lane + (int64_t)(t0 + tt) * p.y_stride_n + half * 32);
 #pragma unroll
           for (int ch = 0; ch < 4; ++ch) {
             uint4 v;
@@ -557,6 +622,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         }
       }
       tc_fence_before_sync();
+      if (YB == 1) warp_arrive(&misc->y_free, lane);
       if (tid == 256) TC_TRACE(1, i, 3);
     }
   }
@@ -612,38 +678,54 @@ bool make_map(CUtensorMap* map, const void* base, int rank, const uint64_t* dims
 }  // namespace
 
 bool prefill_tc_supported(const flare_fwd_args_t* a) {
-  return a->dtype == FLARE_BF16 && a->variant == FLARE_SOFTMAX && a->block_size == 1 && a->M <= M && a->M >= 16 && (a->M % 16) == 0 && a->Dk == D &&
-         a->Dv == D && a->q_dec == nullptr && a->k_dec == nullptr && a->mask == nullptr && a->lse_dec == nullptr &&
-         a->q_stride_m == D && a->N >= 1;
+  return a->dtype == FLARE_BF16 && a->variant == FLARE_SOFTMAX && a->block_size == 1 && a->M <= M && a->M >= 16 &&
+         (a->M % 16) == 0 && (a->Dk == 64 || a->Dk == 128) && a->Dv == a->Dk && a->q_dec == nullptr &&
+         a->k_dec == nullptr && a->mask == nullptr && a->lse_dec == nullptr && a->N >= 1;
 }
+
+namespace {
+
+template <bool PADDED, int DKB>
+int launch_instance(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const TcParams& p, dim3 grid,
+                    cudaStream_t stream) {
+  static bool attr_set = false;
+  auto kern = prefill_tc_kernel<PADDED, DKB>;
+  if (!attr_set) {
+    FLARE_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Lay<DKB>::SMEM_BYTES));
+    attr_set = true;
+  }
+  kern<<<grid, NTHREADS, Lay<DKB>::SMEM_BYTES, stream>>>(tq, tk, tv, p);
+  FLARE_CUDA_CHECK(cudaGetLastError());
+  return FLARE_OK;
+}
+
+}  // namespace
+
+int prefill_tc_ctas_per_lane(const flare_fwd_args_t* a) { return a->Dv / D; }
 
 int launch_prefill_tc(const flare_fwd_args_t* a, const TcParams& p, int nseg_grid, cudaStream_t stream) {
   CUtensorMap tq, tk, tv;
   {
-    const uint64_t dims[3] = {(uint64_t)D, (uint64_t)a->M, (uint64_t)a->H};  // rows beyond M read as zero
+    // latent bank (used by the Dk = 64 instances only; any valid map otherwise)
+    const uint64_t dims[3] = {(uint64_t)a->Dk, (uint64_t)a->M, (uint64_t)a->H};
     const int64_t str[2] = {a->q_stride_m, a->q_stride_h};
     const uint32_t box[3] = {64, 128, 1};
     if (!make_map(&tq, a->q, 3, dims, str, box)) return FLARE_ERR_CUDA;
   }
   {
-    const uint64_t dims[4] = {(uint64_t)D, (uint64_t)a->H, (uint64_t)a->N, (uint64_t)a->B};
+    const uint64_t dimk[4] = {(uint64_t)a->Dk, (uint64_t)a->H, (uint64_t)a->N, (uint64_t)a->B};
+    const uint64_t dimv[4] = {(uint64_t)a->Dv, (uint64_t)a->H, (uint64_t)a->N, (uint64_t)a->B};
     const uint32_t box[4] = {64, 1, 128, 1};
     const int64_t strk[3] = {a->k_stride_h, a->k_stride_n, a->k_stride_b};
     const int64_t strv[3] = {a->v_stride_h, a->v_stride_n, a->v_stride_b};
-    if (!make_map(&tk, a->k, 4, dims, strk, box)) return FLARE_ERR_CUDA;
-    if (!make_map(&tv, a->v, 4, dims, strv, box)) return FLARE_ERR_CUDA;
+    if (!make_map(&tk, a->k, 4, dimk, strk, box)) return FLARE_ERR_CUDA;
+    if (!make_map(&tv, a->v, 4, dimv, strv, box)) return FLARE_ERR_CUDA;
   }
-  static bool attr_set = false;
-  if (!attr_set) {
-    FLARE_CUDA_CHECK(cudaFuncSetAttribute(prefill_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-    FLARE_CUDA_CHECK(cudaFuncSetAttribute(prefill_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-    attr_set = true;
-  }
-  dim3 grid(a->B * a->H, nseg_grid);
-  if (a->M == M) prefill_tc_kernel<false><<<grid, NTHREADS, SMEM_BYTES, stream>>>(tq, tk, tv, p);
-  else prefill_tc_kernel<true><<<grid, NTHREADS, SMEM_BYTES, stream>>>(tq, tk, tv, p);
-  FLARE_CUDA_CHECK(cudaGetLastError());
-  return FLARE_OK;
+  const dim3 grid(a->B * a->H, nseg_grid, a->Dv / D);
+  const bool padded = a->M != M;
+  if (a->Dk == 64)
+    return padded ? launch_instance<true, 1>(tq, tk, tv, p, grid, stream) : launch_instance<false, 1>(tq, tk, tv, p, grid, stream);
+  return padded ? launch_instance<true, 2>(tq, tk, tv, p, grid, stream) : launch_instance<false, 2>(tq, tk, tv, p, grid, stream);
 }
 
 int prefill_tc_error_flag(int* host_value, bool reset) {

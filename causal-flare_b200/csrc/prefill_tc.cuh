@@ -5,10 +5,13 @@
 namespace flare {
 
 struct TcParams {
-  void* y;  // bf16 [B, N, H, 64] (strided) or null
+  void* y;  // bf16 [B, N, H, Dv] (strided) or null
   int64_t y_stride_b, y_stride_n, y_stride_h;
+  const void* q;  // bf16 latent bank [H, M, Dk]
+  int64_t q_stride_h, q_stride_m;
   int N, H;
-  int M;  // latents, <= 128
+  int M;   // latents, <= 128
+  int Dv;  // value width (64 or 128); each CTA handles 64 columns
   float scale;
   int seg_len;
   // carry-in / carry-out states, indexed lane * lane_stride + seg * seg_stride (in states)
@@ -22,6 +25,8 @@ struct TcParams {
 };
 
 bool prefill_tc_supported(const flare_fwd_args_t* a);
+// CTAs the kernel launches per (lane, segment)
+int prefill_tc_ctas_per_lane(const flare_fwd_args_t* a);
 // launches segments 0 .. nseg_grid-1
 int launch_prefill_tc(const flare_fwd_args_t* a, const TcParams& p, int nseg_grid, cudaStream_t stream);
 // reads (and optionally clears) the device-side error flag of the tensor-core kernels; synchronises

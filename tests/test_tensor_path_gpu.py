@@ -115,3 +115,36 @@ def test_tensor_path_fewer_latents(Ml):
     assert_close(st["m"], st_ref["m"], what="m", atol=1e-4, rtol=1e-4)
     assert_close(st["d"], st_ref["d"], what="d", atol=1e-3, rtol=3e-3)
     assert orc.rel_l2(st["u"].cpu(), st_ref["u"]) < 3e-3
+
+
+@pytest.mark.parametrize("Ml, B, N, H", [(128, 1, 256, 1), (128, 2, 700, 2), (64, 2, 520, 3), (128, 1, 2048, 1)])
+def test_tensor_path_wide_heads(Ml, B, N, H):
+    # Dk = Dv = 128: two CTAs per lane, each with 64 value columns, latent bank in tensor memory
+    Dw = 128
+    q, k, v = orc.make_inputs(B, N, H, Ml, Dw, seed0=21, dtype=torch.bfloat16)
+    sc = Dw ** -0.5
+    ref, st_ref = orc.ar_forward(q, k, v, scale=sc, return_state=True)
+    qc, kc, vc = to_dev(q, k, v)
+    assert uses_tensor_path(qc, kc, vc)
+    y, st, _, _ = run(qc, kc, vc, _lib.PATH_TENSOR, want_state=True, scale=sc)
+    assert_bf16_gate(y, ref, f"tensor path D=128 M={Ml} N={N}")
+    assert_close(st["m"], st_ref["m"], what="m", atol=1e-4, rtol=1e-4)
+    assert_close(st["d"], st_ref["d"], what="d", atol=1e-3, rtol=2e-3)
+    assert orc.rel_l2(st["u"].cpu(), st_ref["u"]) < 3e-3
+    # carry-in: second half continued from the first half's state
+    h = (N // 2) // 16 * 16
+    _, st_a, _, _ = run(qc, kc[:, :h], vc[:, :h], _lib.PATH_TENSOR, want_state=True, scale=sc)
+    y_b, _, _, _ = run(qc, kc[:, h:], vc[:, h:], _lib.PATH_TENSOR, state_in=st_a, scale=sc)
+    assert_bf16_gate(y_b, ref[:, h:], "D=128 carry-in")
+
+
+def test_wide_heads_training_shape_vs_exact():
+    # B=4, N=4096, H=16, M=64, D=128 (training shape of the benchmark set): both CUDA paths must agree
+    B, N, H, Ml, Dw = 4, 4096, 16, 64, 128
+    g = torch.Generator(device="cuda").manual_seed(1)
+    q = torch.randn(H, Ml, Dw, generator=g, device="cuda").bfloat16()
+    k = torch.randn(B, N, H, Dw, generator=g, device="cuda").bfloat16()
+    v = torch.randn(B, N, H, Dw, generator=g, device="cuda").bfloat16()
+    y_t, _, _, _ = run(q, k, v, _lib.PATH_TENSOR, scale=Dw ** -0.5)
+    y_e, _, _, _ = run(q, k, v, _lib.PATH_EXACT, scale=Dw ** -0.5)
+    assert_bf16_gate(y_t, y_e.float(), "tensor vs exact, D=128 training shape")
