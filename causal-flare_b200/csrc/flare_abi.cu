@@ -86,10 +86,11 @@ struct FwdPlan {
   int seg_len;
   size_t state_floats;  // floats per state: 2M + M*Dv
   size_t ws_bytes;
+  size_t part_off, part_bytes;  // tensor path with more than 128 latents: partial read-outs behind the segment states
 };
 
 FwdPlan plan_forward(const flare_fwd_args_t* a) {
-  FwdPlan pl{false, 1, a->N > 0 ? a->N : 1, 0, 0};
+  FwdPlan pl{false, 1, a->N > 0 ? a->N : 1, 0, 0, 0, 0};
   if (a->B == 0 || a->N == 0) return pl;
   const int64_t lanes = (int64_t)a->B * a->H;
   pl.state_floats = (size_t)2 * a->M + (size_t)a->M * a->Dv;
@@ -110,6 +111,9 @@ FwdPlan plan_forward(const flare_fwd_args_t* a) {
     pl.nseg = (a->N + seg_len - 1) / seg_len;
     pl.seg_len = seg_len;
     pl.ws_bytes = pl.nseg > 1 ? align_up((size_t)lanes * pl.nseg * pl.state_floats * 4, 256) : 0;
+    pl.part_off = pl.ws_bytes;
+    pl.part_bytes = a->y != nullptr ? align_up(prefill_tc_partial_bytes(a), 256) : 0;
+    pl.ws_bytes += pl.part_bytes;
     return pl;
   }
   const int dd = walk_exact_dd(a->M, a->Dv);
@@ -162,6 +166,10 @@ int launch_walk(const flare_fwd_args_t* a, const FwdPlan& pl, const WalkParams& 
   t.out_m = w.out_m; t.out_d = w.out_d; t.out_u = w.out_u;
   t.out_lane_stride = w.out_lane_stride; t.out_seg_stride = w.out_seg_stride;
   t.out_mode = w.out_mode; t.nseg_total = w.nseg_total;
+  if (pl.part_bytes > 0 && t.y != nullptr) {
+    t.part_y = reinterpret_cast<float*>(reinterpret_cast<char*>(a->workspace) + pl.part_off);
+    t.part_lw = t.part_y + (size_t)prefill_tc_partial_bytes(a) / sizeof(float) / (a->Dv + 1) * a->Dv;
+  }
   t.trace = g_trace;
   return launch_prefill_tc(a, t, nseg_grid, stream);
 }
@@ -184,7 +192,7 @@ int forward_run(const flare_fwd_args_t* a, cudaStream_t stream) {
     w.out_mode = have_out ? 2 : 0;
     w.write_y = a->y != nullptr;
     w.lse_dec = a->lse_dec; w.lse_enc = a->lse_enc;
-    g_last_launches = 1;
+    g_last_launches = 1 + ((pl.part_bytes > 0 && w.write_y) ? 1 : 0);  // + merge of the latent groups
     DominantKernelTimer timer(stream);
     return launch_walk(a, pl, w, 1, stream);
   }
@@ -216,7 +224,7 @@ int forward_run(const flare_fwd_args_t* a, cudaStream_t stream) {
   w.lse_dec = a->lse_dec; w.lse_enc = a->lse_enc;
   g_last_launches = 2;
   if (!w.write_y && !have_out) return FLARE_OK;
-  g_last_launches = 3;
+  g_last_launches = 3 + ((pl.part_bytes > 0 && w.write_y) ? 1 : 0);
   DominantKernelTimer timer(stream);
   return launch_walk(a, pl, w, pl.nseg, stream);
 }

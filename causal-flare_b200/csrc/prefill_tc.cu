@@ -1,9 +1,10 @@
 // Tensor-core (tcgen05 + TMEM + TMA) chunked causal prefill for the softmax encoder, bf16 operands, fp32
-// accumulation and statistics.  Shape class: M <= 128 latents (multiple of 16, padded to 128 rows), Dk = Dv = 64 or 128,
-// shared decode weights, no mask.
+// accumulation and statistics.  Shape class: M <= 512 latents (multiple of 16, in groups of 128 rows, the last one
+// padded), Dk = Dv = 64 or 128, shared decode weights, no mask.
 //
-// One CTA owns a (batch, head, sequence segment, slice of 64 value columns) and walks its chunks of C = 128 tokens in
-// order, carrying the latent state on chip: U [128 latents x 64] fp32 in tensor memory, the latent bank Q as packed
+// One CTA owns a (batch, head, sequence segment, slice of 64 value columns, group of 128 latents) and walks its chunks
+// of C = 128 tokens in order.  With more than one latent group every CTA emits a partial read-out (normalised over its
+// own latents, fp32) and the log2 of its weight mass per token; a small kernel merges the groups.  The CTA keeps carrying the latent state on chip: U [128 latents x 64] fp32 in tensor memory, the latent bank Q as packed
 // bf16 in tensor memory (A operand of the score MMA), running max c and denominator d per latent
 // in registers of the thread that owns the latent (TMEM lane = thread).  Per chunk, with the frame c_m = running
 // max after the chunk and kappa = max_m c_m:
@@ -76,6 +77,7 @@ struct Misc {
   uint32_t tmem_base;
   volatile int abort_flag;
   float wmax[2][4];
+  float kap[2];  // decode frame of the chunk in flight, for the token group (latent-group split only)
   float xmax[2][2][128], xsum[2][2][128];  // [chunk parity][half][latent]
 };
 
@@ -110,16 +112,22 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, Mi
   }
 }
 
-// first value column of this CTA's slice (grid.z slices of D columns; a compile-time zero when there is one slice)
-template <int DKB>
+// grid.z = latent group * DKB + value slice.  First value column of this CTA's slice (a compile-time zero when there
+// is one slice) and first latent of its group (zero without the latent split).
+template <int DKB, bool SPLIT>
 __device__ __forceinline__ int value_col0() {
-  return DKB == 1 ? 0 : (int)blockIdx.z * D;
+  return DKB == 1 ? 0 : (SPLIT ? (int)blockIdx.z % DKB : (int)blockIdx.z) * D;
+}
+template <int DKB, bool SPLIT>
+__device__ __forceinline__ int latent0() {
+  return SPLIT ? ((int)blockIdx.z / DKB) * M : 0;
 }
 
 }  // namespace
 
 // PADDED: fewer than 128 latents (rows padded); the full-width instance carries none of the padding predicates
-template <bool PADDED, int DKB>
+// SPLIT: more than 128 latents, partial read-outs
+template <bool PADDED, int DKB, bool SPLIT>
 __global__ void __launch_bounds__(NTHREADS, 1)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                   const __grid_constant__ CUtensorMap tm_v, const TcParams p) {
@@ -185,9 +193,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       prefetch_tensormap(&tm_v);
       if (Q_SMEM) {
         mbar_arrive_expect_tx(&misc->q_full, 16384);
-        tma_load_3d(smem + OFF_Q, &tm_q, &misc->q_full, 0, 0, h);  // rows beyond M read as zero
+        tma_load_3d(smem + OFF_Q, &tm_q, &misc->q_full, 0, latent0<DKB, SPLIT>(), h);  // rows beyond M read as zero
       }
-      const int vc0 = value_col0<DKB>();
+      const int vc0 = value_col0<DKB, SPLIT>();
       for (int i = 0; ok && i < nchunks; ++i) {
         const int t0 = seg_begin + i * C;
         // K tile: free once the score MMA of the previous chunk has run
@@ -308,16 +316,23 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     const int64_t st_idx = (int64_t)lane_id * p.in_lane_stride + (int64_t)seg * p.in_seg_stride;
     // Fewer than 128 latents: the missing rows are padding (zero rows of Q).  A padding latent gets the frame +inf,
     // so its E = exp2(0 - inf) is exactly zero without any predicate in the element loops, and a denominator of 1.
-    const bool live = !PADDED || m < p.M;
-    float c2 = !live ? 0.f : (p.in_m ? p.in_m[st_idx * p.M + m] * kLog2e : -INFINITY);  // running max, log2 units
-    float dsum = !live ? 1.f : (p.in_d ? p.in_d[st_idx * p.M + m] : 0.f);  // denominator in frame c2
+    const bool live = !PADDED || latent0<DKB, SPLIT>() + m < p.M;
+    float c2 = -INFINITY, dsum = 0.f;  // running max (log2 units) and the denominator in that frame
+    if (!live) {
+      c2 = 0.f;
+      dsum = 1.f;
+    } else if (p.in_m != nullptr) {
+      c2 = p.in_m[st_idx * p.M + latent0<DKB, SPLIT>() + m] * kLog2e;
+      dsum = p.in_d[st_idx * p.M + latent0<DKB, SPLIT>() + m];
+    }
     float d_prev = 0.f;                                  // denominator before the chunk in flight, in its frame
     if constexpr (!Q_SMEM) {
       // latent bank row m -> tensor memory as packed bf16 (element k in column k / 2); each half-group thread
       // writes half of the row.  Rows beyond M are zero.
       uint32_t r[DKB * 16];
       const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.q) +
-                                                        (int64_t)h * p.q_stride_h + (int64_t)(live ? m : 0) * p.q_stride_m +
+                                                        (int64_t)h * p.q_stride_h +
+                                                        (int64_t)(live ? latent0<DKB, SPLIT>() + m : 0) * p.q_stride_m +
                                                         hf * (DKB * 32));
 #pragma unroll
       for (int i = 0; i < DKB * 4; ++i) {
@@ -335,7 +350,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       uint32_t r[32];
 #pragma unroll
       for (int i = 0; i < 32; ++i)
-        r[i] = (p.in_u && live) ? __float_as_uint(p.in_u[(st_idx * p.M + m) * DV + value_col0<DKB>() + hf * 32 + i]) : 0u;
+        r[i] = (p.in_u && live) ? __float_as_uint(p.in_u[(st_idx * p.M + latent0<DKB, SPLIT>() + m) * DV +
+                                                         value_col0<DKB, SPLIT>() + hf * 32 + i])
+                                : 0u;
       tmem_st32(tl + TM_U + hf * 32, r);
       tmem_wait_st();
     }
@@ -408,6 +425,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       }
       const float* wsrc = misc->wmax[i == 0 ? 0 : ((i - 1) & 1)];
       const float kappa = fmaxf(fmaxf(wsrc[0], wsrc[1]), fmaxf(wsrc[2], wsrc[3]));
+      if (SPLIT && tid == 0) misc->kap[par] = kappa;  // ordered before the token group's read by the barrier chain
       if (tid == 0) TC_TRACE(0, i, 1);
       float a_m = ex2_approx(c_new - kappa);
       float d_carry = dsum * alpha;  // denominator of the carried state in the new frame
@@ -534,15 +552,17 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       tc_fence_after_sync();
       if (ok) {
         const int64_t so = (int64_t)lane_id * p.out_lane_stride + (int64_t)seg * p.out_seg_stride;
-        if (hf == 0 && live && blockIdx.z == 0) {
-          p.out_m[so * p.M + m] = c2 * kLn2;
-          p.out_d[so * p.M + m] = dsum * fin;
+        const int mg = latent0<DKB, SPLIT>() + m;  // latent index in the whole bank
+        if (hf == 0 && live && value_col0<DKB, SPLIT>() == 0) {
+          p.out_m[so * p.M + mg] = c2 * kLn2;
+          p.out_d[so * p.M + mg] = dsum * fin;
         }
         uint32_t r[32];
         tmem_ld32(tl + TM_U + hf * 32, r);
         tmem_wait_ld();
         tmem_fence_regs(r);
-        float4* dst = reinterpret_cast<float4*>(p.out_u + (so * p.M + (live ? m : 0)) * DV + value_col0<DKB>() + hf * 32);
+        float4* dst =
+            reinterpret_cast<float4*>(p.out_u + (so * p.M + (live ? mg : 0)) * DV + value_col0<DKB, SPLIT>() + hf * 32);
 #pragma unroll
         for (int k = 0; k < 8; ++k)
           if (live) dst[k] = make_float4(__uint_as_float(r[4 * k]) * fin, __uint_as_float(r[4 * k + 1]) * fin,
@@ -555,7 +575,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     const uint32_t tl = tmem + ((uint32_t)(wq * 32) << 16);
     const int tt = wq * 32 + lane;  // token index inside the chunk
     __nv_bfloat16* const y_lane = reinterpret_cast<__nv_bfloat16*>(p.y) + (int64_t)b * p.y_stride_b +
-                                  (int64_t)h * p.y_stride_h + value_col0<DKB>();
+                                  (int64_t)h * p.y_stride_h + value_col0<DKB, SPLIT>();
+    // latent-group split: dense fp32 partials [group][B][N][H][DV] and log2 weight masses [group][B][N][H]
+    const int64_t part_row0 = SPLIT ? (((int64_t)(blockIdx.z / DKB) * (gridDim.x / p.H) + b) * p.N) : 0;
     for (int i = 0; ok && i < nchunks; ++i) {
       const uint32_t par = i & 1;
       const int t0 = seg_begin + i * C;
@@ -599,16 +621,29 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       tmem_ld1(tl + TM_DEN + (i & (YB - 1)) * 16, den0);
       tmem_wait_ld();
       const float den = __uint_as_float(den0) + rowsum;
+      const bool den_ok = den > 0.f && den < INFINITY;
       // outside the numeric domain of this path (scores of a token more than ~80 nats below the running maxima):
-      // every weight underflowed.  Flag it; the exact path has no such limit.
-      if (tt < nvalid && !(den > 0.f && den < INFINITY)) atomicOr(&g_tc_error, 2);
-      const float inv = 1.0f / den;
+      // every weight underflowed.  Flag it; the exact path has no such limit.  With a latent-group split one group
+      // may legitimately carry no weight; the merge kernel flags a token only when every group is empty.
+      if (!SPLIT && tt < nvalid && !den_ok) atomicOr(&g_tc_error, 2);
+      const float inv = (SPLIT && !den_ok) ? 0.f : 1.0f / den;
+      if (SPLIT && p.part_y != nullptr && tt < nvalid && value_col0<DKB, SPLIT>() == 0)
+        p.part_lw[(part_row0 + t0 + tt) * p.H + h] = den_ok ? misc->kap[par] + __log2f(den) : -INFINITY;
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
         uint32_t r[32];
         tmem_ld32(tl + TM_Y + (i & (YB - 1)) * 64 + half * 32, r);
         tmem_wait_ld();
-        if (p.y != nullptr && tt < nvalid) {
+        if (SPLIT) {
+          if (p.part_y != nullptr && tt < nvalid) {
+            float4* dst = reinterpret_cast<float4*>(p.part_y + ((part_row0 + t0 + tt) * p.H + h) * DV +
+                                                    value_col0<DKB, SPLIT>() + half * 32);
+#pragma unroll
+            for (int k = 0; k < 8; ++k)
+              dst[k] = make_float4(__uint_as_float(r[4 * k]) * inv, __uint_as_float(r[4 * k + 1]) * inv,
+                                   __uint_as_float(r[4 * k + 2]) * inv, __uint_as_float(r[4 * k + 3]) * inv);
+          }
+        } else if (p.y != nullptr && tt < nvalid) {
           uint4* dst = reinterpret_cast<uint4*>(y_lane + (int64_t)(t0 + tt) * p.y_stride_n + half * 32);
 #pragma unroll
           for (int ch = 0; ch < 4; ++ch) {
@@ -678,18 +713,63 @@ bool make_map(CUtensorMap* map, const void* base, int rank, const uint64_t* dims
 }  // namespace
 
 bool prefill_tc_supported(const flare_fwd_args_t* a) {
-  return a->dtype == FLARE_BF16 && a->variant == FLARE_SOFTMAX && a->block_size == 1 && a->M <= M && a->M >= 16 &&
+  return a->dtype == FLARE_BF16 && a->variant == FLARE_SOFTMAX && a->block_size == 1 && a->M <= 4 * M && a->M >= 16 &&
          (a->M % 16) == 0 && (a->Dk == 64 || a->Dk == 128) && a->Dv == a->Dk && a->q_dec == nullptr &&
          a->k_dec == nullptr && a->mask == nullptr && a->lse_dec == nullptr && a->N >= 1;
 }
 
+// Merge of the latent groups' partial read-outs: y = sum_g w_g y_g / sum_g w_g with w_g = exp2(lw_g - max lw).
+// One thread per (token, head, 8 value columns).
+__global__ void __launch_bounds__(256) tc_merge_groups_kernel(const float* __restrict__ part_y, const float* __restrict__ part_lw,
+                                                               int groups, int64_t rows /* B*N*H */, int N, int H, int dv,
+                                                               __nv_bfloat16* y, int64_t y_stride_b, int64_t y_stride_n,
+                                                               int64_t y_stride_h) {
+  const int cols8 = dv >> 3;
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= rows * cols8) return;
+  const int64_t row = idx / cols8;
+  const int c8 = (int)(idx % cols8);
+  float lw[4], mx = -INFINITY;
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    lw[g] = g < groups ? part_lw[g * rows + row] : -INFINITY;
+    mx = fmaxf(mx, lw[g]);
+  }
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, wsum = 0.f;
+  if (mx == -INFINITY) {
+    if (c8 == 0) atomicOr(&g_tc_error, 2);  // every group's weights underflowed: outside the numeric domain
+  } else {
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      if (g >= groups) break;
+      const float w = exp2f(lw[g] - mx);
+      wsum += w;
+      const float4* src = reinterpret_cast<const float4*>(part_y + (g * rows + row) * dv + c8 * 8);
+      const float4 a = src[0], b = src[1];
+      acc[0] += w * a.x; acc[1] += w * a.y; acc[2] += w * a.z; acc[3] += w * a.w;
+      acc[4] += w * b.x; acc[5] += w * b.y; acc[6] += w * b.z; acc[7] += w * b.w;
+    }
+  }
+  const float inv = wsum > 0.f ? 1.0f / wsum : 0.f;
+  const int h = (int)(row % H);
+  const int64_t bn = row / H;
+  const int n = (int)(bn % N);
+  const int64_t b = bn / N;
+  uint4 v;
+  v.x = pack_bf16(acc[0] * inv, acc[1] * inv);
+  v.y = pack_bf16(acc[2] * inv, acc[3] * inv);
+  v.z = pack_bf16(acc[4] * inv, acc[5] * inv);
+  v.w = pack_bf16(acc[6] * inv, acc[7] * inv);
+  *reinterpret_cast<uint4*>(y + b * y_stride_b + (int64_t)n * y_stride_n + (int64_t)h * y_stride_h + c8 * 8) = v;
+}
+
 namespace {
 
-template <bool PADDED, int DKB>
+template <bool PADDED, int DKB, bool SPLIT>
 int launch_instance(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const TcParams& p, dim3 grid,
                     cudaStream_t stream) {
   static bool attr_set = false;
-  auto kern = prefill_tc_kernel<PADDED, DKB>;
+  auto kern = prefill_tc_kernel<PADDED, DKB, SPLIT>;
   if (!attr_set) {
     FLARE_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Lay<DKB>::SMEM_BYTES));
     attr_set = true;
@@ -699,9 +779,24 @@ int launch_instance(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensor
   return FLARE_OK;
 }
 
+template <int DKB, bool SPLIT>
+int launch_padded(bool padded, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const TcParams& p,
+                  dim3 grid, cudaStream_t stream) {
+  return padded ? launch_instance<true, DKB, SPLIT>(tq, tk, tv, p, grid, stream)
+                : launch_instance<false, DKB, SPLIT>(tq, tk, tv, p, grid, stream);
+}
+
 }  // namespace
 
-int prefill_tc_ctas_per_lane(const flare_fwd_args_t* a) { return a->Dv / D; }
+int prefill_tc_latent_groups(const flare_fwd_args_t* a) { return (a->M + M - 1) / M; }
+
+int prefill_tc_ctas_per_lane(const flare_fwd_args_t* a) { return a->Dv / D * prefill_tc_latent_groups(a); }
+
+size_t prefill_tc_partial_bytes(const flare_fwd_args_t* a) {
+  const int groups = prefill_tc_latent_groups(a);
+  if (groups == 1) return 0;
+  return (size_t)groups * a->B * a->N * a->H * (a->Dv + 1) * sizeof(float);
+}
 
 int launch_prefill_tc(const flare_fwd_args_t* a, const TcParams& p, int nseg_grid, cudaStream_t stream) {
   CUtensorMap tq, tk, tv;
@@ -721,11 +816,24 @@ int launch_prefill_tc(const flare_fwd_args_t* a, const TcParams& p, int nseg_gri
     if (!make_map(&tk, a->k, 4, dimk, strk, box)) return FLARE_ERR_CUDA;
     if (!make_map(&tv, a->v, 4, dimv, strv, box)) return FLARE_ERR_CUDA;
   }
-  const dim3 grid(a->B * a->H, nseg_grid, a->Dv / D);
-  const bool padded = a->M != M;
+  const int groups = prefill_tc_latent_groups(a);
+  const dim3 grid(a->B * a->H, nseg_grid, a->Dv / D * groups);
+  const bool padded = (a->M % M) != 0;
+  int rc;
   if (a->Dk == 64)
-    return padded ? launch_instance<true, 1>(tq, tk, tv, p, grid, stream) : launch_instance<false, 1>(tq, tk, tv, p, grid, stream);
-  return padded ? launch_instance<true, 2>(tq, tk, tv, p, grid, stream) : launch_instance<false, 2>(tq, tk, tv, p, grid, stream);
+    rc = groups > 1 ? launch_padded<1, true>(padded, tq, tk, tv, p, grid, stream)
+                    : launch_padded<1, false>(padded, tq, tk, tv, p, grid, stream);
+  else
+    rc = groups > 1 ? launch_padded<2, true>(padded, tq, tk, tv, p, grid, stream)
+                    : launch_padded<2, false>(padded, tq, tk, tv, p, grid, stream);
+  if (rc != FLARE_OK || groups == 1 || p.y == nullptr) return rc;
+  const int64_t rows = (int64_t)a->B * a->N * a->H;
+  const int64_t threads = rows * (a->Dv / 8);
+  tc_merge_groups_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, stream>>>(
+      p.part_y, p.part_lw, groups, rows, a->N, a->H, a->Dv, reinterpret_cast<__nv_bfloat16*>(p.y), p.y_stride_b,
+      p.y_stride_n, p.y_stride_h);
+  FLARE_CUDA_CHECK(cudaGetLastError());
+  return FLARE_OK;
 }
 
 int prefill_tc_error_flag(int* host_value, bool reset) {

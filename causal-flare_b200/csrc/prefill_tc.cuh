@@ -10,7 +10,7 @@ struct TcParams {
   const void* q;  // bf16 latent bank [H, M, Dk]
   int64_t q_stride_h, q_stride_m;
   int N, H;
-  int M;   // latents, <= 128
+  int M;   // latents, <= 512; groups of 128 go to separate CTAs
   int Dv;  // value width (64 or 128); each CTA handles 64 columns
   float scale;
   int seg_len;
@@ -19,6 +19,9 @@ struct TcParams {
   int64_t in_lane_stride, in_seg_stride;
   float *out_m, *out_d, *out_u;
   int64_t out_lane_stride, out_seg_stride;
+  // more than 128 latents: per-group partial read-outs, fp32 [groups][B][N][H][Dv] and [groups][B][N][H]; the launch
+  // merges them into y afterwards
+  float *part_y, *part_lw;
   int out_mode;  // 0: none, 1: every segment, 2: last segment only
   int nseg_total;
   long long* trace;  // optional diagnostic cycle stamps of CTA (0, 0), see TC_TRACE; null in normal use
@@ -27,6 +30,8 @@ struct TcParams {
 bool prefill_tc_supported(const flare_fwd_args_t* a);
 // CTAs the kernel launches per (lane, segment)
 int prefill_tc_ctas_per_lane(const flare_fwd_args_t* a);
+// scratch for the partial read-outs of the latent groups (0 for M <= 128)
+size_t prefill_tc_partial_bytes(const flare_fwd_args_t* a);
 // launches segments 0 .. nseg_grid-1
 int launch_prefill_tc(const flare_fwd_args_t* a, const TcParams& p, int nseg_grid, cudaStream_t stream);
 // reads (and optionally clears) the device-side error flag of the tensor-core kernels; synchronises

@@ -148,3 +148,40 @@ def test_wide_heads_training_shape_vs_exact():
     y_t, _, _, _ = run(q, k, v, _lib.PATH_TENSOR, scale=Dw ** -0.5)
     y_e, _, _, _ = run(q, k, v, _lib.PATH_EXACT, scale=Dw ** -0.5)
     assert_bf16_gate(y_t, y_e.float(), "tensor vs exact, D=128 training shape")
+
+
+@pytest.mark.parametrize("Ml, Dw, B, N, H", [(256, 64, 1, 256, 1), (256, 128, 2, 600, 2), (192, 64, 1, 900, 2),
+                                             (512, 128, 1, 384, 1), (256, 128, 1, 4096, 1)])
+def test_tensor_path_latent_groups(Ml, Dw, B, N, H):
+    # more than 128 latents: one CTA per group of 128, partial read-outs merged by a second kernel
+    q, k, v = orc.make_inputs(B, N, H, Ml, Dw, seed0=31, dtype=torch.bfloat16)
+    sc = Dw ** -0.5
+    ref, st_ref = orc.ar_forward(q, k, v, scale=sc, return_state=True)
+    qc, kc, vc = to_dev(q, k, v)
+    assert uses_tensor_path(qc, kc, vc)
+    y, st, _, _ = run(qc, kc, vc, _lib.PATH_TENSOR, want_state=True, scale=sc)
+    assert_bf16_gate(y, ref, f"tensor path M={Ml} D={Dw} N={N}")
+    assert_close(st["m"], st_ref["m"], what="m", atol=1e-4, rtol=1e-4)
+    assert_close(st["d"], st_ref["d"], what="d", atol=1e-3, rtol=2e-3)
+    assert orc.rel_l2(st["u"].cpu(), st_ref["u"]) < 3e-3
+    h = (N // 2) // 16 * 16
+    _, st_a, _, _ = run(qc, kc[:, :h], vc[:, :h], _lib.PATH_TENSOR, want_state=True, scale=sc)
+    y_b, _, _, _ = run(qc, kc[:, h:], vc[:, h:], _lib.PATH_TENSOR, state_in=st_a, scale=sc)
+    assert_bf16_gate(y_b, ref[:, h:], "latent groups, carry-in")
+
+
+def test_latent_groups_decode_cache_shape_vs_exact():
+    # B=64, H=32, M=256, D=128 (decode benchmark's cache shape), prefix of 512 tokens, then decode continues
+    B, N, H, Ml, Dw = 64, 512, 32, 256, 128
+    g = torch.Generator(device="cuda").manual_seed(2)
+    q = torch.randn(H, Ml, Dw, generator=g, device="cuda").bfloat16()
+    k = torch.randn(B, N + 1, H, Dw, generator=g, device="cuda").bfloat16()
+    v = torch.randn(B, N + 1, H, Dw, generator=g, device="cuda").bfloat16()
+    sc = Dw ** -0.5
+    y_t, st_t, _, _ = run(q, k[:, :N], v[:, :N], _lib.PATH_TENSOR, want_state=True, scale=sc)
+    y_e, st_e, _, _ = run(q, k[:, :N], v[:, :N], _lib.PATH_EXACT, want_state=True, scale=sc)
+    assert_bf16_gate(y_t, y_e.float(), "tensor vs exact, M=256 D=128")
+    assert orc.rel_l2(st_t["u"], st_e["u"]) < 3e-3
+    y1, _ = cf.flare_autoregressive_decode_triton(q, k[:, N], v[:, N], st_t, scale=sc)
+    y2, _ = cf.flare_autoregressive_decode_triton(q, k[:, N], v[:, N], st_e, scale=sc)
+    assert_bf16_gate(y1, y2.float(), "decode after M=256 prefill")
