@@ -26,7 +26,8 @@ UNITS = [
     *[("walk_exact.cu", [f"-DFLARE_WALK_MM={mm}"], f"walk_exact_mm{mm}") for mm in (2, 8, 16, 32, 64)],
     ("decode_step.cu", [], "decode_step"),
     ("state_ops.cu", [], "state_ops"),
-    ("prefill_tc.cu", [], "prefill_tc"),
+    ("prefill_tc.cu", [], "prefill_tc_host"),
+    *[("prefill_tc.cu", [f"-DFLARE_TC_UNIT={u}"], f"prefill_tc_unit{u}") for u in range(4)],
     ("noalloc.cu", [], "noalloc"),
     ("bwd_exact.cu", [], "bwd_exact_dispatch"),
     *[("bwd_exact.cu", [f"-DFLARE_WALK_MM={mm}"], f"bwd_exact_mm{mm}") for mm in (2, 8, 16, 32, 64)],

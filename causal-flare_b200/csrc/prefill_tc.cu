@@ -81,7 +81,6 @@ struct Misc {
   float xmax[2][2][128], xsum[2][2][128];  // [chunk parity][half][latent]
 };
 
-__device__ int g_tc_error = 0;
 
 // optional cycle trace of CTA (0, 0): [role][chunk < 16][slot < 8] clock64 stamps (diagnostic hook, null in normal use)
 #define TC_TRACE(role, chunk, slot)                                                                   \
@@ -125,9 +124,21 @@ __device__ __forceinline__ int latent0() {
 
 }  // namespace
 
+// The kernel instances are compiled in separate translation units (FLARE_TC_UNIT = 0..3: head width 64 / 128, without /
+// with the latent-group split) to keep build times short; the unit without FLARE_TC_UNIT holds the host side.
+template <int UNIT>
+int launch_prefill_tc_unit(bool padded, bool block, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
+                           const TcParams& p, dim3 grid, cudaStream_t stream);
+
+#ifdef FLARE_TC_UNIT
+
+
 // PADDED: fewer than 128 latents (rows padded); the full-width instance carries none of the padding predicates
 // SPLIT: more than 128 latents, partial read-outs
-template <bool PADDED, int DKB, bool SPLIT>
+// BLOCK: block-causal (semi-autoregressive) read-out with blocks of 16, 32, 64 or 128 tokens: a token reads the state
+//        at the end of its block, so the denominator of a block's tokens is the one at the block's end and the mask
+//        of W is "column <= end of the row's block"
+template <bool PADDED, int DKB, bool SPLIT, bool BLOCK>
 __global__ void __launch_bounds__(NTHREADS, 1)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                   const __grid_constant__ CUtensorMap tm_v, const TcParams p) {
@@ -425,7 +436,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       }
       const float* wsrc = misc->wmax[i == 0 ? 0 : ((i - 1) & 1)];
       const float kappa = fmaxf(fmaxf(wsrc[0], wsrc[1]), fmaxf(wsrc[2], wsrc[3]));
-      if (SPLIT && tid == 0) misc->kap[par] = kappa;  // ordered before the token group's read by the barrier chain
+      // ordered before the token group's read by the barrier chain
+      if ((SPLIT || BLOCK) && tid == 0) misc->kap[par] = kappa;
       if (tid == 0) TC_TRACE(0, i, 1);
       float a_m = ex2_approx(c_new - kappa);
       float d_carry = dsum * alpha;  // denominator of the carried state in the new frame
@@ -438,6 +450,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       c2 = c_new;
       // phase a: E for the 64 tokens of this half (in place of the scores), their sum, E operand rows
       float tot0 = 0.f, tot1 = 0.f;
+      float g16[4] = {0.f, 0.f, 0.f, 0.f};  // BLOCK: sums of the four groups of 16 tokens of this half
       if (nvalid == C) {
 #pragma unroll
         for (int k = 0; k < 32; ++k) {
@@ -445,8 +458,13 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           const float e1 = ex2_approx(__uint_as_float(rb[k]) * sc2 - c_new);
           ra[k] = __float_as_uint(e0);
           rb[k] = __float_as_uint(e1);
-          tot0 += e0;
-          tot1 += e1;
+          if (BLOCK) {
+            g16[k >> 4] += e0;
+            g16[2 + (k >> 4)] += e1;
+          } else {
+            tot0 += e0;
+            tot1 += e1;
+          }
         }
       } else {
 #pragma unroll
@@ -455,9 +473,18 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           const float e1 = (tok0 + 32 + k < nvalid) ? ex2_approx(__uint_as_float(rb[k]) * sc2 - c_new) : 0.f;
           ra[k] = __float_as_uint(e0);
           rb[k] = __float_as_uint(e1);
-          tot0 += e0;
-          tot1 += e1;
+          if (BLOCK) {
+            g16[k >> 4] += e0;
+            g16[2 + (k >> 4)] += e1;
+          } else {
+            tot0 += e0;
+            tot1 += e1;
+          }
         }
+      }
+      if (BLOCK) {
+        tot0 = g16[0] + g16[1];
+        tot1 = g16[2] + g16[3];
       }
       misc->xsum[par][hf][m] = tot0 + tot1;
       warp_arrive(&misc->psum[q], lane);
@@ -476,30 +503,80 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       }
       d_prev = d_carry;
       // the upper half continues the lower half's running denominator; the lower half needs nothing from its partner
+      // (except for blocks of 128 tokens, whose end lies in the upper half)
       float run = d_carry;
-      if (hf) {
+      if (hf || (BLOCK && p.block == 128)) {
         if (!(ok = wait_or_abort(&misc->psum[q], par, misc))) break;
         run += misc->xsum[par][0][m];
+        if (BLOCK && p.block == 128 && hf == 0) run = d_carry;  // lower half: only the wait was needed
       }
       if (tid == 0) TC_TRACE(0, i, 2);
-      // phase b: D = running denominator, R = E a_m / D, R operand rows
+      if constexpr (!BLOCK) {
+        // phase b: D = running denominator, R = E a_m / D, R operand rows
 #pragma unroll
-      for (int blk = 0; blk < 2; ++blk) {
-        uint32_t rp[16];
+        for (int blk = 0; blk < 2; ++blk) {
+          uint32_t rp[16];
 #pragma unroll
-        for (int k = 0; k < 32; k += 2) {
-          const float e0 = __uint_as_float(blk ? rb[k] : ra[k]);
-          const float e1 = __uint_as_float(blk ? rb[k + 1] : ra[k + 1]);
-          run += e0;
-          const float r0 = e0 * (a_m * rcp_approx(run));  // special-function unit
-          run += e1;
-          const float r1 = e1 * (a_m * rcp_fma(run));     // FMA pipe: the two units share the divisions
-          rp[k >> 1] = pack_bf16(r0, r1);
+          for (int k = 0; k < 32; k += 2) {
+            const float e0 = __uint_as_float(blk ? rb[k] : ra[k]);
+            const float e1 = __uint_as_float(blk ? rb[k + 1] : ra[k + 1]);
+            run += e0;
+            const float r0 = e0 * (a_m * rcp_approx(run));  // special-function unit
+            run += e1;
+            const float r1 = e1 * (a_m * rcp_fma(run));     // FMA pipe: the two units share the divisions
+            rp[k >> 1] = pack_bf16(r0, r1);
+          }
+#pragma unroll
+          for (int ch = 0; ch < 4; ++ch)
+            *reinterpret_cast<uint4*>(r_row + swz_chunk_off(m, blk * 4 + ch)) =
+                make_uint4(rp[ch * 4], rp[ch * 4 + 1], rp[ch * 4 + 2], rp[ch * 4 + 3]);
         }
+      } else {
+        // phase b, block-causal: the denominator of a token is the one at the end of its block.  dend[g] is that
+        // value for the g-th group of 16 tokens of this half (`run` = denominator before this half).
+        const int bs = p.block;
+        float dend[4];
+        {
+          const float p0 = run + g16[0], p1 = p0 + g16[1], p2 = p1 + g16[2], p3 = p2 + g16[3];
+          if (bs == 16) {
+            dend[0] = p0; dend[1] = p1; dend[2] = p2; dend[3] = p3;
+          } else if (bs == 32) {
+            dend[0] = dend[1] = p1; dend[2] = dend[3] = p3;
+          } else if (bs == 64) {
+            dend[0] = dend[1] = dend[2] = dend[3] = p3;
+          } else {
+            // one block per chunk: both halves use the chunk's end
+            const float whole = d_carry + (misc->xsum[par][0][m] + misc->xsum[par][1][m]);
+            dend[0] = dend[1] = dend[2] = dend[3] = whole;
+          }
+        }
+        // log normaliser after each block that ends in this half (natural log, exact-frame independent)
+        if (p.lse_enc != nullptr && live && value_col0<DKB, SPLIT>() == 0) {
+          const int t_half = seg_begin + i * C + tok0;  // first token of this half in the sequence
+          float* dst = p.lse_enc + ((int64_t)lane_id * (p.N / bs)) * p.M + latent0<DKB, SPLIT>() + m;
 #pragma unroll
-        for (int ch = 0; ch < 4; ++ch)
-          *reinterpret_cast<uint4*>(r_row + swz_chunk_off(m, blk * 4 + ch)) =
-              make_uint4(rp[ch * 4], rp[ch * 4 + 1], rp[ch * 4 + 2], rp[ch * 4 + 3]);
+          for (int g = 0; g < 4; ++g) {
+            const int t_end = t_half + g * 16 + 15;            // last token of the group
+            const bool ends = ((t_end + 1) % bs) == 0;         // a block ends with this group
+            if (ends && tok0 + g * 16 < nvalid) dst[(int64_t)(t_end / bs) * p.M] = (c_new + __log2f(dend[g])) * kLn2;
+          }
+        }
+        float inv[4];
+#pragma unroll
+        for (int g = 0; g < 4; ++g) inv[g] = a_m * rcp_approx(dend[g]);
+#pragma unroll
+        for (int blk = 0; blk < 2; ++blk) {
+          uint32_t rp[16];
+#pragma unroll
+          for (int k = 0; k < 32; k += 2) {
+            const float w = inv[blk * 2 + (k >> 4)];
+            rp[k >> 1] = pack_bf16(__uint_as_float(blk ? rb[k] : ra[k]) * w, __uint_as_float(blk ? rb[k + 1] : ra[k + 1]) * w);
+          }
+#pragma unroll
+          for (int ch = 0; ch < 4; ++ch)
+            *reinterpret_cast<uint4*>(r_row + swz_chunk_off(m, blk * 4 + ch)) =
+                make_uint4(rp[ch * 4], rp[ch * 4 + 1], rp[ch * 4 + 2], rp[ch * 4 + 3]);
+        }
       }
       if (tid == 0) TC_TRACE(0, i, 3);
       // state part: needs the numerator update of the previous chunk to have landed
@@ -587,17 +664,19 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       tc_fence_after_sync();
       if (tid == 256) TC_TRACE(1, i, 0);
       float rowsum = 0.f;
+      // last column (token of the chunk) this row may see: itself, or the end of its block
+      const int be = BLOCK ? (tt | (p.block - 1)) : tt;
 #pragma unroll 1
       for (int j = 0; j < 4; ++j) {
         uint32_t wp[16];
-        if (j <= wq) {
+        if (BLOCK ? (j * 32 <= be) : (j <= wq)) {
           uint32_t r[32];
           tmem_ld32(tl + TM_W + j * 32, r);
           tmem_wait_ld();
 #pragma unroll
           for (int k = 0; k < 32; k += 2) {
-            const float w0 = (j < wq || k <= lane) ? __uint_as_float(r[k]) : 0.f;
-            const float w1 = (j < wq || k + 1 <= lane) ? __uint_as_float(r[k + 1]) : 0.f;
+            const float w0 = (BLOCK ? (j * 32 + k <= be) : (j < wq || k <= lane)) ? __uint_as_float(r[k]) : 0.f;
+            const float w1 = (BLOCK ? (j * 32 + k + 1 <= be) : (j < wq || k + 1 <= lane)) ? __uint_as_float(r[k + 1]) : 0.f;
             const uint32_t pk = pack_bf16(w0, w1);
             wp[k >> 1] = pk;
             rowsum += __uint_as_float(pk << 16) + __uint_as_float(pk & 0xffff0000u);
@@ -625,10 +704,13 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       // outside the numeric domain of this path (scores of a token more than ~80 nats below the running maxima):
       // every weight underflowed.  Flag it; the exact path has no such limit.  With a latent-group split one group
       // may legitimately carry no weight; the merge kernel flags a token only when every group is empty.
-      if (!SPLIT && tt < nvalid && !den_ok) atomicOr(&g_tc_error, 2);
+      if (!SPLIT && tt < nvalid && !den_ok) atomicOr(p.err, 2);
       const float inv = (SPLIT && !den_ok) ? 0.f : 1.0f / den;
       if (SPLIT && p.part_y != nullptr && tt < nvalid && value_col0<DKB, SPLIT>() == 0)
         p.part_lw[(part_row0 + t0 + tt) * p.H + h] = den_ok ? misc->kap[par] + __log2f(den) : -INFINITY;
+      // log-sum-exp of the token's decode scores = log of the decode weights' mass in the frame kappa
+      if (BLOCK && !SPLIT && p.lse_dec != nullptr && tt < nvalid && value_col0<DKB, SPLIT>() == 0)
+        p.lse_dec[(int64_t)lane_id * p.N + t0 + tt] = (misc->kap[par] + __log2f(den)) * kLn2;
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
         uint32_t r[32];
@@ -663,13 +745,49 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   }
   if (!ok) {
     misc->abort_flag = 1;
-    atomicOr(&g_tc_error, 1);
+    atomicOr(p.err, 1);
   }
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 12) tmem_dealloc(tmem, TM_COLS);
 }
 
+
+
+namespace {
+
+template <bool PADDED, int DKB, bool SPLIT, bool BLOCK>
+int launch_instance(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const TcParams& p, dim3 grid,
+                    cudaStream_t stream) {
+  auto kern = prefill_tc_kernel<PADDED, DKB, SPLIT, BLOCK>;
+  FLARE_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Lay<DKB>::SMEM_BYTES));
+  kern<<<grid, NTHREADS, Lay<DKB>::SMEM_BYTES, stream>>>(tq, tk, tv, p);
+  FLARE_CUDA_CHECK(cudaGetLastError());
+  return FLARE_OK;
+}
+
+}  // namespace
+
+template <>
+int launch_prefill_tc_unit<FLARE_TC_UNIT>(bool padded, bool block, const CUtensorMap& tq, const CUtensorMap& tk,
+                                          const CUtensorMap& tv, const TcParams& p, dim3 grid, cudaStream_t stream) {
+  constexpr int DKB = 1 + (FLARE_TC_UNIT & 1);
+  constexpr bool SPLIT = (FLARE_TC_UNIT >> 1) != 0;
+  if (block)
+    return padded ? launch_instance<true, DKB, SPLIT, true>(tq, tk, tv, p, grid, stream)
+                  : launch_instance<false, DKB, SPLIT, true>(tq, tk, tv, p, grid, stream);
+  return padded ? launch_instance<true, DKB, SPLIT, false>(tq, tk, tv, p, grid, stream)
+                : launch_instance<false, DKB, SPLIT, false>(tq, tk, tv, p, grid, stream);
+}
+
+#else  // host side and the merge kernel
+
+__device__ int g_tc_error = 0;
+
+template <> int launch_prefill_tc_unit<0>(bool, bool, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const TcParams&, dim3, cudaStream_t);
+template <> int launch_prefill_tc_unit<1>(bool, bool, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const TcParams&, dim3, cudaStream_t);
+template <> int launch_prefill_tc_unit<2>(bool, bool, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const TcParams&, dim3, cudaStream_t);
+template <> int launch_prefill_tc_unit<3>(bool, bool, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const TcParams&, dim3, cudaStream_t);
 
 // -------------------------------------------------------------------------------------------------
 // host side
@@ -713,9 +831,13 @@ bool make_map(CUtensorMap* map, const void* base, int rank, const uint64_t* dims
 }  // namespace
 
 bool prefill_tc_supported(const flare_fwd_args_t* a) {
-  return a->dtype == FLARE_BF16 && a->variant == FLARE_SOFTMAX && a->block_size == 1 && a->M <= 4 * M && a->M >= 16 &&
+  const int bs = a->block_size;
+  const bool block_ok = bs == 1 || ((bs == 16 || bs == 32 || bs == 64 || bs == 128) && a->N % bs == 0);
+  // the log normalisers are emitted in block-causal mode only (the token-causal entry points never ask for them)
+  const bool lse_ok = (a->lse_enc == nullptr && a->lse_dec == nullptr) || bs > 1;
+  return a->dtype == FLARE_BF16 && a->variant == FLARE_SOFTMAX && block_ok && lse_ok && a->M <= 4 * M && a->M >= 16 &&
          (a->M % 16) == 0 && (a->Dk == 64 || a->Dk == 128) && a->Dv == a->Dk && a->q_dec == nullptr &&
-         a->k_dec == nullptr && a->mask == nullptr && a->lse_dec == nullptr && a->N >= 1;
+         a->k_dec == nullptr && a->mask == nullptr && a->N >= 1;
 }
 
 // Merge of the latent groups' partial read-outs: y = sum_g w_g y_g / sum_g w_g with w_g = exp2(lw_g - max lw).
@@ -723,7 +845,7 @@ bool prefill_tc_supported(const flare_fwd_args_t* a) {
 __global__ void __launch_bounds__(256) tc_merge_groups_kernel(const float* __restrict__ part_y, const float* __restrict__ part_lw,
                                                                int groups, int64_t rows /* B*N*H */, int N, int H, int dv,
                                                                __nv_bfloat16* y, int64_t y_stride_b, int64_t y_stride_n,
-                                                               int64_t y_stride_h) {
+                                                               int64_t y_stride_h, float* lse_dec /* [B, H, N] or null */) {
   const int cols8 = dv >> 3;
   const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= rows * cols8) return;
@@ -755,6 +877,7 @@ __global__ void __launch_bounds__(256) tc_merge_groups_kernel(const float* __res
   const int64_t bn = row / H;
   const int n = (int)(bn % N);
   const int64_t b = bn / N;
+  if (lse_dec != nullptr && c8 == 0) lse_dec[(b * H + h) * N + n] = (mx + log2f(wsum)) * kLn2;
   uint4 v;
   v.x = pack_bf16(acc[0] * inv, acc[1] * inv);
   v.y = pack_bf16(acc[2] * inv, acc[3] * inv);
@@ -763,30 +886,6 @@ __global__ void __launch_bounds__(256) tc_merge_groups_kernel(const float* __res
   *reinterpret_cast<uint4*>(y + b * y_stride_b + (int64_t)n * y_stride_n + (int64_t)h * y_stride_h + c8 * 8) = v;
 }
 
-namespace {
-
-template <bool PADDED, int DKB, bool SPLIT>
-int launch_instance(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const TcParams& p, dim3 grid,
-                    cudaStream_t stream) {
-  static bool attr_set = false;
-  auto kern = prefill_tc_kernel<PADDED, DKB, SPLIT>;
-  if (!attr_set) {
-    FLARE_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Lay<DKB>::SMEM_BYTES));
-    attr_set = true;
-  }
-  kern<<<grid, NTHREADS, Lay<DKB>::SMEM_BYTES, stream>>>(tq, tk, tv, p);
-  FLARE_CUDA_CHECK(cudaGetLastError());
-  return FLARE_OK;
-}
-
-template <int DKB, bool SPLIT>
-int launch_padded(bool padded, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const TcParams& p,
-                  dim3 grid, cudaStream_t stream) {
-  return padded ? launch_instance<true, DKB, SPLIT>(tq, tk, tv, p, grid, stream)
-                : launch_instance<false, DKB, SPLIT>(tq, tk, tv, p, grid, stream);
-}
-
-}  // namespace
 
 int prefill_tc_latent_groups(const flare_fwd_args_t* a) { return (a->M + M - 1) / M; }
 
@@ -798,7 +897,17 @@ size_t prefill_tc_partial_bytes(const flare_fwd_args_t* a) {
   return (size_t)groups * a->B * a->N * a->H * (a->Dv + 1) * sizeof(float);
 }
 
-int launch_prefill_tc(const flare_fwd_args_t* a, const TcParams& p, int nseg_grid, cudaStream_t stream) {
+int launch_prefill_tc(const flare_fwd_args_t* a, const TcParams& p_in, int nseg_grid, cudaStream_t stream) {
+  TcParams p = p_in;
+  {
+    void* err = nullptr;
+    FLARE_CUDA_CHECK(cudaGetSymbolAddress(&err, g_tc_error));  // of the current device
+    p.err = reinterpret_cast<int*>(err);
+  }
+  p.block = a->block_size;
+  p.lse_dec = a->lse_dec;
+  p.lse_enc = a->lse_enc;
+  if (p.y == nullptr) p.lse_dec = p.lse_enc = nullptr;  // state-only passes emit nothing else
   CUtensorMap tq, tk, tv;
   {
     // latent bank (used by the Dk = 64 instances only; any valid map otherwise)
@@ -819,19 +928,20 @@ int launch_prefill_tc(const flare_fwd_args_t* a, const TcParams& p, int nseg_gri
   const int groups = prefill_tc_latent_groups(a);
   const dim3 grid(a->B * a->H, nseg_grid, a->Dv / D * groups);
   const bool padded = (a->M % M) != 0;
+  const bool block = a->block_size > 1;
   int rc;
   if (a->Dk == 64)
-    rc = groups > 1 ? launch_padded<1, true>(padded, tq, tk, tv, p, grid, stream)
-                    : launch_padded<1, false>(padded, tq, tk, tv, p, grid, stream);
+    rc = groups > 1 ? launch_prefill_tc_unit<2>(padded, block, tq, tk, tv, p, grid, stream)
+                    : launch_prefill_tc_unit<0>(padded, block, tq, tk, tv, p, grid, stream);
   else
-    rc = groups > 1 ? launch_padded<2, true>(padded, tq, tk, tv, p, grid, stream)
-                    : launch_padded<2, false>(padded, tq, tk, tv, p, grid, stream);
+    rc = groups > 1 ? launch_prefill_tc_unit<3>(padded, block, tq, tk, tv, p, grid, stream)
+                    : launch_prefill_tc_unit<1>(padded, block, tq, tk, tv, p, grid, stream);
   if (rc != FLARE_OK || groups == 1 || p.y == nullptr) return rc;
   const int64_t rows = (int64_t)a->B * a->N * a->H;
   const int64_t threads = rows * (a->Dv / 8);
   tc_merge_groups_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, stream>>>(
       p.part_y, p.part_lw, groups, rows, a->N, a->H, a->Dv, reinterpret_cast<__nv_bfloat16*>(p.y), p.y_stride_b,
-      p.y_stride_n, p.y_stride_h);
+      p.y_stride_n, p.y_stride_h, p.lse_dec);
   FLARE_CUDA_CHECK(cudaGetLastError());
   return FLARE_OK;
 }
@@ -846,5 +956,7 @@ int prefill_tc_error_flag(int* host_value, bool reset) {
   *host_value = v;
   return FLARE_OK;
 }
+
+#endif  // FLARE_TC_UNIT
 
 }  // namespace flare

@@ -191,7 +191,8 @@ def test_semi_ar_forward(golden, sep):
     assert torch.equal(y, y2), "chunk_size must not change the result"
 
 
-def test_semi_ar_bf16_long_and_segmented():
+def test_semi_ar_bf16_long_and_segmented(monkeypatch):
+    monkeypatch.setenv("FLARE_B200_PATH", "exact")  # the tensor path has its own test with its own LSE tolerance
     q, k, v = orc.make_inputs(1, 1024, 2, 64, 64, seed0=41, dtype=torch.bfloat16)
     ref, lse_dec, lse_enc = orc.semi_ar_forward(q, k, v, block_size=64)
     y, aux = cf.flare_semi_autoregressive_trition(*to_dev(q, k, v), block_size=64, chunk_size=64)
