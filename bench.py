@@ -279,6 +279,54 @@ def bench_decode(args, rank, world):
     }
 
 
+def bench_other_shapes():
+    """Short device-timed runs of the other benchmark shapes (not the headline metric): training-shape forward and
+    forward+backward, and the long block-causal shape on one GPU."""
+    import causal_flare as cf
+
+    def timed(fn, warm=2, n=5):
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for _ in range(n):
+            fn()
+        t1.record()
+        torch.cuda.synchronize()
+        return t0.elapsed_time(t1) / n
+
+    out = {}
+    g = torch.Generator(device="cuda").manual_seed(7)
+    B, N, H, M, D = 4, 4096, 16, 64, 128
+    q = torch.randn(H, M, D, generator=g, device="cuda").bfloat16().requires_grad_()
+    k = torch.randn(B, N, H, D, generator=g, device="cuda").bfloat16().requires_grad_()
+    v = torch.randn(B, N, H, D, generator=g, device="cuda").bfloat16().requires_grad_()
+    dy = torch.randn(B, N, H, D, generator=g, device="cuda").bfloat16()
+    with torch.no_grad():
+        out["C4_forward_ms"] = timed(lambda: cf.flare_autoregressive_triton(q, k, v))
+
+    def train_step(fn):
+        q.grad = k.grad = v.grad = None
+        fn(q, k, v).backward(dy)
+
+    out["C4_fwd_bwd_softmax_ms"] = timed(lambda: train_step(cf.flare_autoregressive_triton), n=3)
+    from causal_flare.autoregressive import flare_autoregressive_stablemax_triton
+
+    out["C4_fwd_bwd_stablemax_ms"] = timed(lambda: train_step(flare_autoregressive_stablemax_triton), n=3)
+    out["C4"] = f"B={B} N={N} H={H} M={M} D={D} bf16"
+    del q, k, v, dy
+    B, N, H, M, D, bs = 2, 65536, 32, 256, 128, 64
+    q = torch.randn(H, M, D, generator=g, device="cuda").bfloat16()
+    k = torch.randn(B, N, H, D, generator=g, device="cuda").bfloat16()
+    v = torch.randn(B, N, H, D, generator=g, device="cuda").bfloat16()
+    with torch.no_grad():
+        out["C5_one_gpu_semi_ar_forward_ms"] = timed(
+            lambda: cf.flare_semi_autoregressive_trition(q, k, v, block_size=bs, chunk_size=64), n=3)
+    out["C5"] = f"B={B} N={N} H={H} M={M} D={D} block={bs} bf16, whole sequence on one GPU"
+    return out
+
+
 def cpu_reference_sample(threads=None):
     """The reference algorithm on the host: fp32 token recurrence over a bounded slice of C2."""
     from oracle import flare_oracle as orc
@@ -318,6 +366,7 @@ def main():
     ap.add_argument("--only", default="all", choices=["all", "prefill", "decode"],
                     help="profiling aid: run one section only (the JSON line then lacks the other)")
     ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--skip-other", action="store_true", help="skip the short runs of the other benchmark shapes")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -351,6 +400,9 @@ def main():
         return
     pre = bench_prefill(args, rank, world)
     dec = None if (args.skip_decode or args.only == "prefill") else bench_decode(args, rank, world)
+    other = None
+    if world == 1 and args.only == "all" and not args.skip_other:
+        other = bench_other_shapes()
     cpu = None
     if rank == 0 and world == 1 and not args.skip_cpu:
         cpu = cpu_reference_sample()
@@ -361,7 +413,7 @@ def main():
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": pre["ms_per_step"], "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config_block(world),
             "roofline": pre["roofline"], "cpu_baseline": cpu, "e2e": pre["e2e"], "gpu_launches": pre["gpu_launches"],
-            "clocks": pre["clocks"], "decode": dec,
+            "clocks": pre["clocks"], "decode": dec, "other_shapes": other,
         }
         print(json.dumps(line))
     if world > 1:

@@ -568,67 +568,73 @@ struct RowsParams {
   float scale;
 };
 
-constexpr int RT = 32;  // token rows per CTA
+constexpr int RT = 64;    // token rows per CTA
+constexpr int RM = 32;    // latents per shared-memory stage
+constexpr int RC = 128;   // output columns per CTA (grid.z tiles wider rows)
 
+// Register-tiled fp32 product: 256 threads, thread (ty, tx) owns rows ty*4 .. +3 and columns tx*8 .. +7 of the
+// RT x RC output tile; per latent 6 shared-memory loads feed 32 FMAs.
 __global__ void __launch_bounds__(NT) bwd_rows_kernel(const RowsParams p) {
-  extern __shared__ __align__(16) float smem_raw[];
-  const int lane_id = blockIdx.x, t0 = blockIdx.y * RT;
+  __shared__ __align__(16) float ds_s[RT][RM + 4];
+  __shared__ __align__(16) float lat_s[RM][RC];
+  const int lane_id = blockIdx.x, t0 = blockIdx.y * RT, c0 = blockIdx.z * RC;
   const int b = lane_id / p.H, h = lane_id % p.H;
-  const int M = p.M, Dk = p.Dk, N = p.N, mp = M + 4;
-  float* ds_s = smem_raw;  // [RT][mp]
-  const int tid = threadIdx.x;
-  const int c4n = Dk / 4;
-  // every thread owns a fixed column group and a set of rows
-  float4 acc[RT];  // row i of this thread is r0 + i * rows_per_pass; only the first nrow entries are used
-  const int rows_per_pass = NT / c4n > 0 ? NT / c4n : 1;
-  const int c4 = tid % c4n, r0 = tid / c4n;
-  const int nrow = (RT - r0 + rows_per_pass - 1) / rows_per_pass;
+  const int M = p.M, Dk = p.Dk, N = p.N;
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  float acc[4][8];
 #pragma unroll
-  for (int i = 0; i < RT; ++i) acc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
   for (int src = 0; src < p.nsrc; ++src) {
-    __syncthreads();
-    const int q4 = M / 4;
-    for (int idx = tid; idx < RT * q4; idx += NT) {
-      const int t = idx / q4, c = (idx % q4) * 4;
-      float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (t0 + t < N) {
-        for (int part = 0; part < p.parts[src]; ++part) {
-          const float4 x = *reinterpret_cast<const float4*>(p.ds[src] + (int64_t)part * p.plane +
-                                                            ((int64_t)lane_id * N + t0 + t) * M + c);
-          a.x += x.x; a.y += x.y; a.z += x.z; a.w += x.w;
-        }
-      }
-      *reinterpret_cast<float4*>(ds_s + t * mp + c) = a;
-    }
-    __syncthreads();
-    if (tid < c4n * rows_per_pass) {
-      const int64_t lat_off = (int64_t)h * p.lat_stride_h[src];
-      for (int m = 0; m < M; ++m) {
-        float l0, l1, l2, l3;
-        {
-          const int64_t o = lat_off + (int64_t)m * p.lat_stride_m[src] + c4 * 4;
-          l0 = load1(p.lat[src], p.dtype, o);
-          l1 = load1(p.lat[src], p.dtype, o + 1);
-          l2 = load1(p.lat[src], p.dtype, o + 2);
-          l3 = load1(p.lat[src], p.dtype, o + 3);
-        }
-#pragma unroll
-        for (int i = 0; i < RT; ++i) {
-          if (i < nrow) {
-            const float d = ds_s[(r0 + i * rows_per_pass) * mp + m];
-            acc[i].x += d * l0; acc[i].y += d * l1; acc[i].z += d * l2; acc[i].w += d * l3;
+    for (int m0 = 0; m0 < M; m0 += RM) {
+      __syncthreads();
+      // dS tile (summed over the value-tile partials), zero outside the sequence / the latent range
+      for (int idx = tid; idx < RT * (RM / 4); idx += NT) {
+        const int t = idx / (RM / 4), c = (idx % (RM / 4)) * 4;
+        float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (t0 + t < N && m0 + c < M) {
+          for (int part = 0; part < p.parts[src]; ++part) {
+            const float4 x = __ldcs(reinterpret_cast<const float4*>(p.ds[src] + (int64_t)part * p.plane +
+                                                                    ((int64_t)lane_id * N + t0 + t) * M + m0 + c));
+            a.x += x.x; a.y += x.y; a.z += x.z; a.w += x.w;
           }
+        }
+        *reinterpret_cast<float4*>(&ds_s[t][c]) = a;
+      }
+      // latent rows m0 .. m0 + RM - 1, columns c0 .. c0 + RC - 1, as fp32
+      for (int idx = tid; idx < RM * (RC / 8); idx += NT) {
+        const int m = idx / (RC / 8), c = (idx % (RC / 8)) * 8;
+        float x[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        if (m0 + m < M && c0 + c < Dk)
+          load8(p.lat[src], p.dtype, (int64_t)h * p.lat_stride_h[src] + (int64_t)(m0 + m) * p.lat_stride_m[src] + c0 + c, x);
+        *reinterpret_cast<float4*>(&lat_s[m][c]) = make_float4(x[0], x[1], x[2], x[3]);
+        *reinterpret_cast<float4*>(&lat_s[m][c + 4]) = make_float4(x[4], x[5], x[6], x[7]);
+      }
+      __syncthreads();
+#pragma unroll 4
+      for (int m = 0; m < RM; ++m) {
+        const float4 l0 = *reinterpret_cast<const float4*>(&lat_s[m][tx * 8]);
+        const float4 l1 = *reinterpret_cast<const float4*>(&lat_s[m][tx * 8 + 4]);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float d = ds_s[ty * 4 + i][m];
+          acc[i][0] += d * l0.x; acc[i][1] += d * l0.y; acc[i][2] += d * l0.z; acc[i][3] += d * l0.w;
+          acc[i][4] += d * l1.x; acc[i][5] += d * l1.y; acc[i][6] += d * l1.z; acc[i][7] += d * l1.w;
         }
       }
     }
   }
-  if (tid < c4n * rows_per_pass) {
+  const int c = c0 + tx * 8;
+  if (c < Dk) {
 #pragma unroll
-    for (int i = 0; i < RT; ++i) {
-      const int t = t0 + r0 + i * rows_per_pass;
-      if (i < nrow && t < N)
-        store4(p.out, p.dtype, (((int64_t)b * N + t) * p.H + h) * Dk + c4 * 4, acc[i].x * p.scale, acc[i].y * p.scale,
-               acc[i].z * p.scale, acc[i].w * p.scale);
+    for (int i = 0; i < 4; ++i) {
+      const int t = t0 + ty * 4 + i;
+      if (t < N) {
+        const int64_t o = (((int64_t)b * N + t) * p.H + h) * Dk + c;
+        store4(p.out, p.dtype, o, acc[i][0] * p.scale, acc[i][1] * p.scale, acc[i][2] * p.scale, acc[i][3] * p.scale);
+        store4(p.out, p.dtype, o + 4, acc[i][4] * p.scale, acc[i][5] * p.scale, acc[i][6] * p.scale, acc[i][7] * p.scale);
+      }
     }
   }
 }
@@ -865,13 +871,10 @@ int bwd_exact(const flare_bwd_args_t& a, cudaStream_t stream) {
   }
 
   // ---- dK (+ dQ_dec): products of the dS planes with the latent banks ------------------------------
-  const size_t rows_smem = (size_t)RT * (f.M + 4) * 4;
-  if (rows_smem > 48 * 1024)
-    FLARE_CUDA_CHECK(cudaFuncSetAttribute(bwd_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)rows_smem));
   auto rows_launch = [&](RowsParams& r) -> int {
     r.plane = pl.plane; r.B = f.B; r.N = f.N; r.H = f.H; r.M = f.M; r.Dk = f.Dk; r.dtype = f.dtype; r.scale = f.scale;
-    dim3 g(f.B * f.H, (f.N + RT - 1) / RT);
-    bwd_rows_kernel<<<g, NT, rows_smem, stream>>>(r);
+    dim3 g(f.B * f.H, (f.N + RT - 1) / RT, (f.Dk + RC - 1) / RC);
+    bwd_rows_kernel<<<g, NT, 0, stream>>>(r);
     FLARE_CUDA_CHECK(cudaGetLastError());
     return FLARE_OK;
   };
