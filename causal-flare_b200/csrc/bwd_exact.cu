@@ -17,6 +17,7 @@
 // (4) latents: per-split partial dQ / dK_dec = dS^T Rows; (5) fixed-order sum of the partials
 // (deterministic: no atomics anywhere).
 #include "bwd_exact.cuh"
+#include <stdlib.h>
 
 #include <string.h>
 
@@ -48,6 +49,13 @@ struct BwdParams {
   int DT;
   int64_t plane;  // lanes * N * M
   void* dv_out;   // [B, N, H, Dv] contiguous, input dtype
+  // Sequence segments (token-causal read-out only; nseg == 1: one CTA walks the whole sequence).  grid.z walks
+  // segments seg_first .. ; the replay starts every segment from its exclusive prefix state, the reverse walk from
+  // the carries (b, c) of the segment to its right.
+  int seg_len, nseg, seg_first;
+  const float *in_m, *in_d, *in_u;   // [lanes][nseg][M], [lanes][nseg][M], [lanes][nseg][M][Dv]
+  float *seg_b, *seg_c, *seg_gam;    // [lanes][nseg][M][Dv], [lanes][nseg][M], [lanes][nseg][M]
+  int rev_mode;                      // reverse walk: 0 = gradients (carry-in when nseg > 1), 1 = carries only
 };
 
 // defined once per MM_MAX in {2, 8, 16, 32, 64}, each in its own translation unit; stage 0 = replay, 1 = reverse
@@ -88,14 +96,22 @@ __global__ void __launch_bounds__(NT, (MM_MAX * DD <= 32) ? 2 : 1) bwd_replay_ke
   const bool stablemax = p.variant == FLARE_STABLEMAX;
   const int dtype = p.dtype;
 
+  const int seg = p.seg_first + blockIdx.z;
+  const int tbeg = seg * p.seg_len, tend = min(N, tbeg + p.seg_len);
+  const bool carry_in = p.nseg > 1 && seg > 0;
+  const int64_t st = (int64_t)lane_id * p.nseg + seg;  // index of this segment's prefix state
+
   float U[MM_MAX][DD];
 #pragma unroll
   for (int mi = 0; mi < MM_MAX; ++mi)
 #pragma unroll
-    for (int j = 0; j < DD; ++j) U[mi][j] = 0.f;
+    for (int j = 0; j < DD; ++j) {
+      const int m = warp * mm + mi, col = dv0 + lane + 32 * j;
+      U[mi][j] = (carry_in && mi < mm && col < Dv) ? p.in_u[(st * M + m) * Dv + col] : 0.f;
+    }
   for (int m = tid; m < M; m += NT) {
-    m_run[m] = stablemax ? 0.f : kNegInf;
-    d_run[m] = 0.f;
+    m_run[m] = carry_in ? p.in_m[st * M + m] : (stablemax ? 0.f : kNegInf);
+    d_run[m] = carry_in ? p.in_d[st * M + m] : 0.f;
   }
   __syncthreads();
 
@@ -136,7 +152,7 @@ __global__ void __launch_bounds__(NT, (MM_MAX * DD <= 32) ? 2 : 1) bwd_replay_ke
   };
 
   if (p.block_size <= 1) {
-    for (int t0 = 0; t0 < N; t0 += BT) {
+    for (int t0 = tbeg; t0 < tend; t0 += BT) {
       __syncthreads();
       set_valid(t0);
       load_rows(ks, ldk, p.k, dtype, k_off, p.k_stride_n, t0, N, Dk, 0, Dk);
@@ -304,6 +320,7 @@ __global__ void __launch_bounds__(NT, (MM_MAX * DD <= 32) ? 2 : 1) bwd_reverse_k
   float* rho_in = base; base += mp;     // decay applied when stepping from the next tile / block into this one
   float* c_run = base; base += mp;
   float* esum = base; base += mp;
+  float* gam_run = base; base += mp;    // product of the decays applied so far (segment carries)
   float* gp = base; base += BT;
   float* dvpart = base; base += NW * BT * dvt;
   int* valid = reinterpret_cast<int*>(base);
@@ -311,20 +328,31 @@ __global__ void __launch_bounds__(NT, (MM_MAX * DD <= 32) ? 2 : 1) bwd_reverse_k
   const int mm = M / NW;
   const int dtype = p.dtype;
 
+  const int seg = p.seg_first + blockIdx.z;
+  const int tbeg = seg * p.seg_len, tend = min(N, tbeg + p.seg_len);
+  const int64_t row_base = (int64_t)lane_id * N;
+  const int64_t st = (int64_t)lane_id * p.nseg + seg;
+  // carries from the segment to the right (zero at the end of the sequence and in the carries-only mode)
+  const bool carry_in = p.nseg > 1 && p.rev_mode == 0 && tend < N;
+
   float Bc[MM_MAX][DD];
 #pragma unroll
   for (int mi = 0; mi < MM_MAX; ++mi)
 #pragma unroll
-    for (int j = 0; j < DD; ++j) Bc[mi][j] = 0.f;
+    for (int j = 0; j < DD; ++j) {
+      const int m = warp * mm + mi, col = dv0 + lane + 32 * j;
+      Bc[mi][j] = (carry_in && mi < mm && col < Dv) ? p.seg_b[(st * M + m) * Dv + col] : 0.f;
+    }
   for (int m = tid; m < M; m += NT) {
-    rho_in[m] = 0.f;
-    c_run[m] = 0.f;
+    // decay of the first step = 1 - e of the first token of the segment to the right
+    rho_in[m] = tend < N ? 1.0f - p.E[(row_base + tend) * M + m] : 0.f;
+    c_run[m] = carry_in ? p.seg_c[st * M + m] : 0.f;
     esum[m] = 0.f;
+    gam_run[m] = 1.0f;
   }
 
   const int64_t v_off = (int64_t)b * p.v_stride_b + (int64_t)h * p.v_stride_h;
   const int64_t dy_off = (int64_t)b * p.dy_stride_b + (int64_t)h * p.dy_stride_h;
-  const int64_t row_base = (int64_t)lane_id * N;
   float* dSe_part = p.dSe + (int64_t)dt * p.plane;
 
   auto load_plane = [&](float* dst, const float* src, int t0, int parts) {
@@ -410,9 +438,65 @@ __global__ void __launch_bounds__(NT, (MM_MAX * DD <= 32) ? 2 : 1) bwd_reverse_k
     }
   };
 
-  if (p.block_size <= 1) {
-    const int last_tile = ((N - 1) / BT) * BT;
-    for (int t0 = last_tile; t0 >= 0; t0 -= BT) {
+  if (p.block_size <= 1 && p.rev_mode == 1) {
+    // carries only: (b, c) at the first token of the segment for a zero carry-in, and the product of all decays
+    const int last_tile = ((tend - 1) / BT) * BT;
+    for (int t0 = last_tile; t0 >= tbeg; t0 -= BT) {
+      __syncthreads();
+      set_valid(t0);
+      load_rows(dos, dvt, p.dy, dtype, dy_off, p.dy_stride_n, t0, N, Dv, dv0, dvt);
+      load_plane(e_s, p.E, t0, 1);
+      load_plane(g_s, p.G, t0, 1);
+      load_plane(p_s, p.P, t0, p.DT);
+      __syncthreads();
+      for (int m = tid; m < M; m += NT) {
+        float c = c_run[m], rho = rho_in[m], gam = gam_run[m];
+        for (int t = BT - 1; t >= 0; --t) {
+          if (!valid[t]) continue;
+          c = g_s[t * mp + m] * p_s[t * mp + m] + rho * c;
+          gam *= rho;
+          rho = 1.0f - e_s[t * mp + m];
+        }
+        c_run[m] = c;
+        gam_run[m] = gam;
+      }
+#pragma unroll
+      for (int t = BT - 1; t >= 0; --t) {
+        if (!valid[t]) continue;
+        const bool next_in_tile = (t + 1 < BT) && valid[t + 1 < BT ? t + 1 : t];
+        float dd[DD];
+#pragma unroll
+        for (int j = 0; j < DD; ++j) dd[j] = dos[t * dvt + lane + 32 * j];
+#pragma unroll
+        for (int mi = 0; mi < MM_MAX; ++mi) {
+          if (mi < mm) {
+            const int m = warp * mm + mi;
+            const float rho = next_in_tile ? 1.0f - e_s[(t + 1 < BT ? t + 1 : t) * mp + m] : rho_in[m];
+            const float g = g_s[t * mp + m];
+#pragma unroll
+            for (int j = 0; j < DD; ++j) Bc[mi][j] = Bc[mi][j] * rho + g * dd[j];
+          }
+        }
+      }
+      __syncthreads();
+      for (int m = tid; m < M; m += NT) rho_in[m] = 1.0f - e_s[m];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int mi = 0; mi < MM_MAX; ++mi)
+#pragma unroll
+      for (int j = 0; j < DD; ++j) {
+        const int m = warp * mm + mi, col = dv0 + lane + 32 * j;
+        if (mi < mm && col < Dv) p.seg_b[(st * M + m) * Dv + col] = Bc[mi][j];
+      }
+    if (dt == 0)
+      for (int m = tid; m < M; m += NT) {
+        p.seg_c[st * M + m] = c_run[m];
+        p.seg_gam[st * M + m] = gam_run[m];
+      }
+  } else if (p.block_size <= 1) {
+    const int last_tile = ((tend - 1) / BT) * BT;
+    for (int t0 = last_tile; t0 >= tbeg; t0 -= BT) {
       __syncthreads();
       set_valid(t0);
       load_rows(vs, dvt, p.v, dtype, v_off, p.v_stride_n, t0, N, Dv, dv0, dvt);
@@ -658,9 +742,11 @@ struct LatParams {
 constexpr int LM = 64;    // latents per CTA
 constexpr int LDK = 128;  // score columns per CTA
 
+constexpr int LT = 32;    // token rows per shared-memory stage
+
 __global__ void __launch_bounds__(NT) bwd_lat_kernel(const LatParams p) {
-  __shared__ __align__(16) float ds_s[BT][LM + 4];
-  __shared__ __align__(16) float rw_s[BT][LDK + 4];
+  __shared__ __align__(16) float ds_s[LT][LM + 4];
+  __shared__ __align__(16) float rw_s[LT][LDK + 4];
   const int mtiles = (p.M + LM - 1) / LM;
   const int h = blockIdx.x / mtiles, m0 = (blockIdx.x % mtiles) * LM;
   const int split = blockIdx.y, dk0 = blockIdx.z * LDK;
@@ -675,36 +761,42 @@ __global__ void __launch_bounds__(NT) bwd_lat_kernel(const LatParams p) {
   const int64_t r_begin = (int64_t)split * p.rows_per_split;
   const int64_t r_end = min(total_rows, r_begin + p.rows_per_split);
   for (int src = 0; src < p.nsrc; ++src) {
-    for (int64_t r0 = r_begin; r0 < r_end; r0 += BT) {
+    for (int64_t r0 = r_begin; r0 < r_end; r0 += LT) {
       __syncthreads();
-      for (int idx = tid; idx < BT * LM; idx += NT) {
-        const int t = idx / LM, mi = idx % LM;
+      // dS tile: LT rows x LM latents, 128-bit loads, summed over the value-tile partials
+      for (int idx = tid; idx < LT * (LM / 4); idx += NT) {
+        const int t = idx / (LM / 4), c = (idx % (LM / 4)) * 4;
         const int64_t r = r0 + t;
-        float a = 0.f;
-        if (r < r_end && m0 + mi < M) {
-          const int64_t bb = r / N, tt = r % N;
-          const int64_t o = ((bb * p.H + h) * N + tt) * M + m0 + mi;
-          for (int part = 0; part < p.parts[src]; ++part) a += p.ds[src][(int64_t)part * p.plane + o];
+        float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (r < r_end && m0 + c < M) {
+          const int64_t bb = r / N, tt = r - bb * N;
+          const float* src_p = p.ds[src] + ((bb * p.H + h) * N + tt) * M + m0 + c;
+          for (int part = 0; part < p.parts[src]; ++part) {
+            const float4 x = __ldcs(reinterpret_cast<const float4*>(src_p + (int64_t)part * p.plane));
+            a.x += x.x; a.y += x.y; a.z += x.z; a.w += x.w;
+          }
         }
-        ds_s[t][mi] = a;
+        *reinterpret_cast<float4*>(&ds_s[t][c]) = a;
       }
-      for (int idx = tid; idx < BT * LDK; idx += NT) {
-        const int t = idx / LDK, di = idx % LDK;
+      // token rows: LT rows x LDK columns, 8 elements per load
+      for (int idx = tid; idx < LT * (LDK / 8); idx += NT) {
+        const int t = idx / (LDK / 8), c = (idx % (LDK / 8)) * 8;
         const int64_t r = r0 + t;
-        float a = 0.f;
-        if (r < r_end && dk0 + di < Dk) {
-          const int64_t bb = r / N, tt = r % N;
-          a = load1(p.rows[src], p.dtype,
-                    bb * p.rows_stride_b[src] + tt * p.rows_stride_n[src] + (int64_t)h * p.rows_stride_h[src] + dk0 + di);
+        float x[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        if (r < r_end && dk0 + c < Dk) {
+          const int64_t bb = r / N, tt = r - bb * N;
+          load8(p.rows[src], p.dtype,
+                bb * p.rows_stride_b[src] + tt * p.rows_stride_n[src] + (int64_t)h * p.rows_stride_h[src] + dk0 + c, x);
         }
-        rw_s[t][di] = a;
+        *reinterpret_cast<float4*>(&rw_s[t][c]) = make_float4(x[0], x[1], x[2], x[3]);
+        *reinterpret_cast<float4*>(&rw_s[t][c + 4]) = make_float4(x[4], x[5], x[6], x[7]);
       }
       __syncthreads();
-#pragma unroll
-      for (int t = 0; t < BT; ++t) {
+#pragma unroll 8
+      for (int t = 0; t < LT; ++t) {
         float dsv[4], rv[8];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) dsv[i] = ds_s[t][tm * 4 + i];
+        const float4 d4 = *reinterpret_cast<const float4*>(&ds_s[t][tm * 4]);
+        dsv[0] = d4.x; dsv[1] = d4.y; dsv[2] = d4.z; dsv[3] = d4.w;
 #pragma unroll
         for (int j = 0; j < 8; ++j) rv[j] = rw_s[t][td + 16 * j];
 #pragma unroll
@@ -738,14 +830,16 @@ size_t replay_smem(int M, int Dk, int dd) {
 }
 size_t reverse_smem(int M, int dd, bool stablemax) {
   const int mp = M + 4, dvt = 32 * dd;
-  return ((size_t)2 * BT * dvt + (size_t)(stablemax ? 6 : 5) * BT * mp + 3 * mp + BT + (size_t)NW * BT * dvt) * 4 +
+  return ((size_t)2 * BT * dvt + (size_t)(stablemax ? 6 : 5) * BT * mp + 4 * mp + BT + (size_t)NW * BT * dvt) * 4 +
          BT * sizeof(int);
 }
 
 struct BwdPlan {
   int dd, DT, splits, rows_per_split;
+  int nseg, seg_len;  // sequence segments of the replay / reverse walks (token-causal read-out only)
   int64_t plane;
   size_t off_E, off_G, off_W2, off_P, off_dSe, off_dSd, off_part_q, off_part_kd, total;
+  size_t off_seg_m, off_seg_d, off_seg_u, off_seg_b, off_seg_c, off_seg_gam;
 };
 
 BwdPlan plan_backward(const flare_bwd_args_t& a) {
@@ -753,6 +847,23 @@ BwdPlan plan_backward(const flare_bwd_args_t& a) {
   BwdPlan pl;
   pl.dd = walk_exact_dd(f.M, f.Dv);
   pl.DT = (f.Dv + 32 * pl.dd - 1) / (32 * pl.dd);
+  // The walks are sequential in the tokens; with few (lane, value tile) CTAs the sequence is cut into segments that
+  // run concurrently (prefix states for the replay, carries (b, c) for the reverse walk, see bwd_exact()).
+  pl.nseg = 1;
+  pl.seg_len = f.N;
+  if (f.block_size <= 1) {
+    const int64_t ctas = (int64_t)f.B * f.H * pl.DT, target = 4LL * sm_count();
+    int nseg = (int)((target + ctas - 1) / ctas);
+    if (const char* e = getenv("FLARE_BWD_NSEG")) nseg = atoi(e);
+    const int max_seg = f.N / 256;
+    if (nseg > max_seg) nseg = max_seg;
+    if (nseg > 1) {
+      int seg_len = (f.N + nseg - 1) / nseg;
+      seg_len = (seg_len + 127) / 128 * 128;
+      pl.seg_len = seg_len;
+      pl.nseg = (f.N + seg_len - 1) / seg_len;
+    }
+  }
   pl.plane = (int64_t)f.B * f.H * f.N * f.M;
   const bool stablemax = f.variant == FLARE_STABLEMAX;
   const bool shared_w = f.q_dec == nullptr && f.k_dec == nullptr;
@@ -763,7 +874,7 @@ BwdPlan plan_backward(const flare_bwd_args_t& a) {
   if (splits > max_splits) splits = max_splits;
   if (splits < 1) splits = 1;
   int64_t rps = (rows + splits - 1) / splits;
-  rps = (rps + BT - 1) / BT * BT;
+  rps = (rps + LT - 1) / LT * LT;
   splits = (rows + rps - 1) / rps;
   pl.splits = (int)splits;
   pl.rows_per_split = (int)rps;
@@ -783,6 +894,16 @@ BwdPlan plan_backward(const flare_bwd_args_t& a) {
   const size_t lat = (size_t)f.H * f.M * f.Dk;
   pl.off_part_q = take(lat * pl.splits);
   pl.off_part_kd = f.k_dec ? take(lat * pl.splits) : 0;
+  pl.off_seg_m = pl.off_seg_d = pl.off_seg_u = pl.off_seg_b = pl.off_seg_c = pl.off_seg_gam = 0;
+  if (pl.nseg > 1) {
+    const size_t ls = (size_t)f.B * f.H * pl.nseg;
+    pl.off_seg_m = take(ls * f.M);
+    pl.off_seg_d = take(ls * f.M);
+    pl.off_seg_u = take(ls * f.M * f.Dv);
+    pl.off_seg_b = take(ls * f.M * f.Dv);
+    pl.off_seg_c = take(ls * f.M);
+    pl.off_seg_gam = take(ls * f.M);
+  }
   pl.total = off;
   return pl;
 }
@@ -822,6 +943,27 @@ int launch_bwd_mm<FLARE_WALK_MM>(const BwdParams& p, int dd, dim3 grid, size_t s
 }
 #else
 
+// Right-to-left scan of the segment carries: on entry slot s holds (b, c) at the first token of segment s for a zero
+// carry-in and gam the product of its decays; on exit slot s holds the carry that enters segment s from the right.
+__global__ void __launch_bounds__(256) bwd_seg_scan_kernel(float* seg_b, float* seg_c, const float* seg_gam, int nseg,
+                                                           int64_t lanes, int M, int Dv) {
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t per_lane = (int64_t)M * (Dv + 1);  // Dv columns of b, then c
+  if (idx >= lanes * per_lane) return;
+  const int64_t lane_id = idx / per_lane;
+  const int r = (int)(idx % per_lane);
+  const int m = r / (Dv + 1), col = r % (Dv + 1);
+  float run = 0.f;
+  for (int s = nseg - 1; s >= 0; --s) {
+    const int64_t st = lane_id * nseg + s;
+    float* slot = col < Dv ? seg_b + (st * M + m) * Dv + col : seg_c + st * M + m;
+    const float own = s > 0 ? *slot : 0.f;  // segment 0 hands nothing on
+    const float gam = seg_gam[st * M + m];
+    *slot = run;
+    run = own + gam * run;
+  }
+}
+
 size_t bwd_exact_workspace_bytes(const flare_bwd_args_t& a) {
   if (a.fwd.B == 0 || a.fwd.N == 0) return 0;
   return plan_backward(a).total;
@@ -855,20 +997,48 @@ int bwd_exact(const flare_bwd_args_t& a, cudaStream_t stream) {
   p.dSe = reinterpret_cast<float*>(ws + pl.off_dSe);
   p.dSd = shared_w ? nullptr : reinterpret_cast<float*>(ws + pl.off_dSd);
   p.DT = pl.DT; p.plane = pl.plane; p.dv_out = a.dv;
+  p.nseg = pl.nseg; p.seg_len = pl.seg_len; p.seg_first = 0; p.rev_mode = 0;
+  const int64_t lanes = (int64_t)f.B * f.H;
+  if (pl.nseg > 1) {
+    float* seg_m = reinterpret_cast<float*>(ws + pl.off_seg_m);
+    float* seg_d = reinterpret_cast<float*>(ws + pl.off_seg_d);
+    float* seg_u = reinterpret_cast<float*>(ws + pl.off_seg_u);
+    // exclusive prefix state of every segment, from the forward kernels
+    const int rc = segment_prefix_states(&f, pl.nseg, pl.seg_len, seg_m, seg_d, seg_u, stream);
+    if (rc != FLARE_OK) return rc;
+    p.in_m = seg_m; p.in_d = seg_d; p.in_u = seg_u;
+    p.seg_b = reinterpret_cast<float*>(ws + pl.off_seg_b);
+    p.seg_c = reinterpret_cast<float*>(ws + pl.off_seg_c);
+    p.seg_gam = reinterpret_cast<float*>(ws + pl.off_seg_gam);
+  }
 
   const int mm = f.M / NW;
   const size_t smem1 = replay_smem(f.M, f.Dk, pl.dd), smem2 = reverse_smem(f.M, pl.dd, stablemax);
   if (smem1 > 227 * 1024 || smem2 > 227 * 1024) return FLARE_ERR_UNSUPPORTED;
-  dim3 grid(f.B * f.H, pl.DT);
-  for (int stage = 0; stage < 2; ++stage) {
-    int rc;
-    if (mm <= 2) rc = launch_bwd_mm<2>(p, pl.dd, grid, smem1, smem2, stream, stage);
-    else if (mm <= 8) rc = launch_bwd_mm<8>(p, pl.dd, grid, smem1, smem2, stream, stage);
-    else if (mm <= 16) rc = launch_bwd_mm<16>(p, pl.dd, grid, smem1, smem2, stream, stage);
-    else if (mm <= 32) rc = launch_bwd_mm<32>(p, pl.dd, grid, smem1, smem2, stream, stage);
-    else rc = launch_bwd_mm<64>(p, pl.dd, grid, smem1, smem2, stream, stage);
-    if (rc != FLARE_OK) return rc;
+  auto walk = [&](int stage, int seg_first, int seg_count, int rev_mode) -> int {
+    BwdParams q = p;
+    q.seg_first = seg_first;
+    q.rev_mode = rev_mode;
+    dim3 grid(f.B * f.H, pl.DT, seg_count);
+    if (mm <= 2) return launch_bwd_mm<2>(q, pl.dd, grid, smem1, smem2, stream, stage);
+    if (mm <= 8) return launch_bwd_mm<8>(q, pl.dd, grid, smem1, smem2, stream, stage);
+    if (mm <= 16) return launch_bwd_mm<16>(q, pl.dd, grid, smem1, smem2, stream, stage);
+    if (mm <= 32) return launch_bwd_mm<32>(q, pl.dd, grid, smem1, smem2, stream, stage);
+    return launch_bwd_mm<64>(q, pl.dd, grid, smem1, smem2, stream, stage);
+  };
+  int rcw = walk(0, 0, pl.nseg, 0);  // replay: planes e, g, p
+  if (rcw != FLARE_OK) return rcw;
+  if (pl.nseg > 1) {
+    // carries of segments 1 .. nseg-1 for a zero carry-in, then their right-to-left scan
+    rcw = walk(1, 1, pl.nseg - 1, 1);
+    if (rcw != FLARE_OK) return rcw;
+    const int64_t n = lanes * f.M * (f.Dv + 1);
+    bwd_seg_scan_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(p.seg_b, p.seg_c, p.seg_gam, pl.nseg, lanes, f.M,
+                                                                        f.Dv);
+    FLARE_CUDA_CHECK(cudaGetLastError());
   }
+  rcw = walk(1, 0, pl.nseg, 0);  // reverse walk: dV and the dS planes
+  if (rcw != FLARE_OK) return rcw;
 
   // ---- dK (+ dQ_dec): products of the dS planes with the latent banks ------------------------------
   auto rows_launch = [&](RowsParams& r) -> int {

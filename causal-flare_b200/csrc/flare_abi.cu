@@ -230,6 +230,36 @@ int forward_run(const flare_fwd_args_t* a, cudaStream_t stream) {
 }
 
 }  // namespace
+
+int segment_prefix_states(const flare_fwd_args_t* f, int nseg, int seg_len, float* seg_m, float* seg_d, float* seg_u,
+                          cudaStream_t stream) {
+  flare_fwd_args_t a = *f;
+  a.y = nullptr;
+  a.mask = nullptr;
+  a.lse_dec = a.lse_enc = nullptr;
+  memset(&a.state_in, 0, sizeof(a.state_in));
+  memset(&a.state_out, 0, sizeof(a.state_out));
+  a.state_out.m = seg_m; a.state_out.d = seg_d; a.state_out.u = seg_u;  // marks "a state is wanted" for the checks
+  FwdPlan pl{false, nseg, seg_len, (size_t)2 * a.M + (size_t)a.M * a.Dv, 0, 0, 0};
+  pl.use_tc = a.path != FLARE_PATH_EXACT && (seg_len % 128) == 0 && prefill_tc_supported(&a);
+  const int64_t lanes = (int64_t)a.B * a.H;
+  WalkParams w;
+  fill_walk(w, &a);
+  w.seg_len = seg_len;
+  w.nseg_total = nseg;
+  w.y = nullptr; w.write_y = 0;
+  w.out_m = seg_m; w.out_d = seg_d; w.out_u = seg_u;
+  w.out_lane_stride = nseg; w.out_seg_stride = 1; w.out_mode = 1;
+  int rc = launch_walk(&a, pl, w, nseg - 1, stream);  // local states of all segments but the last
+  if (rc != FLARE_OK) return rc;
+  FoldParams fp;
+  memset(&fp, 0, sizeof(fp));
+  fp.s_m = seg_m; fp.s_d = seg_d; fp.s_u = seg_u;
+  fp.lane_stride = nseg; fp.seg_stride = 1; fp.count = nseg; fp.mode = 0;
+  fp.lanes = lanes; fp.M = a.M; fp.Dv = a.Dv; fp.stablemax = a.variant == FLARE_STABLEMAX;
+  return launch_fold(fp, stream);  // exclusive scan from the empty state
+}
+
 }  // namespace flare
 
 using namespace flare;

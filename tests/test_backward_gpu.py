@@ -66,7 +66,8 @@ def test_no_upstream_gradient_returns_none(golden):
 
 
 @pytest.mark.parametrize("shape", [(1, 7, 2, 16, 16, 16), (2, 129, 2, 32, 64, 128), (1, 200, 1, 48, 32, 48),
-                                   (1, 96, 1, 256, 128, 128), (1, 40, 1, 512, 16, 32)])
+                                   (1, 96, 1, 256, 128, 128), (1, 40, 1, 512, 16, 32),
+                                   (1, 1024, 2, 32, 32, 64), (1, 1100, 1, 64, 64, 32)])  # long: sequence segments
 def test_ar_grads_fp32_shapes(shape):
     B, N, H, M, Dk, Dv = shape
     q, k, v, dy = orc.make_inputs(B, N, H, M, Dk, Dv, seed0=7, with_dy=True)
@@ -75,6 +76,23 @@ def test_ar_grads_fp32_shapes(shape):
     assert_close(got["dq"], ref["dQ"], what="dq", **GRAD32)
     assert_close(got["dk"], ref["dK"], what="dk", **GRAD32)
     assert_close(got["dv"], ref["dV"], what="dv", **GRAD32)
+
+
+def test_segmented_backward_separate_decode_weights_and_stablemax():
+    # long sequence, few lanes: the replay and reverse walks run as concurrent sequence segments
+    B, N, H, M, D = 1, 768, 2, 32, 32
+    q, k, v, dy = orc.make_inputs(B, N, H, M, D, seed0=17, with_dy=True)
+    g = torch.Generator().manual_seed(5)
+    qd, kd = torch.randn(B, N, H, D, generator=g), torch.randn(H, M, D, generator=g)
+    ref = orc.ar_backward_closed_form(q, k, v, dy, Q_dec=qd, K_dec=kd)
+    got = run_grads(lambda q, k, v, qd, kd: cf.flare_autoregressive_triton(q, k, v, Q_dec=qd, K_dec=kd),
+                    *to_dev(dy, q, k, v, qd, kd))
+    for name, key in (("dq", "dQ"), ("dk", "dK"), ("dv", "dV"), ("dq_dec", "dQ_dec"), ("dk_dec", "dK_dec")):
+        assert_close(got[name], ref[key], what=f"segmented {name}", **GRAD32)
+    ref = orc.ar_backward_closed_form(q, k, v, dy, variant="stablemax", power=2.0)
+    got = run_grads(lambda q, k, v, qd, kd: flare_autoregressive_stablemax_triton(q, k, v), *to_dev(dy, q, k, v))
+    for name, key in (("dq", "dQ"), ("dk", "dK"), ("dv", "dV")):
+        assert_close(got[name], ref[key], what=f"segmented stablemax {name}", **GRAD32)
 
 
 @pytest.mark.parametrize("variant", ["softmax", "stablemax"])
