@@ -196,6 +196,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   tc_fence_after_sync();
   const uint32_t tmem = misc->tmem_base;
   bool ok = true;
+  // No read-out wanted (segment states for a scan, prefix states): only E and U += E V are computed; R, W, the
+  // read-out MMAs and the token group are skipped.
+  const bool state_only = p.y == nullptr;
 
   if (warp == 13) {
     // ======================================= TMA producer =======================================
@@ -274,7 +277,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       for (int i = 0; ok && i < nchunks; ++i) {
         const uint32_t par = i & 1;
         TC_TRACE(2, i, 0);
-        if (i >= 1 && !(ok = issue_tail(i - 1))) break;
+        if (!state_only && i >= 1 && !(ok = issue_tail(i - 1))) break;
         TC_TRACE(2, i, 1);
         if (i + 1 < nchunks) {
           // the latent group has read S of chunk i: the columns can take the next chunk's scores
@@ -289,31 +292,34 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         const uint64_t eoff = (uint64_t)((i & 1) * (32768 >> 4));
         const uint64_t dek = de_k0 + eoff, dem = de_mn0 + eoff, drm = dr_mn0 + eoff;
         const uint64_t dv = dv_mn0 + (uint64_t)((i & 1) * (16384 >> 4));
-        // W = R^T E  (k = latents, 8 steps of 16 rows = 2048 bytes)
+        if (!state_only) {
+          // W = R^T E  (k = latents, 8 steps of 16 rows = 2048 bytes)
 #pragma unroll
-        for (int j = 0; j < 8; ++j) mma_ss(tmem + TM_W, drm + (j * 2048 >> 4), dem + (j * 2048 >> 4), ID_W, j > 0);
-        tc_commit(&misc->w_ready);
-        TC_TRACE(2, i, 5);
-        // Y = R^T U_bf16, Den0 = R^T d.  Single-buffered accumulators: the token group must have read chunk i - 1.
-        if (YB == 1 && i >= 1) {
-          if (!(ok = wait_or_abort(&misc->y_free, (i - 1) & 1, misc))) break;
-          tc_fence_after_sync();
-        }
+          for (int j = 0; j < 8; ++j) mma_ss(tmem + TM_W, drm + (j * 2048 >> 4), dem + (j * 2048 >> 4), ID_W, j > 0);
+          tc_commit(&misc->w_ready);
+          TC_TRACE(2, i, 5);
+          // Y = R^T U_bf16, Den0 = R^T d.  Single-buffered accumulators: the token group must have read chunk i - 1.
+          if (YB == 1 && i >= 1) {
+            if (!(ok = wait_or_abort(&misc->y_free, (i - 1) & 1, misc))) break;
+            tc_fence_after_sync();
+          }
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          mma_ss(tmem + TM_Y + (i & (YB - 1)) * 64, drm + (j * 2048 >> 4), du + (j * 2048 >> 4), ID_Y0, j > 0);
-          mma_ss(tmem + TM_DEN + (i & (YB - 1)) * 16, drm + (j * 2048 >> 4),
-                 db16 + (((j >> 2) * 2048 + (j & 3) * 32) >> 4), ID_DEN, j > 0);
+          for (int j = 0; j < 8; ++j) {
+            mma_ss(tmem + TM_Y + (i & (YB - 1)) * 64, drm + (j * 2048 >> 4), du + (j * 2048 >> 4), ID_Y0, j > 0);
+            mma_ss(tmem + TM_DEN + (i & (YB - 1)) * 16, drm + (j * 2048 >> 4),
+                   db16 + (((j >> 2) * 2048 + (j & 3) * 32) >> 4), ID_DEN, j > 0);
+          }
+          TC_TRACE(2, i, 6);
         }
-        TC_TRACE(2, i, 6);
         // U += E V_c  (k = tokens of the chunk)
 #pragma unroll
         for (int j = 0; j < 8; ++j)
           mma_ss(tmem + TM_U, dek + (((j >> 2) * 16384 + (j & 3) * 32) >> 4), dv + (j * 2048 >> 4), ID_U, 1);
         tc_commit(&misc->u_done);
+        if (state_only) tc_commit(&misc->v_empty[i & 1]);  // no read-out MMA will read this V stage
         TC_TRACE(2, i, 4);
       }
-      if (ok && nchunks > 0) ok = issue_tail(nchunks - 1);
+      if (!state_only && ok && nchunks > 0) ok = issue_tail(nchunks - 1);
     }
   } else if (warp < 8) {
     // ===================== latent group: 8 warps, thread = (latent = TMEM lane, half of the chunk's tokens) =====================
@@ -505,13 +511,15 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       // the upper half continues the lower half's running denominator; the lower half needs nothing from its partner
       // (except for blocks of 128 tokens, whose end lies in the upper half)
       float run = d_carry;
-      if (hf || (BLOCK && p.block == 128)) {
+      if (!state_only && (hf || (BLOCK && p.block == 128))) {
         if (!(ok = wait_or_abort(&misc->psum[q], par, misc))) break;
         run += misc->xsum[par][0][m];
         if (BLOCK && p.block == 128 && hf == 0) run = d_carry;  // lower half: only the wait was needed
       }
       if (tid == 0) TC_TRACE(0, i, 2);
-      if constexpr (!BLOCK) {
+      if (state_only) {
+        // no read-out: R is not needed
+      } else if constexpr (!BLOCK) {
         // phase b: D = running denominator, R = E a_m / D, R operand rows
 #pragma unroll
         for (int blk = 0; blk < 2; ++blk) {
@@ -583,11 +591,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       if (i > 0 && !(ok = wait_or_abort(&misc->u_done, (i - 1) & 1, misc))) break;
       tc_fence_after_sync();
       if (tid == 0) TC_TRACE(0, i, 4);
-      if (hf == 0)
+      if (hf == 0 && !state_only)
         *reinterpret_cast<__nv_bfloat16*>(smem + OFF_B16 + (m >> 6) * 2048 + ((m & 63) >> 3) * 16 + (m & 7) * 2) =
             __float2bfloat16_rn(d_carry);
-      {
-        const bool need = __any_sync(0xffffffffu, alpha != 1.0f);
+      const bool need = __any_sync(0xffffffffu, alpha != 1.0f);
+      if (!state_only || need) {
         uint32_t r[32];
         tmem_ld32(tl + TM_U + hf * 32, r);
         tmem_wait_ld();
@@ -597,14 +605,16 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           for (int k = 0; k < 32; ++k) r[k] = __float_as_uint(__uint_as_float(r[k]) * alpha);
           tmem_st32(tl + TM_U + hf * 32, r);
         }
+        if (!state_only) {
 #pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {
-          uint4 v;
-          v.x = pack_bf16(__uint_as_float(r[ch * 8 + 0]), __uint_as_float(r[ch * 8 + 1]));
-          v.y = pack_bf16(__uint_as_float(r[ch * 8 + 2]), __uint_as_float(r[ch * 8 + 3]));
-          v.z = pack_bf16(__uint_as_float(r[ch * 8 + 4]), __uint_as_float(r[ch * 8 + 5]));
-          v.w = pack_bf16(__uint_as_float(r[ch * 8 + 6]), __uint_as_float(r[ch * 8 + 7]));
-          *reinterpret_cast<uint4*>(smem + OFF_U + swz_chunk_off(m, hf * 4 + ch)) = v;
+          for (int ch = 0; ch < 4; ++ch) {
+            uint4 v;
+            v.x = pack_bf16(__uint_as_float(r[ch * 8 + 0]), __uint_as_float(r[ch * 8 + 1]));
+            v.y = pack_bf16(__uint_as_float(r[ch * 8 + 2]), __uint_as_float(r[ch * 8 + 3]));
+            v.z = pack_bf16(__uint_as_float(r[ch * 8 + 4]), __uint_as_float(r[ch * 8 + 5]));
+            v.w = pack_bf16(__uint_as_float(r[ch * 8 + 6]), __uint_as_float(r[ch * 8 + 7]));
+            *reinterpret_cast<uint4*>(smem + OFF_U + swz_chunk_off(m, hf * 4 + ch)) = v;
+          }
         }
         if (need) tmem_wait_st();
       }
@@ -655,7 +665,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                                   (int64_t)h * p.y_stride_h + value_col0<DKB, SPLIT>();
     // latent-group split: dense fp32 partials [group][B][N][H][DV] and log2 weight masses [group][B][N][H]
     const int64_t part_row0 = SPLIT ? (((int64_t)(blockIdx.z / DKB) * (gridDim.x / p.H) + b) * p.N) : 0;
-    for (int i = 0; ok && i < nchunks; ++i) {
+    for (int i = 0; !state_only && ok && i < nchunks; ++i) {
       const uint32_t par = i & 1;
       const int t0 = seg_begin + i * C;
       const int nvalid = min(C, seg_end - t0);

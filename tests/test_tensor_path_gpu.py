@@ -203,3 +203,16 @@ def test_tensor_path_block_causal(bs, Ml, Dw, B, N, H):
     # the public API takes the same kernel
     y2, aux = cf.flare_semi_autoregressive_trition(qc, kc, vc, block_size=bs, chunk_size=16, scale=sc)
     assert torch.equal(y2, y) and torch.equal(aux["LSE_enc"], le)
+
+
+@pytest.mark.parametrize("Ml, Dw", [(128, 64), (256, 128), (64, 128)])
+def test_tensor_path_state_only(Ml, Dw):
+    # no read-out wanted: the kernel skips R, W and the read-out MMAs and must still deliver the exact state
+    q, k, v = orc.make_inputs(2, 700, 2, Ml, Dw, seed0=51, dtype=torch.bfloat16)
+    sc = Dw ** -0.5
+    _, st_ref = orc.ar_forward(q, k, v, scale=sc, return_state=True)
+    y, st, _, _ = run(*to_dev(q, k, v), _lib.PATH_TENSOR, want_state=True, want_y=False, scale=sc)
+    assert y is None
+    assert_close(st["m"], st_ref["m"], what="m", atol=1e-4, rtol=1e-4)
+    assert_close(st["d"], st_ref["d"], what="d", atol=1e-3, rtol=2e-3)
+    assert orc.rel_l2(st["u"].cpu(), st_ref["u"]) < 3e-3
