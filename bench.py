@@ -279,6 +279,43 @@ def bench_decode(args, rank, world):
     }
 
 
+def bench_seqpar(args, rank, world):
+    """C5: block-causal long context, tokens sharded across the GPUs (state-only pass, all-gather of the span
+    states, fold of the lower ranks, span pass with carry-in).  One GPU: the whole sequence, no exchange."""
+    from causal_flare import _ops, parallel
+
+    B, N, H, M, D, bs = 2, 65536, 32, 256, 128, 64
+    span = N // world
+    g = torch.Generator(device="cuda").manual_seed(5 + rank)
+    q = torch.randn(H, M, D, generator=torch.Generator(device="cuda").manual_seed(5), device="cuda").bfloat16()
+    k = torch.randn(B, span, H, D, generator=g, device="cuda").bfloat16()
+    v = torch.randn(B, span, H, D, generator=g, device="cuda").bfloat16()
+    sc = D ** -0.5
+
+    def step():
+        if world == 1:
+            return _ops.forward(q, k, v, scale=sc, block_size=bs)[0]
+        return parallel.sequence_parallel_prefill(q, k, v, scale=sc, block_size=bs)[0]
+
+    for _ in range(max(args.warmup, 3)):
+        y = step()
+    steps = min(args.steps, 20)
+    barrier(world)
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(steps):
+        y = step()
+    t1.record()
+    barrier(world)
+    ms = max_over_ranks(t0.elapsed_time(t1), world) / steps
+    assert torch.isfinite(y.float()).all() and _ops.device_status() == 0
+    return {"metric": "block-causal long-context prefill throughput", "value": B * N / (ms * 1e-3) / 1e6, "unit": "Mtok/s",
+            "n_gpus": world, "steps": steps, "ms_per_step": ms, "scaling": "strong", "higher_is_better": True,
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"C5 semi-AR B={B} N={N} H={H} M={M} D={D} block={bs}, {span} tokens per GPU",
+                       "parallelism": f"sequence parallel over {world} GPU(s), one all-gather of span states per step"}}
+
+
 def bench_other_shapes():
     """Short device-timed runs of the other benchmark shapes (not the headline metric): training-shape forward and
     forward+backward, and the long block-causal shape on one GPU."""
@@ -363,7 +400,7 @@ def main():
     ap.add_argument("--skip-cpu", action="store_true")
     ap.add_argument("--decode-prefix", type=int, default=C3["prefix"])
     ap.add_argument("--decode-steps", type=int, default=C3["steps"])
-    ap.add_argument("--only", default="all", choices=["all", "prefill", "decode"],
+    ap.add_argument("--only", default="all", choices=["all", "prefill", "decode", "seqpar"],
                     help="profiling aid: run one section only (the JSON line then lacks the other)")
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-other", action="store_true", help="skip the short runs of the other benchmark shapes")
@@ -393,6 +430,15 @@ def main():
 
     assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU fallback)"
     rank, world, _ = dist_setup(args.gpus)
+    if args.only == "seqpar":
+        res = bench_seqpar(args, rank, world)
+        if rank == 0:
+            print(json.dumps(res))
+        if world > 1:
+            import torch.distributed as dist
+
+            dist.destroy_process_group()
+        return
     if args.only == "decode":
         dec = bench_decode(args, rank, world)
         if rank == 0:

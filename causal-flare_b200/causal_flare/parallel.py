@@ -41,19 +41,22 @@ def prefix_state(states, rank: int, merge_fn, empty_state):
     return merge_fn(empty_state, states[:rank])
 
 
-def sequence_parallel_prefill(Q, K_local, V_local, *, scale, group=None):
+def sequence_parallel_prefill(Q, K_local, V_local, *, scale, group=None, block_size=1):
     """Causal FLARE over a sequence whose tokens are sharded across the ranks of ``group``.
 
     K_local / V_local: this rank's span [B, N_local, H, D] (rank r holds tokens [r*N_local, (r+1)*N_local)).
+    ``block_size`` > 1 selects the block-causal (semi-autoregressive) read-out; spans must then be whole blocks.
     Returns (Y_local, state_after_this_rank's_span).
     """
     from . import _ops
     from .autoregressive.inference import _init_flare_recurrent_state
 
     rank = dist.get_rank(group)
-    B, _, H, _ = K_local.shape
+    B, n_local, H, _ = K_local.shape
     M, Dv = Q.shape[1], V_local.shape[-1]
-    # (1) span summary: final state only
+    if block_size > 1 and n_local % block_size != 0:
+        raise ValueError(f"a rank's span ({n_local} tokens) must be a multiple of block_size ({block_size})")
+    # (1) span summary: final state only (the kernels skip the read-out work)
     _, local, _, _ = _ops.forward(Q, K_local, V_local, scale=scale, want_state=True, want_y=False)
     # (2) one collective over NVLink
     states = exchange_states(local, group)
@@ -61,5 +64,5 @@ def sequence_parallel_prefill(Q, K_local, V_local, *, scale, group=None):
     empty = _init_flare_recurrent_state(B, H, M, Dv, K_local.device)
     carry = prefix_state(states, rank, _ops.merge_states, empty)
     # (4) the span itself, from the carry-in
-    Y, st, _, _ = _ops.forward(Q, K_local, V_local, scale=scale, state_in=carry, want_state=True)
+    Y, st, _, _ = _ops.forward(Q, K_local, V_local, scale=scale, state_in=carry, want_state=True, block_size=block_size)
     return Y, st
