@@ -187,6 +187,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   }
   // zero the denominator operand tile once (rows 1..15 stay zero for the whole kernel)
   for (int i = tid; i < 4096 / 16; i += NTHREADS) reinterpret_cast<uint4*>(smem + OFF_B16)[i] = make_uint4(0, 0, 0, 0);
+
   if (warp == 12) {
     tmem_alloc(&misc->tmem_base, TM_COLS);
     tmem_relinquish();
@@ -397,11 +398,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       if (nvalid == C && sc2 >= 0.f) {
         // the scale is monotone: take the maximum of the raw scores and scale once
 #pragma unroll
-        for (int k = 0; k < 32; k += 2) {
-          cm0 = fmaxf(cm0, __uint_as_float(ra[k]));
-          cm1 = fmaxf(cm1, __uint_as_float(ra[k + 1]));
-          cm2 = fmaxf(cm2, __uint_as_float(rb[k]));
-          cm3 = fmaxf(cm3, __uint_as_float(rb[k + 1]));
+        for (int k = 0; k < 32; k += 4) {
+          cm0 = fmax3(cm0, __uint_as_float(ra[k]), __uint_as_float(ra[k + 1]));
+          cm1 = fmax3(cm1, __uint_as_float(ra[k + 2]), __uint_as_float(ra[k + 3]));
+          cm2 = fmax3(cm2, __uint_as_float(rb[k]), __uint_as_float(rb[k + 1]));
+          cm3 = fmax3(cm3, __uint_as_float(rb[k + 2]), __uint_as_float(rb[k + 3]));
         }
         cm0 = fmaxf(fmaxf(cm0, cm1), fmaxf(cm2, cm3)) * sc2;
         cm1 = cm2 = cm3 = cm0;
@@ -673,7 +674,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       if (!(ok = wait_or_abort(&misc->w_ready, par, misc))) break;
       tc_fence_after_sync();
       if (tid == 256) TC_TRACE(1, i, 0);
-      float rowsum = 0.f;
+      float rowsum = 0.f;  // of the bf16-rounded masked W, the values the read-out MMA multiplies
       // last column (token of the chunk) this row may see: itself, or the end of its block
       const int be = BLOCK ? (tt | (p.block - 1)) : tt;
 #pragma unroll 1
@@ -683,13 +684,23 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           uint32_t r[32];
           tmem_ld32(tl + TM_W + j * 32, r);
           tmem_wait_ld();
+          if (BLOCK ? (j * 32 + 31 <= be) : (j < wq)) {
+            // the whole 32-column block is visible to every row of this warp
 #pragma unroll
-          for (int k = 0; k < 32; k += 2) {
-            const float w0 = (BLOCK ? (j * 32 + k <= be) : (j < wq || k <= lane)) ? __uint_as_float(r[k]) : 0.f;
-            const float w1 = (BLOCK ? (j * 32 + k + 1 <= be) : (j < wq || k + 1 <= lane)) ? __uint_as_float(r[k + 1]) : 0.f;
-            const uint32_t pk = pack_bf16(w0, w1);
-            wp[k >> 1] = pk;
-            rowsum += __uint_as_float(pk << 16) + __uint_as_float(pk & 0xffff0000u);
+            for (int k = 0; k < 32; k += 2) {
+              const uint32_t pk = pack_bf16(__uint_as_float(r[k]), __uint_as_float(r[k + 1]));
+              wp[k >> 1] = pk;
+              rowsum += __uint_as_float(pk << 16) + __uint_as_float(pk & 0xffff0000u);
+            }
+          } else {
+#pragma unroll
+            for (int k = 0; k < 32; k += 2) {
+              const float w0 = (BLOCK ? (j * 32 + k <= be) : (k <= lane)) ? __uint_as_float(r[k]) : 0.f;
+              const float w1 = (BLOCK ? (j * 32 + k + 1 <= be) : (k + 1 <= lane)) ? __uint_as_float(r[k + 1]) : 0.f;
+              const uint32_t pk = pack_bf16(w0, w1);
+              wp[k >> 1] = pk;
+              rowsum += __uint_as_float(pk << 16) + __uint_as_float(pk & 0xffff0000u);
+            }
           }
         } else {
 #pragma unroll
