@@ -202,6 +202,9 @@ int launch_decode_step(const DecodeParams& p, cudaStream_t stream) {
   const size_t smem = (size_t)(3 * p.M + 2 * p.Dk + p.Dv + NW) * 4 + NT * 16;
   // Measured on B200 at B=64, H=32, M=256, D=128 (us per step): <2,4,8> 112.0, <8,8,4> 113.8, <4,8,4> 115.6,
   // <4,4,6> 116.8, <4,8,1> 141.9, <4,16,2> 157.8: occupancy (8 CTAs of 32 registers per SM) beats deeper unrolling.
+  // Also measured and rejected: 128-thread CTAs at 16 per SM (121.7), and moving the state with bulk async copies
+  // through a shared-memory ring (4 x 8 KB: 115.5, 4 x 16 KB: 131.3, 8 x 16 KB: 207.2) - the per-lane score and
+  // softmax phases are hidden best by many resident CTAs, not by more bytes in flight per CTA.
   return launch_variant<2, 4, 8>(p, smem, stream);
 }
 
