@@ -172,26 +172,34 @@ def bench_prefill(args, rank, world):
     yh = torch.empty(y.shape, dtype=y.dtype).pin_memory()
     kd, vd = torch.empty_like(k), torch.empty_like(v)
 
-    # the batch is cut into slices that travel on two streams: the upload of one slice overlaps the kernel and the
-    # download of the previous one (PCIe is full duplex)
-    n_slices = 4
+    # The batch is cut into slices that flow through three streams (upload, kernels, download) linked by events, so
+    # the upload engine never waits for a download and consecutive steps overlap (PCIe is full duplex).
+    n_slices = 8
     bs = cfg["B"] // n_slices
-    streams = [torch.cuda.Stream() for _ in range(2)]
+    s_in, s_cp, s_out = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
+    ev_in = [torch.cuda.Event() for _ in range(n_slices)]
+    ev_cp = [torch.cuda.Event() for _ in range(n_slices)]
 
     def e2e_step():
-        cur = torch.cuda.current_stream()
-        for st in streams:
-            st.wait_stream(cur)
         for sl in range(n_slices):
-            st = streams[sl % 2]
             rows = slice(sl * bs, (sl + 1) * bs)
-            with torch.cuda.stream(st):
+            with torch.cuda.stream(s_in):
+                s_in.wait_event(ev_cp[sl])  # the previous step's kernels have read this slice of the device buffers
                 kd[rows].copy_(kh[rows], non_blocking=True)
                 vd[rows].copy_(vh[rows], non_blocking=True)
+                ev_in[sl].record(s_in)
+            with torch.cuda.stream(s_cp):
+                s_cp.wait_event(ev_in[sl])
                 yy = cf.flare_autoregressive_triton(q, kd[rows], vd[rows])
+                ev_cp[sl].record(s_cp)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(ev_cp[sl])
                 yh[rows].copy_(yy, non_blocking=True)
-                yy.record_stream(st)
-        for st in streams:
+                yy.record_stream(s_out)
+
+    def e2e_join():
+        cur = torch.cuda.current_stream()
+        for st in (s_in, s_cp, s_out):
             cur.wait_stream(st)
 
     e2e_steps = max(2, min(args.steps, 5))
@@ -199,20 +207,26 @@ def bench_prefill(args, rank, world):
         e2e_steps = 0
         return dict(value=value, ms_per_step=ms / args.steps, e2e=None, roofline=_roofline(cfg, q, k, v, y, kern_ms),
                     clocks=clk.summary(), gpu_launches=launches, tokens_per_step=tokens)
+    for st in (s_in, s_cp, s_out):
+        st.wait_stream(torch.cuda.current_stream())
     e2e_step()
+    e2e_join()
     barrier(world)
     s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     s0.record()
+    for st in (s_in, s_cp, s_out):
+        st.wait_stream(torch.cuda.current_stream())
     for _ in range(e2e_steps):
         e2e_step()
+    e2e_join()
     s1.record()
     barrier(world)
     e2e_ms = max_over_ranks(s0.elapsed_time(s1), world)
     e2e = {
         "value": world * tokens * e2e_steps / (e2e_ms * 1e-3) / 1e6, "unit": "Mtok/s",
         "h2d_bytes_per_step": kh.numel() * 2 + vh.numel() * 2, "d2h_bytes_per_step": yh.numel() * 2,
-        "steps": e2e_steps, "call": "causal_flare.flare_autoregressive_triton(q, k[rows], v[rows]) per batch slice of 2, "
-        "two streams, pinned host K/V in and Y out",
+        "steps": e2e_steps, "call": "causal_flare.flare_autoregressive_triton(q, k[rows], v[rows]) per batch row, "
+        "upload / kernel / download streams linked by events, pinned host K/V in and Y out",
     }
 
     return dict(value=value, ms_per_step=ms / args.steps, e2e=e2e, roofline=_roofline(cfg, q, k, v, y, kern_ms),

@@ -111,6 +111,18 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, Mi
   }
 }
 
+// stablemax encoder weight with approximate reciprocal; powers 1..4 by multiplication
+__device__ __forceinline__ float sigma_fast(float x, float p) {
+  const float base = 1.0f + fabsf(x);
+  float r;
+  if (p == 1.0f) r = base;
+  else if (p == 2.0f) r = base * base;
+  else if (p == 3.0f) r = base * base * base;
+  else if (p == 4.0f) { const float b2 = base * base; r = b2 * b2; }
+  else r = exp2f(p * __log2f(base));
+  return x >= 0.0f ? r : rcp_approx(r);
+}
+
 // grid.z = latent group * DKB + value slice.  First value column of this CTA's slice (a compile-time zero when there
 // is one slice) and first latent of its group (zero without the latent split).
 template <int DKB, bool SPLIT>
@@ -127,7 +139,7 @@ __device__ __forceinline__ int latent0() {
 // The kernel instances are compiled in separate translation units (FLARE_TC_UNIT = 0..3: head width 64 / 128, without /
 // with the latent-group split) to keep build times short; the unit without FLARE_TC_UNIT holds the host side.
 template <int UNIT>
-int launch_prefill_tc_unit(bool padded, bool block, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
+int launch_prefill_tc_unit(bool padded, int mode, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                            const TcParams& p, dim3 grid, cudaStream_t stream);
 
 #ifdef FLARE_TC_UNIT
@@ -138,11 +150,15 @@ int launch_prefill_tc_unit(bool padded, bool block, const CUtensorMap& tq, const
 // BLOCK: block-causal (semi-autoregressive) read-out with blocks of 16, 32, 64 or 128 tokens: a token reads the state
 //        at the end of its block, so the denominator of a block's tokens is the one at the block's end and the mask
 //        of W is "column <= end of the row's block"
-template <bool PADDED, int DKB, bool SPLIT, bool BLOCK>
+// MODE 2 (STABLE): stablemax encoder weights sigma(s) = (1+s)^p | (1-s)^-p.  The encoder side then has no frames
+//        (E = sigma(s), D = plain running sum, the state is never rescaled); the decode weights stay a softmax over
+//        the latents, whose numerator exp2(s - c) a_m is formed with the same running-max machinery as before.
+template <bool PADDED, int DKB, bool SPLIT, int MODE>
 __global__ void __launch_bounds__(NTHREADS, 1)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                   const __grid_constant__ CUtensorMap tm_v, const TcParams p) {
   using L = Lay<DKB>;
+  constexpr bool BLOCK = MODE == 1, STABLE = MODE == 2;
   constexpr int OFF_K = L::OFF_K, OFF_V = L::OFF_V, OFF_E = L::OFF_E, OFF_R = L::OFF_R, OFF_U = L::OFF_U,
                 OFF_B16 = L::OFF_B16, OFF_Q = L::OFF_Q, OFF_MISC = L::OFF_MISC, YB = L::YB;
   constexpr bool Q_SMEM = L::Q_SMEM;
@@ -340,7 +356,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       c2 = 0.f;
       dsum = 1.f;
     } else if (p.in_m != nullptr) {
-      c2 = p.in_m[st_idx * p.M + latent0<DKB, SPLIT>() + m] * kLog2e;
+      // (stablemax: the carried m is a constant zero and not a frame; the decode frame starts empty)
+      if (!STABLE) c2 = p.in_m[st_idx * p.M + latent0<DKB, SPLIT>() + m] * kLog2e;
       dsum = p.in_d[st_idx * p.M + latent0<DKB, SPLIT>() + m];
     }
     float d_prev = 0.f;                                  // denominator before the chunk in flight, in its frame
@@ -429,7 +446,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         dsum = d_prev + (misc->xsum[par ^ 1][0][m] + misc->xsum[par ^ 1][1][m]);
         c_new = fmaxf(c2, fmaxf(misc->xmax[par ^ 1][0][m], misc->xmax[par ^ 1][1][m]));
       }
-      float alpha = ex2_approx(c2 - c_new);  // 0 when the old state is empty
+      float alpha = STABLE ? 1.0f : ex2_approx(c2 - c_new);  // 0 when the old state is empty
       // kappa: common frame of the decode weights = max over latents of the running max.  Chunk 0 synchronises;
       // later chunks use the value published during the previous chunk (one chunk stale, which only changes a
       // per-token scale that cancels in y).
@@ -458,7 +475,21 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       // phase a: E for the 64 tokens of this half (in place of the scores), their sum, E operand rows
       float tot0 = 0.f, tot1 = 0.f;
       float g16[4] = {0.f, 0.f, 0.f, 0.f};  // BLOCK: sums of the four groups of 16 tokens of this half
-      if (nvalid == C) {
+      if constexpr (STABLE) {
+        // encoder weights sigma(s): packed and stored 8 tokens at a time; the raw scores stay in ra / rb for phase b
+#pragma unroll
+        for (int ch = 0; ch < 8; ++ch) {
+          float sg[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const float raw = __uint_as_float(ch < 4 ? ra[ch * 8 + j] : rb[(ch - 4) * 8 + j]);
+            sg[j] = (tok0 + ch * 8 + j < nvalid) ? sigma_fast(raw * p.scale, p.power) : 0.f;
+            tot0 += sg[j];
+          }
+          *reinterpret_cast<uint4*>(e_row + swz_chunk_off(m, ch)) =
+              make_uint4(pack_bf16(sg[0], sg[1]), pack_bf16(sg[2], sg[3]), pack_bf16(sg[4], sg[5]), pack_bf16(sg[6], sg[7]));
+        }
+      } else if (nvalid == C) {
 #pragma unroll
         for (int k = 0; k < 32; ++k) {
           const float e0 = ex2_approx(__uint_as_float(ra[k]) * sc2 - c_new);
@@ -495,6 +526,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       }
       misc->xsum[par][hf][m] = tot0 + tot1;
       warp_arrive(&misc->psum[q], lane);
+      if constexpr (!STABLE)
 #pragma unroll
       for (int ch = 0; ch < 4; ++ch) {
         *reinterpret_cast<uint4*>(e_row + swz_chunk_off(m, ch)) =
@@ -520,6 +552,26 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       if (tid == 0) TC_TRACE(0, i, 2);
       if (state_only) {
         // no read-out: R is not needed
+      } else if constexpr (STABLE) {
+        // phase b, stablemax: D = running sum of sigma (recomputed), decode numerator exp2(s - c) a_m, R = numerator / D
+#pragma unroll
+        for (int blk = 0; blk < 2; ++blk) {
+          uint32_t rp[16];
+#pragma unroll
+          for (int k = 0; k < 32; k += 2) {
+            const float s0 = __uint_as_float(blk ? rb[k] : ra[k]), s1 = __uint_as_float(blk ? rb[k + 1] : ra[k + 1]);
+            const int tk = tok0 + blk * 32 + k;
+            run += (tk < nvalid) ? sigma_fast(s0 * p.scale, p.power) : 0.f;
+            const float r0 = ex2_approx(s0 * sc2 - c_new) * (a_m * rcp_approx(run));
+            run += (tk + 1 < nvalid) ? sigma_fast(s1 * p.scale, p.power) : 0.f;
+            const float r1 = ex2_approx(s1 * sc2 - c_new) * (a_m * rcp_approx(run));
+            rp[k >> 1] = pack_bf16(r0, r1);
+          }
+#pragma unroll
+          for (int ch = 0; ch < 4; ++ch)
+            *reinterpret_cast<uint4*>(r_row + swz_chunk_off(m, blk * 4 + ch)) =
+                make_uint4(rp[ch * 4], rp[ch * 4 + 1], rp[ch * 4 + 2], rp[ch * 4 + 3]);
+        }
       } else if constexpr (!BLOCK) {
         // phase b: D = running denominator, R = E a_m / D, R operand rows
 #pragma unroll
@@ -632,9 +684,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         ok = wait_or_abort(&misc->u_done, lp, misc) && wait_or_abort(&misc->psum[q], lp, misc);
         if (ok) {
           dsum = d_prev + (misc->xsum[lp][0][m] + misc->xsum[lp][1][m]);
-          const float c_true = fmaxf(c2, fmaxf(misc->xmax[lp][0][m], misc->xmax[lp][1][m]));
-          fin = ex2_approx(c2 - c_true);
-          c2 = c_true;
+          if (!STABLE) {
+            const float c_true = fmaxf(c2, fmaxf(misc->xmax[lp][0][m], misc->xmax[lp][1][m]));
+            fin = ex2_approx(c2 - c_true);
+            c2 = c_true;
+          }
         }
       }
       tc_fence_after_sync();
@@ -642,7 +696,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         const int64_t so = (int64_t)lane_id * p.out_lane_stride + (int64_t)seg * p.out_seg_stride;
         const int mg = latent0<DKB, SPLIT>() + m;  // latent index in the whole bank
         if (hf == 0 && live && value_col0<DKB, SPLIT>() == 0) {
-          p.out_m[so * p.M + mg] = c2 * kLn2;
+          p.out_m[so * p.M + mg] = STABLE ? 0.f : c2 * kLn2;
           p.out_d[so * p.M + mg] = dsum * fin;
         }
         uint32_t r[32];
@@ -777,10 +831,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 
 namespace {
 
-template <bool PADDED, int DKB, bool SPLIT, bool BLOCK>
+template <bool PADDED, int DKB, bool SPLIT, int MODE>
 int launch_instance(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const TcParams& p, dim3 grid,
                     cudaStream_t stream) {
-  auto kern = prefill_tc_kernel<PADDED, DKB, SPLIT, BLOCK>;
+  auto kern = prefill_tc_kernel<PADDED, DKB, SPLIT, MODE>;
   FLARE_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Lay<DKB>::SMEM_BYTES));
   kern<<<grid, NTHREADS, Lay<DKB>::SMEM_BYTES, stream>>>(tq, tk, tv, p);
   FLARE_CUDA_CHECK(cudaGetLastError());
@@ -790,25 +844,28 @@ int launch_instance(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensor
 }  // namespace
 
 template <>
-int launch_prefill_tc_unit<FLARE_TC_UNIT>(bool padded, bool block, const CUtensorMap& tq, const CUtensorMap& tk,
+int launch_prefill_tc_unit<FLARE_TC_UNIT>(bool padded, int mode, const CUtensorMap& tq, const CUtensorMap& tk,
                                           const CUtensorMap& tv, const TcParams& p, dim3 grid, cudaStream_t stream) {
   constexpr int DKB = 1 + (FLARE_TC_UNIT & 1);
   constexpr bool SPLIT = (FLARE_TC_UNIT >> 1) != 0;
-  if (block)
-    return padded ? launch_instance<true, DKB, SPLIT, true>(tq, tk, tv, p, grid, stream)
-                  : launch_instance<false, DKB, SPLIT, true>(tq, tk, tv, p, grid, stream);
-  return padded ? launch_instance<true, DKB, SPLIT, false>(tq, tk, tv, p, grid, stream)
-                : launch_instance<false, DKB, SPLIT, false>(tq, tk, tv, p, grid, stream);
+  if (mode == 1)
+    return padded ? launch_instance<true, DKB, SPLIT, 1>(tq, tk, tv, p, grid, stream)
+                  : launch_instance<false, DKB, SPLIT, 1>(tq, tk, tv, p, grid, stream);
+  if (mode == 2)
+    return padded ? launch_instance<true, DKB, SPLIT, 2>(tq, tk, tv, p, grid, stream)
+                  : launch_instance<false, DKB, SPLIT, 2>(tq, tk, tv, p, grid, stream);
+  return padded ? launch_instance<true, DKB, SPLIT, 0>(tq, tk, tv, p, grid, stream)
+                : launch_instance<false, DKB, SPLIT, 0>(tq, tk, tv, p, grid, stream);
 }
 
 #else  // host side and the merge kernel
 
 __device__ int g_tc_error = 0;
 
-template <> int launch_prefill_tc_unit<0>(bool, bool, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const TcParams&, dim3, cudaStream_t);
-template <> int launch_prefill_tc_unit<1>(bool, bool, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const TcParams&, dim3, cudaStream_t);
-template <> int launch_prefill_tc_unit<2>(bool, bool, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const TcParams&, dim3, cudaStream_t);
-template <> int launch_prefill_tc_unit<3>(bool, bool, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const TcParams&, dim3, cudaStream_t);
+template <> int launch_prefill_tc_unit<0>(bool, int, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const TcParams&, dim3, cudaStream_t);
+template <> int launch_prefill_tc_unit<1>(bool, int, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const TcParams&, dim3, cudaStream_t);
+template <> int launch_prefill_tc_unit<2>(bool, int, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const TcParams&, dim3, cudaStream_t);
+template <> int launch_prefill_tc_unit<3>(bool, int, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const TcParams&, dim3, cudaStream_t);
 
 // -------------------------------------------------------------------------------------------------
 // host side
@@ -856,7 +913,9 @@ bool prefill_tc_supported(const flare_fwd_args_t* a) {
   const bool block_ok = bs == 1 || ((bs == 16 || bs == 32 || bs == 64 || bs == 128) && a->N % bs == 0);
   // the log normalisers are emitted in block-causal mode only (the token-causal entry points never ask for them)
   const bool lse_ok = (a->lse_enc == nullptr && a->lse_dec == nullptr) || bs > 1;
-  return a->dtype == FLARE_BF16 && a->variant == FLARE_SOFTMAX && block_ok && lse_ok && a->M <= 4 * M && a->M >= 16 &&
+  // stablemax encoder weights: token-causal only
+  const bool variant_ok = a->variant == FLARE_SOFTMAX || (a->variant == FLARE_STABLEMAX && bs == 1 && a->power > 0.f);
+  return a->dtype == FLARE_BF16 && variant_ok && block_ok && lse_ok && a->M <= 4 * M && a->M >= 16 &&
          (a->M % 16) == 0 && (a->Dk == 64 || a->Dk == 128) && a->Dv == a->Dk && a->q_dec == nullptr &&
          a->k_dec == nullptr && a->mask == nullptr && a->N >= 1;
 }
@@ -926,6 +985,7 @@ int launch_prefill_tc(const flare_fwd_args_t* a, const TcParams& p_in, int nseg_
     p.err = reinterpret_cast<int*>(err);
   }
   p.block = a->block_size;
+  p.power = a->power;
   p.lse_dec = a->lse_dec;
   p.lse_enc = a->lse_enc;
   if (p.y == nullptr) p.lse_dec = p.lse_enc = nullptr;  // state-only passes emit nothing else
@@ -949,14 +1009,14 @@ int launch_prefill_tc(const flare_fwd_args_t* a, const TcParams& p_in, int nseg_
   const int groups = prefill_tc_latent_groups(a);
   const dim3 grid(a->B * a->H, nseg_grid, a->Dv / D * groups);
   const bool padded = (a->M % M) != 0;
-  const bool block = a->block_size > 1;
+  const int mode = a->variant == FLARE_STABLEMAX ? 2 : (a->block_size > 1 ? 1 : 0);
   int rc;
   if (a->Dk == 64)
-    rc = groups > 1 ? launch_prefill_tc_unit<2>(padded, block, tq, tk, tv, p, grid, stream)
-                    : launch_prefill_tc_unit<0>(padded, block, tq, tk, tv, p, grid, stream);
+    rc = groups > 1 ? launch_prefill_tc_unit<2>(padded, mode, tq, tk, tv, p, grid, stream)
+                    : launch_prefill_tc_unit<0>(padded, mode, tq, tk, tv, p, grid, stream);
   else
-    rc = groups > 1 ? launch_prefill_tc_unit<3>(padded, block, tq, tk, tv, p, grid, stream)
-                    : launch_prefill_tc_unit<1>(padded, block, tq, tk, tv, p, grid, stream);
+    rc = groups > 1 ? launch_prefill_tc_unit<3>(padded, mode, tq, tk, tv, p, grid, stream)
+                    : launch_prefill_tc_unit<1>(padded, mode, tq, tk, tv, p, grid, stream);
   if (rc != FLARE_OK || groups == 1 || p.y == nullptr) return rc;
   const int64_t rows = (int64_t)a->B * a->N * a->H;
   const int64_t threads = rows * (a->Dv / 8);

@@ -25,6 +25,7 @@ struct TcParams {
   int out_mode;  // 0: none, 1: every segment, 2: last segment only
   int nseg_total;
   int block;                 // 1 = token-causal; 16, 32, 64, 128 = block-causal
+  float power;               // stablemax exponent (stablemax encoder only)
   float *lse_dec, *lse_enc;  // optional outputs, fp32 natural log: [B, H, N] and [B, H, N / block, M]
   int* err;                  // device error word (bit 0: a wait gave up, bit 1: numeric domain exceeded)
   long long* trace;  // optional diagnostic cycle stamps of CTA (0, 0), see TC_TRACE; null in normal use

@@ -216,3 +216,25 @@ def test_tensor_path_state_only(Ml, Dw):
     assert_close(st["m"], st_ref["m"], what="m", atol=1e-4, rtol=1e-4)
     assert_close(st["d"], st_ref["d"], what="d", atol=1e-3, rtol=2e-3)
     assert orc.rel_l2(st["u"].cpu(), st_ref["u"]) < 3e-3
+
+
+@pytest.mark.parametrize("power, Ml, Dw, B, N, H", [(2.0, 128, 64, 1, 256, 1), (1.0, 64, 128, 2, 520, 2), (3.0, 256, 128, 1, 700, 2),
+                                                    (2.5, 128, 64, 2, 384, 1), (2.0, 128, 64, 1, 4096, 1)])
+def test_tensor_path_stablemax(power, Ml, Dw, B, N, H):
+    # stablemax encoder weights on the tensor path: no frames on the encoder side, softmax decode weights
+    q, k, v = orc.make_inputs(B, N, H, Ml, Dw, seed0=61, dtype=torch.bfloat16)
+    sc = Dw ** -0.5
+    ref, st_ref = orc.ar_forward(q, k, v, scale=sc, variant="stablemax", power=power, return_state=True)
+    qc, kc, vc = to_dev(q, k, v)
+    y, st, _, _ = run(qc, kc, vc, _lib.PATH_TENSOR, variant=_lib.STABLEMAX, power=power, want_state=True, scale=sc)
+    assert_bf16_gate(y, ref, f"stablemax tensor path p={power} M={Ml} D={Dw}")
+    assert_close(st["d"], st_ref["d"], what="d", atol=1e-3, rtol=2e-3)
+    assert orc.rel_l2(st["u"].cpu(), st_ref["u"]) < 3e-3
+    y_e, _, _, _ = run(qc, kc, vc, _lib.PATH_EXACT, variant=_lib.STABLEMAX, power=power, scale=sc)
+    assert_bf16_gate(y, y_e.float(), "stablemax tensor vs exact")
+    h = (N // 2) // 16 * 16
+    _, st_a, _, _ = run(qc, kc[:, :h], vc[:, :h], _lib.PATH_TENSOR, variant=_lib.STABLEMAX, power=power, want_state=True,
+                        scale=sc)
+    y_b, _, _, _ = run(qc, kc[:, h:], vc[:, h:], _lib.PATH_TENSOR, variant=_lib.STABLEMAX, power=power, state_in=st_a,
+                       scale=sc)
+    assert_bf16_gate(y_b, ref[:, h:], "stablemax carry-in")
