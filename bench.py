@@ -233,6 +233,11 @@ def bench_prefill(args, rank, world):
                 clocks=clk.summary(), gpu_launches=launches, tokens_per_step=tokens)
 
 
+# DRAM traffic of one C2 forward launch as measured by ncu (268.8 MB read + 101.8 MB written; part of Y is still in L2
+# when the kernel ends, hence below the algorithmic bytes)
+NCU_TRAFFIC_C2_BYTES = 370_560_000
+
+
 def _roofline(cfg, q, k, v, y, kern_ms):
     """Algorithmic bytes of one forward = K + V read, Y written, Q read (bf16) over the dominant kernel's time."""
     pk = peaks()
@@ -241,7 +246,9 @@ def _roofline(cfg, q, k, v, y, kern_ms):
     achieved = alg_bytes / (kern_ms * 1e-3) / 1e9
     return {
         "bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": achieved / pk["hbm_gbs"],
-        "traffic": None, "peak_source": pk["source"], "kernel_ms": kern_ms,
+        "traffic": NCU_TRAFFIC_C2_BYTES, "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of one ncu "
+        "capture of this kernel on this workload (profiles/prefill_tc_c2.md)", "peak_source": pk["source"],
+        "kernel_ms": kern_ms,
         "kernel": "dominant forward kernel (CUDA events recorded around it inside flare_forward)",
         "algorithmic_bytes": alg_bytes,
         "tensor_frac": alg_flops / (kern_ms * 1e-3) / 1e12 / pk["bf16_tflops"],
