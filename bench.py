@@ -337,7 +337,7 @@ def bench_seqpar(args, rank, world):
                        "parallelism": f"sequence parallel over {world} GPU(s), one all-gather of span states per step"}}
 
 
-def bench_other_shapes():
+def bench_other_shapes(which="all"):
     """Short device-timed runs of the other benchmark shapes (not the headline metric): training-shape forward and
     forward+backward, and the long block-causal shape on one GPU."""
     import causal_flare as cf
@@ -369,6 +369,9 @@ def bench_other_shapes():
         fn(q, k, v).backward(dy)
 
     out["C4_fwd_bwd_softmax_ms"] = timed(lambda: train_step(cf.flare_autoregressive_triton), n=3)
+    out["C4"] = f"B={B} N={N} H={H} M={M} D={D} bf16"
+    if which == "train":
+        return out
     from causal_flare.autoregressive import flare_autoregressive_stablemax_triton
 
     out["C4_fwd_bwd_stablemax_ms"] = timed(lambda: train_step(flare_autoregressive_stablemax_triton), n=3)
@@ -421,7 +424,7 @@ def main():
     ap.add_argument("--skip-cpu", action="store_true")
     ap.add_argument("--decode-prefix", type=int, default=C3["prefix"])
     ap.add_argument("--decode-steps", type=int, default=C3["steps"])
-    ap.add_argument("--only", default="all", choices=["all", "prefill", "decode", "seqpar"],
+    ap.add_argument("--only", default="all", choices=["all", "prefill", "decode", "seqpar", "train"],
                     help="profiling aid: run one section only (the JSON line then lacks the other)")
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-other", action="store_true", help="skip the short runs of the other benchmark shapes")
@@ -451,6 +454,10 @@ def main():
 
     assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU fallback)"
     rank, world, _ = dist_setup(args.gpus)
+    if args.only == "train":
+        if rank == 0:
+            print(json.dumps({"metric": "training step time", "unit": "ms", "other_shapes": bench_other_shapes("train")}))
+        return
     if args.only == "seqpar":
         res = bench_seqpar(args, rank, world)
         if rank == 0:
