@@ -28,7 +28,7 @@ class State(C.Structure):
 class FwdArgs(C.Structure):
     _fields_ = [
         ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("q_dec", C.c_void_p), ("k_dec", C.c_void_p),
-        ("y", C.c_void_p), ("mask", C.c_void_p),
+        ("y", C.c_void_p), ("mask", C.c_void_p), ("lengths", C.c_void_p),
         ("state_in", State), ("state_out", State),
         ("lse_dec", C.c_void_p), ("lse_enc", C.c_void_p),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
@@ -171,12 +171,13 @@ def state_struct(st) -> State:
 
 
 def make_fwd_args(q, k, v, q_dec, k_dec, y, *, scale, variant=SOFTMAX, power=2.0, block_size=1, mask=None,
-                  state_in=None, state_out=None, lse_dec=None, lse_enc=None, path=PATH_AUTO) -> FwdArgs:
+                  state_in=None, state_out=None, lse_dec=None, lse_enc=None, path=PATH_AUTO, lengths=None) -> FwdArgs:
     """q [H,M,Dk]; k, v, q_dec, y given as [B,N,H,D] views (any b/n/h strides)."""
     B, N, H, Dk = k.shape
     a = FwdArgs()
     a.q, a.k, a.v, a.q_dec, a.k_dec, a.y = ptr(q), ptr(k), ptr(v), ptr(q_dec), ptr(k_dec), ptr(y)
     a.mask = ptr(mask)
+    a.lengths = ptr(lengths)
     a.state_in = state_struct(state_in)
     a.state_out = state_struct(state_out)
     a.lse_dec, a.lse_enc = ptr(lse_dec), ptr(lse_enc)

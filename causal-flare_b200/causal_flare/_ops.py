@@ -67,7 +67,11 @@ def forward(Q, K, V, *, scale, Q_dec=None, K_dec=None, variant=_lib.SOFTMAX, pow
             lse_enc = torch.empty((B, H, N // block_size, M), device=dev, dtype=torch.float32)
     if mask is not None:
         mask = mask.to(device=dev, dtype=torch.int32).contiguous()
-    if B > 0 and N > 0 or want_state:
+    if mask is not None and B > 0 and N > 0 and _masked_on_tensor_path(q, k, v, qd, kd, y, st_out, scale, variant, power,
+                                                                      block_size, path, want_lse):
+        _forward_compacted(q, k, v, y, mask, scale=scale, variant=variant, power=power, state_in=state_in,
+                           st_out=st_out, path=path)
+    elif B > 0 and N > 0 or want_state:
         args = _lib.make_fwd_args(q, k, v, qd, kd, y, scale=scale, variant=variant, power=power,
                                   block_size=block_size, mask=mask, state_in=state_in, state_out=st_out,
                                   lse_dec=lse_dec, lse_enc=lse_enc, path=path)
@@ -76,6 +80,37 @@ def forward(Q, K, V, *, scale, Q_dec=None, K_dec=None, variant=_lib.SOFTMAX, pow
     if want_y:
         out = y_store if out_dtype in (None, dt) else y_store.to(out_dtype)
     return out, st_out, lse_dec, lse_enc
+
+
+def _masked_on_tensor_path(q, k, v, qd, kd, y, st_out, scale, variant, power, block_size, path, want_lse) -> bool:
+    """True when the same call without the mask would run on the tensor-core kernels (they take per-row lengths, not
+    arbitrary masks, so a masked call is served by compacting the valid tokens to the front of every row)."""
+    if path == _lib.PATH_EXACT or want_lse or qd is not None or kd is not None or (y is None and st_out is None):
+        return False
+    probe = _lib.make_fwd_args(q, k, v, None, None, y, scale=scale, variant=variant, power=power, block_size=block_size,
+                               state_out=st_out, path=path)
+    return _lib.load().flare_forward_uses_tensor_path(C.byref(probe)) == 1
+
+
+def _forward_compacted(q, k, v, y, mask, *, scale, variant, power, state_in, st_out, path):
+    """Masked forward on the tensor path: gather the valid tokens of every batch row to the front (stable order), run
+    the kernel with per-row lengths, scatter the outputs back; masked positions get y = 0 and leave the state as is."""
+    B, N, H, Dk = k.shape
+    Dv = v.shape[-1]
+    valid = mask != 0
+    order = torch.argsort((~valid).to(torch.uint8), dim=1, stable=True)  # valid positions first, original order kept
+    lens = valid.sum(dim=1).to(torch.int32)
+    idx = order[:, :, None, None]
+    kc = torch.gather(k, 1, idx.expand(B, N, H, Dk))
+    vc = torch.gather(v, 1, idx.expand(B, N, H, Dv))
+    yc = torch.empty((B, N, H, Dv), device=k.device, dtype=k.dtype) if y is not None else None
+    args = _lib.make_fwd_args(q, kc, vc, None, None, yc, scale=scale, variant=variant, power=power, state_in=state_in,
+                              state_out=st_out, path=path, lengths=lens)
+    _lib.run_forward(args, k.device)
+    if y is not None:
+        pad = torch.arange(N, device=k.device)[None, :] >= lens[:, None]
+        yc.masked_fill_(pad[:, :, None, None], 0)  # rows beyond a row's length were not written by the kernel
+        y.scatter_(1, idx.expand(B, N, H, Dv), yc)
 
 
 def backward(Q, K, V, dY, *, scale, Q_dec=None, K_dec=None, variant=_lib.SOFTMAX, power=2.0, block_size=1,

@@ -76,6 +76,7 @@ int check_forward(const flare_fwd_args_t* a) {
   const bool any_out = a->state_out.m || a->state_out.d || a->state_out.u;
   if (any_out && !(a->state_out.m && a->state_out.d && a->state_out.u)) return FLARE_ERR_BAD_POINTER;
   if (!a->y && !any_out) return FLARE_ERR_BAD_POINTER;
+  if (a->lengths != nullptr && a->mask != nullptr) return FLARE_ERR_UNSUPPORTED;
   if (a->M > 512) return FLARE_ERR_UNSUPPORTED;
   return FLARE_OK;
 }
@@ -176,6 +177,7 @@ int launch_walk(const flare_fwd_args_t* a, const FwdPlan& pl, const WalkParams& 
 
 int forward_run(const flare_fwd_args_t* a, cudaStream_t stream) {
   const FwdPlan pl = plan_forward(a);
+  if (a->lengths != nullptr && !pl.use_tc) return FLARE_ERR_UNSUPPORTED;  // per-row lengths exist on the tensor path only
   if (pl.ws_bytes > 0 && (a->workspace == nullptr || a->workspace_bytes < pl.ws_bytes || !aligned16(a->workspace)))
     return FLARE_ERR_WORKSPACE;
   const int64_t lanes = (int64_t)a->B * a->H;

@@ -174,7 +174,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   constexpr int DV = DKB * D;
   const int b = lane_id / p.H, h = lane_id % p.H;
   const int seg_begin = seg * p.seg_len;
-  const int seg_end = min(p.N, seg_begin + p.seg_len);
+  // rows beyond the batch row's own length are right padding: they are not walked
+  const int n_row = p.lens != nullptr ? min(p.N, max(0, p.lens[b])) : p.N;
+  const int seg_end = max(seg_begin, min(n_row, seg_begin + p.seg_len));
   const int nchunks = (seg_end - seg_begin + C - 1) / C;
 
   if (tid == 0) {
@@ -913,6 +915,7 @@ bool prefill_tc_supported(const flare_fwd_args_t* a) {
   const bool block_ok = bs == 1 || ((bs == 16 || bs == 32 || bs == 64 || bs == 128) && a->N % bs == 0);
   // the log normalisers are emitted in block-causal mode only (the token-causal entry points never ask for them)
   const bool lse_ok = (a->lse_enc == nullptr && a->lse_dec == nullptr) || bs > 1;
+  if (a->lengths != nullptr && bs > 1) return false;  // per-row lengths: token-causal only
   // stablemax encoder weights: token-causal only
   const bool variant_ok = a->variant == FLARE_SOFTMAX || (a->variant == FLARE_STABLEMAX && bs == 1 && a->power > 0.f);
   return a->dtype == FLARE_BF16 && variant_ok && block_ok && lse_ok && a->M <= 4 * M && a->M >= 16 &&
@@ -925,12 +928,14 @@ bool prefill_tc_supported(const flare_fwd_args_t* a) {
 __global__ void __launch_bounds__(256) tc_merge_groups_kernel(const float* __restrict__ part_y, const float* __restrict__ part_lw,
                                                                int groups, int64_t rows /* B*N*H */, int N, int H, int dv,
                                                                __nv_bfloat16* y, int64_t y_stride_b, int64_t y_stride_n,
-                                                               int64_t y_stride_h, float* lse_dec /* [B, H, N] or null */) {
+                                                               int64_t y_stride_h, float* lse_dec /* [B, H, N] or null */,
+                                                               const int32_t* lens /* [B] or null */) {
   const int cols8 = dv >> 3;
   const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= rows * cols8) return;
   const int64_t row = idx / cols8;
   const int c8 = (int)(idx % cols8);
+  if (lens != nullptr && (int)((row / H) % N) >= lens[row / ((int64_t)H * N)]) return;  // right padding: nothing emitted
   float lw[4], mx = -INFINITY;
 #pragma unroll
   for (int g = 0; g < 4; ++g) {
@@ -986,6 +991,7 @@ int launch_prefill_tc(const flare_fwd_args_t* a, const TcParams& p_in, int nseg_
   }
   p.block = a->block_size;
   p.power = a->power;
+  p.lens = a->lengths;
   p.lse_dec = a->lse_dec;
   p.lse_enc = a->lse_enc;
   if (p.y == nullptr) p.lse_dec = p.lse_enc = nullptr;  // state-only passes emit nothing else
@@ -1022,7 +1028,7 @@ int launch_prefill_tc(const flare_fwd_args_t* a, const TcParams& p_in, int nseg_
   const int64_t threads = rows * (a->Dv / 8);
   tc_merge_groups_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, stream>>>(
       p.part_y, p.part_lw, groups, rows, a->N, a->H, a->Dv, reinterpret_cast<__nv_bfloat16*>(p.y), p.y_stride_b,
-      p.y_stride_n, p.y_stride_h, p.lse_dec);
+      p.y_stride_n, p.y_stride_h, p.lse_dec, p.lens);
   FLARE_CUDA_CHECK(cudaGetLastError());
   return FLARE_OK;
 }

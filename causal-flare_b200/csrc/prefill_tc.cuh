@@ -24,6 +24,7 @@ struct TcParams {
   float *part_y, *part_lw;
   int out_mode;  // 0: none, 1: every segment, 2: last segment only
   int nseg_total;
+  const int32_t* lens;       // [B] tokens per batch row (right padding beyond), or null
   int block;                 // 1 = token-causal; 16, 32, 64, 128 = block-causal
   float power;               // stablemax exponent (stablemax encoder only)
   float *lse_dec, *lse_enc;  // optional outputs, fp32 natural log: [B, H, N] and [B, H, N / block, M]

@@ -70,6 +70,9 @@ typedef struct flare_fwd_args {
   const void* k_dec; /* NULL: weight sharing with q */
   void* y;           /* same dtype as the inputs; may be NULL when only the final state is wanted */
   const int32_t* mask;      /* [B, N] int32, 0 = token leaves the state untouched and emits y = 0; may be NULL */
+  const int32_t* lengths;   /* [B] int32 or NULL: batch row b has lengths[b] tokens, the rest of its N rows is right
+                               padding (state untouched, those rows of y are NOT written).  Tensor-core path only, not
+                               together with mask; FLARE_ERR_UNSUPPORTED when the call resolves to the exact path. */
   flare_state_t state_in;   /* all NULL: start from the empty state (m=-inf, d=0, u=0) */
   flare_state_t state_out;  /* all NULL: final state not written */
   float* lse_dec;           /* [B, H, N] log-sum-exp of the decode scores; may be NULL */
