@@ -265,3 +265,27 @@ def test_tensor_path_masked_prefill(Ml, Dw):
     y2, st2 = cf.flare_autoregressive_prefill_triton(qc, kc[:, :599], vc[:, :599], scale=sc, attention_mask=mask[:, :599].cuda())
     y3, _ = cf.flare_autoregressive_decode_triton(qc, kc[:, 599], vc[:, 599], st2, scale=sc, attention_mask=mask[:, 599].cuda())
     assert_bf16_gate(y3, ref[:, 599:], "decode after masked tensor prefill")
+
+
+def test_block_causal_long_context_shape_vs_exact():
+    # B=2, N=65536, H=32, M=256, D=128, block 64 (the long-context benchmark shape) on one GPU: both CUDA paths must
+    # agree over the whole output, a prefix of one lane is checked on the CPU, and later blocks must not leak back
+    B, N, H, Ml, Dw, bs = 2, 65536, 32, 256, 128, 64
+    g = torch.Generator(device="cuda").manual_seed(4)
+    q = torch.randn(H, Ml, Dw, generator=g, device="cuda").bfloat16()
+    k = torch.randn(B, N, H, Dw, generator=g, device="cuda").bfloat16()
+    v = torch.randn(B, N, H, Dw, generator=g, device="cuda").bfloat16()
+    sc = Dw ** -0.5
+    y_t, _, ld_t, le_t = run(q, k, v, _lib.PATH_TENSOR, block_size=bs, want_lse=True, scale=sc)
+    y_e, _, ld_e, le_e = run(q, k, v, _lib.PATH_EXACT, block_size=bs, want_lse=True, scale=sc)
+    assert torch.isfinite(y_t.float()).all()
+    assert_bf16_gate(y_t, y_e.float(), "tensor vs exact, long block-causal shape")
+    assert_close(le_t, le_e, what="LSE_enc", atol=5e-4, rtol=5e-4)
+    assert_close(ld_t, ld_e, what="LSE_dec", atol=5e-3, rtol=0)
+    ref, _, _ = orc.semi_ar_forward(q[7:8].cpu(), k[1:2, :256, 7:8].cpu(), v[1:2, :256, 7:8].cpu(), block_size=bs, scale=sc)
+    assert_bf16_gate(y_t[1:2, :256, 7:8], ref, "lane prefix vs oracle")
+    k2, v2 = k.clone(), v.clone()
+    k2[:, N // 2:] = 0
+    v2[:, N // 2:] = 1
+    y2, _, _, _ = run(q, k2, v2, _lib.PATH_TENSOR, block_size=bs, scale=sc)
+    assert torch.equal(y2[:, :N // 2], y_t[:, :N // 2]), "tokens of later blocks changed earlier outputs"
