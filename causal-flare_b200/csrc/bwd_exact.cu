@@ -55,7 +55,10 @@ struct BwdParams {
   int seg_len, nseg, seg_first;
   const float *in_m, *in_d, *in_u;   // [lanes][nseg][M], [lanes][nseg][M], [lanes][nseg][M][Dv]
   float *seg_b, *seg_c, *seg_gam;    // [lanes][nseg][M][Dv], [lanes][nseg][M], [lanes][nseg][M]
-  int rev_mode;                      // reverse walk: 0 = gradients (carry-in when nseg > 1), 1 = carries only
+  // Written by the replay when nseg > 1: X[t, m] = g[t, m] * prod_{tau = a+1 .. t} (1 - e[tau, m]) (a = first token of
+  // the segment of t), the weight with which g dY_t and g p enter the carries (b, c) at the segment's first token;
+  // seg_gam receives the product of all decays of the segment.
+  float* X;                          // [lanes][N][M]
 };
 
 // defined once per MM_MAX in {2, 8, 16, 32, 64}, each in its own translation unit; stage 0 = replay, 1 = reverse
@@ -89,6 +92,7 @@ __global__ void __launch_bounds__(NT, (MM_MAX * DD <= 32) ? 2 : 1) bwd_replay_ke
   float* m_run = base; base += mp;
   float* d_run = base; base += mp;
   float* dinv = base; base += mp;
+  float* gp_run = base; base += mp;  // running product of the decays since the segment's first token
   int* valid = reinterpret_cast<int*>(base);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int mm = M / NW;
@@ -112,6 +116,7 @@ __global__ void __launch_bounds__(NT, (MM_MAX * DD <= 32) ? 2 : 1) bwd_replay_ke
   for (int m = tid; m < M; m += NT) {
     m_run[m] = carry_in ? p.in_m[st * M + m] : (stablemax ? 0.f : kNegInf);
     d_run[m] = carry_in ? p.in_d[st * M + m] : 0.f;
+    gp_run[m] = 1.0f;
   }
   __syncthreads();
 
@@ -168,7 +173,7 @@ __global__ void __launch_bounds__(NT, (MM_MAX * DD <= 32) ? 2 : 1) bwd_replay_ke
       decode_softmax(a_s, shared_w ? s_s : a_s, mp, M, valid, nullptr, t0, N);
       __syncthreads();
       for (int m = tid; m < M; m += NT) {
-        float mr = m_run[m], dr = d_run[m];
+        float mr = m_run[m], dr = d_run[m], gp = gp_run[m];
         for (int t = 0; t < BT; ++t) {
           if (!valid[t]) continue;
           const float s = s_s[t * mp + m];
@@ -194,10 +199,15 @@ __global__ void __launch_bounds__(NT, (MM_MAX * DD <= 32) ? 2 : 1) bwd_replay_ke
             p.E[o] = e;
             p.G[o] = a_s[t * mp + m];
             if (stablemax) p.W2[o] = e * stablemax_slope_ratio(s, p.power);
+            if (p.X != nullptr) {
+              if (t0 + t != tbeg) gp *= 1.0f - e;  // the segment's first token carries no decay
+              p.X[o] = a_s[t * mp + m] * gp;
+            }
           }
         }
         m_run[m] = mr;
         d_run[m] = dr;
+        gp_run[m] = gp;
       }
       __syncthreads();
 #pragma unroll 1
@@ -217,6 +227,12 @@ __global__ void __launch_bounds__(NT, (MM_MAX * DD <= 32) ? 2 : 1) bwd_replay_ke
         }
         emit_p(t0, t, r_s + t * mp);
       }
+    }
+    if (p.X != nullptr && dt == 0) {
+      // product of all decays of the segment, including the one of the next segment's first token
+      __syncthreads();
+      for (int m = tid; m < M; m += NT)
+        p.seg_gam[st * M + m] = gp_run[m];
     }
   } else {
     const int bs = p.block_size;
@@ -320,7 +336,6 @@ __global__ void __launch_bounds__(NT, (MM_MAX * DD <= 32) ? 2 : 1) bwd_reverse_k
   float* rho_in = base; base += mp;     // decay applied when stepping from the next tile / block into this one
   float* c_run = base; base += mp;
   float* esum = base; base += mp;
-  float* gam_run = base; base += mp;    // product of the decays applied so far (segment carries)
   float* gp = base; base += BT;
   float* dvpart = base; base += NW * BT * dvt;
   int* valid = reinterpret_cast<int*>(base);
@@ -333,7 +348,7 @@ __global__ void __launch_bounds__(NT, (MM_MAX * DD <= 32) ? 2 : 1) bwd_reverse_k
   const int64_t row_base = (int64_t)lane_id * N;
   const int64_t st = (int64_t)lane_id * p.nseg + seg;
   // carries from the segment to the right (zero at the end of the sequence and in the carries-only mode)
-  const bool carry_in = p.nseg > 1 && p.rev_mode == 0 && tend < N;
+  const bool carry_in = p.nseg > 1 && tend < N;
 
   float Bc[MM_MAX][DD];
 #pragma unroll
@@ -348,7 +363,6 @@ __global__ void __launch_bounds__(NT, (MM_MAX * DD <= 32) ? 2 : 1) bwd_reverse_k
     rho_in[m] = tend < N ? 1.0f - p.E[(row_base + tend) * M + m] : 0.f;
     c_run[m] = carry_in ? p.seg_c[st * M + m] : 0.f;
     esum[m] = 0.f;
-    gam_run[m] = 1.0f;
   }
 
   const int64_t v_off = (int64_t)b * p.v_stride_b + (int64_t)h * p.v_stride_h;
@@ -438,63 +452,7 @@ __global__ void __launch_bounds__(NT, (MM_MAX * DD <= 32) ? 2 : 1) bwd_reverse_k
     }
   };
 
-  if (p.block_size <= 1 && p.rev_mode == 1) {
-    // carries only: (b, c) at the first token of the segment for a zero carry-in, and the product of all decays
-    const int last_tile = ((tend - 1) / BT) * BT;
-    for (int t0 = last_tile; t0 >= tbeg; t0 -= BT) {
-      __syncthreads();
-      set_valid(t0);
-      load_rows(dos, dvt, p.dy, dtype, dy_off, p.dy_stride_n, t0, N, Dv, dv0, dvt);
-      load_plane(e_s, p.E, t0, 1);
-      load_plane(g_s, p.G, t0, 1);
-      load_plane(p_s, p.P, t0, p.DT);
-      __syncthreads();
-      for (int m = tid; m < M; m += NT) {
-        float c = c_run[m], rho = rho_in[m], gam = gam_run[m];
-        for (int t = BT - 1; t >= 0; --t) {
-          if (!valid[t]) continue;
-          c = g_s[t * mp + m] * p_s[t * mp + m] + rho * c;
-          gam *= rho;
-          rho = 1.0f - e_s[t * mp + m];
-        }
-        c_run[m] = c;
-        gam_run[m] = gam;
-      }
-#pragma unroll
-      for (int t = BT - 1; t >= 0; --t) {
-        if (!valid[t]) continue;
-        const bool next_in_tile = (t + 1 < BT) && valid[t + 1 < BT ? t + 1 : t];
-        float dd[DD];
-#pragma unroll
-        for (int j = 0; j < DD; ++j) dd[j] = dos[t * dvt + lane + 32 * j];
-#pragma unroll
-        for (int mi = 0; mi < MM_MAX; ++mi) {
-          if (mi < mm) {
-            const int m = warp * mm + mi;
-            const float rho = next_in_tile ? 1.0f - e_s[(t + 1 < BT ? t + 1 : t) * mp + m] : rho_in[m];
-            const float g = g_s[t * mp + m];
-#pragma unroll
-            for (int j = 0; j < DD; ++j) Bc[mi][j] = Bc[mi][j] * rho + g * dd[j];
-          }
-        }
-      }
-      __syncthreads();
-      for (int m = tid; m < M; m += NT) rho_in[m] = 1.0f - e_s[m];
-    }
-    __syncthreads();
-#pragma unroll
-    for (int mi = 0; mi < MM_MAX; ++mi)
-#pragma unroll
-      for (int j = 0; j < DD; ++j) {
-        const int m = warp * mm + mi, col = dv0 + lane + 32 * j;
-        if (mi < mm && col < Dv) p.seg_b[(st * M + m) * Dv + col] = Bc[mi][j];
-      }
-    if (dt == 0)
-      for (int m = tid; m < M; m += NT) {
-        p.seg_c[st * M + m] = c_run[m];
-        p.seg_gam[st * M + m] = gam_run[m];
-      }
-  } else if (p.block_size <= 1) {
+  if (p.block_size <= 1) {
     const int last_tile = ((tend - 1) / BT) * BT;
     for (int t0 = last_tile; t0 >= tbeg; t0 -= BT) {
       __syncthreads();
@@ -826,11 +784,11 @@ __global__ void bwd_sum_splits_kernel(float* out, const float* partial, int64_t 
 
 size_t replay_smem(int M, int Dk, int dd) {
   const int mp = M + 4, ldk = Dk + 4, dvt = 32 * dd;
-  return ((size_t)2 * BT * ldk + 2 * BT * dvt + (size_t)4 * BT * mp + 3 * mp) * 4 + BT * sizeof(int);
+  return ((size_t)2 * BT * ldk + 2 * BT * dvt + (size_t)4 * BT * mp + 4 * mp) * 4 + BT * sizeof(int);
 }
 size_t reverse_smem(int M, int dd, bool stablemax) {
   const int mp = M + 4, dvt = 32 * dd;
-  return ((size_t)2 * BT * dvt + (size_t)(stablemax ? 6 : 5) * BT * mp + 4 * mp + BT + (size_t)NW * BT * dvt) * 4 +
+  return ((size_t)2 * BT * dvt + (size_t)(stablemax ? 6 : 5) * BT * mp + 3 * mp + BT + (size_t)NW * BT * dvt) * 4 +
          BT * sizeof(int);
 }
 
@@ -839,7 +797,7 @@ struct BwdPlan {
   int nseg, seg_len;  // sequence segments of the replay / reverse walks (token-causal read-out only)
   int64_t plane;
   size_t off_E, off_G, off_W2, off_P, off_dSe, off_dSd, off_part_q, off_part_kd, total;
-  size_t off_seg_m, off_seg_d, off_seg_u, off_seg_b, off_seg_c, off_seg_gam;
+  size_t off_seg_m, off_seg_d, off_seg_u, off_seg_b, off_seg_c, off_seg_gam, off_X;
 };
 
 BwdPlan plan_backward(const flare_bwd_args_t& a) {
@@ -894,7 +852,7 @@ BwdPlan plan_backward(const flare_bwd_args_t& a) {
   const size_t lat = (size_t)f.H * f.M * f.Dk;
   pl.off_part_q = take(lat * pl.splits);
   pl.off_part_kd = f.k_dec ? take(lat * pl.splits) : 0;
-  pl.off_seg_m = pl.off_seg_d = pl.off_seg_u = pl.off_seg_b = pl.off_seg_c = pl.off_seg_gam = 0;
+  pl.off_seg_m = pl.off_seg_d = pl.off_seg_u = pl.off_seg_b = pl.off_seg_c = pl.off_seg_gam = pl.off_X = 0;
   if (pl.nseg > 1) {
     const size_t ls = (size_t)f.B * f.H * pl.nseg;
     pl.off_seg_m = take(ls * f.M);
@@ -903,6 +861,7 @@ BwdPlan plan_backward(const flare_bwd_args_t& a) {
     pl.off_seg_b = take(ls * f.M * f.Dv);
     pl.off_seg_c = take(ls * f.M);
     pl.off_seg_gam = take(ls * f.M);
+    pl.off_X = take(plane);
   }
   pl.total = off;
   return pl;
@@ -942,6 +901,101 @@ int launch_bwd_mm<FLARE_WALK_MM>(const BwdParams& p, int dd, dim3 grid, size_t s
   return FLARE_ERR_UNSUPPORTED;
 }
 #else
+
+// Carries of a segment for a zero carry-in, as products over its tokens (no sequential walk):
+//   b0[m, :] = sum_t X[t, m] dY_t,   c0[m] = sum_t X[t, m] p[t, m],   and seg_gam[m] *= 1 - e[first token of the next
+// segment, m].  Register-tiled like the latent-gradient kernel: 64 latents x 128 value columns per CTA.
+__global__ void __launch_bounds__(NT) bwd_seg_carry_kernel(const float* __restrict__ X, const float* __restrict__ P,
+                                                           int p_parts, int64_t plane, const float* __restrict__ E,
+                                                           const void* dy, int dtype, int64_t dy_stride_b,
+                                                           int64_t dy_stride_n, int64_t dy_stride_h, float* seg_b,
+                                                           float* seg_c, float* seg_gam, int nseg, int seg_len, int N,
+                                                           int H, int M, int Dv) {
+  __shared__ __align__(16) float x_s[LT][LM + 4];
+  __shared__ __align__(16) float dy_s[LT][LDK + 4];
+  const int mtiles = (M + LM - 1) / LM;
+  const int lane_id = blockIdx.x / mtiles, m0 = (blockIdx.x % mtiles) * LM;
+  const int seg = blockIdx.y + 1, dv0 = blockIdx.z * LDK;
+  const int b = lane_id / H, h = lane_id % H;
+  const int tid = threadIdx.x, tm = tid / 16, td = tid % 16;
+  const int tbeg = seg * seg_len, tend = min(N, tbeg + seg_len);
+  const int64_t row_base = (int64_t)lane_id * N;
+  const int64_t st = (int64_t)lane_id * nseg + seg;
+  float acc[4][8], cacc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
+  for (int t0 = tbeg; t0 < tend; t0 += LT) {
+    __syncthreads();
+    for (int idx = tid; idx < LT * (LM / 4); idx += NT) {
+      const int t = idx / (LM / 4), c = (idx % (LM / 4)) * 4;
+      float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (t0 + t < tend && m0 + c < M) {
+        const int64_t o = (row_base + t0 + t) * M + m0 + c;
+        x = __ldcs(reinterpret_cast<const float4*>(X + o));
+        if (dv0 == 0) {
+          // c0 partial of this thread's four latents for this token (threads of other rows add theirs below)
+          float4 pp = make_float4(0.f, 0.f, 0.f, 0.f);
+          for (int part = 0; part < p_parts; ++part) {
+            const float4 y = __ldcs(reinterpret_cast<const float4*>(P + (int64_t)part * plane + o));
+            pp.x += y.x; pp.y += y.y; pp.z += y.z; pp.w += y.w;
+          }
+          // stash x * p behind the x values of the same row: columns LM/4 apart are not used, so keep it in registers
+          // of the loading thread and reduce through shared memory after the loop instead
+          cacc[0] += x.x * pp.x; cacc[1] += x.y * pp.y; cacc[2] += x.z * pp.z; cacc[3] += x.w * pp.w;
+        }
+      }
+      *reinterpret_cast<float4*>(&x_s[t][c]) = x;
+    }
+    for (int idx = tid; idx < LT * (LDK / 8); idx += NT) {
+      const int t = idx / (LDK / 8), c = (idx % (LDK / 8)) * 8;
+      float x[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      if (t0 + t < tend && dv0 + c < Dv)
+        load8(dy, dtype, (int64_t)b * dy_stride_b + (int64_t)(t0 + t) * dy_stride_n + (int64_t)h * dy_stride_h + dv0 + c, x);
+      *reinterpret_cast<float4*>(&dy_s[t][c]) = make_float4(x[0], x[1], x[2], x[3]);
+      *reinterpret_cast<float4*>(&dy_s[t][c + 4]) = make_float4(x[4], x[5], x[6], x[7]);
+    }
+    __syncthreads();
+#pragma unroll 8
+    for (int t = 0; t < LT; ++t) {
+      const float4 d4 = *reinterpret_cast<const float4*>(&x_s[t][tm * 4]);
+      const float dsv[4] = {d4.x, d4.y, d4.z, d4.w};
+      float rv[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) rv[j] = dy_s[t][td + 16 * j];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[i][j] += dsv[i] * rv[j];
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int m = m0 + tm * 4 + i, dv = dv0 + td + 16 * j;
+      if (m < M && dv < Dv) seg_b[(st * M + m) * Dv + dv] = acc[i][j];
+    }
+  if (dv0 == 0) {
+    // c0: the loading threads hold partial sums for columns (tid % 16) * 4 .. + 3 over the rows tid / 16 + 16 k
+    __syncthreads();
+    float* red = &dy_s[0][0];  // [16 row groups][LM]
+    if (tid < LT * (LM / 4) && tid < NT) {
+      const int rg = tid / (LM / 4), c = (tid % (LM / 4)) * 4;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) red[rg * LM + c + i] = cacc[i];
+    }
+    __syncthreads();
+    if (tid < LM && m0 + tid < M) {
+      float c0 = 0.f;
+      for (int rg = 0; rg < NT / (LM / 4); ++rg) c0 += red[rg * LM + tid];
+      seg_c[st * M + m0 + tid] = c0;
+      const float rho = tend < N ? 1.0f - E[(row_base + tend) * M + m0 + tid] : 0.f;
+      seg_gam[st * M + m0 + tid] *= rho;
+    }
+  }
+}
 
 // Right-to-left scan of the segment carries: on entry slot s holds (b, c) at the first token of segment s for a zero
 // carry-in and gam the product of its decays; on exit slot s holds the carry that enters segment s from the right.
@@ -997,7 +1051,7 @@ int bwd_exact(const flare_bwd_args_t& a, cudaStream_t stream) {
   p.dSe = reinterpret_cast<float*>(ws + pl.off_dSe);
   p.dSd = shared_w ? nullptr : reinterpret_cast<float*>(ws + pl.off_dSd);
   p.DT = pl.DT; p.plane = pl.plane; p.dv_out = a.dv;
-  p.nseg = pl.nseg; p.seg_len = pl.seg_len; p.seg_first = 0; p.rev_mode = 0;
+  p.nseg = pl.nseg; p.seg_len = pl.seg_len; p.seg_first = 0;
   const int64_t lanes = (int64_t)f.B * f.H;
   if (pl.nseg > 1) {
     float* seg_m = reinterpret_cast<float*>(ws + pl.off_seg_m);
@@ -1010,15 +1064,15 @@ int bwd_exact(const flare_bwd_args_t& a, cudaStream_t stream) {
     p.seg_b = reinterpret_cast<float*>(ws + pl.off_seg_b);
     p.seg_c = reinterpret_cast<float*>(ws + pl.off_seg_c);
     p.seg_gam = reinterpret_cast<float*>(ws + pl.off_seg_gam);
+    p.X = reinterpret_cast<float*>(ws + pl.off_X);
   }
 
   const int mm = f.M / NW;
   const size_t smem1 = replay_smem(f.M, f.Dk, pl.dd), smem2 = reverse_smem(f.M, pl.dd, stablemax);
   if (smem1 > 227 * 1024 || smem2 > 227 * 1024) return FLARE_ERR_UNSUPPORTED;
-  auto walk = [&](int stage, int seg_first, int seg_count, int rev_mode) -> int {
+  auto walk = [&](int stage, int seg_first, int seg_count) -> int {
     BwdParams q = p;
     q.seg_first = seg_first;
-    q.rev_mode = rev_mode;
     dim3 grid(f.B * f.H, pl.DT, seg_count);
     if (mm <= 2) return launch_bwd_mm<2>(q, pl.dd, grid, smem1, smem2, stream, stage);
     if (mm <= 8) return launch_bwd_mm<8>(q, pl.dd, grid, smem1, smem2, stream, stage);
@@ -1026,18 +1080,24 @@ int bwd_exact(const flare_bwd_args_t& a, cudaStream_t stream) {
     if (mm <= 32) return launch_bwd_mm<32>(q, pl.dd, grid, smem1, smem2, stream, stage);
     return launch_bwd_mm<64>(q, pl.dd, grid, smem1, smem2, stream, stage);
   };
-  int rcw = walk(0, 0, pl.nseg, 0);  // replay: planes e, g, p
+  int rcw = walk(0, 0, pl.nseg);  // replay: planes e, g, p (and X, the carry weights, when segmented)
   if (rcw != FLARE_OK) return rcw;
   if (pl.nseg > 1) {
-    // carries of segments 1 .. nseg-1 for a zero carry-in, then their right-to-left scan
-    rcw = walk(1, 1, pl.nseg - 1, 1);
-    if (rcw != FLARE_OK) return rcw;
+    // carries of segments 1 .. nseg-1 for a zero carry-in (products over the planes), then their right-to-left scan
+    {
+      const int mt = (f.M + LM - 1) / LM;
+      dim3 g((unsigned)(lanes * mt), pl.nseg - 1, (f.Dv + LDK - 1) / LDK);
+      bwd_seg_carry_kernel<<<g, NT, 0, stream>>>(p.X, p.P, pl.DT, pl.plane, p.E, a.dy, f.dtype, a.dy_stride_b,
+                                                 a.dy_stride_n, a.dy_stride_h, p.seg_b, p.seg_c, p.seg_gam, pl.nseg,
+                                                 pl.seg_len, f.N, f.H, f.M, f.Dv);
+      FLARE_CUDA_CHECK(cudaGetLastError());
+    }
     const int64_t n = lanes * f.M * (f.Dv + 1);
     bwd_seg_scan_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(p.seg_b, p.seg_c, p.seg_gam, pl.nseg, lanes, f.M,
                                                                         f.Dv);
     FLARE_CUDA_CHECK(cudaGetLastError());
   }
-  rcw = walk(1, 0, pl.nseg, 0);  // reverse walk: dV and the dS planes
+  rcw = walk(1, 0, pl.nseg);  // reverse walk: dV and the dS planes
   if (rcw != FLARE_OK) return rcw;
 
   // ---- dK (+ dQ_dec): products of the dS planes with the latent banks ------------------------------
