@@ -290,6 +290,18 @@ def bench_decode(args, rank, world):
     ms = max_over_ranks(t0.elapsed_time(t1), world)
     assert torch.isfinite(y.float()).all()
     step_bytes = 2 * B * H * M * Dv * 4 + 4 * B * H * M * 4 + H * M * Dk * 2 + B * H * (Dk + Dv) * 2 + B * H * Dv * 2
+    # the same tokens as one fused multi-step call: prefill continuing from the state (the state stays on chip)
+    kk, vv = ks.transpose(0, 1).contiguous(), vs.transpose(0, 1).contiguous()
+    for _ in range(2):
+        cf.flare_autoregressive_prefill_triton(q, kk, vv, state=state, scale=sc)
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    f0.record()
+    for _ in range(3):
+        cf.flare_autoregressive_prefill_triton(q, kk, vv, state=state, scale=sc)
+    f1.record()
+    torch.cuda.synchronize()
+    fused_ms = f0.elapsed_time(f1) / 3
+    del kk, vv
     pk = peaks()
     gbs = step_bytes * steps / (ms * 1e-3) / 1e9
     return {
@@ -297,6 +309,8 @@ def bench_decode(args, rank, world):
         "tok_per_s": world * B * steps / (ms * 1e-3), "us_per_step": ms * 1e3 / steps, "hbm_gbs": gbs,
         "hbm_frac": gbs / pk["hbm_gbs"], "bytes_per_step": step_bytes, "gpu_launches": steps,
         "state_bytes": B * H * M * Dv * 4, "l2": "state 268 MB > 126 MB L2",
+        "fused_multi_step": {"call": f"one flare_autoregressive_prefill_triton(state=...) over the same {steps} tokens",
+                             "ms": fused_ms, "tok_per_s": B * steps / (fused_ms * 1e-3)},
     }
 
 

@@ -228,3 +228,28 @@ def test_profile_returns_timings(golden):
     assert "forward" in prof and prof["forward_total_ms"] > 0 and "backward" in prof
     (y2, st), prof2 = cf.flare_autoregressive_prefill_triton(q, k, v, profile=True)
     assert prof2["forward_total_ms"] > 0
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_semi_ar_block_granular_cached_prefill(dtype):
+    # feeding whole blocks with a carried state equals the one-shot block-causal forward (exact path for fp32,
+    # tensor path for bf16); a single block per call is block-granular decoding
+    from causal_flare.semi_autoregressive.inference import flare_semi_autoregressive_block_prefill
+
+    B, N, H, M, D, bs = 2, 384, 2, 64, 64, 32
+    q, k, v = orc.make_inputs(B, N, H, M, D, seed0=81, dtype=dtype)
+    ref, _, _ = orc.semi_ar_forward(q, k, v, block_size=bs)
+    qc, kc, vc = to_dev(q, k, v)
+    state, ys = None, []
+    for lo, hi in ((0, 160), (160, 192), (192, 384)):
+        y, state = flare_semi_autoregressive_block_prefill(qc, kc[:, lo:hi], vc[:, lo:hi], block_size=bs, state=state)
+        ys.append(y)
+    y = torch.cat(ys, 1)
+    if dtype == torch.float32:
+        assert_close(y, ref, what="block-granular prefill", **FWD32)
+    else:
+        assert_bf16_gate(y, ref, "block-granular prefill bf16")
+    _, st_full = cf.flare_autoregressive_prefill_triton(qc, kc, vc, scale=D ** -0.5)
+    assert_close(state["d"], st_full["d"], what="final state d", atol=1e-3, rtol=2e-3)
+    with pytest.raises(ValueError):
+        flare_semi_autoregressive_block_prefill(qc, kc[:, :40], vc[:, :40], block_size=bs)
