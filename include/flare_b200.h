@@ -186,9 +186,10 @@ int flare_last_launch_count(void);
  * the phases of its first CTA (roles: latent group, token group, MMA issuer; first 16 chunks).  NULL disables. */
 void flare_set_trace_buffer(void* device_buffer);
 
-/* 1 when flare_forward would take the tcgen05 tensor-core path for this problem (path AUTO or TENSOR and a
- * supported shape: bf16, softmax encoder, M <= 128 (multiple of 16), Dk = Dv = 64, shared decode weights, no mask),
- * else 0. */
+/* 1 when flare_forward would take the tcgen05 tensor-core path for this problem, else 0.  That is: path AUTO or
+ * TENSOR, bf16, 16 <= M <= 512 (multiple of 16), Dk = Dv = 64 or 128, shared decode weights (q_dec = k_dec = NULL),
+ * mask = NULL, and either the softmax encoder with block_size 1 / 16 / 32 / 64 / 128 (N a multiple of it) or the
+ * stablemax encoder with block_size 1; lse_dec / lse_enc only with block_size > 1; lengths only with block_size 1. */
 int flare_forward_uses_tensor_path(const flare_fwd_args_t* args);
 
 /* Device-side health of the tensor-core kernels: synchronises the device and returns a bit set (0 = healthy), or a
