@@ -58,6 +58,9 @@ struct BwdParams {
   // the segment of t), the weight with which g dY_t and g p enter the carries (b, c) at the segment's first token;
   // seg_gam receives the product of all decays of the segment.
   float* X;                          // [lanes][N][M]
+  // Block-causal read-out with segments: decay of every block, rho[j, m] = 1 - sum_{t in block j} e[t, m]; the decays
+  // in X and seg_gam are then per block.
+  float* RHO;                        // [lanes][N / block_size][M]
 };
 
 // defined once per MM_MAX in {2, 8, 16, 32, 64}, each in its own translation unit; stage 0 = replay, 1 = reverse
@@ -92,6 +95,8 @@ __global__ void __launch_bounds__(NT, (MM_MAX * DD <= 32) ? 2 : 1) bwd_replay_ke
   float* d_run = base; base += mp;
   float* dinv = base; base += mp;
   float* gp_run = base; base += mp;  // running product of the decays since the segment's first token
+  float* m0_s = base; base += mp;    // block-causal: running max / denominator at the start of the current block
+  float* d0_s = base; base += mp;
   int* valid = reinterpret_cast<int*>(base);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int mm = M / NW;
@@ -235,8 +240,13 @@ __global__ void __launch_bounds__(NT, (MM_MAX * DD <= 32) ? 2 : 1) bwd_replay_ke
     }
   } else {
     const int bs = p.block_size;
-    for (int blk0 = 0; blk0 < N; blk0 += bs) {
+    for (int blk0 = tbeg; blk0 < tend; blk0 += bs) {
       const int blk_end = blk0 + bs;
+      __syncthreads();
+      for (int m = tid; m < M; m += NT) {
+        m0_s[m] = m_run[m];
+        d0_s[m] = d_run[m];
+      }
       for (int t0 = blk0; t0 < blk_end; t0 += BT) {
         __syncthreads();
         set_valid(t0);
@@ -278,7 +288,16 @@ __global__ void __launch_bounds__(NT, (MM_MAX * DD <= 32) ? 2 : 1) bwd_replay_ke
         }
       }
       __syncthreads();
-      for (int m = tid; m < M; m += NT) dinv[m] = 1.0f / d_run[m];
+      for (int m = tid; m < M; m += NT) {
+        const float di = 1.0f / d_run[m];
+        dinv[m] = di;
+        if (p.X != nullptr) {
+          // decay of this block = denominator before the block over the one after it, in the block-end frame
+          const float rho = (m0_s[m] == kNegInf) ? 0.f : d0_s[m] * __expf(m0_s[m] - m_run[m]) * di;
+          if (blk0 != tbeg) gp_run[m] *= rho;  // the segment's first block carries no decay
+          if (dt == 0) p.RHO[((int64_t)lane_id * (N / bs) + blk0 / bs) * M + m] = rho;
+        }
+      }
       for (int t0 = blk0; t0 < blk_end; t0 += BT) {
         __syncthreads();
         set_valid(t0);
@@ -299,11 +318,16 @@ __global__ void __launch_bounds__(NT, (MM_MAX * DD <= 32) ? 2 : 1) bwd_replay_ke
             const int64_t o = (row_base + t0 + t) * M + m;
             p.E[o] = __expf(s_s[t * mp + m] - m_run[m]) * dinv[m];
             p.G[o] = a_s[t * mp + m];
+            if (p.X != nullptr) p.X[o] = a_s[t * mp + m] * gp_run[m];
           }
         }
 #pragma unroll 1
         for (int t = 0; t < BT; ++t) emit_p(t0, t, dinv);
       }
+    }
+    if (p.X != nullptr && dt == 0) {
+      __syncthreads();
+      for (int m = tid; m < M; m += NT) p.seg_gam[st * M + m] = gp_run[m];
     }
   }
 }
@@ -359,7 +383,9 @@ __global__ void __launch_bounds__(NT, (MM_MAX * DD <= 32) ? 2 : 1) bwd_reverse_k
     }
   for (int m = tid; m < M; m += NT) {
     // decay of the first step = 1 - e of the first token of the segment to the right
-    rho_in[m] = tend < N ? 1.0f - p.E[(row_base + tend) * M + m] : 0.f;
+    rho_in[m] = tend >= N ? 0.f
+                : p.block_size <= 1 ? 1.0f - p.E[(row_base + tend) * M + m]
+                                    : p.RHO[((int64_t)lane_id * (N / p.block_size) + tend / p.block_size) * M + m];
     c_run[m] = carry_in ? p.seg_c[st * M + m] : 0.f;
     esum[m] = 0.f;
   }
@@ -509,7 +535,7 @@ __global__ void __launch_bounds__(NT, (MM_MAX * DD <= 32) ? 2 : 1) bwd_reverse_k
     }
   } else {
     const int bs = p.block_size;
-    for (int blk0 = N - bs; blk0 >= 0; blk0 -= bs) {
+    for (int blk0 = tend - bs; blk0 >= tbeg; blk0 -= bs) {
       const int blk_end = blk0 + bs;
       // pass 1: fold the whole block into the carries
       __syncthreads();
@@ -783,7 +809,7 @@ __global__ void bwd_sum_splits_kernel(float* out, const float* partial, int64_t 
 
 size_t replay_smem(int M, int Dk, int dd) {
   const int mp = M + 4, ldk = Dk + 4, dvt = 32 * dd;
-  return ((size_t)2 * BT * ldk + 2 * BT * dvt + (size_t)4 * BT * mp + 4 * mp) * 4 + BT * sizeof(int);
+  return ((size_t)2 * BT * ldk + 2 * BT * dvt + (size_t)4 * BT * mp + 6 * mp) * 4 + BT * sizeof(int);
 }
 size_t reverse_smem(int M, int dd, bool stablemax) {
   const int mp = M + 4, dvt = 32 * dd;
@@ -796,7 +822,7 @@ struct BwdPlan {
   int nseg, seg_len;  // sequence segments of the replay / reverse walks (token-causal read-out only)
   int64_t plane;
   size_t off_E, off_G, off_W2, off_P, off_dSe, off_dSd, off_part_q, off_part_kd, total;
-  size_t off_seg_m, off_seg_d, off_seg_u, off_seg_b, off_seg_c, off_seg_gam, off_X;
+  size_t off_seg_m, off_seg_d, off_seg_u, off_seg_b, off_seg_c, off_seg_gam, off_X, off_RHO;
 };
 
 BwdPlan plan_backward(const flare_bwd_args_t& a) {
@@ -810,14 +836,22 @@ BwdPlan plan_backward(const flare_bwd_args_t& a) {
   // narrower value tiles (more CTAs, repeated score work) are slower once the sequence is segmented (5.1-8.9).
   pl.nseg = 1;
   pl.seg_len = f.N;
-  if (f.block_size <= 1) {
+  {
+    // segments are whole 128-token chunks (forward kernels) and whole blocks (block-causal read-out)
+    int unit = 128;
+    if (f.block_size > 1) {
+      int a = f.block_size, b = 128;
+      while (b != 0) { const int t = a % b; a = b; b = t; }
+      unit = f.block_size / a * 128;
+    }
+    const int min_seg = unit > 256 ? unit : 256;
     const int64_t ctas = (int64_t)f.B * f.H * pl.DT, target = 4LL * sm_count();
     int nseg = (int)((target + ctas - 1) / ctas);
-    const int max_seg = f.N / 256;
+    const int max_seg = f.N / min_seg;
     if (nseg > max_seg) nseg = max_seg;
     if (nseg > 1) {
       int seg_len = (f.N + nseg - 1) / nseg;
-      seg_len = (seg_len + 127) / 128 * 128;
+      seg_len = (seg_len + unit - 1) / unit * unit;
       pl.seg_len = seg_len;
       pl.nseg = (f.N + seg_len - 1) / seg_len;
     }
@@ -852,7 +886,7 @@ BwdPlan plan_backward(const flare_bwd_args_t& a) {
   const size_t lat = (size_t)f.H * f.M * f.Dk;
   pl.off_part_q = take(lat * pl.splits);
   pl.off_part_kd = f.k_dec ? take(lat * pl.splits) : 0;
-  pl.off_seg_m = pl.off_seg_d = pl.off_seg_u = pl.off_seg_b = pl.off_seg_c = pl.off_seg_gam = pl.off_X = 0;
+  pl.off_seg_m = pl.off_seg_d = pl.off_seg_u = pl.off_seg_b = pl.off_seg_c = pl.off_seg_gam = pl.off_X = pl.off_RHO = 0;
   if (pl.nseg > 1) {
     const size_t ls = (size_t)f.B * f.H * pl.nseg;
     pl.off_seg_m = take(ls * f.M);
@@ -862,6 +896,7 @@ BwdPlan plan_backward(const flare_bwd_args_t& a) {
     pl.off_seg_c = take(ls * f.M);
     pl.off_seg_gam = take(ls * f.M);
     pl.off_X = take(plane);
+    pl.off_RHO = f.block_size > 1 ? take((size_t)f.B * f.H * (f.N / f.block_size) * f.M) : 0;
   }
   pl.total = off;
   return pl;
@@ -910,7 +945,8 @@ __global__ void __launch_bounds__(NT) bwd_seg_carry_kernel(const float* __restri
                                                            const void* dy, int dtype, int64_t dy_stride_b,
                                                            int64_t dy_stride_n, int64_t dy_stride_h, float* seg_b,
                                                            float* seg_c, float* seg_gam, int nseg, int seg_len, int N,
-                                                           int H, int M, int Dv) {
+                                                           int H, int M, int Dv, const float* __restrict__ RHO,
+                                                           int block_size) {
   __shared__ __align__(16) float x_s[LT][LM + 4];
   __shared__ __align__(16) float dy_s[LT][LDK + 4];
   const int mtiles = (M + LM - 1) / LM;
@@ -991,7 +1027,10 @@ __global__ void __launch_bounds__(NT) bwd_seg_carry_kernel(const float* __restri
       float c0 = 0.f;
       for (int rg = 0; rg < NT / (LM / 4); ++rg) c0 += red[rg * LM + tid];
       seg_c[st * M + m0 + tid] = c0;
-      const float rho = tend < N ? 1.0f - E[(row_base + tend) * M + m0 + tid] : 0.f;
+      const float rho = tend >= N ? 0.f
+                        : block_size <= 1
+                            ? 1.0f - E[(row_base + tend) * M + m0 + tid]
+                            : RHO[((int64_t)lane_id * (N / block_size) + tend / block_size) * M + m0 + tid];
       seg_gam[st * M + m0 + tid] *= rho;
     }
   }
@@ -1065,6 +1104,7 @@ int bwd_exact(const flare_bwd_args_t& a, cudaStream_t stream) {
     p.seg_c = reinterpret_cast<float*>(ws + pl.off_seg_c);
     p.seg_gam = reinterpret_cast<float*>(ws + pl.off_seg_gam);
     p.X = reinterpret_cast<float*>(ws + pl.off_X);
+    p.RHO = f.block_size > 1 ? reinterpret_cast<float*>(ws + pl.off_RHO) : nullptr;
   }
 
   const int mm = f.M / NW;
@@ -1089,7 +1129,7 @@ int bwd_exact(const flare_bwd_args_t& a, cudaStream_t stream) {
       dim3 g((unsigned)(lanes * mt), pl.nseg - 1, (f.Dv + LDK - 1) / LDK);
       bwd_seg_carry_kernel<<<g, NT, 0, stream>>>(p.X, p.P, pl.DT, pl.plane, p.E, a.dy, f.dtype, a.dy_stride_b,
                                                  a.dy_stride_n, a.dy_stride_h, p.seg_b, p.seg_c, p.seg_gam, pl.nseg,
-                                                 pl.seg_len, f.N, f.H, f.M, f.Dv);
+                                                 pl.seg_len, f.N, f.H, f.M, f.Dv, p.RHO, f.block_size);
       FLARE_CUDA_CHECK(cudaGetLastError());
     }
     const int64_t n = lanes * f.M * (f.Dv + 1);

@@ -239,6 +239,7 @@ int segment_prefix_states(const flare_fwd_args_t* f, int nseg, int seg_len, floa
   a.y = nullptr;
   a.mask = nullptr;
   a.lse_dec = a.lse_enc = nullptr;
+  a.block_size = 1;  // the state at a segment boundary does not depend on the read-out mode
   memset(&a.state_in, 0, sizeof(a.state_in));
   memset(&a.state_out, 0, sizeof(a.state_out));
   a.state_out.m = seg_m; a.state_out.d = seg_d; a.state_out.u = seg_u;  // marks "a state is wanted" for the checks

@@ -228,14 +228,6 @@ __device__ __forceinline__ float rcp_approx(float x) {
   asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-// 1 / x for normal positive x on the FMA pipe (keeps the special-function unit free for the exponentials):
-// exponent-flip seed (about 12 % off) and two Newton steps, relative error about 2e-4, enough for a bf16 operand.
-__device__ __forceinline__ float rcp_fma(float x) {
-  float r = __uint_as_float(0x7EF311C7u - __float_as_uint(x));
-  r = r * fmaf(-x, r, 2.0f);
-  r = r * fmaf(-x, r, 2.0f);
-  return r;
-}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   uint32_t r;
   asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));

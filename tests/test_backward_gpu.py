@@ -157,6 +157,18 @@ def test_semi_ar_grads_bf16_tiled_value_dim():
         assert_bf16_gate(got[name], ref[key], f"semi-AR bf16 {name}", max_abs=2e-2 * max(1.0, float(ref[key].abs().max())))
 
 
+@pytest.mark.parametrize("N, bs", [(1024, 32), (1152, 48), (2048, 128)])
+def test_semi_ar_grads_long_sequence_segments(N, bs):
+    # few lanes, long sequence: the block-causal backward runs as concurrent sequence segments of whole blocks
+    B, H, M, D = 1, 2, 32, 32
+    q, k, v, dy = orc.make_inputs(B, N, H, M, D, seed0=23, with_dy=True)
+    ref = orc.ar_backward_closed_form(q, k, v, dy, block_size=bs)
+    got = run_grads(lambda q, k, v, qd, kd: cf.flare_semi_autoregressive_trition(q, k, v, block_size=bs, chunk_size=16),
+                    *to_dev(dy, q, k, v))
+    for name, key in (("dq", "dQ"), ("dk", "dK"), ("dv", "dV")):
+        assert_close(got[name], ref[key], what=f"segmented semi-AR {name}", **GRAD32)
+
+
 def test_recurrent_grads(golden):
     g = golden("recurrent")
     q, k, v = g["q"], g["k"], g["v"]
