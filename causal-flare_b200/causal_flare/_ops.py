@@ -187,6 +187,25 @@ def decode_step(Q, k, v, state, *, scale, q_dec=None, K_dec=None, mask=None):
     return y
 
 
+def merge_stacked(a, stacked, count):
+    """Fold the first ``count`` states of ``stacked`` ({"m": [n, B, H, M], "d": ..., "u": [n, B, H, M, Dv]}, fp32,
+    contiguous) in order into ``a``; returns a new state dict."""
+    lib = _lib.load()
+    dev = a["u"].device
+    B, H, M, Dv = a["u"].shape
+    a32 = {k: a[k].float().contiguous() for k in ("m", "d", "u")}
+    for k in ("m", "d", "u"):
+        if stacked[k].dtype != torch.float32 or not stacked[k].is_contiguous():
+            raise ValueError("stacked states must be contiguous fp32 tensors")
+    out = {k: torch.empty_like(a32[k]) for k in ("m", "d", "u")}
+    sa = _lib.state_struct(a32)
+    sb = _lib.State(stacked["m"].data_ptr(), stacked["d"].data_ptr(), stacked["u"].data_ptr())
+    so = _lib.state_struct(out)
+    rc = lib.flare_state_merge(C.byref(sa), C.byref(sb), C.byref(so), B * H, M, Dv, int(count), _lib.stream_handle(dev))
+    _lib.check(rc, "flare_state_merge")
+    return out
+
+
 def merge_states(a, b_list):
     """Fold the states in ``b_list`` (in order) into ``a``; returns a new state dict."""
     lib = _lib.load()

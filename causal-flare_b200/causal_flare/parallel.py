@@ -34,6 +34,22 @@ def exchange_states(local_state, group=None):
     return [unpack_state(g) for g in gathered]
 
 
+def exchange_states_stacked(local_state, group=None):
+    """All-gather of the span states without repacking: one collective per field straight into stacked buffers
+    ``{"m": [world, B, H, M], "d": [world, B, H, M], "u": [world, B, H, M, Dv]}`` (rank-major), the layout the merge
+    kernel folds in one launch."""
+    world = dist.get_world_size(group)
+    out = {}
+    for key in STATE_KEYS:
+        mine = local_state[key].contiguous()
+        out[key] = torch.empty((world,) + tuple(mine.shape), device=mine.device, dtype=mine.dtype)
+        if dist.get_backend(group) == "nccl":
+            dist.all_gather_into_tensor(out[key], mine, group=group)
+        else:  # backends without the flat variant: gather into the slices of the same stacked buffer
+            dist.all_gather(list(out[key].unbind(0)), mine, group=group)
+    return out
+
+
 def prefix_state(states, rank: int, merge_fn, empty_state):
     """Exclusive scan: the carry-in of ``rank`` is the in-order fold of the states of ranks < rank."""
     if rank == 0:
@@ -58,11 +74,12 @@ def sequence_parallel_prefill(Q, K_local, V_local, *, scale, group=None, block_s
         raise ValueError(f"a rank's span ({n_local} tokens) must be a multiple of block_size ({block_size})")
     # (1) span summary: final state only (the kernels skip the read-out work)
     _, local, _, _ = _ops.forward(Q, K_local, V_local, scale=scale, want_state=True, want_y=False)
-    # (2) one collective over NVLink
-    states = exchange_states(local, group)
-    # (3) fold lower ranks
-    empty = _init_flare_recurrent_state(B, H, M, Dv, K_local.device)
-    carry = prefix_state(states, rank, _ops.merge_states, empty)
+    # (2) the exchange over NVLink: the span states land rank-major in stacked buffers
+    stacked = exchange_states_stacked(local, group)
+    # (3) fold lower ranks: one merge launch over the first `rank` entries
+    carry = _init_flare_recurrent_state(B, H, M, Dv, K_local.device)
+    if rank > 0:
+        carry = _ops.merge_stacked(carry, stacked, rank)
     # (4) the span itself, from the carry-in
     Y, st, _, _ = _ops.forward(Q, K_local, V_local, scale=scale, state_in=carry, want_state=True, block_size=block_size)
     return Y, st

@@ -31,6 +31,9 @@ def _worker(rank, world, port, ret):
     assert all(torch.equal(back[key], local[key]) for key in parallel.STATE_KEYS)
     states = parallel.exchange_states(local)
     assert len(states) == world
+    stacked = parallel.exchange_states_stacked(local)  # same exchange, rank-major stacked buffers
+    for r in range(world):
+        assert all(torch.equal(stacked[key][r], states[r][key]) for key in parallel.STATE_KEYS)
 
     def merge(a, bs):
         for b in bs:
