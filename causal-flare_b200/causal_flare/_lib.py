@@ -50,6 +50,9 @@ class BwdArgs(C.Structure):
         ("dy", C.c_void_p),
         ("dy_stride_b", C.c_int64), ("dy_stride_n", C.c_int64), ("dy_stride_h", C.c_int64),
         ("dq", C.c_void_p), ("dk", C.c_void_p), ("dv", C.c_void_p), ("dq_dec", C.c_void_p), ("dk_dec", C.c_void_p),
+        ("carry_b", C.c_void_p), ("carry_c", C.c_void_p), ("carry_rho", C.c_void_p),
+        ("span_b0", C.c_void_p), ("span_c0", C.c_void_p), ("span_gam", C.c_void_p), ("span_rho_first", C.c_void_p),
+        ("phase", C.c_int32),
     ]
 
 

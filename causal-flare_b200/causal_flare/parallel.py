@@ -57,7 +57,7 @@ def prefix_state(states, rank: int, merge_fn, empty_state):
     return merge_fn(empty_state, states[:rank])
 
 
-def sequence_parallel_prefill(Q, K_local, V_local, *, scale, group=None, block_size=1):
+def sequence_parallel_prefill(Q, K_local, V_local, *, scale, group=None, block_size=1, return_prefix=False):
     """Causal FLARE over a sequence whose tokens are sharded across the ranks of ``group``.
 
     K_local / V_local: this rank's span [B, N_local, H, D] (rank r holds tokens [r*N_local, (r+1)*N_local)).
@@ -82,4 +82,43 @@ def sequence_parallel_prefill(Q, K_local, V_local, *, scale, group=None, block_s
         carry = _ops.merge_stacked(carry, stacked, rank)
     # (4) the span itself, from the carry-in
     Y, st, _, _ = _ops.forward(Q, K_local, V_local, scale=scale, state_in=carry, want_state=True, block_size=block_size)
+    if return_prefix:
+        return Y, st, carry  # the state before this rank's span: what the backward of the span starts from
     return Y, st
+
+
+def sequence_parallel_backward(Q, K_local, V_local, dY_local, *, scale, prefix_state, group=None, block_size=1):
+    """Gradients of the sequence-parallel forward.  Every rank replays its span from ``prefix_state`` (the third value
+    of ``sequence_parallel_prefill(..., return_prefix=True)``), the spans' reverse-carry summaries (b, c at the span's
+    first token for a zero carry-in, the product of its decays, the decay of its first token) are all-gathered, every
+    rank folds the summaries of the ranks to its right into the carry that enters its span, and finishes its span.
+    Returns (dQ summed over all ranks, dK_local, dV_local)."""
+    from . import _ops
+
+    rank, world = dist.get_rank(group), dist.get_world_size(group)
+
+    def exchange(summary):
+        stacked = {}
+        for key, mine in summary.items():
+            stacked[key] = torch.empty((world,) + tuple(mine.shape), device=mine.device, dtype=mine.dtype)
+            if dist.get_backend(group) == "nccl":
+                dist.all_gather_into_tensor(stacked[key], mine.contiguous(), group=group)
+            else:
+                dist.all_gather(list(stacked[key].unbind(0)), mine.contiguous(), group=group)
+        if rank == world - 1:
+            return None
+        run_b = torch.zeros_like(summary["b0"])
+        run_c = torch.zeros_like(summary["c0"])
+        for j in range(world - 1, rank, -1):  # b at the first token of span j, given everything to its right
+            if j + 1 < world:
+                w = stacked["gam"][j] * stacked["rho_first"][j + 1]
+                run_b = stacked["b0"][j] + w[..., None] * run_b
+                run_c = stacked["c0"][j] + w * run_c
+            else:
+                run_b, run_c = stacked["b0"][j], stacked["c0"][j]
+        return {"b": run_b, "c": run_c, "rho": stacked["rho_first"][rank + 1]}
+
+    dq, dk, dv = _ops.backward_span(Q, K_local, V_local, dY_local, scale=scale, state_in=prefix_state,
+                                    exchange=exchange, block_size=block_size)
+    dist.all_reduce(dq, op=dist.ReduceOp.SUM, group=group)
+    return dq, dk, dv

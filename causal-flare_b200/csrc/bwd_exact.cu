@@ -61,6 +61,8 @@ struct BwdParams {
   // Block-causal read-out with segments: decay of every block, rho[j, m] = 1 - sum_{t in block j} e[t, m]; the decays
   // in X and seg_gam are then per block.
   float* RHO;                        // [lanes][N / block_size][M]
+  // Span of a longer sequence (sequence parallelism): carries entering from the tokens after the span, or null
+  const float *carry_b, *carry_c, *carry_rho;  // [lanes][M][Dv], [lanes][M], [lanes][M] (decay of the first token after)
 };
 
 // defined once per MM_MAX in {2, 8, 16, 32, 64}, each in its own translation unit; stage 0 = replay, 1 = reverse
@@ -106,7 +108,7 @@ __global__ void __launch_bounds__(NT, (MM_MAX * DD <= 32) ? 2 : 1) bwd_replay_ke
 
   const int seg = p.seg_first + blockIdx.z;
   const int tbeg = seg * p.seg_len, tend = min(N, tbeg + p.seg_len);
-  const bool carry_in = p.nseg > 1 && seg > 0;
+  const bool carry_in = p.in_u != nullptr;  // slot 0 holds the state before the sequence / span (possibly empty)
   const int64_t st = (int64_t)lane_id * p.nseg + seg;  // index of this segment's prefix state
 
   float U[MM_MAX][DD];
@@ -371,7 +373,9 @@ __global__ void __launch_bounds__(NT, (MM_MAX * DD <= 32) ? 2 : 1) bwd_reverse_k
   const int64_t row_base = (int64_t)lane_id * N;
   const int64_t st = (int64_t)lane_id * p.nseg + seg;
   // carries from the segment to the right (zero at the end of the sequence and in the carries-only mode)
+  // carries from the segment to the right; for the last segment, from the tokens after the span (if any)
   const bool carry_in = p.nseg > 1 && tend < N;
+  const bool span_carry = tend >= N && p.carry_b != nullptr;
 
   float Bc[MM_MAX][DD];
 #pragma unroll
@@ -379,14 +383,17 @@ __global__ void __launch_bounds__(NT, (MM_MAX * DD <= 32) ? 2 : 1) bwd_reverse_k
 #pragma unroll
     for (int j = 0; j < DD; ++j) {
       const int m = warp * mm + mi, col = dv0 + lane + 32 * j;
-      Bc[mi][j] = (carry_in && mi < mm && col < Dv) ? p.seg_b[(st * M + m) * Dv + col] : 0.f;
+      Bc[mi][j] = (mi >= mm || col >= Dv) ? 0.f
+                  : carry_in            ? p.seg_b[(st * M + m) * Dv + col]
+                  : span_carry          ? p.carry_b[((int64_t)lane_id * M + m) * Dv + col]
+                                        : 0.f;
     }
   for (int m = tid; m < M; m += NT) {
     // decay of the first step = 1 - e of the first token of the segment to the right
-    rho_in[m] = tend >= N ? 0.f
+    rho_in[m] = tend >= N ? (span_carry ? p.carry_rho[(int64_t)lane_id * M + m] : 0.f)
                 : p.block_size <= 1 ? 1.0f - p.E[(row_base + tend) * M + m]
                                     : p.RHO[((int64_t)lane_id * (N / p.block_size) + tend / p.block_size) * M + m];
-    c_run[m] = carry_in ? p.seg_c[st * M + m] : 0.f;
+    c_run[m] = carry_in ? p.seg_c[st * M + m] : span_carry ? p.carry_c[(int64_t)lane_id * M + m] : 0.f;
     esum[m] = 0.f;
   }
 
@@ -825,6 +832,11 @@ struct BwdPlan {
   size_t off_seg_m, off_seg_d, off_seg_u, off_seg_b, off_seg_c, off_seg_gam, off_X, off_RHO;
 };
 
+// a span of a longer sequence: prefix state, carries from the right or a summary wanted
+bool span_mode(const flare_bwd_args_t& a) {
+  return a.fwd.state_in.u != nullptr || a.carry_b != nullptr || a.span_b0 != nullptr || a.phase != 0;
+}
+
 BwdPlan plan_backward(const flare_bwd_args_t& a) {
   const flare_fwd_args_t& f = a.fwd;
   BwdPlan pl;
@@ -887,7 +899,7 @@ BwdPlan plan_backward(const flare_bwd_args_t& a) {
   pl.off_part_q = take(lat * pl.splits);
   pl.off_part_kd = f.k_dec ? take(lat * pl.splits) : 0;
   pl.off_seg_m = pl.off_seg_d = pl.off_seg_u = pl.off_seg_b = pl.off_seg_c = pl.off_seg_gam = pl.off_X = pl.off_RHO = 0;
-  if (pl.nseg > 1) {
+  if (pl.nseg > 1 || span_mode(a)) {
     const size_t ls = (size_t)f.B * f.H * pl.nseg;
     pl.off_seg_m = take(ls * f.M);
     pl.off_seg_d = take(ls * f.M);
@@ -938,20 +950,18 @@ int launch_bwd_mm<FLARE_WALK_MM>(const BwdParams& p, int dd, dim3 grid, size_t s
 #else
 
 // Carries of a segment for a zero carry-in, as products over its tokens (no sequential walk):
-//   b0[m, :] = sum_t X[t, m] dY_t,   c0[m] = sum_t X[t, m] p[t, m],   and seg_gam[m] *= 1 - e[first token of the next
-// segment, m].  Register-tiled like the latent-gradient kernel: 64 latents x 128 value columns per CTA.
+//   b0[m, :] = sum_t X[t, m] dY_t,   c0[m] = sum_t X[t, m] p[t, m].
+// Register-tiled like the latent-gradient kernel: 64 latents x 128 value columns per CTA; grid.y = segment.
 __global__ void __launch_bounds__(NT) bwd_seg_carry_kernel(const float* __restrict__ X, const float* __restrict__ P,
-                                                           int p_parts, int64_t plane, const float* __restrict__ E,
-                                                           const void* dy, int dtype, int64_t dy_stride_b,
+                                                           int p_parts, int64_t plane, const void* dy, int dtype, int64_t dy_stride_b,
                                                            int64_t dy_stride_n, int64_t dy_stride_h, float* seg_b,
                                                            float* seg_c, float* seg_gam, int nseg, int seg_len, int N,
-                                                           int H, int M, int Dv, const float* __restrict__ RHO,
-                                                           int block_size) {
+                                                           int H, int M, int Dv) {
   __shared__ __align__(16) float x_s[LT][LM + 4];
   __shared__ __align__(16) float dy_s[LT][LDK + 4];
   const int mtiles = (M + LM - 1) / LM;
   const int lane_id = blockIdx.x / mtiles, m0 = (blockIdx.x % mtiles) * LM;
-  const int seg = blockIdx.y + 1, dv0 = blockIdx.z * LDK;
+  const int seg = blockIdx.y, dv0 = blockIdx.z * LDK;
   const int b = lane_id / H, h = lane_id % H;
   const int tid = threadIdx.x, tm = tid / 16, td = tid % 16;
   const int tbeg = seg * seg_len, tend = min(N, tbeg + seg_len);
@@ -1027,33 +1037,54 @@ __global__ void __launch_bounds__(NT) bwd_seg_carry_kernel(const float* __restri
       float c0 = 0.f;
       for (int rg = 0; rg < NT / (LM / 4); ++rg) c0 += red[rg * LM + tid];
       seg_c[st * M + m0 + tid] = c0;
-      const float rho = tend >= N ? 0.f
-                        : block_size <= 1
-                            ? 1.0f - E[(row_base + tend) * M + m0 + tid]
-                            : RHO[((int64_t)lane_id * (N / block_size) + tend / block_size) * M + m0 + tid];
-      seg_gam[st * M + m0 + tid] *= rho;
     }
   }
 }
 
-// Right-to-left scan of the segment carries: on entry slot s holds (b, c) at the first token of segment s for a zero
-// carry-in and gam the product of its decays; on exit slot s holds the carry that enters segment s from the right.
+// Right-to-left scan of the segment carries.  On entry slot s holds (b, c) at the first token of segment s for a zero
+// carry-in and seg_gam the product of its internal decays; with rho_next(s) = decay of the first token (block) after
+// segment s, b(s) = own(s) + gam(s) rho_next(s) b(s + 1).  write_slots: slot s receives the carry that enters segment
+// s from the right (what the reverse walk starts from).  The totals of the whole span (b, c at its first token for the
+// given right-hand carry, the product of all its decays, the decay of its own first token) go to the span_* outputs
+// when those are given.
 __global__ void __launch_bounds__(256) bwd_seg_scan_kernel(float* seg_b, float* seg_c, const float* seg_gam, int nseg,
-                                                           int64_t lanes, int M, int Dv) {
+                                                           int seg_len, int64_t lanes, int N, int M, int Dv,
+                                                           const float* __restrict__ E, const float* __restrict__ RHO,
+                                                           int block_size, const float* carry_b, const float* carry_c,
+                                                           const float* carry_rho, int write_slots, float* span_b0,
+                                                           float* span_c0, float* span_gam, float* span_rho_first) {
   const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int64_t per_lane = (int64_t)M * (Dv + 1);  // Dv columns of b, then c
   if (idx >= lanes * per_lane) return;
   const int64_t lane_id = idx / per_lane;
   const int r = (int)(idx % per_lane);
   const int m = r / (Dv + 1), col = r % (Dv + 1);
+  auto decay_at = [&](int t) -> float {  // decay of the token (block) that starts at t
+    return block_size <= 1 ? 1.0f - E[(lane_id * N + t) * M + m]
+                           : RHO[(lane_id * (N / block_size) + t / block_size) * M + m];
+  };
   float run = 0.f;
+  if (carry_b != nullptr) run = col < Dv ? carry_b[(lane_id * M + m) * Dv + col] : carry_c[lane_id * M + m];
+  float gprod = 1.0f;
   for (int s = nseg - 1; s >= 0; --s) {
     const int64_t st = lane_id * nseg + s;
     float* slot = col < Dv ? seg_b + (st * M + m) * Dv + col : seg_c + st * M + m;
-    const float own = s > 0 ? *slot : 0.f;  // segment 0 hands nothing on
+    const float own = *slot;
+    const int t_next = (s + 1) * seg_len;
+    const float rho_next = t_next < N ? decay_at(t_next) : (carry_rho != nullptr ? carry_rho[lane_id * M + m] : 0.f);
     const float gam = seg_gam[st * M + m];
-    *slot = run;
-    run = own + gam * run;
+    if (write_slots) *slot = run;
+    run = own + gam * rho_next * run;
+    gprod *= gam * (t_next < N ? rho_next : 1.0f);  // internal decays only
+  }
+  if (span_b0 != nullptr) {
+    if (col < Dv) {
+      span_b0[(lane_id * M + m) * Dv + col] = run;
+    } else {
+      span_c0[lane_id * M + m] = run;
+      span_gam[lane_id * M + m] = gprod;
+      span_rho_first[lane_id * M + m] = decay_at(0);
+    }
   }
 }
 
@@ -1092,13 +1123,15 @@ int bwd_exact(const flare_bwd_args_t& a, cudaStream_t stream) {
   p.DT = pl.DT; p.plane = pl.plane; p.dv_out = a.dv;
   p.nseg = pl.nseg; p.seg_len = pl.seg_len; p.seg_first = 0;
   const int64_t lanes = (int64_t)f.B * f.H;
-  if (pl.nseg > 1) {
-    float* seg_m = reinterpret_cast<float*>(ws + pl.off_seg_m);
-    float* seg_d = reinterpret_cast<float*>(ws + pl.off_seg_d);
-    float* seg_u = reinterpret_cast<float*>(ws + pl.off_seg_u);
-    // exclusive prefix state of every segment, from the forward kernels
-    const int rc = segment_prefix_states(&f, pl.nseg, pl.seg_len, seg_m, seg_d, seg_u, stream);
-    if (rc != FLARE_OK) return rc;
+  const bool seg_mode = pl.nseg > 1 || span_mode(a);
+  if (a.phase < 0 || a.phase > 2 || (a.span_b0 != nullptr && !(a.span_c0 && a.span_gam && a.span_rho_first)) ||
+      (a.carry_b != nullptr && !(a.carry_c && a.carry_rho)) || (span_mode(a) && f.block_size > 1 && f.N % f.block_size))
+    return FLARE_ERR_BAD_POINTER;
+  float *seg_m = nullptr, *seg_d = nullptr, *seg_u = nullptr;
+  if (seg_mode) {
+    seg_m = reinterpret_cast<float*>(ws + pl.off_seg_m);
+    seg_d = reinterpret_cast<float*>(ws + pl.off_seg_d);
+    seg_u = reinterpret_cast<float*>(ws + pl.off_seg_u);
     p.in_m = seg_m; p.in_d = seg_d; p.in_u = seg_u;
     p.seg_b = reinterpret_cast<float*>(ws + pl.off_seg_b);
     p.seg_c = reinterpret_cast<float*>(ws + pl.off_seg_c);
@@ -1106,6 +1139,7 @@ int bwd_exact(const flare_bwd_args_t& a, cudaStream_t stream) {
     p.X = reinterpret_cast<float*>(ws + pl.off_X);
     p.RHO = f.block_size > 1 ? reinterpret_cast<float*>(ws + pl.off_RHO) : nullptr;
   }
+  p.carry_b = a.carry_b; p.carry_c = a.carry_c; p.carry_rho = a.carry_rho;
 
   const int mm = f.M / NW;
   const size_t smem1 = replay_smem(f.M, f.Dk, pl.dd), smem2 = reverse_smem(f.M, pl.dd, stablemax);
@@ -1120,22 +1154,43 @@ int bwd_exact(const flare_bwd_args_t& a, cudaStream_t stream) {
     if (mm <= 32) return launch_bwd_mm<32>(q, pl.dd, grid, smem1, smem2, stream, stage);
     return launch_bwd_mm<64>(q, pl.dd, grid, smem1, smem2, stream, stage);
   };
-  int rcw = walk(0, 0, pl.nseg);  // replay: planes e, g, p (and X, the carry weights, when segmented)
-  if (rcw != FLARE_OK) return rcw;
-  if (pl.nseg > 1) {
-    // carries of segments 1 .. nseg-1 for a zero carry-in (products over the planes), then their right-to-left scan
-    {
-      const int mt = (f.M + LM - 1) / LM;
-      dim3 g((unsigned)(lanes * mt), pl.nseg - 1, (f.Dv + LDK - 1) / LDK);
-      bwd_seg_carry_kernel<<<g, NT, 0, stream>>>(p.X, p.P, pl.DT, pl.plane, p.E, a.dy, f.dtype, a.dy_stride_b,
-                                                 a.dy_stride_n, a.dy_stride_h, p.seg_b, p.seg_c, p.seg_gam, pl.nseg,
-                                                 pl.seg_len, f.N, f.H, f.M, f.Dv, p.RHO, f.block_size);
-      FLARE_CUDA_CHECK(cudaGetLastError());
-    }
-    const int64_t n = lanes * f.M * (f.Dv + 1);
-    bwd_seg_scan_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(p.seg_b, p.seg_c, p.seg_gam, pl.nseg, lanes, f.M,
-                                                                        f.Dv);
+  const int64_t nscan = lanes * f.M * (f.Dv + 1);
+  auto scan = [&](bool write_slots, bool with_carry, bool summary) -> int {
+    bwd_seg_scan_kernel<<<(unsigned)((nscan + 255) / 256), 256, 0, stream>>>(
+        p.seg_b, p.seg_c, p.seg_gam, pl.nseg, pl.seg_len, lanes, f.N, f.M, f.Dv, p.E, p.RHO, f.block_size,
+        with_carry ? a.carry_b : nullptr, with_carry ? a.carry_c : nullptr, with_carry ? a.carry_rho : nullptr,
+        write_slots ? 1 : 0, summary ? a.span_b0 : nullptr, a.span_c0, a.span_gam, a.span_rho_first);
     FLARE_CUDA_CHECK(cudaGetLastError());
+    return FLARE_OK;
+  };
+  int rcw = FLARE_OK;
+  if (a.phase != 2) {
+    if (seg_mode) {
+      // exclusive prefix state of every segment, from the forward kernels (slot 0: the state before the span)
+      rcw = segment_prefix_states(&f, pl.nseg, pl.seg_len, seg_m, seg_d, seg_u,
+                                  f.state_in.u != nullptr ? &f.state_in : nullptr, stream);
+      if (rcw != FLARE_OK) return rcw;
+    }
+    rcw = walk(0, 0, pl.nseg);  // replay: planes e, g, p (and X, the carry weights, when segmented)
+    if (rcw != FLARE_OK) return rcw;
+    if (seg_mode) {
+      // carries of every segment for a zero carry-in, as products over the planes
+      const int mt = (f.M + LM - 1) / LM;
+      dim3 g((unsigned)(lanes * mt), pl.nseg, (f.Dv + LDK - 1) / LDK);
+      bwd_seg_carry_kernel<<<g, NT, 0, stream>>>(p.X, p.P, pl.DT, pl.plane, a.dy, f.dtype, a.dy_stride_b, a.dy_stride_n,
+                                                 a.dy_stride_h, p.seg_b, p.seg_c, p.seg_gam, pl.nseg, pl.seg_len, f.N,
+                                                 f.H, f.M, f.Dv);
+      FLARE_CUDA_CHECK(cudaGetLastError());
+      if (a.span_b0 != nullptr) {
+        rcw = scan(false, false, true);  // summary of the span for a zero carry-in from the right
+        if (rcw != FLARE_OK) return rcw;
+      }
+    }
+    if (a.phase == 1) return FLARE_OK;
+  }
+  if (seg_mode) {
+    rcw = scan(true, true, false);  // right-to-left scan: every segment's true carry-in
+    if (rcw != FLARE_OK) return rcw;
   }
   rcw = walk(1, 0, pl.nseg);  // reverse walk: dV and the dS planes
   if (rcw != FLARE_OK) return rcw;

@@ -234,7 +234,7 @@ int forward_run(const flare_fwd_args_t* a, cudaStream_t stream) {
 }  // namespace
 
 int segment_prefix_states(const flare_fwd_args_t* f, int nseg, int seg_len, float* seg_m, float* seg_d, float* seg_u,
-                          cudaStream_t stream) {
+                          const flare_state_t* init, cudaStream_t stream) {
   flare_fwd_args_t a = *f;
   a.y = nullptr;
   a.mask = nullptr;
@@ -253,14 +253,19 @@ int segment_prefix_states(const flare_fwd_args_t* f, int nseg, int seg_len, floa
   w.y = nullptr; w.write_y = 0;
   w.out_m = seg_m; w.out_d = seg_d; w.out_u = seg_u;
   w.out_lane_stride = nseg; w.out_seg_stride = 1; w.out_mode = 1;
-  int rc = launch_walk(&a, pl, w, nseg - 1, stream);  // local states of all segments but the last
-  if (rc != FLARE_OK) return rc;
+  if (nseg > 1) {
+    const int rc = launch_walk(&a, pl, w, nseg - 1, stream);  // local states of all segments but the last
+    if (rc != FLARE_OK) return rc;
+  }
   FoldParams fp;
   memset(&fp, 0, sizeof(fp));
+  if (init != nullptr) {
+    fp.a_m = init->m; fp.a_d = init->d; fp.a_u = init->u;
+  }
   fp.s_m = seg_m; fp.s_d = seg_d; fp.s_u = seg_u;
   fp.lane_stride = nseg; fp.seg_stride = 1; fp.count = nseg; fp.mode = 0;
   fp.lanes = lanes; fp.M = a.M; fp.Dv = a.Dv; fp.stablemax = a.variant == FLARE_STABLEMAX;
-  return launch_fold(fp, stream);  // exclusive scan from the empty state
+  return launch_fold(fp, stream);  // exclusive scan from the initial (or empty) state
 }
 
 }  // namespace flare

@@ -132,6 +132,23 @@ typedef struct flare_bwd_args {
   void* dv;             /* [B, N, H, Dv] contiguous */
   void* dq_dec;         /* [B, N, H, Dk] contiguous or NULL */
   float* dk_dec;        /* [H, M, Dk] fp32 or NULL */
+  /*
+   * Spans of a longer sequence (sequence parallelism over GPUs; no counterpart in the reference).  All NULL / 0 for a
+   * whole sequence.  The span's tokens are fwd.k / fwd.v / dy; fwd.state_in (else ignored) is the forward state of the
+   * tokens before the span.  phase 1 replays the span and writes its summary - (b, c) at its first token for a zero
+   * carry-in from the right, the product of its decays, the decay of its first token (block) - into span_*; the
+   * caller combines the summaries of the spans to its right into carry_* and calls phase 2 with the SAME workspace,
+   * which writes dk, dv and this span's part of dq (to be summed over the spans).  phase 0 does both at once
+   * (carry_* may then be given directly).
+   */
+  const float* carry_b;   /* [B, H, M, Dv]  b at the first token after the span */
+  const float* carry_c;   /* [B, H, M] */
+  const float* carry_rho; /* [B, H, M]      decay (1 - e) of the first token (block) after the span */
+  float* span_b0;         /* [B, H, M, Dv] */
+  float* span_c0;         /* [B, H, M] */
+  float* span_gam;        /* [B, H, M] */
+  float* span_rho_first;  /* [B, H, M] */
+  int32_t phase;          /* 0, 1 or 2 */
 } flare_bwd_args_t;
 
 size_t flare_backward_workspace_bytes(const flare_bwd_args_t* args);

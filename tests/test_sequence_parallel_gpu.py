@@ -56,3 +56,48 @@ def test_sequence_parallel_two_gpus(block_size):
         assert status == 0
         assert err < 2e-2, f"rank {rank}: y differs from the one-GPU run by {err}"
         assert st_err < 5e-3
+
+
+def _bwd_worker(rank, world, port, block_size, ret):
+    for p in (ROOT, os.path.join(ROOT, "causal-flare_b200")):
+        if p not in sys.path:
+            sys.path.insert(0, p)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world)
+    from causal_flare import _ops, parallel
+
+    B, N, H, M, D = 1, 1536, 2, 64, 64
+    g = torch.Generator(device="cuda").manual_seed(13)  # same data on every rank
+    q = torch.randn(H, M, D, generator=g, device="cuda").bfloat16()
+    k = torch.randn(B, N, H, D, generator=g, device="cuda").bfloat16()
+    v = torch.randn(B, N, H, D, generator=g, device="cuda").bfloat16()
+    dy = torch.randn(B, N, H, D, generator=g, device="cuda").bfloat16()
+    sc = D ** -0.5
+    span = N // world
+    sl = slice(rank * span, (rank + 1) * span)
+    kl, vl, dyl = k[:, sl].contiguous(), v[:, sl].contiguous(), dy[:, sl].contiguous()
+    _, _, prefix = parallel.sequence_parallel_prefill(q, kl, vl, scale=sc, block_size=block_size, return_prefix=True)
+    dq, dk, dv = parallel.sequence_parallel_backward(q, kl, vl, dyl, scale=sc, prefix_state=prefix, block_size=block_size)
+    dq_f, dk_f, dv_f, _, _ = _ops.backward(q, k, v, dy, scale=sc, block_size=block_size)
+
+    def rel(a, b):
+        return float((a.float() - b.float()).norm() / b.float().norm())
+
+    ret[rank] = (rel(dq, dq_f), rel(dk, dk_f[:, sl]), rel(dv, dv_f[:, sl]))
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("block_size", [1, 64])
+def test_sequence_parallel_backward_two_gpus(block_size):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    world = 2
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    port = 29700 + (os.getpid() % 2000) + block_size
+    mp.spawn(_bwd_worker, args=(world, port, block_size, ret), nprocs=world, join=True)
+    for rank in range(world):
+        for name, err in zip(("dq", "dk", "dv"), ret[rank]):
+            assert err < 5e-3, f"rank {rank}: {name} differs from the one-GPU backward by rel-L2 {err}"
