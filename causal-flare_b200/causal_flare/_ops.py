@@ -142,45 +142,49 @@ def backward(Q, K, V, dY, *, scale, Q_dec=None, K_dec=None, variant=_lib.SOFTMAX
     return dq, dk, dv, dqd, dkd
 
 
-def backward_span(Q, K, V, dY, *, scale, state_in, exchange, variant=_lib.SOFTMAX, power=2.0, block_size=1):
-    """Backward of a span of a longer sequence (shared decode weights).
-
-    ``state_in``: forward state of the tokens before the span (dict m, d, u; None for the first span).
-    ``exchange(summary) -> carry | None``: called between the two phases with this span's summary
-    ``{"b0", "c0", "gam", "rho_first"}`` (fp32 tensors [B,H,M(,Dv)]); returns the carries entering from the tokens
-    after the span as ``{"b", "c", "rho"}`` or None for the last span.
-    Returns (dQ fp32 - this span's part, to be summed over the spans -, dK, dV in the input dtype)."""
+def backward_span_begin(Q, K, V, dY, *, scale, state_in, variant=_lib.SOFTMAX, power=2.0, block_size=1):
+    """First phase of the backward of a span of a longer sequence (shared decode weights): replays the span from
+    ``state_in`` (forward state of the tokens before it; None for the first span) and returns a context whose
+    ``summary`` = {"b0", "c0", "gam", "rho_first"} (fp32 [B,H,M(,Dv)]) describes the span to the spans on its left."""
     lib = _lib.load()
     dev, dt = K.device, K.dtype
     B, N, H, Dk = K.shape
     M, Dv = Q.shape[1], V.shape[-1]
-    q, k, v, dy = _prep(Q, dt), _prep(K, dt), _prep(V, dt), _prep(dY, dt)
-    dq = torch.zeros((H, M, Dk), device=dev, dtype=torch.float32)
-    dk = torch.zeros((B, N, H, Dk), device=dev, dtype=dt)
-    dv = torch.zeros((B, N, H, Dv), device=dev, dtype=dt)
+    keep = dict(q=_prep(Q, dt), k=_prep(K, dt), v=_prep(V, dt), dy=_prep(dY, dt))
+    keep["dq"] = torch.zeros((H, M, Dk), device=dev, dtype=torch.float32)
+    keep["dk"] = torch.zeros((B, N, H, Dk), device=dev, dtype=dt)
+    keep["dv"] = torch.zeros((B, N, H, Dv), device=dev, dtype=dt)
     summary = {"b0": torch.empty((B, H, M, Dv), device=dev), "c0": torch.empty((B, H, M), device=dev),
                "gam": torch.empty((B, H, M), device=dev), "rho_first": torch.empty((B, H, M), device=dev)}
-    st = None if state_in is None else {key: state_in[key].float().contiguous() for key in ("m", "d", "u")}
+    keep["st"] = None if state_in is None else {key: state_in[key].float().contiguous() for key in ("m", "d", "u")}
     a = _lib.BwdArgs()
-    a.fwd = _lib.make_fwd_args(q, k, v, None, None, None, scale=scale, variant=variant, power=power,
-                               block_size=block_size, state_in=st)
+    a.fwd = _lib.make_fwd_args(keep["q"], keep["k"], keep["v"], None, None, None, scale=scale, variant=variant,
+                               power=power, block_size=block_size, state_in=keep["st"])
+    dy = keep["dy"]
     a.dy = dy.data_ptr()
     a.dy_stride_b, a.dy_stride_n, a.dy_stride_h = dy.stride(0), dy.stride(1), dy.stride(2)
-    a.dq, a.dk, a.dv = dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
+    a.dq, a.dk, a.dv = keep["dq"].data_ptr(), keep["dk"].data_ptr(), keep["dv"].data_ptr()
     a.span_b0, a.span_c0 = summary["b0"].data_ptr(), summary["c0"].data_ptr()
     a.span_gam, a.span_rho_first = summary["gam"].data_ptr(), summary["rho_first"].data_ptr()
     a.phase = 1
     need = lib.flare_backward_workspace_bytes(C.byref(a))
-    ws = torch.empty(max(need, 16), dtype=torch.uint8, device=dev)  # lives across both phases: it holds the planes
-    a.fwd.workspace, a.fwd.workspace_bytes = ws.data_ptr(), need
+    keep["ws"] = torch.empty(max(need, 16), dtype=torch.uint8, device=dev)  # holds the planes across both phases
+    a.fwd.workspace, a.fwd.workspace_bytes = keep["ws"].data_ptr(), need
     _lib.check(lib.flare_backward(C.byref(a), _lib.stream_handle(dev)), "flare_backward (span, phase 1)")
-    carry = exchange(summary)
+    return {"args": a, "keep": keep, "summary": summary, "device": dev}
+
+
+def backward_span_finish(ctx, carry):
+    """Second phase: ``carry`` = {"b", "c", "rho"} entering from the tokens after the span (None for the last span).
+    Returns (dQ fp32 - this span's part, to be summed over the spans -, dK, dV in the input dtype)."""
+    lib = _lib.load()
+    a, keep = ctx["args"], ctx["keep"]
     if carry is not None:
-        cb, cc, cr = (carry[key].float().contiguous() for key in ("b", "c", "rho"))
-        a.carry_b, a.carry_c, a.carry_rho = cb.data_ptr(), cc.data_ptr(), cr.data_ptr()
+        keep["carry"] = [carry[key].float().contiguous() for key in ("b", "c", "rho")]
+        a.carry_b, a.carry_c, a.carry_rho = (t.data_ptr() for t in keep["carry"])
     a.phase = 2
-    _lib.check(lib.flare_backward(C.byref(a), _lib.stream_handle(dev)), "flare_backward (span, phase 2)")
-    return dq, dk, dv
+    _lib.check(lib.flare_backward(C.byref(a), _lib.stream_handle(ctx["device"])), "flare_backward (span, phase 2)")
+    return keep["dq"], keep["dk"], keep["dv"]
 
 
 def decode_step(Q, k, v, state, *, scale, q_dec=None, K_dec=None, mask=None):

@@ -87,6 +87,22 @@ def sequence_parallel_prefill(Q, K_local, V_local, *, scale, group=None, block_s
     return Y, st
 
 
+def right_carry(stacked, rank: int):
+    """The reverse carries that enter span ``rank`` from the spans to its right, from the stacked span summaries
+    ({"b0": [n, B, H, M, Dv], "c0", "gam", "rho_first": [n, B, H, M]}).  With b(j) = b at the first token of span j given
+    everything to its right: b(j) = b0[j] + gam[j] rho_first[j + 1] b(j + 1); the carry into ``rank`` is b(rank + 1)
+    together with the decay rho_first[rank + 1] of that first token.  None for the last span."""
+    n = stacked["b0"].shape[0]
+    if rank >= n - 1:
+        return None
+    run_b, run_c = stacked["b0"][n - 1], stacked["c0"][n - 1]
+    for j in range(n - 2, rank, -1):
+        w = stacked["gam"][j] * stacked["rho_first"][j + 1]
+        run_b = stacked["b0"][j] + w[..., None] * run_b
+        run_c = stacked["c0"][j] + w * run_c
+    return {"b": run_b, "c": run_c, "rho": stacked["rho_first"][rank + 1]}
+
+
 def sequence_parallel_backward(Q, K_local, V_local, dY_local, *, scale, prefix_state, group=None, block_size=1):
     """Gradients of the sequence-parallel forward.  Every rank replays its span from ``prefix_state`` (the third value
     of ``sequence_parallel_prefill(..., return_prefix=True)``), the spans' reverse-carry summaries (b, c at the span's
@@ -96,29 +112,15 @@ def sequence_parallel_backward(Q, K_local, V_local, dY_local, *, scale, prefix_s
     from . import _ops
 
     rank, world = dist.get_rank(group), dist.get_world_size(group)
-
-    def exchange(summary):
-        stacked = {}
-        for key, mine in summary.items():
-            stacked[key] = torch.empty((world,) + tuple(mine.shape), device=mine.device, dtype=mine.dtype)
-            if dist.get_backend(group) == "nccl":
-                dist.all_gather_into_tensor(stacked[key], mine.contiguous(), group=group)
-            else:
-                dist.all_gather(list(stacked[key].unbind(0)), mine.contiguous(), group=group)
-        if rank == world - 1:
-            return None
-        run_b = torch.zeros_like(summary["b0"])
-        run_c = torch.zeros_like(summary["c0"])
-        for j in range(world - 1, rank, -1):  # b at the first token of span j, given everything to its right
-            if j + 1 < world:
-                w = stacked["gam"][j] * stacked["rho_first"][j + 1]
-                run_b = stacked["b0"][j] + w[..., None] * run_b
-                run_c = stacked["c0"][j] + w * run_c
-            else:
-                run_b, run_c = stacked["b0"][j], stacked["c0"][j]
-        return {"b": run_b, "c": run_c, "rho": stacked["rho_first"][rank + 1]}
-
-    dq, dk, dv = _ops.backward_span(Q, K_local, V_local, dY_local, scale=scale, state_in=prefix_state,
-                                    exchange=exchange, block_size=block_size)
+    ctx = _ops.backward_span_begin(Q, K_local, V_local, dY_local, scale=scale, state_in=prefix_state,
+                                   block_size=block_size)
+    stacked = {}
+    for key, mine in ctx["summary"].items():
+        stacked[key] = torch.empty((world,) + tuple(mine.shape), device=mine.device, dtype=mine.dtype)
+        if dist.get_backend(group) == "nccl":
+            dist.all_gather_into_tensor(stacked[key], mine.contiguous(), group=group)
+        else:
+            dist.all_gather(list(stacked[key].unbind(0)), mine.contiguous(), group=group)
+    dq, dk, dv = _ops.backward_span_finish(ctx, right_carry(stacked, rank))
     dist.all_reduce(dq, op=dist.ReduceOp.SUM, group=group)
     return dq, dk, dv

@@ -187,3 +187,41 @@ def test_profile_backward_timings_filled_in_place(golden):
     assert prof["backward"] == {}
     y.backward(g["dy"].cuda())
     assert prof["backward_total_ms"] > 0 and prof["total_ms"] >= prof["forward_total_ms"]
+
+
+@pytest.mark.parametrize("block_size, dtype", [(1, torch.float32), (32, torch.float32), (1, torch.bfloat16)])
+def test_span_backward_four_spans_on_one_gpu(block_size, dtype):
+    # the sequence-parallel backward with the ranks emulated in one process: every span is replayed from its prefix
+    # state, the span summaries are combined right to left, every span is finished with its carry; the pieces must
+    # equal the gradients of the whole sequence
+    from causal_flare import _ops, parallel
+
+    B, N, H, M, D, spans = 1, 1280, 2, 32, 64, 4
+    q, k, v, dy = orc.make_inputs(B, N, H, M, D, seed0=29, dtype=dtype, with_dy=True)
+    qc, kc, vc, dyc = to_dev(q, k, v, dy)
+    sc = D ** -0.5
+    span = N // spans
+    state, ctxs = None, []
+    for r in range(spans):
+        sl = slice(r * span, (r + 1) * span)
+        ctxs.append(_ops.backward_span_begin(qc, kc[:, sl], vc[:, sl], dyc[:, sl], scale=sc, state_in=state,
+                                             block_size=block_size))
+        _, state, _, _ = _ops.forward(qc, kc[:, sl], vc[:, sl], scale=sc, state_in=state, want_state=True, want_y=False)
+    stacked = {key: torch.stack([c["summary"][key] for c in ctxs]) for key in ("b0", "c0", "gam", "rho_first")}
+    dq = torch.zeros(H, M, D, device="cuda")
+    dks, dvs = [], []
+    for r in range(spans):
+        dq_r, dk_r, dv_r = _ops.backward_span_finish(ctxs[r], parallel.right_carry(stacked, r))
+        dq += dq_r
+        dks.append(dk_r)
+        dvs.append(dv_r)
+    dq_f, dk_f, dv_f, _, _ = _ops.backward(qc, kc, vc, dyc, scale=sc, block_size=block_size)
+    tol = dict(atol=2e-3, rtol=2e-2) if dtype == torch.float32 else dict(atol=5e-2, rtol=5e-2)
+    assert_close(dq, dq_f, what="span dq", **tol)
+    assert_close(torch.cat(dks, 1), dk_f, what="span dk", **tol)
+    assert_close(torch.cat(dvs, 1), dv_f, what="span dv", **tol)
+    if dtype == torch.float32:
+        ref = orc.ar_backward_closed_form(q, k, v, dy, scale=sc, block_size=block_size)
+        assert_close(torch.cat(dks, 1), ref["dK"], what="span dk vs oracle", **GRAD32)
+        assert_close(torch.cat(dvs, 1), ref["dV"], what="span dv vs oracle", **GRAD32)
+        assert_close(dq, ref["dQ"], what="span dq vs oracle", **GRAD32)
