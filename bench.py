@@ -344,7 +344,28 @@ def bench_seqpar(args, rank, world):
     barrier(world)
     ms = max_over_ranks(t0.elapsed_time(t1), world) / steps
     assert torch.isfinite(y.float()).all() and _ops.device_status() == 0
-    return {"metric": "block-causal long-context prefill throughput", "value": B * N / (ms * 1e-3) / 1e6, "unit": "Mtok/s",
+    fwd_bwd_ms = None
+    if args.seqpar_backward:
+        dy = torch.randn(B, span, H, D, generator=g, device="cuda").bfloat16()
+
+        def train_step():
+            if world == 1:
+                _ops.forward(q, k, v, scale=sc, block_size=bs)
+                return _ops.backward(q, k, v, dy, scale=sc, block_size=bs)[0]
+            _, _, prefix = parallel.sequence_parallel_prefill(q, k, v, scale=sc, block_size=bs, return_prefix=True)
+            return parallel.sequence_parallel_backward(q, k, v, dy, scale=sc, prefix_state=prefix, block_size=bs)[0]
+
+        train_step()
+        barrier(world)
+        b0, b1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        b0.record()
+        for _ in range(2):
+            dq = train_step()
+        b1.record()
+        barrier(world)
+        fwd_bwd_ms = max_over_ranks(b0.elapsed_time(b1), world) / 2
+        assert torch.isfinite(dq).all()
+    return {"metric": "block-causal long-context prefill throughput", "fwd_bwd_ms": fwd_bwd_ms, "value": B * N / (ms * 1e-3) / 1e6, "unit": "Mtok/s",
             "n_gpus": world, "steps": steps, "ms_per_step": ms, "scaling": "strong", "higher_is_better": True,
             "dtype": "bf16", "data": "synthetic",
             "config": {"workload": f"C5 semi-AR B={B} N={N} H={H} M={M} D={D} block={bs}, {span} tokens per GPU",
@@ -441,6 +462,7 @@ def main():
     ap.add_argument("--only", default="all", choices=["all", "prefill", "decode", "seqpar", "train"],
                     help="profiling aid: run one section only (the JSON line then lacks the other)")
     ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--seqpar-backward", action="store_true", help="with --only seqpar: also time forward+backward")
     ap.add_argument("--skip-other", action="store_true", help="skip the short runs of the other benchmark shapes")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
