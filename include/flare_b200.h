@@ -124,7 +124,7 @@ size_t flare_noalloc_scratch_capacity(void);
  * folded into dk / dq and dq_dec / dk_dec must be NULL.
  */
 typedef struct flare_bwd_args {
-  flare_fwd_args_t fwd; /* y, mask, state_*, lse_* are ignored */
+  flare_fwd_args_t fwd; /* y, mask, lengths, state_out, lse_* are ignored; state_in only in span mode (below) */
   const void* dy;       /* [B, N, H, Dv], input dtype */
   int64_t dy_stride_b, dy_stride_n, dy_stride_h;
   float* dq;            /* [H, M, Dk] fp32 */
