@@ -56,3 +56,44 @@ def test_sequence_parallel_exchange_world2():
     assert len(ret) == world
     for rank in range(world):
         assert ret[rank] < 1e-5, f"rank {rank}: max-abs {ret[rank]}"
+
+
+def test_right_carry_folds_span_summaries_like_the_token_recurrence():
+    """The cross-rank fold of the backward: for a token-level reverse recurrence b_t = x_t + rho_{t+1} b_{t+1}, span
+    summaries (b at the span's first token for a zero carry-in, product of the span's internal decays, decay of its
+    first token) folded by parallel.right_carry must reproduce b at the first token of the next span."""
+    for p in (ROOT, os.path.join(ROOT, "causal-flare_b200")):
+        if p not in sys.path:
+            sys.path.insert(0, p)
+    from causal_flare import parallel
+
+    g = torch.Generator().manual_seed(0)
+    spans, span_len, B, H, M, Dv = 4, 5, 1, 2, 3, 2
+    T = spans * span_len
+    x = torch.randn(T, B, H, M, Dv, generator=g, dtype=torch.float64)
+    xc = torch.randn(T, B, H, M, generator=g, dtype=torch.float64)
+    rho = torch.rand(T, B, H, M, generator=g, dtype=torch.float64)
+    b = torch.zeros(T + 1, B, H, M, Dv, dtype=torch.float64)
+    c = torch.zeros(T + 1, B, H, M, dtype=torch.float64)
+    for t in range(T - 1, -1, -1):
+        nxt = rho[t + 1] if t + 1 < T else torch.zeros_like(rho[0])
+        b[t] = x[t] + nxt[..., None] * b[t + 1]
+        c[t] = xc[t] + nxt * c[t + 1]
+    summ = {"b0": [], "c0": [], "gam": [], "rho_first": []}
+    for s in range(spans):
+        a, z = s * span_len, (s + 1) * span_len - 1
+        rb, rc, gam = torch.zeros_like(b[0]), torch.zeros_like(c[0]), torch.ones_like(c[0])
+        for t in range(z, a - 1, -1):  # zero carry-in from the right, internal decays only
+            dec = rho[t + 1] if t < z else torch.zeros_like(rho[0])
+            rb = x[t] + dec[..., None] * rb
+            rc = xc[t] + dec * rc
+            if t < z:
+                gam = gam * rho[t + 1]
+        summ["b0"].append(rb); summ["c0"].append(rc); summ["gam"].append(gam); summ["rho_first"].append(rho[a])
+    stacked = {k: torch.stack(v) for k, v in summ.items()}
+    assert parallel.right_carry(stacked, spans - 1) is None
+    for r in range(spans - 1):
+        got = parallel.right_carry(stacked, r)
+        first_next = (r + 1) * span_len
+        assert torch.allclose(got["b"], b[first_next]) and torch.allclose(got["c"], c[first_next])
+        assert torch.equal(got["rho"], rho[first_next])
