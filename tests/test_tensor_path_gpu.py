@@ -289,3 +289,23 @@ def test_block_causal_long_context_shape_vs_exact():
     v2[:, N // 2:] = 1
     y2, _, _, _ = run(q, k2, v2, _lib.PATH_TENSOR, block_size=bs, scale=sc)
     assert torch.equal(y2[:, :N // 2], y_t[:, :N // 2]), "tokens of later blocks changed earlier outputs"
+
+
+@pytest.mark.parametrize("N", [1, 5, 16, 17, 127, 129])
+def test_tensor_path_tiny_and_ragged_lengths(N):
+    # one partial chunk, a chunk boundary, and one token past it, for the three read-out modes
+    Ml, Dw = 64, 64
+    q, k, v = orc.make_inputs(2, N, 2, Ml, Dw, seed0=91, dtype=torch.bfloat16)
+    sc = Dw ** -0.5
+    qc, kc, vc = to_dev(q, k, v)
+    ref, st_ref = orc.ar_forward(q, k, v, scale=sc, return_state=True)
+    y, st, _, _ = run(qc, kc, vc, _lib.PATH_TENSOR, want_state=True, scale=sc)
+    assert_bf16_gate(y, ref, f"softmax N={N}")
+    assert orc.rel_l2(st["u"].cpu(), st_ref["u"]) < 3e-3
+    ref_s = orc.ar_forward(q, k, v, scale=sc, variant="stablemax", power=2.0)
+    y_s, _, _, _ = run(qc, kc, vc, _lib.PATH_TENSOR, variant=_lib.STABLEMAX, power=2.0, scale=sc)
+    assert_bf16_gate(y_s, ref_s, f"stablemax N={N}")
+    if N % 16 == 0:
+        ref_b, _, _ = orc.semi_ar_forward(q, k, v, block_size=16, scale=sc)
+        y_b, _, _, _ = run(qc, kc, vc, _lib.PATH_TENSOR, block_size=16, scale=sc)
+        assert_bf16_gate(y_b, ref_b, f"block-causal N={N}")
