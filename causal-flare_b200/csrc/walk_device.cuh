@@ -59,29 +59,41 @@ static __device__ __forceinline__ void load_rows(float* dst, int ld, const void*
   }
 }
 
-// out[t][m] = scale * <tok[t,:], lat[m,:]> for the 16 tokens of the tile and all M latents.
-static __device__ __forceinline__ void score_tile(float* out, int mp, const float* tok, int ldk, const void* lat, int dtype,
-                                           int64_t lat_off, int64_t lat_stride_m, int M, int Dk, float scale) {
-  for (int idx = threadIdx.x; idx < 2 * M; idx += NT) {
+// out[t][m] = scale * <tok[t,:], lat[m,:]> for the 16 tokens of the tile and all M latents.  A thread owns one latent
+// and TPG consecutive tokens; TPG is chosen so that all NT threads have work (M = 64: 4 tokens, M >= 128: 8 tokens).
+template <int TPG>
+static __device__ __forceinline__ void score_tile_impl(float* out, int mp, const float* tok, int ldk, const void* lat,
+                                                       int dtype, int64_t lat_off, int64_t lat_stride_m, int M, int Dk,
+                                                       float scale) {
+  constexpr int GROUPS = BT / TPG;
+  for (int idx = threadIdx.x; idx < GROUPS * M; idx += NT) {
     const int m = idx % M, th = idx / M;
-    float acc[8];
+    float acc[TPG];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+    for (int i = 0; i < TPG; ++i) acc[i] = 0.f;
     const int64_t row = lat_off + (int64_t)m * lat_stride_m;
     for (int d0 = 0; d0 < Dk; d0 += 8) {
       float qv[8];
       load8(lat, dtype, row + d0, qv);
 #pragma unroll
-      for (int tt = 0; tt < 8; ++tt) {
-        const float4* kr = reinterpret_cast<const float4*>(tok + (th * 8 + tt) * ldk + d0);
+      for (int tt = 0; tt < TPG; ++tt) {
+        const float4* kr = reinterpret_cast<const float4*>(tok + (th * TPG + tt) * ldk + d0);
         const float4 k0 = kr[0], k1 = kr[1];
         acc[tt] += qv[0] * k0.x + qv[1] * k0.y + qv[2] * k0.z + qv[3] * k0.w + qv[4] * k1.x + qv[5] * k1.y +
                    qv[6] * k1.z + qv[7] * k1.w;
       }
     }
 #pragma unroll
-    for (int tt = 0; tt < 8; ++tt) out[(th * 8 + tt) * mp + m] = acc[tt] * scale;
+    for (int tt = 0; tt < TPG; ++tt) out[(th * TPG + tt) * mp + m] = acc[tt] * scale;
   }
+}
+
+static __device__ __forceinline__ void score_tile(float* out, int mp, const float* tok, int ldk, const void* lat, int dtype,
+                                           int64_t lat_off, int64_t lat_stride_m, int M, int Dk, float scale) {
+  if (2 * M >= NT) score_tile_impl<8>(out, mp, tok, ldk, lat, dtype, lat_off, lat_stride_m, M, Dk, scale);
+  else if (4 * M >= NT) score_tile_impl<4>(out, mp, tok, ldk, lat, dtype, lat_off, lat_stride_m, M, Dk, scale);
+  else if (8 * M >= NT) score_tile_impl<2>(out, mp, tok, ldk, lat, dtype, lat_off, lat_stride_m, M, Dk, scale);
+  else score_tile_impl<1>(out, mp, tok, ldk, lat, dtype, lat_off, lat_stride_m, M, Dk, scale);
 }
 
 // a[t][:] <- softmax over latents of src[t][:]; one warp per token.  Invalid tokens get zeros.
