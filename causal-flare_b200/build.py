@@ -27,7 +27,7 @@ UNITS = [
     ("decode_step.cu", [], "decode_step"),
     ("state_ops.cu", [], "state_ops"),
     ("prefill_tc.cu", [], "prefill_tc_host"),
-    *[("prefill_tc.cu", [f"-DFLARE_TC_UNIT={u}"], f"prefill_tc_unit{u}") for u in range(4)],
+    *[("prefill_tc.cu", [f"-DFLARE_TC_UNIT={u}"], f"prefill_tc_unit{u}") for u in range(6)],
     ("noalloc.cu", [], "noalloc"),
     ("bwd_exact.cu", [], "bwd_exact_dispatch"),
     *[("bwd_exact.cu", [f"-DFLARE_WALK_MM={mm}"], f"bwd_exact_mm{mm}") for mm in (2, 8, 16, 32, 64)],

@@ -1,11 +1,13 @@
-// Tensor-core (tcgen05 + TMEM + TMA) chunked causal prefill for the softmax encoder, bf16 operands, fp32
-// accumulation and statistics.  Shape class: M <= 512 latents (multiple of 16, in groups of 128 rows, the last one
-// padded), Dk = Dv = 64 or 128, shared decode weights, no mask.
+// Tensor-core (tcgen05 + TMEM + TMA) chunked causal prefill, bf16 operands, fp32 accumulation and statistics.
+// Shape class: M <= 512 latents (multiple of 16, in groups of 128 rows, the last one padded), (Dk, Dv) = (64, 64),
+// (128, 128) or (64, 128), shared decode weights; softmax encoder token- or block-causal, stablemax encoder
+// token-causal; optional per-row lengths (right padding).
 //
 // One CTA owns a (batch, head, sequence segment, slice of 64 value columns, group of 128 latents) and walks its chunks
 // of C = 128 tokens in order.  With more than one latent group every CTA emits a partial read-out (normalised over its
-// own latents, fp32) and the log2 of its weight mass per token; a small kernel merges the groups.  The CTA keeps carrying the latent state on chip: U [128 latents x 64] fp32 in tensor memory, the latent bank Q as packed
-// bf16 in tensor memory (A operand of the score MMA), running max c and denominator d per latent
+// own latents, fp32) and the log2 of its weight mass per token; a small kernel merges the groups.  The CTA carries the
+// latent state on chip: U [128 latents x 64] fp32 in tensor memory, the latent bank Q in shared memory (Dk = 64) or
+// as packed bf16 in tensor memory (Dk = 128; A operand of the score MMA), running max c and denominator d per latent
 // in registers of the thread that owns the latent (TMEM lane = thread).  Per chunk, with the frame c_m = running
 // max after the chunk and kappa = max_m c_m:
 //
@@ -125,18 +127,18 @@ __device__ __forceinline__ float sigma_fast(float x, float p) {
 
 // grid.z = latent group * DKB + value slice.  First value column of this CTA's slice (a compile-time zero when there
 // is one slice) and first latent of its group (zero without the latent split).
-template <int DKB, bool SPLIT>
+template <int DVB, bool SPLIT>
 __device__ __forceinline__ int value_col0() {
-  return DKB == 1 ? 0 : (SPLIT ? (int)blockIdx.z % DKB : (int)blockIdx.z) * D;
+  return DVB == 1 ? 0 : (SPLIT ? (int)blockIdx.z % DVB : (int)blockIdx.z) * D;
 }
-template <int DKB, bool SPLIT>
+template <int DVB, bool SPLIT>
 __device__ __forceinline__ int latent0() {
-  return SPLIT ? ((int)blockIdx.z / DKB) * M : 0;
+  return SPLIT ? ((int)blockIdx.z / DVB) * M : 0;
 }
 
 }  // namespace
 
-// The kernel instances are compiled in separate translation units (FLARE_TC_UNIT = 0..3: head width 64 / 128, without /
+// The kernel instances are compiled in separate translation units (FLARE_TC_UNIT = 0..5: head widths (64, 64) / (128, 128) / (64, 128), without /
 // with the latent-group split) to keep build times short; the unit without FLARE_TC_UNIT holds the host side.
 template <int UNIT>
 int launch_prefill_tc_unit(bool padded, int mode, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
@@ -153,7 +155,8 @@ int launch_prefill_tc_unit(bool padded, int mode, const CUtensorMap& tq, const C
 // MODE 2 (STABLE): stablemax encoder weights sigma(s) = (1+s)^p | (1-s)^-p.  The encoder side then has no frames
 //        (E = sigma(s), D = plain running sum, the state is never rescaled); the decode weights stay a softmax over
 //        the latents, whose numerator exp2(s - c) a_m is formed with the same running-max machinery as before.
-template <bool PADDED, int DKB, bool SPLIT, int MODE>
+// DVB = Dv / 64 = number of value slices (grid.z); Dv may differ from Dk (Dk = 64 with Dv = 128)
+template <bool PADDED, int DKB, int DVB, bool SPLIT, int MODE>
 __global__ void __launch_bounds__(NTHREADS, 1)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                   const __grid_constant__ CUtensorMap tm_v, const TcParams p) {
@@ -168,10 +171,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   Misc* misc = reinterpret_cast<Misc*>(smem + OFF_MISC);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int lane_id = blockIdx.x, seg = blockIdx.y;
-  // Dv = Dk.  This CTA's slice of the value columns starts at blockIdx.z * D (a compile-time zero when Dv = 64); the
+  // This CTA's slice of the value columns starts at blockIdx.z * D (a compile-time zero when Dv = 64); the
   // roles read it where they need it instead of keeping it in a register across their chunk loops, because the
   // latent group runs at the register cap and an extra live value there cost 4 % of the kernel's time.
-  constexpr int DV = DKB * D;
+  constexpr int DV = DVB * D;
   const int b = lane_id / p.H, h = lane_id % p.H;
   const int seg_begin = seg * p.seg_len;
   // rows beyond the batch row's own length are right padding: they are not walked
@@ -226,9 +229,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       prefetch_tensormap(&tm_v);
       if (Q_SMEM) {
         mbar_arrive_expect_tx(&misc->q_full, 16384);
-        tma_load_3d(smem + OFF_Q, &tm_q, &misc->q_full, 0, latent0<DKB, SPLIT>(), h);  // rows beyond M read as zero
+        tma_load_3d(smem + OFF_Q, &tm_q, &misc->q_full, 0, latent0<DVB, SPLIT>(), h);  // rows beyond M read as zero
       }
-      const int vc0 = value_col0<DKB, SPLIT>();
+      const int vc0 = value_col0<DVB, SPLIT>();
       for (int i = 0; ok && i < nchunks; ++i) {
         const int t0 = seg_begin + i * C;
         // K tile: free once the score MMA of the previous chunk has run
@@ -352,15 +355,15 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     const int64_t st_idx = (int64_t)lane_id * p.in_lane_stride + (int64_t)seg * p.in_seg_stride;
     // Fewer than 128 latents: the missing rows are padding (zero rows of Q).  A padding latent gets the frame +inf,
     // so its E = exp2(0 - inf) is exactly zero without any predicate in the element loops, and a denominator of 1.
-    const bool live = !PADDED || latent0<DKB, SPLIT>() + m < p.M;
+    const bool live = !PADDED || latent0<DVB, SPLIT>() + m < p.M;
     float c2 = -INFINITY, dsum = 0.f;  // running max (log2 units) and the denominator in that frame
     if (!live) {
       c2 = 0.f;
       dsum = 1.f;
     } else if (p.in_m != nullptr) {
       // (stablemax: the carried m is a constant zero and not a frame; the decode frame starts empty)
-      if (!STABLE) c2 = p.in_m[st_idx * p.M + latent0<DKB, SPLIT>() + m] * kLog2e;
-      dsum = p.in_d[st_idx * p.M + latent0<DKB, SPLIT>() + m];
+      if (!STABLE) c2 = p.in_m[st_idx * p.M + latent0<DVB, SPLIT>() + m] * kLog2e;
+      dsum = p.in_d[st_idx * p.M + latent0<DVB, SPLIT>() + m];
     }
     float d_prev = 0.f;                                  // denominator before the chunk in flight, in its frame
     if constexpr (!Q_SMEM) {
@@ -369,7 +372,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       uint32_t r[DKB * 16];
       const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.q) +
                                                         (int64_t)h * p.q_stride_h +
-                                                        (int64_t)(live ? latent0<DKB, SPLIT>() + m : 0) * p.q_stride_m +
+                                                        (int64_t)(live ? latent0<DVB, SPLIT>() + m : 0) * p.q_stride_m +
                                                         hf * (DKB * 32));
 #pragma unroll
       for (int i = 0; i < DKB * 4; ++i) {
@@ -387,8 +390,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       uint32_t r[32];
 #pragma unroll
       for (int i = 0; i < 32; ++i)
-        r[i] = (p.in_u && live) ? __float_as_uint(p.in_u[(st_idx * p.M + latent0<DKB, SPLIT>() + m) * DV +
-                                                         value_col0<DKB, SPLIT>() + hf * 32 + i])
+        r[i] = (p.in_u && live) ? __float_as_uint(p.in_u[(st_idx * p.M + latent0<DVB, SPLIT>() + m) * DV +
+                                                         value_col0<DVB, SPLIT>() + hf * 32 + i])
                                 : 0u;
       tmem_st32(tl + TM_U + hf * 32, r);
       tmem_wait_st();
@@ -617,9 +620,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           }
         }
         // log normaliser after each block that ends in this half (natural log, exact-frame independent)
-        if (p.lse_enc != nullptr && live && value_col0<DKB, SPLIT>() == 0) {
+        if (p.lse_enc != nullptr && live && value_col0<DVB, SPLIT>() == 0) {
           const int t_half = seg_begin + i * C + tok0;  // first token of this half in the sequence
-          float* dst = p.lse_enc + ((int64_t)lane_id * (p.N / bs)) * p.M + latent0<DKB, SPLIT>() + m;
+          float* dst = p.lse_enc + ((int64_t)lane_id * (p.N / bs)) * p.M + latent0<DVB, SPLIT>() + m;
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
             const int t_end = t_half + g * 16 + 15;            // last token of the group
@@ -699,8 +702,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       tc_fence_after_sync();
       if (ok) {
         const int64_t so = (int64_t)lane_id * p.out_lane_stride + (int64_t)seg * p.out_seg_stride;
-        const int mg = latent0<DKB, SPLIT>() + m;  // latent index in the whole bank
-        if (hf == 0 && live && value_col0<DKB, SPLIT>() == 0) {
+        const int mg = latent0<DVB, SPLIT>() + m;  // latent index in the whole bank
+        if (hf == 0 && live && value_col0<DVB, SPLIT>() == 0) {
           p.out_m[so * p.M + mg] = STABLE ? 0.f : c2 * kLn2;
           p.out_d[so * p.M + mg] = dsum * fin;
         }
@@ -709,7 +712,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         tmem_wait_ld();
         tmem_fence_regs(r);
         float4* dst =
-            reinterpret_cast<float4*>(p.out_u + (so * p.M + (live ? mg : 0)) * DV + value_col0<DKB, SPLIT>() + hf * 32);
+            reinterpret_cast<float4*>(p.out_u + (so * p.M + (live ? mg : 0)) * DV + value_col0<DVB, SPLIT>() + hf * 32);
 #pragma unroll
         for (int k = 0; k < 8; ++k)
           if (live) dst[k] = make_float4(__uint_as_float(r[4 * k]) * fin, __uint_as_float(r[4 * k + 1]) * fin,
@@ -722,9 +725,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     const uint32_t tl = tmem + ((uint32_t)(wq * 32) << 16);
     const int tt = wq * 32 + lane;  // token index inside the chunk
     __nv_bfloat16* const y_lane = reinterpret_cast<__nv_bfloat16*>(p.y) + (int64_t)b * p.y_stride_b +
-                                  (int64_t)h * p.y_stride_h + value_col0<DKB, SPLIT>();
+                                  (int64_t)h * p.y_stride_h + value_col0<DVB, SPLIT>();
     // latent-group split: dense fp32 partials [group][B][N][H][DV] and log2 weight masses [group][B][N][H]
-    const int64_t part_row0 = SPLIT ? (((int64_t)(blockIdx.z / DKB) * (gridDim.x / p.H) + b) * p.N) : 0;
+    const int64_t part_row0 = SPLIT ? (((int64_t)(blockIdx.z / DVB) * (gridDim.x / p.H) + b) * p.N) : 0;
     for (int i = 0; !state_only && ok && i < nchunks; ++i) {
       const uint32_t par = i & 1;
       const int t0 = seg_begin + i * C;
@@ -786,10 +789,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       // may legitimately carry no weight; the merge kernel flags a token only when every group is empty.
       if (!SPLIT && tt < nvalid && !den_ok) atomicOr(p.err, 2);
       const float inv = (SPLIT && !den_ok) ? 0.f : 1.0f / den;
-      if (SPLIT && p.part_y != nullptr && tt < nvalid && value_col0<DKB, SPLIT>() == 0)
+      if (SPLIT && p.part_y != nullptr && tt < nvalid && value_col0<DVB, SPLIT>() == 0)
         p.part_lw[(part_row0 + t0 + tt) * p.H + h] = den_ok ? misc->kap[par] + __log2f(den) : -INFINITY;
       // log-sum-exp of the token's decode scores = log of the decode weights' mass in the frame kappa
-      if (BLOCK && !SPLIT && p.lse_dec != nullptr && tt < nvalid && value_col0<DKB, SPLIT>() == 0)
+      if (BLOCK && !SPLIT && p.lse_dec != nullptr && tt < nvalid && value_col0<DVB, SPLIT>() == 0)
         p.lse_dec[(int64_t)lane_id * p.N + t0 + tt] = (misc->kap[par] + __log2f(den)) * kLn2;
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
@@ -799,7 +802,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         if (SPLIT) {
           if (p.part_y != nullptr && tt < nvalid) {
             float4* dst = reinterpret_cast<float4*>(p.part_y + ((part_row0 + t0 + tt) * p.H + h) * DV +
-                                                    value_col0<DKB, SPLIT>() + half * 32);
+                                                    value_col0<DVB, SPLIT>() + half * 32);
 #pragma unroll
             for (int k = 0; k < 8; ++k)
               dst[k] = make_float4(__uint_as_float(r[4 * k]) * inv, __uint_as_float(r[4 * k + 1]) * inv,
@@ -836,10 +839,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 
 namespace {
 
-template <bool PADDED, int DKB, bool SPLIT, int MODE>
+template <bool PADDED, int DKB, int DVB, bool SPLIT, int MODE>
 int launch_instance(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const TcParams& p, dim3 grid,
                     cudaStream_t stream) {
-  auto kern = prefill_tc_kernel<PADDED, DKB, SPLIT, MODE>;
+  auto kern = prefill_tc_kernel<PADDED, DKB, DVB, SPLIT, MODE>;
   FLARE_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Lay<DKB>::SMEM_BYTES));
   kern<<<grid, NTHREADS, Lay<DKB>::SMEM_BYTES, stream>>>(tq, tk, tv, p);
   FLARE_CUDA_CHECK(cudaGetLastError());
@@ -851,16 +854,19 @@ int launch_instance(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensor
 template <>
 int launch_prefill_tc_unit<FLARE_TC_UNIT>(bool padded, int mode, const CUtensorMap& tq, const CUtensorMap& tk,
                                           const CUtensorMap& tv, const TcParams& p, dim3 grid, cudaStream_t stream) {
-  constexpr int DKB = 1 + (FLARE_TC_UNIT & 1);
-  constexpr bool SPLIT = (FLARE_TC_UNIT >> 1) != 0;
+  // units 0..2: (Dk, Dv) = (64, 64), (128, 128), (64, 128); units 3..5: the same with the latent-group split
+  constexpr int COMBO = FLARE_TC_UNIT % 3;
+  constexpr int DKB = COMBO == 1 ? 2 : 1;
+  constexpr int DVB = COMBO == 0 ? 1 : 2;
+  constexpr bool SPLIT = FLARE_TC_UNIT >= 3;
   if (mode == 1)
-    return padded ? launch_instance<true, DKB, SPLIT, 1>(tq, tk, tv, p, grid, stream)
-                  : launch_instance<false, DKB, SPLIT, 1>(tq, tk, tv, p, grid, stream);
+    return padded ? launch_instance<true, DKB, DVB, SPLIT, 1>(tq, tk, tv, p, grid, stream)
+                  : launch_instance<false, DKB, DVB, SPLIT, 1>(tq, tk, tv, p, grid, stream);
   if (mode == 2)
-    return padded ? launch_instance<true, DKB, SPLIT, 2>(tq, tk, tv, p, grid, stream)
-                  : launch_instance<false, DKB, SPLIT, 2>(tq, tk, tv, p, grid, stream);
-  return padded ? launch_instance<true, DKB, SPLIT, 0>(tq, tk, tv, p, grid, stream)
-                : launch_instance<false, DKB, SPLIT, 0>(tq, tk, tv, p, grid, stream);
+    return padded ? launch_instance<true, DKB, DVB, SPLIT, 2>(tq, tk, tv, p, grid, stream)
+                  : launch_instance<false, DKB, DVB, SPLIT, 2>(tq, tk, tv, p, grid, stream);
+  return padded ? launch_instance<true, DKB, DVB, SPLIT, 0>(tq, tk, tv, p, grid, stream)
+                : launch_instance<false, DKB, DVB, SPLIT, 0>(tq, tk, tv, p, grid, stream);
 }
 
 #else  // host side and the merge kernel
@@ -871,6 +877,8 @@ template <> int launch_prefill_tc_unit<0>(bool, int, const CUtensorMap&, const C
 template <> int launch_prefill_tc_unit<1>(bool, int, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const TcParams&, dim3, cudaStream_t);
 template <> int launch_prefill_tc_unit<2>(bool, int, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const TcParams&, dim3, cudaStream_t);
 template <> int launch_prefill_tc_unit<3>(bool, int, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const TcParams&, dim3, cudaStream_t);
+template <> int launch_prefill_tc_unit<4>(bool, int, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const TcParams&, dim3, cudaStream_t);
+template <> int launch_prefill_tc_unit<5>(bool, int, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const TcParams&, dim3, cudaStream_t);
 
 // -------------------------------------------------------------------------------------------------
 // host side
@@ -922,7 +930,7 @@ bool prefill_tc_supported(const flare_fwd_args_t* a) {
   // stablemax encoder weights: token-causal only
   const bool variant_ok = a->variant == FLARE_SOFTMAX || (a->variant == FLARE_STABLEMAX && bs == 1 && a->power > 0.f);
   return a->dtype == FLARE_BF16 && variant_ok && block_ok && lse_ok && a->M <= 4 * M && a->M >= 16 &&
-         (a->M % 16) == 0 && (a->Dk == 64 || a->Dk == 128) && a->Dv == a->Dk && a->q_dec == nullptr &&
+         (a->M % 16) == 0 && ((a->Dk == 64 && (a->Dv == 64 || a->Dv == 128)) || (a->Dk == 128 && a->Dv == 128)) && a->q_dec == nullptr &&
          a->k_dec == nullptr && a->mask == nullptr && a->N >= 1;
 }
 
@@ -1020,12 +1028,16 @@ int launch_prefill_tc(const flare_fwd_args_t* a, const TcParams& p_in, int nseg_
   const bool padded = (a->M % M) != 0;
   const int mode = a->variant == FLARE_STABLEMAX ? 2 : (a->block_size > 1 ? 1 : 0);
   int rc;
-  if (a->Dk == 64)
-    rc = groups > 1 ? launch_prefill_tc_unit<2>(padded, mode, tq, tk, tv, p, grid, stream)
-                    : launch_prefill_tc_unit<0>(padded, mode, tq, tk, tv, p, grid, stream);
-  else
+  const int combo = a->Dk == 128 ? 1 : (a->Dv == 128 ? 2 : 0);  // (64, 64), (128, 128), (64, 128)
+  if (combo == 0)
     rc = groups > 1 ? launch_prefill_tc_unit<3>(padded, mode, tq, tk, tv, p, grid, stream)
+                    : launch_prefill_tc_unit<0>(padded, mode, tq, tk, tv, p, grid, stream);
+  else if (combo == 1)
+    rc = groups > 1 ? launch_prefill_tc_unit<4>(padded, mode, tq, tk, tv, p, grid, stream)
                     : launch_prefill_tc_unit<1>(padded, mode, tq, tk, tv, p, grid, stream);
+  else
+    rc = groups > 1 ? launch_prefill_tc_unit<5>(padded, mode, tq, tk, tv, p, grid, stream)
+                    : launch_prefill_tc_unit<2>(padded, mode, tq, tk, tv, p, grid, stream);
   if (rc != FLARE_OK || groups == 1 || p.y == nullptr) return rc;
   const int64_t rows = (int64_t)a->B * a->N * a->H;
   const int64_t threads = rows * (a->Dv / 8);

@@ -309,3 +309,25 @@ def test_tensor_path_tiny_and_ragged_lengths(N):
         ref_b, _, _ = orc.semi_ar_forward(q, k, v, block_size=16, scale=sc)
         y_b, _, _, _ = run(qc, kc, vc, _lib.PATH_TENSOR, block_size=16, scale=sc)
         assert_bf16_gate(y_b, ref_b, f"block-causal N={N}")
+
+
+@pytest.mark.parametrize("Ml, B, N, H", [(128, 2, 520, 2), (256, 1, 700, 2), (64, 1, 4096, 1)])
+def test_tensor_path_mixed_head_widths(Ml, B, N, H):
+    # Dk = 64 with Dv = 128: score work of the narrow instance, two value slices per lane
+    Dk, Dv = 64, 128
+    q, k, v = orc.make_inputs(B, N, H, Ml, Dk, Dv, seed0=101, dtype=torch.bfloat16)
+    sc = Dk ** -0.5
+    ref, st_ref = orc.ar_forward(q, k, v, scale=sc, return_state=True)
+    qc, kc, vc = to_dev(q, k, v)
+    assert uses_tensor_path(qc, kc, vc)
+    y, st, _, _ = run(qc, kc, vc, _lib.PATH_TENSOR, want_state=True, scale=sc)
+    assert_bf16_gate(y, ref, f"Dk=64 Dv=128 M={Ml}")
+    assert_close(st["d"], st_ref["d"], what="d", atol=1e-3, rtol=2e-3)
+    assert orc.rel_l2(st["u"].cpu(), st_ref["u"]) < 3e-3
+    h = (N // 2) // 16 * 16
+    _, st_a, _, _ = run(qc, kc[:, :h], vc[:, :h], _lib.PATH_TENSOR, want_state=True, scale=sc)
+    y_b, _, _, _ = run(qc, kc[:, h:], vc[:, h:], _lib.PATH_TENSOR, state_in=st_a, scale=sc)
+    assert_bf16_gate(y_b, ref[:, h:], "mixed widths carry-in")
+    ref_b, _, _ = orc.semi_ar_forward(q, k[:, :512], v[:, :512], block_size=32, scale=sc)
+    y_blk, _, _, _ = run(qc, kc[:, :512], vc[:, :512], _lib.PATH_TENSOR, block_size=32, scale=sc)
+    assert_bf16_gate(y_blk, ref_b, "mixed widths block-causal")
