@@ -16,6 +16,26 @@ def default_path() -> int:
         os.environ.get("FLARE_B200_PATH", "auto").strip().lower()]
 
 
+def checked_mode() -> bool:
+    """FLARE_B200_CHECK=1: after every forward that AUTO sent to the tensor-core kernels, synchronise, read the device
+    status and, when the inputs were outside the numeric domain of that path (score spread beyond ~80 nats), run the
+    call again on the exact kernels.  Costs a device synchronisation per call; off by default."""
+    return os.environ.get("FLARE_B200_CHECK", "0").strip() == "1"
+
+
+def _rerun_exact_if_out_of_domain(args, dev) -> None:
+    lib = _lib.load()
+    if lib.flare_forward_uses_tensor_path(C.byref(args)) != 1:
+        return
+    status = device_status(reset=True)
+    if status < 0 or status & 1:
+        raise RuntimeError(f"flare_forward: device status {status} (a tensor-core kernel gave up on a bounded wait)")
+    if status & 2:
+        args.path = _lib.PATH_EXACT
+        args.workspace, args.workspace_bytes = None, 0
+        _lib.run_forward(args, dev)
+
+
 def device_status(reset: bool = True) -> int:
     """0 when every bounded wait inside the tensor-core kernels completed (synchronises the device)."""
     return _lib.load().flare_device_status(1 if reset else 0)
@@ -76,6 +96,8 @@ def forward(Q, K, V, *, scale, Q_dec=None, K_dec=None, variant=_lib.SOFTMAX, pow
                                   block_size=block_size, mask=mask, state_in=state_in, state_out=st_out,
                                   lse_dec=lse_dec, lse_enc=lse_enc, path=path)
         _lib.run_forward(args, dev)
+        if path == _lib.PATH_AUTO and checked_mode():
+            _rerun_exact_if_out_of_domain(args, dev)
     out = None
     if want_y:
         out = y_store if out_dtype in (None, dt) else y_store.to(out_dtype)

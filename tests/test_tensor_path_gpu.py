@@ -102,6 +102,21 @@ def test_sharp_scores_are_flagged_not_silently_wrong():
     assert_bf16_gate(y_e, ref, "sharp scores, exact path")
 
 
+def test_checked_mode_reruns_sharp_inputs_on_the_exact_path(monkeypatch):
+    # FLARE_B200_CHECK=1: the AUTO path reads the device status after the tensor kernels and falls back by itself
+    monkeypatch.setenv("FLARE_B200_CHECK", "1")
+    q, k, v = orc.make_inputs(1, 512, 2, M, D, seed0=13, dtype=torch.bfloat16)
+    q, k = (q.float() * 8).bfloat16(), (k.float() * 8).bfloat16()
+    ref = orc.ar_forward(q, k, v)
+    y = cf.flare_autoregressive_triton(*to_dev(q, k, v))
+    assert_bf16_gate(y, ref, "sharp scores, checked AUTO path")
+    assert _ops.device_status() == 0
+    # in-domain inputs stay on the tensor path and are unchanged by the check
+    q2, k2, v2 = orc.make_inputs(1, 512, 2, M, D, seed0=14, dtype=torch.bfloat16)
+    y2 = cf.flare_autoregressive_triton(*to_dev(q2, k2, v2))
+    assert_bf16_gate(y2, orc.ar_forward(q2, k2, v2), "in-domain, checked AUTO path")
+
+
 @pytest.mark.parametrize("Ml", [16, 64, 96])
 def test_tensor_path_fewer_latents(Ml):
     q, k, v = orc.make_inputs(2, 333, 2, Ml, D, seed0=19, dtype=torch.bfloat16)
