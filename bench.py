@@ -236,6 +236,8 @@ def bench_prefill(args, rank, world):
 # DRAM traffic of one C2 forward launch as measured by ncu (268.8 MB read + 101.8 MB written; part of Y is still in L2
 # when the kernel ends, hence below the algorithmic bytes)
 NCU_TRAFFIC_C2_BYTES = 370_560_000
+# DRAM traffic of one C3 decode step as measured by ncu (profiles/decode_step_c3.md)
+NCU_TRAFFIC_C3_STEP_BYTES = 500_000_000
 
 
 def _roofline(cfg, q, k, v, y, kern_ms):
@@ -253,6 +255,18 @@ def _roofline(cfg, q, k, v, y, kern_ms):
         "algorithmic_bytes": alg_bytes,
         "tensor_frac": alg_flops / (kern_ms * 1e-3) / 1e12 / pk["bf16_tflops"],
     }
+
+
+def _shape_roofline(rows, M, Dk, Dv, ms, flops_per_md, tensors):
+    """Both roofline fractions of a whole step timed with CUDA events: algorithmic bytes (`tensors` bf16 tensors of
+    `rows` x D) over the measured HBM peak, algorithmic flops (flops_per_md x M x D per row) over the measured bf16 peak."""
+    pk = peaks()
+    alg_bytes = tensors * rows * Dv * 2
+    alg_flops = float(flops_per_md) * M * Dk * rows
+    gbs = alg_bytes / (ms * 1e-3) / 1e9
+    tfs = alg_flops / (ms * 1e-3) / 1e12
+    return {"hbm_gbs": gbs, "hbm_frac": gbs / pk["hbm_gbs"], "tflops": tfs, "tensor_frac": tfs / pk["bf16_tflops"],
+            "algorithmic_bytes": alg_bytes, "algorithmic_flops": alg_flops, "peak_source": pk["source"]}
 
 
 def bench_decode(args, rank, world):
@@ -308,6 +322,10 @@ def bench_decode(args, rank, world):
         "workload": f"C3 decode B={B} H={H} M={M} D={Dk}, fp32 state after a {prefix}-token bf16 prefix, {steps} steps",
         "tok_per_s": world * B * steps / (ms * 1e-3), "us_per_step": ms * 1e3 / steps, "hbm_gbs": gbs,
         "hbm_frac": gbs / pk["hbm_gbs"], "bytes_per_step": step_bytes, "gpu_launches": steps,
+        "roofline": {"bound": "hbm", "achieved": gbs, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": gbs / pk["hbm_gbs"],
+                     "traffic": NCU_TRAFFIC_C3_STEP_BYTES, "algorithmic_bytes": step_bytes, "peak_source": pk["source"],
+                     "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of one decode_step_kernel launch "
+                                       "(profiles/decode_step_c3.md)"},
         "state_bytes": B * H * M * Dv * 4, "l2": "state 268 MB > 126 MB L2",
         "fused_multi_step": {"call": f"one flare_autoregressive_prefill_triton(state=...) over the same {steps} tokens",
                              "ms": fused_ms, "tok_per_s": B * steps / (fused_ms * 1e-3)},
@@ -372,6 +390,57 @@ def bench_seqpar(args, rank, world):
                        "parallelism": f"sequence parallel over {world} GPU(s), one all-gather of span states per step"}}
 
 
+def bench_strong(args, rank, world):
+    """The FIXED C2 workload sharded by heads over the ranks (strong scaling; lanes are independent, so no collective):
+    rank r runs heads [r H / world, (r + 1) H / world).  Rank 0 also times the whole workload alone for the ratio."""
+    import causal_flare as cf
+
+    cfg = C2
+    q, k, v = device_inputs(cfg, seed=4321)  # the same tensors on every rank
+    hp = cfg["H"] // world
+    h0 = rank * hp
+    qs, ks, vs = q[h0:h0 + hp], k[:, :, h0:h0 + hp], v[:, :, h0:h0 + hp]  # strided views: no copies
+    steps = min(args.steps, 20)
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        barrier(world)
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for _ in range(steps):
+            fn()
+        t1.record()
+        barrier(world)
+        return t0.elapsed_time(t1) / steps
+
+    full_ms = timed(lambda: cf.flare_autoregressive_triton(q, k, v))  # every rank runs it; rank 0's number is reported
+    split_ms = max_over_ranks(timed(lambda: cf.flare_autoregressive_triton(qs, ks, vs)), world)
+    tokens = cfg["B"] * cfg["N"]
+    return {"workload": f"fixed C2 (B={cfg['B']} N={cfg['N']} H={cfg['H']}), {hp} heads = {hp * cfg['B']} lanes per GPU",
+            "scaling": "strong", "n_gpus": world, "ms_one_gpu": full_ms, "ms_split": split_ms,
+            "value": tokens / (split_ms * 1e-3) / 1e6, "unit": "Mtok/s", "speedup": full_ms / split_ms}
+
+
+def seqpar_check(rank, world):
+    """Reduced block-causal shape: this rank's span of the sequence-parallel run against a local run of the whole
+    sequence (every rank generates the same inputs).  Returns the max-abs difference of y."""
+    from causal_flare import _ops, parallel
+
+    B, H, M, D, bs = 1, 2, 256, 128, 64
+    span = 512
+    N = span * world
+    g = torch.Generator(device="cuda").manual_seed(77)
+    q = torch.randn(H, M, D, generator=g, device="cuda").bfloat16()
+    k = torch.randn(B, N, H, D, generator=g, device="cuda").bfloat16()
+    v = torch.randn(B, N, H, D, generator=g, device="cuda").bfloat16()
+    sc = D ** -0.5
+    whole = _ops.forward(q, k, v, scale=sc, block_size=bs)[0]
+    lo = rank * span
+    mine = parallel.sequence_parallel_prefill(q, k[:, lo:lo + span], v[:, lo:lo + span], scale=sc, block_size=bs)[0]
+    return max_over_ranks(float((mine.float() - whole[:, lo:lo + span].float()).abs().max()), world)
+
+
 def bench_other_shapes(which="all"):
     """Short device-timed runs of the other benchmark shapes (not the headline metric): training-shape forward and
     forward+backward, and the long block-causal shape on one GPU."""
@@ -405,11 +474,14 @@ def bench_other_shapes(which="all"):
 
     out["C4_fwd_bwd_softmax_ms"] = timed(lambda: train_step(cf.flare_autoregressive_triton), n=3)
     out["C4"] = f"B={B} N={N} H={H} M={M} D={D} bf16"
+    # forward + backward: 21 M D flop per (token, head); reads Q, K, V, dY and writes Y, dK, dV = 6 tensors
+    out["C4_fwd_bwd_softmax_roofline"] = _shape_roofline(B * N * H, M, D, D, out["C4_fwd_bwd_softmax_ms"], flops_per_md=21, tensors=6)
     if which == "train":
         return out
     from causal_flare.autoregressive import flare_autoregressive_stablemax_triton
 
     out["C4_fwd_bwd_stablemax_ms"] = timed(lambda: train_step(flare_autoregressive_stablemax_triton), n=3)
+    out["C4_fwd_bwd_stablemax_roofline"] = _shape_roofline(B * N * H, M, D, D, out["C4_fwd_bwd_stablemax_ms"], flops_per_md=21, tensors=6)
     out["C4"] = f"B={B} N={N} H={H} M={M} D={D} bf16"
     del q, k, v, dy
     B, N, H, M, D, bs = 2, 65536, 32, 256, 128, 64
@@ -420,25 +492,34 @@ def bench_other_shapes(which="all"):
         out["C5_one_gpu_semi_ar_forward_ms"] = timed(
             lambda: cf.flare_semi_autoregressive_trition(q, k, v, block_size=bs, chunk_size=64), n=3)
     out["C5"] = f"B={B} N={N} H={H} M={M} D={D} block={bs} bf16, whole sequence on one GPU"
+    out["C5_roofline"] = _shape_roofline(B * N * H, M, D, D, out["C5_one_gpu_semi_ar_forward_ms"], flops_per_md=6, tensors=3)
     return out
 
 
 def cpu_reference_sample(threads=None):
-    """The reference algorithm on the host: fp32 token recurrence over a bounded slice of C2."""
+    """The reference algorithm on the host cores over the whole C2 workload, fp32: the reference's three-phase chunked
+    formulation (``flare_causal_chunked``) and its token recurrence, both as restated by the oracle; the faster of the
+    two is the baseline.  The thread count is set explicitly (a launcher may have pinned OMP_NUM_THREADS to 1)."""
     from oracle import flare_oracle as orc
 
-    if threads:
-        torch.set_num_threads(threads)
+    torch.set_num_threads(threads or os.cpu_count() or 1)
     cfg = C2
-    Bs, Ns = cfg["B"], cfg["N"]  # the whole C2 workload: about 8 s on 16 host cores
+    Bs, Ns = cfg["B"], cfg["N"]  # the whole C2 workload: several seconds per formulation on 16-32 host cores
     q, k, v = orc.make_inputs(Bs, Ns, cfg["H"], cfg["M"], cfg["Dk"], cfg["Dv"], seed0=0, dtype=torch.bfloat16)
     orc.ar_forward(q, k[:, :16], v[:, :16], dtype=torch.float32)
+    times = {}
+    t = time.perf_counter()
+    orc.ar_forward_chunked(q, k, v, chunk_size=64, dtype=torch.float32)
+    times["chunked (three phases, chunk 64)"] = time.perf_counter() - t
     t = time.perf_counter()
     orc.ar_forward(q, k, v, dtype=torch.float32)
-    dt = time.perf_counter() - t
+    times["token recurrence"] = time.perf_counter() - t
+    best = min(times, key=times.get)
+    dt = times[best]
     return dict(value=Bs * Ns / dt / 1e6, unit="Mtok/s", cores=torch.get_num_threads(), kind="port", seconds=dt,
-                sample=f"{Bs} of {cfg['B']} batch rows, all {Ns} tokens and {cfg['H']} heads, fp32 token recurrence "
-                       "(oracle port of the reference's PyTorch path)")
+                sample=f"{Bs} of {cfg['B']} batch rows, all {Ns} tokens and {cfg['H']} heads, fp32; oracle port of the "
+                       f"reference's PyTorch path, faster of two formulations: {best} "
+                       f"({', '.join(f'{k_}: {v_:.1f} s' for k_, v_ in times.items())})")
 
 
 def config_block(world):
@@ -513,6 +594,17 @@ def main():
     other = None
     if world == 1 and args.only == "all" and not args.skip_other:
         other = bench_other_shapes()
+    strong = seqpar = None
+    if world > 1 and args.only == "all" and not args.skip_other:
+        # the two multi-GPU partitions of the path: fixed workload split by heads (no collective), and the long
+        # block-causal sequence split by tokens (one all-gather of span states in the forward, one of span summaries
+        # plus an all-reduce of dQ in the backward)
+        strong = bench_strong(args, rank, world)
+        args.seqpar_backward = True
+        sp_args = argparse.Namespace(**vars(args))
+        sp_args.steps = min(args.steps, 10)
+        seqpar = bench_seqpar(sp_args, rank, world)
+        seqpar["check_max_abs_vs_one_gpu"] = seqpar_check(rank, world)
     cpu = None
     if rank == 0 and world == 1 and not args.skip_cpu:
         cpu = cpu_reference_sample()
@@ -523,7 +615,7 @@ def main():
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": pre["ms_per_step"], "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config_block(world),
             "roofline": pre["roofline"], "cpu_baseline": cpu, "e2e": pre["e2e"], "gpu_launches": pre["gpu_launches"],
-            "clocks": pre["clocks"], "decode": dec, "other_shapes": other,
+            "clocks": pre["clocks"], "decode": dec, "other_shapes": other, "strong": strong, "seqpar": seqpar,
         }
         print(json.dumps(line))
     if world > 1:

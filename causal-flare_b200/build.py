@@ -29,6 +29,8 @@ UNITS = [
     ("prefill_tc.cu", [], "prefill_tc_host"),
     *[("prefill_tc.cu", [f"-DFLARE_TC_UNIT={u}"], f"prefill_tc_unit{u}") for u in range(6)],
     ("noalloc.cu", [], "noalloc"),
+    ("bwd_tc.cu", [], "bwd_tc_host"),
+    *[("bwd_tc.cu", [f"-DFLARE_BT_UNIT={u}"], f"bwd_tc_unit{u}") for u in range(3)],
     ("bwd_exact.cu", [], "bwd_exact_dispatch"),
     *[("bwd_exact.cu", [f"-DFLARE_WALK_MM={mm}"], f"bwd_exact_mm{mm}") for mm in (2, 8, 16, 32, 64)],
 ]

@@ -74,7 +74,7 @@ EXPORTS = (
     "flare_forward_workspace_bytes", "flare_forward", "flare_backward_workspace_bytes", "flare_backward",
     "flare_decode_step", "flare_state_merge", "flare_status_string", "flare_last_cuda_error",
     "flare_abi_version", "flare_abi_sizeof", "flare_set_kernel_events", "flare_last_launch_count",
-    "flare_forward_uses_tensor_path", "flare_device_status", "flare_set_trace_buffer",
+    "flare_forward_uses_tensor_path", "flare_backward_uses_tensor_path", "flare_device_status", "flare_set_trace_buffer",
     "flare_forward_noalloc", "flare_noalloc_scratch_capacity",
 )
 
@@ -114,6 +114,8 @@ def load() -> C.CDLL:
     lib.flare_last_launch_count.restype = C.c_int
     lib.flare_forward_uses_tensor_path.restype = C.c_int
     lib.flare_forward_uses_tensor_path.argtypes = [C.POINTER(FwdArgs)]
+    lib.flare_backward_uses_tensor_path.restype = C.c_int
+    lib.flare_backward_uses_tensor_path.argtypes = [C.POINTER(BwdArgs)]
     lib.flare_device_status.restype = C.c_int
     lib.flare_forward_noalloc.restype = C.c_int
     lib.flare_forward_noalloc.argtypes = [C.POINTER(FwdArgs), C.c_void_p]

@@ -136,9 +136,11 @@ def _forward_compacted(q, k, v, y, mask, *, scale, variant, power, state_in, st_
 
 
 def backward(Q, K, V, dY, *, scale, Q_dec=None, K_dec=None, variant=_lib.SOFTMAX, power=2.0, block_size=1,
-             dy_bhnd=False):
+             dy_bhnd=False, path=None):
     """Run flare_backward.  Returns fp32 dQ, input-dtype dK, dV, and dQ_dec / dK_dec (or None)."""
     _lib.load()
+    if path is None:
+        path = default_path()
     dev = K.device
     dt = K.dtype
     B, N, H, Dk = K.shape
@@ -155,7 +157,7 @@ def backward(Q, K, V, dY, *, scale, Q_dec=None, K_dec=None, variant=_lib.SOFTMAX
     if B > 0 and N > 0:
         a = _lib.BwdArgs()
         a.fwd = _lib.make_fwd_args(q, k, v, qd, kd, None, scale=scale, variant=variant, power=power,
-                                   block_size=block_size)
+                                   block_size=block_size, path=path)
         a.dy = dy.data_ptr()
         a.dy_stride_b, a.dy_stride_n, a.dy_stride_h = dy.stride(0), dy.stride(1), dy.stride(2)
         a.dq, a.dk, a.dv = dq.data_ptr(), dk.data_ptr(), dv.data_ptr()

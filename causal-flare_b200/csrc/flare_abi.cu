@@ -3,6 +3,7 @@
 #include <string.h>
 
 #include "bwd_exact.cuh"
+#include "bwd_tc.cuh"
 #include "decode_step.cuh"
 #include "flare_common.cuh"
 #include "prefill_tc.cuh"
@@ -34,6 +35,10 @@ int sm_count() {
 static thread_local cudaEvent_t g_ev_begin = nullptr, g_ev_end = nullptr;
 static thread_local int g_last_launches = 0;
 static thread_local long long* g_trace = nullptr;
+// per-chunk prefix states the next read-out pass of this thread's forward keeps for the backward (u == null: none)
+static thread_local ChunkStates g_keep = {nullptr, nullptr, nullptr, 0};
+
+void count_launches(int n) { g_last_launches += n; }
 
 namespace {
 
@@ -172,6 +177,9 @@ int launch_walk(const flare_fwd_args_t* a, const FwdPlan& pl, const WalkParams& 
     t.part_lw = t.part_y + (size_t)prefill_tc_partial_bytes(a) / sizeof(float) / (a->Dv + 1) * a->Dv;
   }
   t.trace = g_trace;
+  if (t.y != nullptr && g_keep.u != nullptr) {
+    t.dump_u = g_keep.u; t.dump_c = g_keep.c; t.dump_d = g_keep.d; t.dump_nch = g_keep.nch;
+  }
   return launch_prefill_tc(a, t, nseg_grid, stream);
 }
 
@@ -232,6 +240,16 @@ int forward_run(const flare_fwd_args_t* a, cudaStream_t stream) {
 }
 
 }  // namespace
+
+int forward_keep_states(const flare_fwd_args_t* a, const ChunkStates& keep, cudaStream_t stream) {
+  const int rc = check_forward(a);
+  if (rc != FLARE_OK) return rc;
+  if (!plan_forward(a).use_tc) return FLARE_ERR_UNSUPPORTED;
+  g_keep = keep;
+  const int rc2 = forward_run(a, stream);
+  g_keep = ChunkStates{nullptr, nullptr, nullptr, 0};
+  return rc2;
+}
 
 int segment_prefix_states(const flare_fwd_args_t* f, int nseg, int seg_len, float* seg_m, float* seg_d, float* seg_u,
                           const flare_state_t* init, cudaStream_t stream) {
@@ -320,6 +338,7 @@ static int check_backward(const flare_bwd_args_t* args) {
 
 size_t flare_backward_workspace_bytes(const flare_bwd_args_t* args) {
   if (check_backward(args) != FLARE_OK) return 0;
+  if (bwd_tc_supported(*args)) return bwd_tc_workspace_bytes(*args);
   return bwd_exact_workspace_bytes(*args);
 }
 
@@ -327,6 +346,7 @@ int flare_backward(const flare_bwd_args_t* args, flare_stream_t stream) {
   const int rc = check_backward(args);
   if (rc != FLARE_OK) return rc;
   g_last_launches = 0;
+  if (bwd_tc_supported(*args)) return bwd_tc(*args, stream);
   return bwd_exact(*args, stream);
 }
 
@@ -400,6 +420,11 @@ void flare_set_trace_buffer(void* device_buffer) { g_trace = static_cast<long lo
 int flare_forward_uses_tensor_path(const flare_fwd_args_t* args) {
   if (check_forward(args) != FLARE_OK) return 0;
   return plan_forward(args).use_tc ? 1 : 0;
+}
+
+int flare_backward_uses_tensor_path(const flare_bwd_args_t* args) {
+  if (check_backward(args) != FLARE_OK) return 0;
+  return bwd_tc_supported(*args) ? 1 : 0;
 }
 
 int flare_device_status(int reset) {

@@ -34,6 +34,7 @@
 #include <string.h>
 
 #include "sm100_ptx.cuh"
+#include "tc_device.cuh"
 
 namespace flare {
 
@@ -91,38 +92,13 @@ struct Misc {
       p.trace[((role) * 16 + (chunk)) * 8 + (slot)] = clock64();                                      \
   } while (0)
 
-__device__ __forceinline__ uint32_t swz_chunk_off(int row, int chunk) { return row * 128 + ((chunk ^ (row & 7)) << 4); }
-
-// One arrival per warp: 32 lanes arriving one by one are 32 serialised shared-memory atomics.  __syncwarp orders the
-// lanes' earlier writes before lane 0's releasing arrive.
-__device__ __forceinline__ void warp_arrive(uint64_t* bar, int lane) {
-  __syncwarp();
-  if (lane == 0) mbar_arrive(bar);
-}
+using tc::swz_chunk_off;
+using tc::warp_arrive;
+using tc::sigma_fast;
 
 // bounded wait that also gives up as soon as another role of the CTA has given up
 __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, Misc* misc) {
-  // short waits (partner warp a few hundred cycles behind) are polled; longer ones suspend in hardware
-#pragma unroll 1
-  for (int spin = 0; spin < 24; ++spin)
-    if (mbar_test_wait(bar, parity)) return true;
-  const uint64_t t0 = global_timer_ns();
-  while (true) {
-    if (mbar_try_wait(bar, parity, 50000u)) return true;  // sleeps in hardware, wakes on completion
-    if (misc->abort_flag != 0 || global_timer_ns() - t0 > kWaitLimitNs) return false;
-  }
-}
-
-// stablemax encoder weight with approximate reciprocal; powers 1..4 by multiplication
-__device__ __forceinline__ float sigma_fast(float x, float p) {
-  const float base = 1.0f + fabsf(x);
-  float r;
-  if (p == 1.0f) r = base;
-  else if (p == 2.0f) r = base * base;
-  else if (p == 3.0f) r = base * base * base;
-  else if (p == 4.0f) { const float b2 = base * base; r = b2 * b2; }
-  else r = exp2f(p * __log2f(base));
-  return x >= 0.0f ? r : rcp_approx(r);
+  return tc::wait_or_abort(bar, parity, &misc->abort_flag);
 }
 
 // grid.z = latent group * DKB + value slice.  First value column of this CTA's slice (a compile-time zero when there
@@ -466,7 +442,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       const float* wsrc = misc->wmax[i == 0 ? 0 : ((i - 1) & 1)];
       const float kappa = fmaxf(fmaxf(wsrc[0], wsrc[1]), fmaxf(wsrc[2], wsrc[3]));
       // ordered before the token group's read by the barrier chain
-      if ((SPLIT || BLOCK) && tid == 0) misc->kap[par] = kappa;
+      if ((SPLIT || BLOCK || p.lse_dec != nullptr) && tid == 0) misc->kap[par] = kappa;
       if (tid == 0) TC_TRACE(0, i, 1);
       float a_m = ex2_approx(c_new - kappa);
       float d_carry = dsum * alpha;  // denominator of the carried state in the new frame
@@ -675,6 +651,16 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             v.z = pack_bf16(__uint_as_float(r[ch * 8 + 4]), __uint_as_float(r[ch * 8 + 5]));
             v.w = pack_bf16(__uint_as_float(r[ch * 8 + 6]), __uint_as_float(r[ch * 8 + 7]));
             *reinterpret_cast<uint4*>(smem + OFF_U + swz_chunk_off(m, hf * 4 + ch)) = v;
+            // training: the state before this chunk, as the read-out MMA sees it, is kept for the backward pass
+            if (p.dump_u != nullptr && live)
+              reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.dump_u) +
+                                       (((int64_t)lane_id * p.dump_nch + (seg_begin / C + i)) * p.M + latent0<DVB, SPLIT>() + m) * DV +
+                                       value_col0<DVB, SPLIT>() + hf * 32)[ch] = v;
+          }
+          if (p.dump_u != nullptr && live && hf == 0 && value_col0<DVB, SPLIT>() == 0) {
+            const int64_t o = ((int64_t)lane_id * p.dump_nch + (seg_begin / C + i)) * p.M + latent0<DVB, SPLIT>() + m;
+            p.dump_c[o] = c2;        // frame of the chunk, log2 units (unused for the stablemax encoder)
+            p.dump_d[o] = d_carry;   // denominator before the chunk in that frame
           }
         }
         if (need) tmem_wait_st();
@@ -792,7 +778,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       if (SPLIT && p.part_y != nullptr && tt < nvalid && value_col0<DVB, SPLIT>() == 0)
         p.part_lw[(part_row0 + t0 + tt) * p.H + h] = den_ok ? misc->kap[par] + __log2f(den) : -INFINITY;
       // log-sum-exp of the token's decode scores = log of the decode weights' mass in the frame kappa
-      if (BLOCK && !SPLIT && p.lse_dec != nullptr && tt < nvalid && value_col0<DVB, SPLIT>() == 0)
+      if (!SPLIT && p.lse_dec != nullptr && tt < nvalid && value_col0<DVB, SPLIT>() == 0)
         p.lse_dec[(int64_t)lane_id * p.N + t0 + tt] = (misc->kap[par] + __log2f(den)) * kLn2;
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
@@ -885,38 +871,9 @@ template <> int launch_prefill_tc_unit<5>(bool, int, const CUtensorMap&, const C
 // -------------------------------------------------------------------------------------------------
 namespace {
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (fn) return fn;
-  void* ptr = nullptr;
-  cudaDriverEntryPointQueryResult qres;
-  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) != cudaSuccess ||
-      qres != cudaDriverEntryPointSuccess)
-    return nullptr;
-  fn = reinterpret_cast<EncodeTiledFn>(ptr);
-  return fn;
-}
-
-// bf16 tensor with `rank` dims (innermost first), strides in elements for dims 1..rank-1
 bool make_map(CUtensorMap* map, const void* base, int rank, const uint64_t* dims, const int64_t* strides_elems,
               const uint32_t* box) {
-  EncodeTiledFn fn = encode_fn();
-  if (!fn) return false;
-  cuuint64_t gdim[5], gstride[4];
-  cuuint32_t bx[5], estr[5];
-  for (int i = 0; i < rank; ++i) {
-    gdim[i] = dims[i];
-    bx[i] = box[i];
-    estr[i] = 1;
-  }
-  for (int i = 0; i + 1 < rank; ++i) gstride[i] = (cuuint64_t)strides_elems[i] * 2;
-  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank, const_cast<void*>(base), gdim, gstride, bx, estr,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  return tc::make_map_bf16(map, base, rank, dims, strides_elems, box);
 }
 
 }  // namespace
@@ -924,8 +881,8 @@ bool make_map(CUtensorMap* map, const void* base, int rank, const uint64_t* dims
 bool prefill_tc_supported(const flare_fwd_args_t* a) {
   const int bs = a->block_size;
   const bool block_ok = bs == 1 || ((bs == 16 || bs == 32 || bs == 64 || bs == 128) && a->N % bs == 0);
-  // the log normalisers are emitted in block-causal mode only (the token-causal entry points never ask for them)
-  const bool lse_ok = (a->lse_enc == nullptr && a->lse_dec == nullptr) || bs > 1;
+  // the per-block encoder normalisers exist in block-causal mode only; the decode log-sum-exp in every mode
+  const bool lse_ok = a->lse_enc == nullptr || bs > 1;
   if (a->lengths != nullptr && bs > 1) return false;  // per-row lengths: token-causal only
   // stablemax encoder weights: token-causal only
   const bool variant_ok = a->variant == FLARE_SOFTMAX || (a->variant == FLARE_STABLEMAX && bs == 1 && a->power > 0.f);
@@ -1005,7 +962,10 @@ int launch_prefill_tc(const flare_fwd_args_t* a, const TcParams& p_in, int nseg_
   p.lens = a->lengths;
   p.lse_dec = a->lse_dec;
   p.lse_enc = a->lse_enc;
-  if (p.y == nullptr) p.lse_dec = p.lse_enc = nullptr;  // state-only passes emit nothing else
+  if (p.y == nullptr) {  // state-only passes emit nothing else
+    p.lse_dec = p.lse_enc = nullptr;
+    p.dump_u = nullptr;
+  }
   CUtensorMap tq, tk, tv;
   {
     // latent bank (used by the Dk = 64 instances only; any valid map otherwise)
@@ -1045,6 +1005,13 @@ int launch_prefill_tc(const flare_fwd_args_t* a, const TcParams& p_in, int nseg_
       p.part_y, p.part_lw, groups, rows, a->N, a->H, a->Dv, reinterpret_cast<__nv_bfloat16*>(p.y), p.y_stride_b,
       p.y_stride_n, p.y_stride_h, p.lse_dec, p.lens);
   FLARE_CUDA_CHECK(cudaGetLastError());
+  return FLARE_OK;
+}
+
+int tc_error_word(int** device_address) {
+  void* err = nullptr;
+  FLARE_CUDA_CHECK(cudaGetSymbolAddress(&err, g_tc_error));  // of the current device
+  *device_address = reinterpret_cast<int*>(err);
   return FLARE_OK;
 }
 

@@ -28,6 +28,12 @@ struct TcParams {
   int block;                 // 1 = token-causal; 16, 32, 64, 128 = block-causal
   float power;               // stablemax exponent (stablemax encoder only)
   float *lse_dec, *lse_enc;  // optional outputs, fp32 natural log: [B, H, N] and [B, H, N / block, M]
+  // Training: per-chunk prefix states for the backward pass (chunk = 128 tokens, index over the whole sequence):
+  // dump_u bf16 [lanes][dump_nch][M][Dv] numerator before the chunk in the chunk's frame, dump_c / dump_d fp32
+  // [lanes][dump_nch][M] that frame (log2 units) and the denominator before the chunk.  Null: nothing is kept.
+  void* dump_u;
+  float *dump_c, *dump_d;
+  int dump_nch;
   int* err;                  // device error word (bit 0: a wait gave up, bit 1: numeric domain exceeded)
   long long* trace;  // optional diagnostic cycle stamps of CTA (0, 0), see TC_TRACE; null in normal use
 };
@@ -39,6 +45,8 @@ int prefill_tc_ctas_per_lane(const flare_fwd_args_t* a);
 size_t prefill_tc_partial_bytes(const flare_fwd_args_t* a);
 // launches segments 0 .. nseg_grid-1
 int launch_prefill_tc(const flare_fwd_args_t* a, const TcParams& p, int nseg_grid, cudaStream_t stream);
+// device address (current device) of the error word shared by all tensor-core kernels
+int tc_error_word(int** device_address);
 // reads (and optionally clears) the device-side error flag of the tensor-core kernels; synchronises
 int prefill_tc_error_flag(int* host_value, bool reset);
 

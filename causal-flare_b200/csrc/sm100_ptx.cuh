@@ -90,6 +90,14 @@ __device__ __forceinline__ void tma_load_4d(void* smem_dst, const void* tmap, ui
 __device__ __forceinline__ void prefetch_tensormap(const void* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
 }
+// untiled bulk copy global -> shared (both addresses 16-byte aligned, size a multiple of 16 bytes), completion on an
+// mbarrier of this CTA
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(smem_dst)),
+               "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
 
 // ---------------------------------------------------------------------------------------------
 // tcgen05: tensor memory and MMA

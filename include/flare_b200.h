@@ -118,7 +118,10 @@ size_t flare_noalloc_scratch_capacity(void);
  *   _recurrent_flare_backward_impl         causal_flare/autoregressive/recurrent.py:749-935
  *   FLAREAutoregressiveStablemaxTriton.backward   causal_flare/autoregressive/stablemax_triton.py:1981-2420
  *   _semi_autoregressive_backward_impl     causal_flare/semi_autoregressive/training.py:3768-3987
- * Nothing but the inputs is needed from the forward: intermediates are recomputed.
+ * Nothing but the inputs is needed from the forward: intermediates are recomputed.  Two implementations: the
+ * tensor-core one (bwd_tc.cu: a forward that keeps per-chunk states, then a reverse chunk sweep on tcgen05 and a
+ * tensor-core dK / dQ product) for the shapes flare_backward_uses_tensor_path accepts, and the exact fp32 one
+ * (bwd_exact.cu) for everything else; fwd.path = FLARE_PATH_EXACT forces the latter.
  * dq / dk_dec are fp32 [H, M, Dk] (summed over the batch); dk, dv, dq_dec have the input dtype and the
  * input's shape, densely packed.  With weight sharing (q_dec/k_dec NULL) the decode-side gradients are
  * folded into dk / dq and dq_dec / dk_dec must be NULL.
@@ -206,8 +209,13 @@ void flare_set_trace_buffer(void* device_buffer);
 /* 1 when flare_forward would take the tcgen05 tensor-core path for this problem, else 0.  That is: path AUTO or
  * TENSOR, bf16, 16 <= M <= 512 (multiple of 16), (Dk, Dv) = (64, 64), (128, 128) or (64, 128), shared decode weights (q_dec = k_dec = NULL),
  * mask = NULL, and either the softmax encoder with block_size 1 / 16 / 32 / 64 / 128 (N a multiple of it) or the
- * stablemax encoder with block_size 1; lse_dec / lse_enc only with block_size > 1; lengths only with block_size 1. */
+ * stablemax encoder with block_size 1; lse_enc only with block_size > 1; lengths only with block_size 1. */
 int flare_forward_uses_tensor_path(const flare_fwd_args_t* args);
+
+/* 1 when flare_backward would take the tcgen05 tensor-core backward for this problem, else 0: the conditions of
+ * flare_forward_uses_tensor_path plus M <= 256 at Dk = 128, a whole sequence (no span mode, no fwd.state_in) and
+ * dense 16-byte aligned dY rows.  Everything else runs on the exact fp32 kernels. */
+int flare_backward_uses_tensor_path(const flare_bwd_args_t* args);
 
 /* Device-side health of the tensor-core kernels: synchronises the device and returns a bit set (0 = healthy), or a
  * negative flare_status on a CUDA error.  Bit 0 (1): a kernel gave up on a bounded wait, its outputs are invalid.

@@ -19,6 +19,7 @@ Reference locations each function follows (paths inside the reference project):
                                causal_flare/autoregressive/inference.py:231-315 (online form,
                                state, mask), causal_flare/autoregressive/recurrent.py:17-57
 * stablemax transform          causal_flare/autoregressive/stablemax.py:45-67, forward :588-632
+* ``ar_forward_chunked``       causal_flare/autoregressive/reference.py:203-503, :514 (three-phase chunked form)
 * ``semi_ar_forward``          causal_flare/semi_autoregressive/reference.py:308-497, :560-597
 * closed-form gradients        derived from causal_flare/autoregressive/training.py:3728-4178,
                                cross-checked against autograd through the forward oracle
@@ -186,6 +187,69 @@ def ar_forward(
     if return_state:
         return Y, {"m": m, "d": d, "u": u}
     return Y
+
+
+def ar_forward_chunked(Q, K, V, *, scale=None, chunk_size=64, dtype=torch.float32):
+    """Chunked causal FLARE forward, shared decode weights, no state / mask: the three phases of the reference's
+    ``flare_causal_chunked`` (causal_flare/autoregressive/reference.py:203-503, :514): (1) per-chunk summaries
+    (chunk max, sum of exp, exp-weighted sum of V) as batched products, (2) sequential prefix scan of the summaries
+    over the chunks, (3) replay of the token recurrence inside every chunk from its prefix state.  The reference walks
+    phase 3 chunk by chunk; here the chunks (independent once their prefix states are known) are replayed side by
+    side, which is the same arithmetic in a different loop order."""
+    B, N, H, Dk = K.shape
+    M, Dv = Q.shape[1], V.shape[-1]
+    C = int(chunk_size)
+    scale = resolve_scale(scale, Dk)
+    NC = (N + C - 1) // C
+    pad = NC * C - N
+    Qf = Q.to(dtype)
+    Kf = K.to(dtype).permute(0, 2, 1, 3)
+    Vf = V.to(dtype).permute(0, 2, 1, 3)
+    S = scale * torch.einsum("bhnd,hmd->bhnm", Kf, Qf)
+    if pad:
+        S = torch.cat([S, torch.full((B, H, pad, M), NEG_INF, dtype=dtype)], dim=2)
+        Vf = torch.cat([Vf, torch.zeros((B, H, pad, Dv), dtype=dtype)], dim=2)
+    Sc = S.view(B, H, NC, C, M)
+    Vc = Vf.reshape(B, H, NC, C, Dv)
+    # phase 1: chunk summaries
+    cmax = Sc.amax(dim=3)
+    cmax_safe = torch.where(_is_neg_inf(cmax), torch.zeros_like(cmax), cmax)
+    cexp = torch.exp(Sc - cmax_safe.unsqueeze(3))
+    cden = cexp.sum(dim=3)
+    cnum = torch.einsum("bhctm,bhctd->bhcmd", cexp, Vc)
+    # phase 2: exclusive prefix scan over the chunks
+    pm = torch.empty((B, H, NC, M), dtype=dtype)
+    pd = torch.empty((B, H, NC, M), dtype=dtype)
+    pu = torch.empty((B, H, NC, M, Dv), dtype=dtype)
+    m = torch.full((B, H, M), NEG_INF, dtype=dtype)
+    d = torch.zeros((B, H, M), dtype=dtype)
+    u = torch.zeros((B, H, M, Dv), dtype=dtype)
+    for c in range(NC):
+        pm[:, :, c], pd[:, :, c], pu[:, :, c] = m, d, u
+        m_new = torch.maximum(m, cmax[:, :, c])
+        m_safe = torch.where(_is_neg_inf(m_new), torch.zeros_like(m_new), m_new)
+        a = torch.where(_is_neg_inf(m), torch.zeros_like(m), torch.exp(m - m_safe))
+        b = torch.where(_is_neg_inf(cmax[:, :, c]), torch.zeros_like(m), torch.exp(cmax[:, :, c] - m_safe))
+        d = d * a + cden[:, :, c] * b
+        u = u * a[..., None] + cnum[:, :, c] * b[..., None]
+        m = m_new
+    # phase 3: token replay inside the chunks
+    Y = torch.zeros((B, H, NC, C, Dv), dtype=dtype)
+    m, d, u = pm, pd, pu
+    for t in range(C):
+        s_t = Sc[:, :, :, t]
+        v_t = Vc[:, :, :, t]
+        m_new = torch.maximum(m, s_t)
+        m_safe = torch.where(_is_neg_inf(m_new), torch.zeros_like(m_new), m_new)
+        gamma = torch.where(_is_neg_inf(m), torch.zeros_like(m), torch.exp(m - m_safe))
+        eta = torch.where(_is_neg_inf(s_t), torch.zeros_like(s_t), torch.exp(s_t - m_safe))
+        d = d * gamma + eta
+        u = u * gamma[..., None] + eta[..., None] * v_t[:, :, :, None, :]
+        m = m_new
+        z = u / torch.where(d > 0, d, torch.ones_like(d))[..., None]
+        alpha = torch.softmax(torch.where(_is_neg_inf(s_t), torch.zeros_like(s_t), s_t), dim=-1)
+        Y[:, :, :, t] = torch.einsum("bhcm,bhcmd->bhcd", alpha, z)
+    return Y.reshape(B, H, NC * C, Dv)[:, :, :N].permute(0, 2, 1, 3).contiguous()
 
 
 def decode_step(Q, k, v, state, *, scale=1.0, q_dec=None, K_dec=None, attention_mask=None, dtype=torch.float64):

@@ -75,6 +75,7 @@ def main():
     print(f"C1 checksum y.double().sum() = {y_ref.double().sum().item():.6f}")
     check("C1 definitional", y_orc, y_ref)
     check("C1 chunked", y_orc, y_chk)
+    check("C1 chunked port", orc.ar_forward_chunked(q, k, v, chunk_size=64), flare_causal_chunked(q, k, v, chunk_size=64), atol=0, rtol=0)
     save("ar_c1", q=q, k=k, v=v, y=y_ref, checksum=np.float64(y_ref.double().sum().item()))
 
     # ---- small AR forward+grad cases, the four decode-separation modes ---------------------

@@ -16,6 +16,16 @@ def test_c1_readme_case(golden):
     assert abs(float(y.double().sum()) - g["checksum"]) < 1e-3
 
 
+@pytest.mark.parametrize("chunk", [16, 64, 100])
+def test_chunked_port_matches_fixture_and_token_oracle(golden, chunk):
+    # the three-phase chunked formulation (what the CPU baseline of the benchmark times) against the reference's output
+    g = golden("ar_c1")
+    y = orc.ar_forward_chunked(g["q"], g["k"], g["v"], chunk_size=chunk)
+    assert_close(y, g["y"], what="C1 y (chunked port)", **FWD)
+    q, k, v = orc.make_inputs(2, 77, 2, 16, 16, 32, seed0=3)
+    assert_close(orc.ar_forward_chunked(q, k, v, chunk_size=chunk), orc.ar_forward(q, k, v), what="ragged length", **FWD)
+
+
 @pytest.mark.parametrize("case", ["ar_sep00", "ar_sep10", "ar_sep01", "ar_sep11"])
 def test_ar_forward_and_grads(golden, case):
     g = golden(case)
