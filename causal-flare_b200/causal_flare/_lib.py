@@ -41,6 +41,7 @@ class FwdArgs(C.Structure):
         ("y_stride_b", C.c_int64), ("y_stride_n", C.c_int64), ("y_stride_h", C.c_int64),
         ("scale", C.c_float), ("power", C.c_float),
         ("dtype", C.c_int32), ("variant", C.c_int32), ("block_size", C.c_int32), ("path", C.c_int32),
+        ("keep", C.c_void_p), ("keep_bytes", C.c_size_t),
     ]
 
 
@@ -53,6 +54,8 @@ class BwdArgs(C.Structure):
         ("carry_b", C.c_void_p), ("carry_c", C.c_void_p), ("carry_rho", C.c_void_p),
         ("span_b0", C.c_void_p), ("span_c0", C.c_void_p), ("span_gam", C.c_void_p), ("span_rho_first", C.c_void_p),
         ("phase", C.c_int32),
+        ("y", C.c_void_p), ("y_stride_b", C.c_int64), ("y_stride_n", C.c_int64), ("y_stride_h", C.c_int64),
+        ("lse_dec", C.c_void_p),
     ]
 
 
@@ -71,7 +74,8 @@ class DecodeArgs(C.Structure):
 
 
 EXPORTS = (
-    "flare_forward_workspace_bytes", "flare_forward", "flare_backward_workspace_bytes", "flare_backward",
+    "flare_forward_workspace_bytes", "flare_forward", "flare_forward_keep_bytes", "flare_backward_workspace_bytes",
+    "flare_backward",
     "flare_decode_step", "flare_state_merge", "flare_status_string", "flare_last_cuda_error",
     "flare_abi_version", "flare_abi_sizeof", "flare_set_kernel_events", "flare_last_launch_count",
     "flare_forward_uses_tensor_path", "flare_backward_uses_tensor_path", "flare_device_status", "flare_set_trace_buffer",
@@ -94,6 +98,8 @@ def load() -> C.CDLL:
     lib = C.CDLL(LIB_PATH)
     lib.flare_forward_workspace_bytes.restype = C.c_size_t
     lib.flare_forward_workspace_bytes.argtypes = [C.POINTER(FwdArgs)]
+    lib.flare_forward_keep_bytes.restype = C.c_size_t
+    lib.flare_forward_keep_bytes.argtypes = [C.POINTER(FwdArgs)]
     lib.flare_forward.restype = C.c_int
     lib.flare_forward.argtypes = [C.POINTER(FwdArgs), C.c_void_p]
     lib.flare_backward_workspace_bytes.restype = C.c_size_t

@@ -16,28 +16,11 @@ def default_path() -> int:
         os.environ.get("FLARE_B200_PATH", "auto").strip().lower()]
 
 
-def checked_mode() -> bool:
-    """FLARE_B200_CHECK=1: after every forward that AUTO sent to the tensor-core kernels, synchronise, read the device
-    status and, when the inputs were outside the numeric domain of that path (score spread beyond ~80 nats), run the
-    call again on the exact kernels.  Costs a device synchronisation per call; off by default."""
-    return os.environ.get("FLARE_B200_CHECK", "0").strip() == "1"
-
-
-def _rerun_exact_if_out_of_domain(args, dev) -> None:
-    lib = _lib.load()
-    if lib.flare_forward_uses_tensor_path(C.byref(args)) != 1:
-        return
-    status = device_status(reset=True)
-    if status < 0 or status & 1:
-        raise RuntimeError(f"flare_forward: device status {status} (a tensor-core kernel gave up on a bounded wait)")
-    if status & 2:
-        args.path = _lib.PATH_EXACT
-        args.workspace, args.workspace_bytes = None, 0
-        _lib.run_forward(args, dev)
-
-
 def device_status(reset: bool = True) -> int:
-    """0 when every bounded wait inside the tensor-core kernels completed (synchronises the device)."""
+    """Health word of the tensor-core kernels (synchronises the device).  0: nothing to report.  Bit 0: a bounded wait
+    gave up, results are invalid.  Bit 1: some call's inputs were outside the numeric domain of the tensor kernels
+    (score spreads of several hundred nats); calls on the default path (auto) were completed by the exact kernels on
+    their own and are correct, calls that forced ``FLARE_B200_PATH=tensor`` are not."""
     return _lib.load().flare_device_status(1 if reset else 0)
 
 
@@ -51,8 +34,12 @@ def _prep(t, dtype):
 
 def forward(Q, K, V, *, scale, Q_dec=None, K_dec=None, variant=_lib.SOFTMAX, power=2.0, block_size=1, mask=None,
             state_in=None, want_state=False, want_lse=False, out_dtype=None, out_bhnd=False, path=None,
-            want_y=True):
+            want_y=True, keep_for_backward=None):
     """Run flare_forward.  Q_dec / K_dec are None for the shared-weight default.
+
+    ``keep_for_backward``: a dict (or None).  When the call runs on the tensor-core kernels, the forward leaves in it
+    what ``backward(..., saved=...)`` needs to skip its own replay of the forward ("y", "lse_dec", "keep"); the dict
+    stays empty for every other problem.
 
     Returns (Y, state_out | None, lse_dec | None, lse_enc | None)."""
     _lib.load()
@@ -86,6 +73,8 @@ def forward(Q, K, V, *, scale, Q_dec=None, K_dec=None, variant=_lib.SOFTMAX, pow
         if block_size > 1:
             lse_enc = torch.empty((B, H, N // block_size, M), device=dev, dtype=torch.float32)
     if mask is not None:
+        if block_size > 1:
+            raise ValueError("attention masks are not supported together with block_size > 1 (block-causal read-out)")
         mask = mask.to(device=dev, dtype=torch.int32).contiguous()
     if mask is not None and B > 0 and N > 0 and _masked_on_tensor_path(q, k, v, qd, kd, y, st_out, scale, variant, power,
                                                                       block_size, path, want_lse):
@@ -95,9 +84,20 @@ def forward(Q, K, V, *, scale, Q_dec=None, K_dec=None, variant=_lib.SOFTMAX, pow
         args = _lib.make_fwd_args(q, k, v, qd, kd, y, scale=scale, variant=variant, power=power,
                                   block_size=block_size, mask=mask, state_in=state_in, state_out=st_out,
                                   lse_dec=lse_dec, lse_enc=lse_enc, path=path)
+        keep = None
+        if keep_for_backward is not None and y is not None and out_dtype in (None, dt):
+            need = _lib.load().flare_forward_keep_bytes(C.byref(args))
+            if need > 0:
+                if lse_dec is None:
+                    lse_dec = torch.empty((B, H, N), device=dev, dtype=torch.float32)
+                    args.lse_dec = lse_dec.data_ptr()
+                keep = torch.empty(need, dtype=torch.uint8, device=dev)
+                args.keep, args.keep_bytes = keep.data_ptr(), need
         _lib.run_forward(args, dev)
-        if path == _lib.PATH_AUTO and checked_mode():
-            _rerun_exact_if_out_of_domain(args, dev)
+        if keep is not None:
+            keep_for_backward.update(y=y, lse_dec=lse_dec, keep=keep)
+            if not want_lse:
+                lse_dec = None
     out = None
     if want_y:
         out = y_store if out_dtype in (None, dt) else y_store.to(out_dtype)
@@ -136,8 +136,9 @@ def _forward_compacted(q, k, v, y, mask, *, scale, variant, power, state_in, st_
 
 
 def backward(Q, K, V, dY, *, scale, Q_dec=None, K_dec=None, variant=_lib.SOFTMAX, power=2.0, block_size=1,
-             dy_bhnd=False, path=None):
-    """Run flare_backward.  Returns fp32 dQ, input-dtype dK, dV, and dQ_dec / dK_dec (or None)."""
+             dy_bhnd=False, path=None, saved=None):
+    """Run flare_backward.  ``saved``: what a forward with ``keep_for_backward`` left behind (or None / empty: the
+    backward replays the forward itself).  Returns fp32 dQ, input-dtype dK, dV, and dQ_dec / dK_dec (or None)."""
     _lib.load()
     if path is None:
         path = default_path()
@@ -149,11 +150,13 @@ def backward(Q, K, V, dY, *, scale, Q_dec=None, K_dec=None, variant=_lib.SOFTMAX
     qd, kd = _prep(Q_dec, dt), _prep(K_dec, dt)
     dy = dY.permute(0, 2, 1, 3) if dy_bhnd else dY
     dy = _prep(dy, dt)
-    dq = torch.zeros((H, M, Dk), device=dev, dtype=torch.float32)
-    dk = torch.zeros((B, N, H, Dk), device=dev, dtype=dt)
-    dv = torch.zeros((B, N, H, Dv), device=dev, dtype=dt)
-    dqd = torch.zeros((B, N, H, Dk), device=dev, dtype=dt) if qd is not None else None
-    dkd = torch.zeros((H, M, Dk), device=dev, dtype=torch.float32) if kd is not None else None
+    # the kernels write every element of every gradient; only an empty problem needs explicit zeros
+    alloc = torch.empty if (B > 0 and N > 0) else torch.zeros
+    dq = alloc((H, M, Dk), device=dev, dtype=torch.float32)
+    dk = alloc((B, N, H, Dk), device=dev, dtype=dt)
+    dv = alloc((B, N, H, Dv), device=dev, dtype=dt)
+    dqd = alloc((B, N, H, Dk), device=dev, dtype=dt) if qd is not None else None
+    dkd = alloc((H, M, Dk), device=dev, dtype=torch.float32) if kd is not None else None
     if B > 0 and N > 0:
         a = _lib.BwdArgs()
         a.fwd = _lib.make_fwd_args(q, k, v, qd, kd, None, scale=scale, variant=variant, power=power,
@@ -162,6 +165,12 @@ def backward(Q, K, V, dY, *, scale, Q_dec=None, K_dec=None, variant=_lib.SOFTMAX
         a.dy_stride_b, a.dy_stride_n, a.dy_stride_h = dy.stride(0), dy.stride(1), dy.stride(2)
         a.dq, a.dk, a.dv = dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
         a.dq_dec, a.dk_dec = _lib.ptr(dqd), _lib.ptr(dkd)
+        if saved:
+            ys = saved["y"]
+            a.y = ys.data_ptr()
+            a.y_stride_b, a.y_stride_n, a.y_stride_h = ys.stride(0), ys.stride(1), ys.stride(2)
+            a.lse_dec = saved["lse_dec"].data_ptr()
+            a.fwd.keep, a.fwd.keep_bytes = saved["keep"].data_ptr(), saved["keep"].numel()
         _lib.run_backward(a, dev)
     return dq, dk, dv, dqd, dkd
 
@@ -178,8 +187,9 @@ def backward_span_begin(Q, K, V, dY, *, scale, state_in, variant=_lib.SOFTMAX, p
     keep["dq"] = torch.zeros((H, M, Dk), device=dev, dtype=torch.float32)
     keep["dk"] = torch.zeros((B, N, H, Dk), device=dev, dtype=dt)
     keep["dv"] = torch.zeros((B, N, H, Dv), device=dev, dtype=dt)
-    summary = {"b0": torch.empty((B, H, M, Dv), device=dev), "c0": torch.empty((B, H, M), device=dev),
-               "gam": torch.empty((B, H, M), device=dev), "rho_first": torch.empty((B, H, M), device=dev)}
+    f32 = dict(device=dev, dtype=torch.float32)  # explicit: the kernels write fp32 whatever torch's default dtype is
+    summary = {"b0": torch.empty((B, H, M, Dv), **f32), "c0": torch.empty((B, H, M), **f32),
+               "gam": torch.empty((B, H, M), **f32), "rho_first": torch.empty((B, H, M), **f32)}
     keep["st"] = None if state_in is None else {key: state_in[key].float().contiguous() for key in ("m", "d", "u")}
     a = _lib.BwdArgs()
     a.fwd = _lib.make_fwd_args(keep["q"], keep["k"], keep["v"], None, None, None, scale=scale, variant=variant,

@@ -41,10 +41,13 @@ class FLAREAutoregressiveStablemaxTriton(autograd.Function):
         ctx.empty = False
         if not K.is_cuda:
             raise RuntimeError("flare_autoregressive_stablemax requires CUDA tensors.")
+        kept = {} if (ctx.alias_q and ctx.alias_k and any(ctx.needs_input_grad[:5])) else None
         Y, _, _, _ = _ops.forward(Q, K, V, scale=scale_f, Q_dec=None if ctx.alias_q else Q_dec_r,
                                   K_dec=None if ctx.alias_k else K_dec_r, variant=_lib.STABLEMAX, power=float(power),
-                                  out_dtype=V.dtype)
-        ctx.save_for_backward(Q, K, V, Q_dec_r, K_dec_r)
+                                  out_dtype=V.dtype, keep_for_backward=kept)
+        ctx.has_kept = bool(kept)
+        extra = [kept["y"], kept["lse_dec"], kept["keep"]] if kept else []
+        ctx.save_for_backward(Q, K, V, Q_dec_r, K_dec_r, *extra)
         return Y
 
     @staticmethod
@@ -58,7 +61,15 @@ class FLAREAutoregressiveStablemaxTriton(autograd.Function):
                 torch.zeros((B, N, H, Dv), device=dev, dtype=vdt), torch.zeros((B, N, H, Dk), device=dev, dtype=qddt),
                 torch.zeros((H, M, Dk), device=dev, dtype=kddt), None, None, None, None,
             )
-        Q, K, V, Q_dec, K_dec = ctx.saved_tensors
+        Q, K, V, Q_dec, K_dec = ctx.saved_tensors[:5]
+        kept = dict(zip(("y", "lse_dec", "keep"), ctx.saved_tensors[5:8])) if ctx.has_kept else None
+        if ctx.alias_q and ctx.alias_k:
+            # Both decode tensors ARE the encode tensors: one score matrix, the decode-side gradients folded into dQ /
+            # dK by the kernels (autograd would add the two contributions of the same tensor anyway), which is the
+            # shape class of the tensor-core backward.  The two decode slots then receive no separate gradient.
+            dq, dk, dv, _, _ = _ops.backward(Q, K, V, dY, scale=ctx.scale, variant=_lib.STABLEMAX, power=ctx.power,
+                                             saved=kept)
+            return dq.to(qdt), dk.to(kdt), dv.to(vdt), None, None, None, None, None, None
         # Run the kernels with the decode tensors treated as separate so the five gradients come out unfolded.
         dq, dk, dv, dqd, dkd = _ops.backward(Q, K, V, dY, scale=ctx.scale, Q_dec=Q_dec, K_dec=K_dec,
                                              variant=_lib.STABLEMAX, power=ctx.power)

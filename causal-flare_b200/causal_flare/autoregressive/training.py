@@ -49,15 +49,20 @@ class AutoRegressiveFLARE(autograd.Function):
         profile_data = {"forward": {}, "backward": {}} if profile else None
         qd = Q_dec if separate_Q_dec else None
         kd = K_dec if separate_K_dec else None
+        # with gradients wanted, the tensor-core forward keeps its per-chunk states for the backward
+        kept = {} if any(ctx.needs_input_grad[:3]) else None
         Y, _, _, _ = _timed(
             K.device, profile_data["forward"] if profile else None, "flare_forward",
-            lambda: _ops.forward(Q, K, V, scale=scale, Q_dec=qd, K_dec=kd),
+            lambda: _ops.forward(Q, K, V, scale=scale, Q_dec=qd, K_dec=kd, keep_for_backward=kept),
         )
         saved = [Q, K, V]
         if separate_Q_dec:
             saved.append(Q_dec)
         if separate_K_dec:
             saved.append(K_dec)
+        ctx.has_kept = bool(kept)
+        if kept:
+            saved += [kept["y"], kept["lse_dec"], kept["keep"]]  # through save_for_backward: y is this node's output
         ctx.save_for_backward(*saved)
         ctx.scale = scale
         ctx.separate_Q_dec = separate_Q_dec
@@ -77,10 +82,11 @@ class AutoRegressiveFLARE(autograd.Function):
         rest = saved[3:]
         Q_dec = rest.pop(0) if ctx.separate_Q_dec else None
         K_dec = rest.pop(0) if ctx.separate_K_dec else None
+        kept = dict(y=rest[0], lse_dec=rest[1], keep=rest[2]) if ctx.has_kept else None
         prof = ctx.profile_timings
         dq, dk, dv, dqd, dkd = _timed(
             K.device, prof["backward"] if prof is not None else None, "flare_backward",
-            lambda: _ops.backward(Q, K, V, dO, scale=ctx.scale, Q_dec=Q_dec, K_dec=K_dec),
+            lambda: _ops.backward(Q, K, V, dO, scale=ctx.scale, Q_dec=Q_dec, K_dec=K_dec, saved=kept),
         )
         if prof is not None:
             _refresh_profile_totals(prof)

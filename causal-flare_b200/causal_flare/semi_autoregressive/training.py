@@ -31,13 +31,18 @@ class SemiAutoRegressiveFLARE(autograd.Function):
         if not K.is_cuda:
             raise RuntimeError("flare_semi_autoregressive requires CUDA tensors.")
         profile_data = {"forward": {}, "backward": {}} if profile else None
+        kept = {} if any(ctx.needs_input_grad[:3]) else None
         Y, _, lse_dec, lse_enc = _timed(
             K.device, profile_data["forward"] if profile else None, "flare_forward",
             lambda: _ops.forward(Q, K, V, scale=resolved_scale, Q_dec=Q_dec if sep_q else None,
-                                 K_dec=K_dec if sep_k else None, block_size=block_size, want_lse=True, out_dtype=V.dtype),
+                                 K_dec=K_dec if sep_k else None, block_size=block_size, want_lse=True, out_dtype=V.dtype,
+                                 keep_for_backward=kept),
         )
+        ctx.has_kept = bool(kept)
         aux = {"LSE_dec": lse_dec, "LSE_enc": lse_enc}
         saved = [Q, K, V] + ([Q_dec] if sep_q else []) + ([K_dec] if sep_k else [])
+        if kept:
+            saved += [kept["y"], kept["lse_dec"], kept["keep"]]
         ctx.save_for_backward(*saved)
         ctx.scale, ctx.block_size, ctx.sep_q, ctx.sep_k = resolved_scale, block_size, sep_q, sep_k
         ctx.profile_timings = profile_data
@@ -56,10 +61,12 @@ class SemiAutoRegressiveFLARE(autograd.Function):
         rest = saved[3:]
         Q_dec = rest.pop(0) if ctx.sep_q else None
         K_dec = rest.pop(0) if ctx.sep_k else None
+        kept = dict(y=rest[0], lse_dec=rest[1], keep=rest[2]) if ctx.has_kept else None
         prof = ctx.profile_timings
         dq, dk, dv, dqd, dkd = _timed(
             K.device, prof["backward"] if prof is not None else None, "flare_backward",
-            lambda: _ops.backward(Q, K, V, dY, scale=ctx.scale, Q_dec=Q_dec, K_dec=K_dec, block_size=ctx.block_size),
+            lambda: _ops.backward(Q, K, V, dY, scale=ctx.scale, Q_dec=Q_dec, K_dec=K_dec, block_size=ctx.block_size,
+                                  saved=kept),
         )
         if prof is not None:
             _refresh_profile_totals(prof)

@@ -63,6 +63,9 @@ struct BwdParams {
   float* RHO;                        // [lanes][N / block_size][M]
   // Span of a longer sequence (sequence parallelism): carries entering from the tokens after the span, or null
   const float *carry_b, *carry_c, *carry_rho;  // [lanes][M][Dv], [lanes][M], [lanes][M] (decay of the first token after)
+  // Optional gate word: every kernel of this pass returns at once unless *gate != 0 (the pass then stands by behind
+  // the tensor-core backward and only runs when that one reported inputs outside its numeric domain).
+  const int* gate;
 };
 
 // defined once per MM_MAX in {2, 8, 16, 32, 64}, each in its own translation unit; stage 0 = replay, 1 = reverse
@@ -77,6 +80,7 @@ namespace {
 // --------------------------------------------------------------------------------------------------
 template <int MM_MAX, int DD>
 __global__ void __launch_bounds__(NT, (MM_MAX * DD <= 32) ? 2 : 1) bwd_replay_kernel(const BwdParams p) {
+  if (p.gate != nullptr && *p.gate == 0) return;
   extern __shared__ __align__(16) float smem_raw[];
   const int lane_id = blockIdx.x, dt = blockIdx.y;
   const int b = lane_id / p.H, h = lane_id % p.H;
@@ -339,6 +343,7 @@ __global__ void __launch_bounds__(NT, (MM_MAX * DD <= 32) ? 2 : 1) bwd_replay_ke
 // --------------------------------------------------------------------------------------------------
 template <int MM_MAX, int DD>
 __global__ void __launch_bounds__(NT, (MM_MAX * DD <= 32) ? 2 : 1) bwd_reverse_kernel(const BwdParams p) {
+  if (p.gate != nullptr && *p.gate == 0) return;
   extern __shared__ __align__(16) float smem_raw[];
   const int lane_id = blockIdx.x, dt = blockIdx.y;
   const int b = lane_id / p.H, h = lane_id % p.H;
@@ -640,6 +645,7 @@ struct RowsParams {
   void* out;  // [B, N, H, Dk] contiguous
   int B, N, H, M, Dk, dtype;
   float scale;
+  const int* gate;  // optional: nothing is done unless *gate != 0
 };
 
 constexpr int RT = 64;    // token rows per CTA
@@ -649,6 +655,7 @@ constexpr int RC = 128;   // output columns per CTA (grid.z tiles wider rows)
 // Register-tiled fp32 product: 256 threads, thread (ty, tx) owns rows ty*4 .. +3 and columns tx*8 .. +7 of the
 // RT x RC output tile; per latent 6 shared-memory loads feed 32 FMAs.
 __global__ void __launch_bounds__(NT) bwd_rows_kernel(const RowsParams p) {
+  if (p.gate != nullptr && *p.gate == 0) return;
   __shared__ __align__(16) float ds_s[RT][RM + 4];
   __shared__ __align__(16) float lat_s[RM][RC];
   const int lane_id = blockIdx.x, t0 = blockIdx.y * RT, c0 = blockIdx.z * RC;
@@ -727,6 +734,7 @@ struct LatParams {
   int B, N, H, M, Dk, dtype;
   int rows_per_split, splits;
   float scale;
+  const int* gate;  // optional: nothing is done unless *gate != 0
 };
 
 constexpr int LM = 64;    // latents per CTA
@@ -735,6 +743,7 @@ constexpr int LDK = 128;  // score columns per CTA
 constexpr int LT = 32;    // token rows per shared-memory stage
 
 __global__ void __launch_bounds__(NT) bwd_lat_kernel(const LatParams p) {
+  if (p.gate != nullptr && *p.gate == 0) return;
   __shared__ __align__(16) float ds_s[LT][LM + 4];
   __shared__ __align__(16) float rw_s[LT][LDK + 4];
   const int mtiles = (p.M + LM - 1) / LM;
@@ -806,7 +815,8 @@ __global__ void __launch_bounds__(NT) bwd_lat_kernel(const LatParams p) {
 }
 
 // (5) out[i] = sum_split partial[split][i], fixed order
-__global__ void bwd_sum_splits_kernel(float* out, const float* partial, int64_t n, int splits) {
+__global__ void bwd_sum_splits_kernel(float* out, const float* partial, int64_t n, int splits, const int* gate) {
+  if (gate != nullptr && *gate == 0) return;
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   float acc = 0.f;
@@ -956,7 +966,8 @@ __global__ void __launch_bounds__(NT) bwd_seg_carry_kernel(const float* __restri
                                                            int p_parts, int64_t plane, const void* dy, int dtype, int64_t dy_stride_b,
                                                            int64_t dy_stride_n, int64_t dy_stride_h, float* seg_b,
                                                            float* seg_c, float* seg_gam, int nseg, int seg_len, int N,
-                                                           int H, int M, int Dv) {
+                                                           int H, int M, int Dv, const int* gate) {
+  if (gate != nullptr && *gate == 0) return;
   __shared__ __align__(16) float x_s[LT][LM + 4];
   __shared__ __align__(16) float dy_s[LT][LDK + 4];
   const int mtiles = (M + LM - 1) / LM;
@@ -1052,7 +1063,9 @@ __global__ void __launch_bounds__(256) bwd_seg_scan_kernel(float* seg_b, float* 
                                                            const float* __restrict__ E, const float* __restrict__ RHO,
                                                            int block_size, const float* carry_b, const float* carry_c,
                                                            const float* carry_rho, int write_slots, float* span_b0,
-                                                           float* span_c0, float* span_gam, float* span_rho_first) {
+                                                           float* span_c0, float* span_gam, float* span_rho_first,
+                                                           const int* gate) {
+  if (gate != nullptr && *gate == 0) return;
   const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int64_t per_lane = (int64_t)M * (Dv + 1);  // Dv columns of b, then c
   if (idx >= lanes * per_lane) return;
@@ -1093,7 +1106,7 @@ size_t bwd_exact_workspace_bytes(const flare_bwd_args_t& a) {
   return plan_backward(a).total;
 }
 
-int bwd_exact(const flare_bwd_args_t& a, cudaStream_t stream) {
+int bwd_exact(const flare_bwd_args_t& a, cudaStream_t stream, const int* gate) {
   const flare_fwd_args_t& f = a.fwd;
   if (f.B == 0 || f.N == 0) return FLARE_OK;
   if (f.M > 512) return FLARE_ERR_UNSUPPORTED;
@@ -1140,6 +1153,7 @@ int bwd_exact(const flare_bwd_args_t& a, cudaStream_t stream) {
     p.RHO = f.block_size > 1 ? reinterpret_cast<float*>(ws + pl.off_RHO) : nullptr;
   }
   p.carry_b = a.carry_b; p.carry_c = a.carry_c; p.carry_rho = a.carry_rho;
+  p.gate = gate;
 
   const int mm = f.M / NW;
   const size_t smem1 = replay_smem(f.M, f.Dk, pl.dd), smem2 = reverse_smem(f.M, pl.dd, stablemax);
@@ -1159,7 +1173,7 @@ int bwd_exact(const flare_bwd_args_t& a, cudaStream_t stream) {
     bwd_seg_scan_kernel<<<(unsigned)((nscan + 255) / 256), 256, 0, stream>>>(
         p.seg_b, p.seg_c, p.seg_gam, pl.nseg, pl.seg_len, lanes, f.N, f.M, f.Dv, p.E, p.RHO, f.block_size,
         with_carry ? a.carry_b : nullptr, with_carry ? a.carry_c : nullptr, with_carry ? a.carry_rho : nullptr,
-        write_slots ? 1 : 0, summary ? a.span_b0 : nullptr, a.span_c0, a.span_gam, a.span_rho_first);
+        write_slots ? 1 : 0, summary ? a.span_b0 : nullptr, a.span_c0, a.span_gam, a.span_rho_first, gate);
     FLARE_CUDA_CHECK(cudaGetLastError());
     return FLARE_OK;
   };
@@ -1168,7 +1182,7 @@ int bwd_exact(const flare_bwd_args_t& a, cudaStream_t stream) {
     if (seg_mode) {
       // exclusive prefix state of every segment, from the forward kernels (slot 0: the state before the span)
       rcw = segment_prefix_states(&f, pl.nseg, pl.seg_len, seg_m, seg_d, seg_u,
-                                  f.state_in.u != nullptr ? &f.state_in : nullptr, stream);
+                                  f.state_in.u != nullptr ? &f.state_in : nullptr, stream, gate);
       if (rcw != FLARE_OK) return rcw;
     }
     rcw = walk(0, 0, pl.nseg);  // replay: planes e, g, p (and X, the carry weights, when segmented)
@@ -1179,7 +1193,7 @@ int bwd_exact(const flare_bwd_args_t& a, cudaStream_t stream) {
       dim3 g((unsigned)(lanes * mt), pl.nseg, (f.Dv + LDK - 1) / LDK);
       bwd_seg_carry_kernel<<<g, NT, 0, stream>>>(p.X, p.P, pl.DT, pl.plane, a.dy, f.dtype, a.dy_stride_b, a.dy_stride_n,
                                                  a.dy_stride_h, p.seg_b, p.seg_c, p.seg_gam, pl.nseg, pl.seg_len, f.N,
-                                                 f.H, f.M, f.Dv);
+                                                 f.H, f.M, f.Dv, gate);
       FLARE_CUDA_CHECK(cudaGetLastError());
       if (a.span_b0 != nullptr) {
         rcw = scan(false, false, true);  // summary of the span for a zero carry-in from the right
@@ -1198,6 +1212,7 @@ int bwd_exact(const flare_bwd_args_t& a, cudaStream_t stream) {
   // ---- dK (+ dQ_dec): products of the dS planes with the latent banks ------------------------------
   auto rows_launch = [&](RowsParams& r) -> int {
     r.plane = pl.plane; r.B = f.B; r.N = f.N; r.H = f.H; r.M = f.M; r.Dk = f.Dk; r.dtype = f.dtype; r.scale = f.scale;
+    r.gate = gate;
     dim3 g(f.B * f.H, (f.N + RT - 1) / RT, (f.Dk + RC - 1) / RC);
     bwd_rows_kernel<<<g, NT, 0, stream>>>(r);
     FLARE_CUDA_CHECK(cudaGetLastError());
@@ -1234,11 +1249,12 @@ int bwd_exact(const flare_bwd_args_t& a, cudaStream_t stream) {
   const int64_t lat_n = (int64_t)f.H * f.M * f.Dk;
   auto lat_launch = [&](LatParams& l, float* partial, float* out) -> int {
     l.plane = pl.plane; l.B = f.B; l.N = f.N; l.H = f.H; l.M = f.M; l.Dk = f.Dk; l.dtype = f.dtype; l.scale = f.scale;
+    l.gate = gate;
     l.rows_per_split = pl.rows_per_split; l.splits = pl.splits; l.partial = partial;
     dim3 g(f.H * mt, pl.splits, dkc);
     bwd_lat_kernel<<<g, NT, 0, stream>>>(l);
     FLARE_CUDA_CHECK(cudaGetLastError());
-    bwd_sum_splits_kernel<<<(unsigned)((lat_n + 255) / 256), 256, 0, stream>>>(out, partial, lat_n, pl.splits);
+    bwd_sum_splits_kernel<<<(unsigned)((lat_n + 255) / 256), 256, 0, stream>>>(out, partial, lat_n, pl.splits, gate);
     FLARE_CUDA_CHECK(cudaGetLastError());
     return FLARE_OK;
   };

@@ -28,6 +28,7 @@
 #include <cuda.h>
 #include <string.h>
 
+#include "bwd_exact.cuh"
 #include "prefill_tc.cuh"
 #include "sm100_ptx.cuh"
 #include "tc_device.cuh"
@@ -53,10 +54,13 @@ struct BwdTcParams {
   float scale, power;
   const float *chunk_c, *chunk_d;  // [lanes][nch][M]
   const float *tok_l2, *tok_delta;  // [lanes][npad]
-  void* ds;      // bf16 [lanes][M][npad]
+  void* ds;      // bf16 [2][lanes][M][npad]: dS as a hi + lo pair of planes
+  int64_t ds_plane;  // elements per plane
   void* dv;      // bf16 [B, N, H, Dv] contiguous, or (more than one latent group) bf16 [groups][B][N][H][Dv]
   int groups;
+  int* gate;  // per-call gate word (may be null): raised when a carry turns non-finite (inputs outside the numeric domain)
   int* err;
+  long long* trace;  // optional diagnostic cycle stamps of CTA (0, 0), see BT_TRACE; null in normal use
 };
 
 struct GradTcParams {
@@ -115,11 +119,17 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, Mi
   return tc::wait_or_abort(bar, parity, &misc->abort_flag);
 }
 
+// optional cycle trace of CTA (0, 0): [role < 4][chunk step < 8][slot < 8] clock64 stamps (diagnostic hook)
+#define BT_TRACE(role, step, slot)                                                             \
+  do {                                                                                         \
+    if (p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && (step) < 8)                \
+      p.trace[((role) * 8 + (step)) * 8 + (slot)] = clock64();                                 \
+  } while (0)
+
 __device__ __forceinline__ float unpack8(const uint4& v, int j) {
   const uint32_t w = j < 2 ? v.x : (j < 4 ? v.y : (j < 6 ? v.z : v.w));
   return (j & 1) ? bf16_hi(w) : bf16_lo(w);
 }
-
 // slope sigma'(s) / sigma(s) = p / (1 + |s|) recovered from the (rounded) weight: 1 + |s| = E^(1/p) for s >= 0
 // (E >= 1) and E^(-1/p) for s < 0
 __device__ __forceinline__ float slope_from_sigma(float e, float p) {
@@ -232,11 +242,15 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
   } else if (warp == 12) {
     // ======================================= MMA issuer =======================================
     if (lane == 0) {
+      // All operands are bf16: tcgen05.mma kind::f16 wants A and B in ONE format (a descriptor that mixes fp16 and
+      // bf16 operands is rejected by the hardware as an illegal instruction), and everything that scales with the
+      // caller's data (V, dY, U, G, the masked A, R) needs the bf16 range.
       constexpr uint32_t ID_SS = make_idesc_bf16(128, 128, 0, 0);   // K-major x K-major (scores, A, U dY^T, G V^T, R A^T)
       constexpr uint32_t ID_PE = make_idesc_bf16(128, 128, 0, 1);   // E (K-major) x masked A (MN-major)
       constexpr uint32_t ID_WT = make_idesc_bf16(128, 128, 1, 1);   // E (MN-major) x R (MN-major)
       constexpr uint32_t ID_DV1 = make_idesc_bf16(128, DV, 1, 1);   // E (MN-major) x G (MN-major)
-      constexpr uint32_t ID_DV2 = make_idesc_bf16(128, DV, 0, 1);   // masked E^T R (TMEM) x dY (MN-major); R x dY
+      constexpr uint32_t ID_DV2 = make_idesc_bf16(128, DV, 0, 1);   // masked E^T R (TMEM) x dY (MN-major)
+      constexpr uint32_t ID_G = make_idesc_bf16(128, DV, 0, 1);     // R (K-major) x dY (MN-major)
       const uint64_t d_k = make_desc_sw128(smem_u32(smem + L::OFF_KA), 16, 1024);        // K tile, K-major
       const uint64_t d_am_k = d_k;                                                        // masked A, K-major (N = tau)
       const uint64_t d_am_mn = make_desc_sw128(smem_u32(smem + L::OFF_KA), 16384, 1024);  // masked A, MN-major (N = t)
@@ -259,6 +273,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
         if (!(ok = wait_or_abort(&misc->k_full, par, misc))) break;
         if (j > 0 && !(ok = wait_or_abort(&misc->x_done, pp, misc))) break;
         tc_fence_after_sync();
+        BT_TRACE(2, j, 0);
 #pragma unroll
         for (int s = 0; s < 4 * DKB; ++s) mma_ts(tmem + T1, tmem + TQ + s * 8, kmaj_step(d_k, s), ID_SS, s > 0);
         tc_commit(&misc->s_ready);
@@ -267,6 +282,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
         if (!(ok = wait_or_abort(&misc->dy_full, par, misc))) break;
         if (j > 0 && !(ok = wait_or_abort(&misc->dv_free, pp, misc))) break;
         tc_fence_after_sync();
+        BT_TRACE(2, j, 1);
 #pragma unroll
         for (int s = 0; s < 4 * DVB; ++s) mma_ss(tmem + T0, kmaj_step(d_v_k, s), kmaj_step(d_dy_k, s), ID_SS, s > 0);
         tc_commit(&misc->a_ready);
@@ -276,6 +292,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
         if (!(ok = wait_or_abort(&misc->u_full, par, misc))) break;
         if (j > 0 && !(ok = wait_or_abort(&misc->gc_done, pp, misc))) break;
         tc_fence_after_sync();
+        BT_TRACE(2, j, 2);
 #pragma unroll
         for (int s = 0; s < 4 * DVB; ++s) mma_ss(tmem + T0, kmaj_step(d_u_k, s), kmaj_step(d_dy_k, s), ID_SS, s > 0);
 #pragma unroll
@@ -289,16 +306,18 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
         tc_commit(&misc->px_ready);
 #pragma unroll
         for (int s = 0; s < 8; ++s)
-          mma_ss(tmem + TG, kmaj_step(d_r_k, s), mnmaj_step(d_dy_mn, s), ID_DV2, (j > 0 || s > 0) ? 1u : 0u);
+          mma_ss(tmem + TG, kmaj_step(d_r_k, s), mnmaj_step(d_dy_mn, s), ID_G, (j > 0 || s > 0) ? 1u : 0u);
         tc_commit(&misc->g_ready);
         // W^T = E^T R -> T0 (P has been read)
         if (!(ok = wait_or_abort(&misc->p_free, par, misc))) break;
         tc_fence_after_sync();
+        BT_TRACE(2, j, 3);
         for (int s = 0; s < ksm; ++s) mma_ss(tmem + T0, mnmaj_step(d_e_mn, s), mnmaj_step(d_r_mn, s), ID_WT, s > 0);
         tc_commit(&misc->wt_ready);
         // dV = E^T G + (masked W^T) dY -> T0
         if (!(ok = wait_or_abort(&misc->wm_done, par, misc))) break;
         tc_fence_after_sync();
+        BT_TRACE(2, j, 4);
         if (j > 0)
           for (int s = 0; s < ksm; ++s) mma_ss(tmem + T0, mnmaj_step(d_e_mn, s), mnmaj_step(d_g_mn, s), ID_DV1, s > 0);
 #pragma unroll
@@ -361,6 +380,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
       if (!(ok = wait_or_abort(&misc->tok_full, par, misc))) break;
       if (!(ok = wait_or_abort(&misc->s_ready, par, misc))) break;
       tc_fence_after_sync();
+      if (tid == 0) BT_TRACE(0, j, 0);
       uint32_t ra[32], rb[32];  // the 64 raw scores of this thread
       tmem_ld32(tl + T1 + tok0, ra);
       tmem_ld32(tl + T1 + tok0 + 32, rb);
@@ -435,11 +455,13 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
       fence_proxy_async_smem();
       tc_fence_before_sync();
       warp_arrive(&misc->er_done, lane);
+      if (tid == 0) BT_TRACE(0, j, 1);
 
       // ---- phase 2a (ascending): p = P / D, rows R p, decode part of dS
       if (!(ok = wait_or_abort(&misc->px_ready, par, misc))) break;
       tc_fence_after_sync();
-      uint32_t dsd[32];  // decode-side dS of the 64 tokens, packed bf16 pairs; later the finished dS
+      if (tid == 0) BT_TRACE(0, j, 2);
+      float dec[64];  // decode-side dS of the 64 tokens (fp32: what does not fit in registers lives in local memory)
       float rg16[4] = {0.f, 0.f, 0.f, 0.f};  // sums of the rounded R p per 16 tokens
       {
         float run = base_run;
@@ -479,15 +501,14 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
             rg16[ch >> 1] += (bf16_lo(v.x) + bf16_hi(v.x)) + (bf16_lo(v.y) + bf16_hi(v.y)) + (bf16_lo(v.z) + bf16_hi(v.z)) +
                              (bf16_lo(v.w) + bf16_hi(v.w));
             *reinterpret_cast<uint4*>(rp_row + swz_chunk_off(m, ch)) = v;
-            dsd[ch * 4 + 0] = pack_bf16(dd[0], dd[1]);
-            dsd[ch * 4 + 1] = pack_bf16(dd[2], dd[3]);
-            dsd[ch * 4 + 2] = pack_bf16(dd[4], dd[5]);
-            dsd[ch * 4 + 3] = pack_bf16(dd[6], dd[7]);
+#pragma unroll
+            for (int jj = 0; jj < 8; ++jj) dec[ch * 8 + jj] = dd[jj];
           }
         }
       }
       tc_fence_before_sync();
       warp_arrive(&misc->p_free, lane);  // T0 may take E^T R; the per-token statistics may be replaced
+      if (tid == 0) BT_TRACE(0, j, 3);
       const float rp_tot = (rg16[0] + rg16[1]) + (rg16[2] + rg16[3]);
       misc->xch[hf][m] = rp_tot;
       warp_arrive(&misc->prp[q], lane);
@@ -506,6 +527,8 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
           else if (bs == 64) { ccg[0] = ccg[1] = ccg[2] = ccg[3] = cc + s0; }
           else { ccg[0] = ccg[1] = ccg[2] = ccg[3] = cc_carry + (rp_tot + rp_other); }
         }
+        uint4* const dst_hi = reinterpret_cast<uint4*>(ds_row + t0 + tok0);
+        uint4* const dst_lo = reinterpret_cast<uint4*>(ds_row + p.ds_plane + t0 + tok0);
 #pragma unroll
         for (int blk = 1; blk >= 0; --blk) {
           uint32_t xr[32];
@@ -529,35 +552,43 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
                 cc += unpack8(pv, jj);
                 csub = cc;
               }
-              const uint32_t w = dsd[ch * 4 + (jj >> 1)];
-              const float dec = (jj & 1) ? bf16_hi(w) : bf16_lo(w);
               float enc = eb * (x - csub);
               if constexpr (STABLE) enc *= slope_from_sigma(eb, p.power);
-              ds[jj] = dec + ((STABLE && eb == 0.f) ? 0.f : enc);
+              ds[jj] = dec[ch * 8 + jj] + ((STABLE && eb == 0.f) ? 0.f : enc);
             }
-            dsd[ch * 4 + 0] = pack_bf16(ds[0], ds[1]);
-            dsd[ch * 4 + 1] = pack_bf16(ds[2], ds[3]);
-            dsd[ch * 4 + 2] = pack_bf16(ds[4], ds[5]);
-            dsd[ch * 4 + 3] = pack_bf16(ds[6], ds[7]);
+            // dS = hi + lo, two bf16 values: the dK / dQ products then see it with 16 mantissa bits
+            uint4 hi, lo;
+            hi.x = pack_bf16(ds[0], ds[1]); hi.y = pack_bf16(ds[2], ds[3]); hi.z = pack_bf16(ds[4], ds[5]); hi.w = pack_bf16(ds[6], ds[7]);
+            lo.x = pack_bf16(ds[0] - bf16_lo(hi.x), ds[1] - bf16_hi(hi.x));
+            lo.y = pack_bf16(ds[2] - bf16_lo(hi.y), ds[3] - bf16_hi(hi.y));
+            lo.z = pack_bf16(ds[4] - bf16_lo(hi.z), ds[5] - bf16_hi(hi.z));
+            lo.w = pack_bf16(ds[6] - bf16_lo(hi.w), ds[7] - bf16_hi(hi.w));
+            if (live) {
+              dst_hi[ch] = hi;
+              dst_lo[ch] = lo;
+            }
           }
-        }
-        if (live) {
-          uint4* dst = reinterpret_cast<uint4*>(ds_row + t0 + tok0);
-#pragma unroll
-          for (int ch = 0; ch < 8; ++ch) dst[ch] = make_uint4(dsd[ch * 4], dsd[ch * 4 + 1], dsd[ch * 4 + 2], dsd[ch * 4 + 3]);
         }
       }
       fence_proxy_async_smem();  // the rows R p were read with generic loads; the next write of the buffer is a TMA copy
       tc_fence_before_sync();
       warp_arrive(&misc->x_done, lane);
+      if (tid == 0) BT_TRACE(0, j, 4);
       // carries into the previous chunk's frame
       const float phi = STABLE ? 1.0f : ex2_approx(c_prev - c_i);
       cc_carry = (cc_carry + (rp_tot + rp_other)) * phi;
+      if (!(fabsf(cc_carry) < INFINITY)) {
+        // an overflow or 0 / 0 upstream (score spreads beyond what these frames hold) has reached the carries: the
+        // results of this call are invalid; the exact kernels standing by behind this pass redo it
+        atomicOr(p.err, 2);
+        if (p.gate != nullptr) p.gate[0] = 1;
+      }
       if (i > 0) {
         // G has taken this chunk's R dY: rescale it in tensor memory and pack it as bf16.  The shared-memory copy is
         // still read by this chunk's dV product, so the packed rows wait in registers until that product has run.
         if (!(ok = wait_or_abort(&misc->g_ready, par, misc))) break;
         tc_fence_after_sync();
+        if (tid == 0) BT_TRACE(0, j, 5);
         const bool need = __any_sync(0xffffffffu, phi != 1.0f);
         uint4 gv[DVB * 4];
 #pragma unroll
@@ -582,6 +613,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
         }
         if (need) tmem_wait_st();
         if (!(ok = wait_or_abort(&misc->dv_ready, par, misc))) break;
+        if (tid == 0) BT_TRACE(0, j, 6);
 #pragma unroll
         for (int b32 = 0; b32 < DVB; ++b32) {
           const int col = hf * (DVB * 32) + b32 * 32;
@@ -593,6 +625,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
         fence_proxy_async_smem();
         tc_fence_before_sync();
         warp_arrive(&misc->gc_done, lane);
+        if (tid == 0) BT_TRACE(0, j, 7);
       }
     }
   } else {
@@ -615,6 +648,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
       // masked A (bf16) into the K tile's buffer
       if (!(ok = wait_or_abort(&misc->a_ready, par, misc))) break;
       tc_fence_after_sync();
+      if (tid == 256) BT_TRACE(1, j, 0);
 #pragma unroll 1
       for (int jb = 0; jb < 4; ++jb) {
         uint32_t wp[16];
@@ -645,9 +679,11 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
       fence_proxy_async_smem();
       tc_fence_before_sync();
       warp_arrive(&misc->am_done, lane);
+      if (tid == 256) BT_TRACE(1, j, 1);
       // masked E^T R (bf16) into tensor memory
       if (!(ok = wait_or_abort(&misc->wt_ready, par, misc))) break;
       tc_fence_after_sync();
+      if (tid == 256) BT_TRACE(1, j, 2);
 #pragma unroll 1
       for (int jb = 0; jb < 4; ++jb) {
         uint32_t wp[16];
@@ -674,9 +710,11 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
       tmem_wait_st();
       tc_fence_before_sync();
       warp_arrive(&misc->wm_done, lane);
+      if (tid == 256) BT_TRACE(1, j, 3);
       // dV rows
       if (!(ok = wait_or_abort(&misc->dv_ready, par, misc))) break;
       tc_fence_after_sync();
+      if (tid == 256) BT_TRACE(1, j, 4);
 #pragma unroll
       for (int half = 0; half < DV / 32; ++half) {
         uint32_t r[32];
@@ -698,6 +736,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
       }
       tc_fence_before_sync();
       warp_arrive(&misc->dv_free, lane);
+      if (tid == 256) BT_TRACE(1, j, 5);
     }
   }
   if (!ok) {
@@ -752,32 +791,29 @@ __global__ void __launch_bounds__(256) bwd_tc_token_stats_kernel(const __nv_bflo
                                                                   int64_t y_sn, int64_t y_sh, const float* __restrict__ lse,
                                                                   int B, int N, int H, int Dv, int npad, float* tok_l2,
                                                                   float* tok_delta) {
-  const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);  // (b, n, h), h fastest
-  const int lane = threadIdx.x & 31;
-  if (row >= (int64_t)B * npad * H) return;
-  const int h = (int)(row % H);
-  const int64_t bn = row / H;
+  // Dv / 8 threads per (b, n, h) row (8 or 16, a divisor of the warp size), one 16-byte load of dY and of y each
+  const int tpr = Dv >> 3;
+  const int64_t row = (int64_t)blockIdx.x * (256 / tpr) + threadIdx.x / tpr;  // (b, n, h), h fastest
+  const int sub = threadIdx.x % tpr;
+  const bool in_range = row < (int64_t)B * npad * H;
+  const int h = in_range ? (int)(row % H) : 0;
+  const int64_t bn = in_range ? row / H : 0;
   const int n = (int)(bn % npad);
   const int b = (int)(bn / npad);
-  const int64_t o = ((int64_t)b * H + h) * npad + n;
-  if (n >= N) {
-    if (lane == 0) {
-      tok_l2[o] = INFINITY;
-      tok_delta[o] = 0.f;
-    }
-    return;
-  }
   float acc = 0.f;
-  const int c0 = lane * 4;  // Dv <= 128: four columns per lane
-  if (c0 < Dv) {
-    const uint2 a = *reinterpret_cast<const uint2*>(dy + b * dy_sb + (int64_t)n * dy_sn + h * dy_sh + c0);
-    const uint2 c = *reinterpret_cast<const uint2*>(y + b * y_sb + (int64_t)n * y_sn + h * y_sh + c0);
-    acc = bf16_lo(a.x) * bf16_lo(c.x) + bf16_hi(a.x) * bf16_hi(c.x) + bf16_lo(a.y) * bf16_lo(c.y) + bf16_hi(a.y) * bf16_hi(c.y);
+  if (in_range && n < N) {
+    const uint4 a = __ldg(reinterpret_cast<const uint4*>(dy + b * dy_sb + (int64_t)n * dy_sn + h * dy_sh + sub * 8));
+    const uint4 c = __ldg(reinterpret_cast<const uint4*>(y + b * y_sb + (int64_t)n * y_sn + h * y_sh + sub * 8));
+    acc = (bf16_lo(a.x) * bf16_lo(c.x) + bf16_hi(a.x) * bf16_hi(c.x)) + (bf16_lo(a.y) * bf16_lo(c.y) + bf16_hi(a.y) * bf16_hi(c.y)) +
+          (bf16_lo(a.z) * bf16_lo(c.z) + bf16_hi(a.z) * bf16_hi(c.z)) + (bf16_lo(a.w) * bf16_lo(c.w) + bf16_hi(a.w) * bf16_hi(c.w));
   }
-  acc = warp_sum(acc);
-  if (lane == 0) {
-    tok_delta[o] = acc;
-    tok_l2[o] = lse[((int64_t)b * H + h) * N + n] * kLog2e;
+#pragma unroll
+  for (int o = 8; o > 0; o >>= 1)
+    if (o < tpr) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if (in_range && sub == 0) {
+    const int64_t o = ((int64_t)b * H + h) * npad + n;
+    tok_delta[o] = n < N ? acc : 0.f;
+    tok_l2[o] = n < N ? lse[((int64_t)b * H + h) * N + n] * kLog2e : INFINITY;
   }
 }
 
@@ -890,12 +926,14 @@ bwd_tc_grads_kernel(const __grid_constant__ CUtensorMap tm_ds, const __grid_cons
         mbar_arrive_expect_tx(&misc->k_full[ks], DKB * 16384);
         for (int kb = 0; kb < DKB; ++kb)
           tma_load_4d(smem + L::OFF_K + (ks * DKB + kb) * 16384, &tm_k, &misc->k_full[ks], kb * 64, h, t0, b);
-        for (int g = 0; ok && g < G; ++g, ++it) {
+        for (int gp = 0; ok && gp < 2 * G; ++gp, ++it) {  // (group, hi | lo plane)
+          const int g = gp >> 1, part = gp & 1;
           const int s = it & 1;
           if (it >= 2 && !(ok = wait(&misc->ds_empty[s], ((it - 2) >> 1) & 1))) break;
           mbar_arrive_expect_tx(&misc->ds_full[s], 32768);
           for (int tb = 0; tb < 2; ++tb)
-            tma_load_3d(smem + L::OFF_DS + s * 32768 + tb * 16384, &tm_ds, &misc->ds_full[s], t0 + tb * 64, g * 128, lane_id);
+            tma_load_3d(smem + L::OFF_DS + s * 32768 + tb * 16384, &tm_ds, &misc->ds_full[s], t0 + tb * 64, g * 128,
+                        part * (int)gridDim.x + lane_id);
         }
       }
     }
@@ -911,7 +949,8 @@ bwd_tc_grads_kernel(const __grid_constant__ CUtensorMap tm_ds, const __grid_cons
         if (cc >= 2 && !(ok = wait(&misc->dk_free[kb], ((cc - 2) >> 1) & 1))) break;
         tc_fence_after_sync();
         const uint64_t d_k_mn = make_desc_sw128(smem_u32(smem + L::OFF_K + ks * DKB * 16384), 16384, 1024);
-        for (int g = 0; ok && g < G; ++g, ++it) {
+        for (int gp = 0; ok && gp < 2 * G; ++gp, ++it) {  // (group, hi | lo plane): lo accumulates on top of hi
+          const int g = gp >> 1;
           const int s = it & 1;
           if (!(ok = wait(&misc->ds_full[s], (it >> 1) & 1))) break;
           tc_fence_after_sync();
@@ -921,10 +960,11 @@ bwd_tc_grads_kernel(const __grid_constant__ CUtensorMap tm_ds, const __grid_cons
           const int rows = min(128, p.M - g * 128);
           const int ksm = (rows + 15) >> 4;
           for (int st = 0; st < ksm; ++st)
-            mma_ss(tmem + L::TM_DK + kb * DK, mnmaj_step(d_ds_mn, st), mnmaj_step(d_q_mn, st), ID_DK, (g > 0 || st > 0) ? 1u : 0u);
+            mma_ss(tmem + L::TM_DK + kb * DK, mnmaj_step(d_ds_mn, st), mnmaj_step(d_q_mn, st), ID_DK, (gp > 0 || st > 0) ? 1u : 0u);
 #pragma unroll
           for (int st = 0; st < 8; ++st)
-            mma_ss(tmem + L::TM_DQ + g * DK, kmaj_step(d_ds_k, st), mnmaj_step(d_k_mn, st), ID_DQ, (cc > 0 || st > 0) ? 1u : 0u);
+            mma_ss(tmem + L::TM_DQ + g * DK, kmaj_step(d_ds_k, st), mnmaj_step(d_k_mn, st), ID_DQ,
+                   (cc > 0 || (gp & 1) || st > 0) ? 1u : 0u);
           tc_commit(&misc->ds_empty[s]);
         }
         if (!ok) break;
@@ -1015,9 +1055,13 @@ int launch_grads(const CUtensorMap& tds, const CUtensorMap& tk, const CUtensorMa
 // -------------------------------------------------------------------------------------------------
 // host: plan, workspace, launch sequence
 // -------------------------------------------------------------------------------------------------
+bool have_saved(const flare_bwd_args_t& a);  // defined below, with the keep-buffer layout
+
 struct TcBwdPlan {
   int nch, npad, groups, nsplit, chunks_per_split;
-  size_t fwd_ws;  // the forward's own scratch comes first
+  size_t gate_bytes;  // per-call gate words come first
+  size_t exact_bytes;  // path AUTO: scratch of the exact pass standing by (shares the space behind the gate words)
+  size_t fwd_ws;  // then the forward's own scratch
   size_t off_y, off_lse, off_l2, off_delta, off_cu, off_cc, off_cd, off_ds, off_dqp, off_dvp, total;
 };
 
@@ -1041,44 +1085,89 @@ TcBwdPlan plan_tc(const flare_bwd_args_t& a) {
   probe.lse_dec = nullptr; probe.lse_enc = nullptr;
   memset(&probe.state_in, 0, sizeof(probe.state_in));
   memset(&probe.state_out, 0, sizeof(probe.state_out));
-  pl.fwd_ws = align_up(flare_forward_workspace_bytes(&probe), 256);
-  size_t off = pl.fwd_ws;
+  probe.path = FLARE_PATH_TENSOR;
+  probe.keep = nullptr; probe.keep_bytes = 0;
+  const bool saved = have_saved(a);
+  pl.fwd_ws = saved ? 0 : align_up(flare_forward_workspace_bytes(&probe), 256);
+  pl.gate_bytes = align_up((size_t)(1 + lanes) * sizeof(int), 256);
+  size_t off = pl.gate_bytes + pl.fwd_ws;
   auto take = [&](size_t bytes) {
     const size_t o = off;
     off += align_up(bytes, 256);
     return o;
   };
-  pl.off_y = take((size_t)f.B * f.N * f.H * f.Dv * 2);
-  pl.off_lse = take((size_t)lanes * f.N * 4);
+  pl.off_y = saved ? 0 : take((size_t)f.B * f.N * f.H * f.Dv * 2);
+  pl.off_lse = saved ? 0 : take((size_t)lanes * f.N * 4);
   pl.off_l2 = take((size_t)lanes * pl.npad * 4);
   pl.off_delta = take((size_t)lanes * pl.npad * 4);
-  pl.off_cu = take((size_t)lanes * pl.nch * f.M * f.Dv * 2);
-  pl.off_cc = take((size_t)lanes * pl.nch * f.M * 4);
-  pl.off_cd = take((size_t)lanes * pl.nch * f.M * 4);
-  pl.off_ds = take((size_t)lanes * f.M * pl.npad * 2);
+  pl.off_cu = saved ? 0 : take((size_t)lanes * pl.nch * f.M * f.Dv * 2);
+  pl.off_cc = saved ? 0 : take((size_t)lanes * pl.nch * f.M * 4);
+  pl.off_cd = saved ? 0 : take((size_t)lanes * pl.nch * f.M * 4);
+  pl.off_ds = take((size_t)2 * lanes * f.M * pl.npad * 2);  // hi and lo planes
   pl.off_dqp = take((size_t)f.B * pl.nsplit * f.H * f.M * f.Dk * 4);
   pl.off_dvp = pl.groups > 1 ? take((size_t)pl.groups * f.B * f.N * f.H * f.Dv * 2) : 0;
   pl.total = off;
+  if (f.path == FLARE_PATH_AUTO) {
+    flare_bwd_args_t ex = a;
+    ex.fwd.path = FLARE_PATH_EXACT;
+    pl.exact_bytes = bwd_exact_workspace_bytes(ex);
+    if (pl.gate_bytes + pl.exact_bytes > pl.total) pl.total = pl.gate_bytes + pl.exact_bytes;
+  }
   return pl;
 }
 
 }  // namespace
 
-bool bwd_tc_supported(const flare_bwd_args_t& a) {
-  const flare_fwd_args_t& f = a.fwd;
-  if (f.path == FLARE_PATH_EXACT || f.B <= 0 || f.N <= 0) return false;
-  if (a.carry_b || a.carry_c || a.carry_rho || a.span_b0 || a.span_c0 || a.span_gam || a.span_rho_first || a.phase != 0 ||
-      f.state_in.u != nullptr)
-    return false;  // spans of a longer sequence run on the exact kernels
+// the forward problems whose backward runs on the tensor kernels (everything but the gradient-side conditions)
+static bool tc_trainable(const flare_fwd_args_t& f) {
+  if (f.path == FLARE_PATH_EXACT || f.B <= 0 || f.N <= 0 || f.state_in.u != nullptr) return false;
   flare_fwd_args_t probe = f;
-  probe.y = const_cast<void*>(a.dy);
+  if (probe.y == nullptr) probe.y = const_cast<void*>(f.k);  // any aligned non-null pointer: "an output is wanted"
   probe.mask = nullptr; probe.lengths = nullptr; probe.lse_dec = nullptr; probe.lse_enc = nullptr;
   memset(&probe.state_in, 0, sizeof(probe.state_in));
   memset(&probe.state_out, 0, sizeof(probe.state_out));
   probe.path = FLARE_PATH_TENSOR;
-  if (!prefill_tc_supported(&probe)) return false;
+  if (f.mask != nullptr || f.lengths != nullptr || !prefill_tc_supported(&probe)) return false;
   const int groups = (f.M + 127) / 128;
-  if ((2 + groups) * f.Dk > 512) return false;  // tensor-memory columns of the dK / dQ kernel
+  return (2 + groups) * f.Dk <= 512;  // tensor-memory columns of the dK / dQ kernel
+}
+
+KeepLayout keep_layout(const flare_fwd_args_t& f) {
+  KeepLayout k;
+  memset(&k, 0, sizeof(k));
+  if (!tc_trainable(f)) return k;
+  const size_t lanes = (size_t)f.B * f.H;
+  k.nch = (f.N + C - 1) / C;
+  size_t off = 0;
+  auto take = [&](size_t bytes) {
+    const size_t o = off;
+    off += align_up(bytes, 256);
+    return o;
+  };
+  k.off_gate = take((1 + lanes) * sizeof(int));
+  k.off_u = take(lanes * k.nch * f.M * f.Dv * 2);
+  k.off_c = take(lanes * k.nch * f.M * 4);
+  k.off_d = take(lanes * k.nch * f.M * 4);
+  k.total = off;
+  return k;
+}
+
+// true when the caller handed over what a forward with `keep` left behind
+namespace {
+bool have_saved(const flare_bwd_args_t& a) {
+  if (a.y == nullptr || a.lse_dec == nullptr || a.fwd.keep == nullptr) return false;
+  const KeepLayout k = keep_layout(a.fwd);
+  return k.total > 0 && a.fwd.keep_bytes >= k.total && (reinterpret_cast<uintptr_t>(a.fwd.keep) & 255u) == 0 &&
+         (reinterpret_cast<uintptr_t>(a.y) & 15u) == 0 && (a.y_stride_b % 8) == 0 && (a.y_stride_n % 8) == 0 &&
+         (a.y_stride_h % 8) == 0;
+}
+}  // namespace
+
+bool bwd_tc_supported(const flare_bwd_args_t& a) {
+  const flare_fwd_args_t& f = a.fwd;
+  if (a.carry_b || a.carry_c || a.carry_rho || a.span_b0 || a.span_c0 || a.span_gam || a.span_rho_first || a.phase != 0)
+    return false;  // spans of a longer sequence run on the exact kernels
+  if (!tc_trainable(f)) return false;
   if ((reinterpret_cast<uintptr_t>(a.dy) & 15u) || (a.dy_stride_b % 8) || (a.dy_stride_n % 8) || (a.dy_stride_h % 8)) return false;
   return true;
 }
@@ -1092,32 +1181,52 @@ int bwd_tc(const flare_bwd_args_t& a, cudaStream_t stream) {
     return FLARE_ERR_WORKSPACE;
   char* ws = reinterpret_cast<char*>(f.workspace);
   const int64_t lanes = (int64_t)f.B * f.H;
-  void* y = ws + pl.off_y;
-  float* lse = reinterpret_cast<float*>(ws + pl.off_lse);
-  float* tok_l2 = reinterpret_cast<float*>(ws + pl.off_l2);
-  float* tok_delta = reinterpret_cast<float*>(ws + pl.off_delta);
-  ChunkStates keep{ws + pl.off_cu, reinterpret_cast<float*>(ws + pl.off_cc), reinterpret_cast<float*>(ws + pl.off_cd), pl.nch};
-
-  // (1) forward on the tensor path: y, the decode log-sum-exp and the per-chunk prefix states
-  {
+  int* gate = reinterpret_cast<int*>(ws);
+  const bool saved = have_saved(a);
+  const void* y = nullptr;
+  int64_t y_sb, y_sn, y_sh;
+  const float* lse = nullptr;
+  ChunkStates keep{nullptr, nullptr, nullptr, pl.nch};
+  if (saved) {
+    // (1') the training forward kept everything: its output, its log-sum-exp, the chunk states, its gate words
+    const KeepLayout kl = keep_layout(f);
+    char* kb = reinterpret_cast<char*>(f.keep);
+    FLARE_CUDA_CHECK(cudaMemcpyAsync(gate, kb + kl.off_gate, (size_t)(1 + lanes) * sizeof(int), cudaMemcpyDeviceToDevice, stream));
+    keep.u = kb + kl.off_u;
+    keep.c = reinterpret_cast<float*>(kb + kl.off_c);
+    keep.d = reinterpret_cast<float*>(kb + kl.off_d);
+    y = a.y; y_sb = a.y_stride_b; y_sn = a.y_stride_n; y_sh = a.y_stride_h;
+    lse = a.lse_dec;
+  } else {
+    // (1) forward on the tensor path: y, the decode log-sum-exp and the per-chunk prefix states
+    FLARE_CUDA_CHECK(cudaMemsetAsync(gate, 0, pl.gate_bytes, stream));
+    keep.u = ws + pl.off_cu;
+    keep.c = reinterpret_cast<float*>(ws + pl.off_cc);
+    keep.d = reinterpret_cast<float*>(ws + pl.off_cd);
     flare_fwd_args_t fw = f;
-    fw.y = y;
+    fw.y = ws + pl.off_y;
     fw.y_stride_b = (int64_t)f.N * f.H * f.Dv; fw.y_stride_n = (int64_t)f.H * f.Dv; fw.y_stride_h = f.Dv;
     fw.mask = nullptr; fw.lengths = nullptr;
-    fw.lse_dec = lse; fw.lse_enc = nullptr;
+    fw.lse_dec = reinterpret_cast<float*>(ws + pl.off_lse); fw.lse_enc = nullptr;
+    fw.keep = nullptr; fw.keep_bytes = 0;
     memset(&fw.state_in, 0, sizeof(fw.state_in));
     memset(&fw.state_out, 0, sizeof(fw.state_out));
-    fw.workspace = ws; fw.workspace_bytes = pl.fwd_ws;
+    fw.workspace = ws + pl.gate_bytes; fw.workspace_bytes = pl.fwd_ws;
     fw.path = FLARE_PATH_TENSOR;
-    const int rc = forward_keep_states(&fw, keep, stream);
+    const int rc = forward_keep_states(&fw, keep, gate, stream);
     if (rc != FLARE_OK) return rc;
+    y = fw.y; y_sb = fw.y_stride_b; y_sn = fw.y_stride_n; y_sh = fw.y_stride_h;
+    lse = fw.lse_dec;
   }
+  float* tok_l2 = reinterpret_cast<float*>(ws + pl.off_l2);
+  float* tok_delta = reinterpret_cast<float*>(ws + pl.off_delta);
   // (2) per-token statistics
   {
     const int64_t rows = (int64_t)f.B * pl.npad * f.H;
-    bwd_tc_token_stats_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, stream>>>(
+    const int rows_per_block = 256 / (f.Dv / 8);
+    bwd_tc_token_stats_kernel<<<(unsigned)((rows + rows_per_block - 1) / rows_per_block), 256, 0, stream>>>(
         reinterpret_cast<const __nv_bfloat16*>(a.dy), a.dy_stride_b, a.dy_stride_n, a.dy_stride_h,
-        reinterpret_cast<const __nv_bfloat16*>(y), (int64_t)f.N * f.H * f.Dv, (int64_t)f.H * f.Dv, (int64_t)f.Dv, lse, f.B, f.N,
+        reinterpret_cast<const __nv_bfloat16*>(y), y_sb, y_sn, y_sh, lse, f.B, f.N,
         f.H, f.Dv, pl.npad, tok_l2, tok_delta);
     FLARE_CUDA_CHECK(cudaGetLastError());
     count_launches(1);
@@ -1139,7 +1248,7 @@ int bwd_tc(const flare_bwd_args_t& a, cudaStream_t stream) {
     const uint64_t dimu[4] = {(uint64_t)f.Dv, (uint64_t)f.M, (uint64_t)pl.nch, (uint64_t)lanes};
     const int64_t stru[3] = {f.Dv, (int64_t)f.M * f.Dv, (int64_t)pl.nch * f.M * f.Dv};
     const uint32_t boxu[4] = {64, 128, 1, 1};
-    const uint64_t dims[3] = {(uint64_t)pl.npad, (uint64_t)f.M, (uint64_t)lanes};
+    const uint64_t dims[3] = {(uint64_t)pl.npad, (uint64_t)f.M, (uint64_t)(2 * lanes)};
     const int64_t strs[2] = {pl.npad, (int64_t)f.M * pl.npad};
     const uint32_t boxs[3] = {64, 128, 1};
     const uint64_t dimq[3] = {(uint64_t)f.Dk, (uint64_t)f.M, (uint64_t)f.H};
@@ -1160,9 +1269,12 @@ int bwd_tc(const flare_bwd_args_t& a, cudaStream_t stream) {
     p.scale = f.scale; p.power = f.power;
     p.chunk_c = keep.c; p.chunk_d = keep.d; p.tok_l2 = tok_l2; p.tok_delta = tok_delta;
     p.ds = ws + pl.off_ds;
+    p.ds_plane = lanes * f.M * pl.npad;
     p.groups = pl.groups;
     p.dv = pl.groups > 1 ? static_cast<void*>(ws + pl.off_dvp) : a.dv;
     p.err = err;
+    p.gate = gate;
+    p.trace = trace_buffer();
     const int mode = f.variant == FLARE_STABLEMAX ? 2 : (f.block_size > 1 ? 1 : 0);
     const dim3 grid((unsigned)lanes, pl.groups, 1);
     int rc;
@@ -1194,6 +1306,16 @@ int bwd_tc(const flare_bwd_args_t& a, cudaStream_t stream) {
     bwd_tc_sum_dq_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, stream>>>(g.dq_part, f.B * pl.nsplit, n4, a.dq);
     FLARE_CUDA_CHECK(cudaGetLastError());
     count_launches(2);
+  }
+  // (5) path AUTO: the exact pass stands by.  Each of its kernels looks at the gate word and returns at once unless the
+  // tensor kernels above found the inputs outside their numeric domain, in which case it rewrites dq, dk, dv.
+  if (f.path == FLARE_PATH_AUTO) {
+    flare_bwd_args_t ex = a;
+    ex.fwd.path = FLARE_PATH_EXACT;
+    ex.fwd.workspace = ws + pl.gate_bytes;
+    ex.fwd.workspace_bytes = pl.total - pl.gate_bytes;
+    const int rc = bwd_exact(ex, stream, gate);
+    if (rc != FLARE_OK) return rc;
   }
   return FLARE_OK;
 }

@@ -19,15 +19,19 @@ void set_cuda_error(cudaError_t e, const char* where) {
 }
 
 int sm_count() {
-  static int cached = 0;
-  if (cached > 0) return cached;
+  constexpr int kMaxDevices = 64;
+  static int cached[kMaxDevices] = {};  // per device ordinal; racing first calls write the same value
   int dev = 0, n = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
-      n <= 0) {
+  if (cudaGetDevice(&dev) != cudaSuccess) {
     (void)cudaGetLastError();
     return 148;  // B200; used only for planning when no device is visible
   }
-  cached = n;
+  if (dev >= 0 && dev < kMaxDevices && cached[dev] > 0) return cached[dev];
+  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) {
+    (void)cudaGetLastError();
+    return 148;
+  }
+  if (dev >= 0 && dev < kMaxDevices) cached[dev] = n;
   return n;
 }
 
@@ -37,8 +41,11 @@ static thread_local int g_last_launches = 0;
 static thread_local long long* g_trace = nullptr;
 // per-chunk prefix states the next read-out pass of this thread's forward keeps for the backward (u == null: none)
 static thread_local ChunkStates g_keep = {nullptr, nullptr, nullptr, 0};
+// gate words of the tensor-core forward in flight on this thread (null: none), see FwdPlan::gate_bytes
+static thread_local int* g_gate = nullptr;
 
 void count_launches(int n) { g_last_launches += n; }
+long long* trace_buffer() { return g_trace; }
 
 namespace {
 
@@ -93,10 +100,13 @@ struct FwdPlan {
   size_t state_floats;  // floats per state: 2M + M*Dv
   size_t ws_bytes;
   size_t part_off, part_bytes;  // tensor path with more than 128 latents: partial read-outs behind the segment states
+  // Path AUTO on the tensor kernels: per-call gate words (1 + lanes ints) that the kernels raise for tokens outside
+  // their numeric domain; the exact kernels then run for the flagged lanes only (0 bytes: no guard)
+  size_t gate_off, gate_bytes;
 };
 
 FwdPlan plan_forward(const flare_fwd_args_t* a) {
-  FwdPlan pl{false, 1, a->N > 0 ? a->N : 1, 0, 0, 0, 0};
+  FwdPlan pl{false, 1, a->N > 0 ? a->N : 1, 0, 0, 0, 0, 0, 0};
   if (a->B == 0 || a->N == 0) return pl;
   const int64_t lanes = (int64_t)a->B * a->H;
   pl.state_floats = (size_t)2 * a->M + (size_t)a->M * a->Dv;
@@ -120,6 +130,11 @@ FwdPlan plan_forward(const flare_fwd_args_t* a) {
     pl.part_off = pl.ws_bytes;
     pl.part_bytes = a->y != nullptr ? align_up(prefill_tc_partial_bytes(a), 256) : 0;
     pl.ws_bytes += pl.part_bytes;
+    if (a->path == FLARE_PATH_AUTO && a->lengths == nullptr) {
+      pl.gate_off = pl.ws_bytes;
+      pl.gate_bytes = align_up((size_t)(1 + lanes) * sizeof(int), 256);
+      pl.ws_bytes += pl.gate_bytes;
+    }
     return pl;
   }
   const int dd = walk_exact_dd(a->M, a->Dv);
@@ -177,14 +192,76 @@ int launch_walk(const flare_fwd_args_t* a, const FwdPlan& pl, const WalkParams& 
     t.part_lw = t.part_y + (size_t)prefill_tc_partial_bytes(a) / sizeof(float) / (a->Dv + 1) * a->Dv;
   }
   t.trace = g_trace;
+  t.gate = g_gate;
   if (t.y != nullptr && g_keep.u != nullptr) {
     t.dump_u = g_keep.u; t.dump_c = g_keep.c; t.dump_d = g_keep.d; t.dump_nch = g_keep.nch;
   }
   return launch_prefill_tc(a, t, nseg_grid, stream);
 }
 
+int forward_tensor_or_exact(const flare_fwd_args_t* a, const FwdPlan& pl, cudaStream_t stream);
+
+// The exact kernels standing by behind a tensor-core forward: one CTA per (lane, value tile) walks the whole sequence,
+// but only for the lanes whose gate word the tensor kernels raised (inputs outside their numeric domain, e.g. score
+// spreads of several hundred nats).  For in-domain calls this launch ends at once.
+int launch_guard_walk(const flare_fwd_args_t* a, const int* lane_gates, cudaStream_t stream) {
+  WalkParams w;
+  fill_walk(w, a);
+  w.seg_len = a->N;
+  w.nseg_total = 1;
+  w.in_m = a->state_in.m; w.in_d = a->state_in.d; w.in_u = a->state_in.u;
+  w.in_lane_stride = 1; w.in_seg_stride = 0;
+  w.out_m = a->state_out.m; w.out_d = a->state_out.d; w.out_u = a->state_out.u;
+  w.out_lane_stride = 1; w.out_seg_stride = 0;
+  w.out_mode = a->state_out.u != nullptr ? 2 : 0;
+  w.write_y = a->y != nullptr;
+  w.lse_dec = a->lse_dec; w.lse_enc = a->lse_enc;
+  w.gate = lane_gates;
+  w.gate_stride = 1;
+  return launch_walk_exact(w, 1, stream);
+}
+
 int forward_run(const flare_fwd_args_t* a, cudaStream_t stream) {
   const FwdPlan pl = plan_forward(a);
+  if (g_keep.u != nullptr) return forward_tensor_or_exact(a, pl, stream);  // the backward's own replay of the forward
+  const int64_t lanes = (int64_t)a->B * a->H;
+  int* gate = nullptr;
+  size_t gate_bytes = 0;
+  if (a->keep != nullptr) {
+    // training: the chunk states and the gate words go to the caller's keep buffer
+    const KeepLayout kl = keep_layout(*a);
+    if (kl.total == 0 || !pl.use_tc || a->y == nullptr || a->lse_dec == nullptr || a->keep_bytes < kl.total ||
+        (reinterpret_cast<uintptr_t>(a->keep) & 255u) != 0)
+      return FLARE_ERR_BAD_CONFIG;
+    char* kb = reinterpret_cast<char*>(a->keep);
+    gate = reinterpret_cast<int*>(kb + kl.off_gate);
+    gate_bytes = (size_t)(1 + lanes) * sizeof(int);
+    g_keep = ChunkStates{kb + kl.off_u, reinterpret_cast<float*>(kb + kl.off_c), reinterpret_cast<float*>(kb + kl.off_d), kl.nch};
+  } else if (pl.gate_bytes > 0) {
+    if (a->workspace == nullptr || a->workspace_bytes < pl.ws_bytes || !aligned16(a->workspace)) return FLARE_ERR_WORKSPACE;
+    gate = reinterpret_cast<int*>(reinterpret_cast<char*>(a->workspace) + pl.gate_off);
+    gate_bytes = pl.gate_bytes;
+  }
+  if (gate == nullptr) return forward_tensor_or_exact(a, pl, stream);
+  const cudaError_t e = cudaMemsetAsync(gate, 0, gate_bytes, stream);
+  if (e != cudaSuccess) {
+    g_keep = ChunkStates{nullptr, nullptr, nullptr, 0};
+    set_cuda_error(e, "cudaMemsetAsync (gate words)");
+    return FLARE_ERR_CUDA;
+  }
+  g_gate = gate;
+  int rc = forward_tensor_or_exact(a, pl, stream);
+  g_gate = nullptr;
+  g_keep = ChunkStates{nullptr, nullptr, nullptr, 0};
+  if (rc != FLARE_OK) return rc;
+  if (a->path == FLARE_PATH_AUTO && a->lengths == nullptr) {
+    rc = launch_guard_walk(a, gate + 1, stream);
+    g_last_launches += 1;
+  }
+  return rc;
+}
+
+int forward_tensor_or_exact(const flare_fwd_args_t* a, const FwdPlan& pl, cudaStream_t stream) {
   if (a->lengths != nullptr && !pl.use_tc) return FLARE_ERR_UNSUPPORTED;  // per-row lengths exist on the tensor path only
   if (pl.ws_bytes > 0 && (a->workspace == nullptr || a->workspace_bytes < pl.ws_bytes || !aligned16(a->workspace)))
     return FLARE_ERR_WORKSPACE;
@@ -241,18 +318,20 @@ int forward_run(const flare_fwd_args_t* a, cudaStream_t stream) {
 
 }  // namespace
 
-int forward_keep_states(const flare_fwd_args_t* a, const ChunkStates& keep, cudaStream_t stream) {
+int forward_keep_states(const flare_fwd_args_t* a, const ChunkStates& keep, int* gate, cudaStream_t stream) {
   const int rc = check_forward(a);
   if (rc != FLARE_OK) return rc;
   if (!plan_forward(a).use_tc) return FLARE_ERR_UNSUPPORTED;
   g_keep = keep;
+  g_gate = gate;  // raised by the kernels when a token leaves their numeric domain; no exact rerun here
   const int rc2 = forward_run(a, stream);
+  g_gate = nullptr;
   g_keep = ChunkStates{nullptr, nullptr, nullptr, 0};
   return rc2;
 }
 
 int segment_prefix_states(const flare_fwd_args_t* f, int nseg, int seg_len, float* seg_m, float* seg_d, float* seg_u,
-                          const flare_state_t* init, cudaStream_t stream) {
+                          const flare_state_t* init, cudaStream_t stream, const int* gate) {
   flare_fwd_args_t a = *f;
   a.y = nullptr;
   a.mask = nullptr;
@@ -261,7 +340,7 @@ int segment_prefix_states(const flare_fwd_args_t* f, int nseg, int seg_len, floa
   memset(&a.state_in, 0, sizeof(a.state_in));
   memset(&a.state_out, 0, sizeof(a.state_out));
   a.state_out.m = seg_m; a.state_out.d = seg_d; a.state_out.u = seg_u;  // marks "a state is wanted" for the checks
-  FwdPlan pl{false, nseg, seg_len, (size_t)2 * a.M + (size_t)a.M * a.Dv, 0, 0, 0};
+  FwdPlan pl{false, nseg, seg_len, (size_t)2 * a.M + (size_t)a.M * a.Dv, 0, 0, 0, 0, 0};
   pl.use_tc = a.path != FLARE_PATH_EXACT && (seg_len % 128) == 0 && prefill_tc_supported(&a);
   const int64_t lanes = (int64_t)a.B * a.H;
   WalkParams w;
@@ -271,6 +350,7 @@ int segment_prefix_states(const flare_fwd_args_t* f, int nseg, int seg_len, floa
   w.y = nullptr; w.write_y = 0;
   w.out_m = seg_m; w.out_d = seg_d; w.out_u = seg_u;
   w.out_lane_stride = nseg; w.out_seg_stride = 1; w.out_mode = 1;
+  w.gate = gate; w.gate_stride = 0;  // (a gated pass always runs on the exact kernels: its caller forces that path)
   if (nseg > 1) {
     const int rc = launch_walk(&a, pl, w, nseg - 1, stream);  // local states of all segments but the last
     if (rc != FLARE_OK) return rc;
@@ -283,6 +363,7 @@ int segment_prefix_states(const flare_fwd_args_t* f, int nseg, int seg_len, floa
   fp.s_m = seg_m; fp.s_d = seg_d; fp.s_u = seg_u;
   fp.lane_stride = nseg; fp.seg_stride = 1; fp.count = nseg; fp.mode = 0;
   fp.lanes = lanes; fp.M = a.M; fp.Dv = a.Dv; fp.stablemax = a.variant == FLARE_STABLEMAX;
+  fp.gate = gate;
   return launch_fold(fp, stream);  // exclusive scan from the initial (or empty) state
 }
 
@@ -295,6 +376,12 @@ extern "C" {
 size_t flare_forward_workspace_bytes(const flare_fwd_args_t* args) {
   if (check_forward(args) != FLARE_OK) return 0;
   return plan_forward(args).ws_bytes;
+}
+
+size_t flare_forward_keep_bytes(const flare_fwd_args_t* args) {
+  if (check_forward(args) != FLARE_OK || args->B == 0 || args->N == 0) return 0;
+  if (!plan_forward(args).use_tc) return 0;
+  return keep_layout(*args).total;
 }
 
 int flare_forward(const flare_fwd_args_t* args, flare_stream_t stream) {

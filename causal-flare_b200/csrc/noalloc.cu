@@ -15,40 +15,28 @@
 
 static __device__ __align__(256) unsigned char g_flare_noalloc_scratch[FLARE_NOALLOC_SCRATCH_BYTES];
 
-namespace {
-
-constexpr int kMaxDevices = 64;
-// Device address of the scratch array per device ordinal.  The array's name is only a host-side handle here;
-// the address a kernel can use must be asked for, once per device, while that device is current.
-void* g_scratch_ptr[kMaxDevices] = {};
-
-}  // namespace
-
 extern "C" {
 
 size_t flare_noalloc_scratch_capacity(void) { return FLARE_NOALLOC_SCRATCH_BYTES; }
 
 int flare_forward_noalloc(const flare_fwd_args_t* args, flare_stream_t stream) {
   if (args == nullptr) return FLARE_ERR_BAD_POINTER;
-  int dev = 0;
-  FLARE_CUDA_CHECK(cudaGetDevice(&dev));
-  if (dev < 0 || dev >= kMaxDevices) return FLARE_ERR_UNSUPPORTED;
-  if (g_scratch_ptr[dev] == nullptr) {
-    // first call on this device: resolve the device address of the scratch array (not a stream operation;
-    // make this first call before any stream capture)
-    void* ptr = nullptr;
-    FLARE_CUDA_CHECK(cudaGetSymbolAddress(&ptr, g_flare_noalloc_scratch));
-    if (ptr == nullptr) return FLARE_ERR_CUDA;
-    g_scratch_ptr[dev] = ptr;
-  }
+  // The array's name is only a host-side handle: the address a kernel can use is asked for here, for the device that
+  // is current now, on every call (a lookup in the loaded module, no allocation; nothing is cached, so a context that
+  // was torn down and rebuilt, or several host threads, cannot see a stale address).  It is not a stream operation:
+  // make the first call on a device before any stream capture.
+  void* scratch = nullptr;
+  FLARE_CUDA_CHECK(cudaGetSymbolAddress(&scratch, g_flare_noalloc_scratch));
+  if (scratch == nullptr) return FLARE_ERR_CUDA;
   flare_fwd_args_t a = *args;
   a.workspace = nullptr;
   a.workspace_bytes = 0;
   const size_t need = flare_forward_workspace_bytes(&a);
   if (need > FLARE_NOALLOC_SCRATCH_BYTES) return FLARE_ERR_TOO_LARGE;
-  // Nothing in the scratch has to start at zero: the segment pass writes every state slot before the scan and the
-  // output pass read it.  The contents of the previous call are simply overwritten.
-  a.workspace = g_scratch_ptr[dev];
+  // What must start at zero is cleared by flare_forward itself, on the stream (the gate words of the default path);
+  // the segment pass writes every state slot before the scan and the output pass read it.  The rest of the previous
+  // call's contents is simply overwritten.
+  a.workspace = scratch;
   a.workspace_bytes = FLARE_NOALLOC_SCRATCH_BYTES;
   return flare_forward(&a, stream);
 }

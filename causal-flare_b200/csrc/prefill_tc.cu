@@ -506,6 +506,15 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         tot1 = g16[2] + g16[3];
       }
       misc->xsum[par][hf][m] = tot0 + tot1;
+      if (!(tot0 + tot1 < INFINITY)) {
+        // an encoder weight overflowed (the running max grew by more than fp32 holds inside one chunk): outside the
+        // numeric domain of this path
+        atomicOr(p.err, 2);
+        if (p.gate != nullptr) {
+          p.gate[0] = 1;
+          p.gate[1 + lane_id] = 1;
+        }
+      }
       warp_arrive(&misc->psum[q], lane);
       if constexpr (!STABLE)
 #pragma unroll
@@ -651,16 +660,35 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             v.z = pack_bf16(__uint_as_float(r[ch * 8 + 4]), __uint_as_float(r[ch * 8 + 5]));
             v.w = pack_bf16(__uint_as_float(r[ch * 8 + 6]), __uint_as_float(r[ch * 8 + 7]));
             *reinterpret_cast<uint4*>(smem + OFF_U + swz_chunk_off(m, hf * 4 + ch)) = v;
-            // training: the state before this chunk, as the read-out MMA sees it, is kept for the backward pass
-            if (p.dump_u != nullptr && live)
-              reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.dump_u) +
-                                       (((int64_t)lane_id * p.dump_nch + (seg_begin / C + i)) * p.M + latent0<DVB, SPLIT>() + m) * DV +
-                                       value_col0<DVB, SPLIT>() + hf * 32)[ch] = v;
           }
-          if (p.dump_u != nullptr && live && hf == 0 && value_col0<DVB, SPLIT>() == 0) {
-            const int64_t o = ((int64_t)lane_id * p.dump_nch + (seg_begin / C + i)) * p.M + latent0<DVB, SPLIT>() + m;
-            p.dump_c[o] = c2;        // frame of the chunk, log2 units (unused for the stablemax encoder)
-            p.dump_d[o] = d_carry;   // denominator before the chunk in that frame
+          if (p.dump_u != nullptr) {
+            // Training: the state before this chunk is kept for the backward pass, in the EXACT running-max frame
+            // through this chunk (= the frame the next chunk will use), so that the backward's encoder weights of
+            // the chunk never exceed 1.  Both halves' maxima of this chunk are published once its psum phase completed.
+            if (!(ok = wait_or_abort(&misc->psum[q], par, misc))) break;
+            float fin = 1.0f, c_true = c2;
+            if (!STABLE) {
+              c_true = fmaxf(c2, fmaxf(misc->xmax[par][0][m], misc->xmax[par][1][m]));
+              fin = ex2_approx(c2 - c_true);
+            }
+            if (live) {
+              const int64_t o = ((int64_t)lane_id * p.dump_nch + (seg_begin / C + i)) * p.M + latent0<DVB, SPLIT>() + m;
+              uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.dump_u) + o * DV +
+                                                    value_col0<DVB, SPLIT>() + hf * 32);
+#pragma unroll
+              for (int ch = 0; ch < 4; ++ch) {
+                uint4 v;
+                v.x = pack_bf16(__uint_as_float(r[ch * 8 + 0]) * fin, __uint_as_float(r[ch * 8 + 1]) * fin);
+                v.y = pack_bf16(__uint_as_float(r[ch * 8 + 2]) * fin, __uint_as_float(r[ch * 8 + 3]) * fin);
+                v.z = pack_bf16(__uint_as_float(r[ch * 8 + 4]) * fin, __uint_as_float(r[ch * 8 + 5]) * fin);
+                v.w = pack_bf16(__uint_as_float(r[ch * 8 + 6]) * fin, __uint_as_float(r[ch * 8 + 7]) * fin);
+                dst[ch] = v;
+              }
+              if (hf == 0 && value_col0<DVB, SPLIT>() == 0) {
+                p.dump_c[o] = c_true;          // log2 units (unused for the stablemax encoder)
+                p.dump_d[o] = d_carry * fin;   // denominator before the chunk in that frame
+              }
+            }
           }
         }
         if (need) tmem_wait_st();
@@ -773,7 +801,13 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       // outside the numeric domain of this path (scores of a token more than ~80 nats below the running maxima):
       // every weight underflowed.  Flag it; the exact path has no such limit.  With a latent-group split one group
       // may legitimately carry no weight; the merge kernel flags a token only when every group is empty.
-      if (!SPLIT && tt < nvalid && !den_ok) atomicOr(p.err, 2);
+      if (!SPLIT && tt < nvalid && !den_ok) {
+        atomicOr(p.err, 2);
+        if (p.gate != nullptr) {
+          p.gate[0] = 1;
+          p.gate[1 + lane_id] = 1;
+        }
+      }
       const float inv = (SPLIT && !den_ok) ? 0.f : 1.0f / den;
       if (SPLIT && p.part_y != nullptr && tt < nvalid && value_col0<DVB, SPLIT>() == 0)
         p.part_lw[(part_row0 + t0 + tt) * p.H + h] = den_ok ? misc->kap[par] + __log2f(den) : -INFINITY;
@@ -886,6 +920,12 @@ bool prefill_tc_supported(const flare_fwd_args_t* a) {
   if (a->lengths != nullptr && bs > 1) return false;  // per-row lengths: token-causal only
   // stablemax encoder weights: token-causal only
   const bool variant_ok = a->variant == FLARE_SOFTMAX || (a->variant == FLARE_STABLEMAX && bs == 1 && a->power > 0.f);
+  // the tiled copies need positive strides whose byte size is a multiple of 16 and stays below 2^40; anything else
+  // (a tensor expanded over heads with stride 0, say) is served by the exact kernels
+  const int64_t strides[] = {a->k_stride_b, a->k_stride_n, a->k_stride_h, a->v_stride_b, a->v_stride_n, a->v_stride_h,
+                             a->q_stride_h, a->q_stride_m};
+  for (int64_t st : strides)
+    if (st <= 0 || (st % 8) != 0 || st >= (int64_t(1) << 39)) return false;
   return a->dtype == FLARE_BF16 && variant_ok && block_ok && lse_ok && a->M <= 4 * M && a->M >= 16 &&
          (a->M % 16) == 0 && ((a->Dk == 64 && (a->Dv == 64 || a->Dv == 128)) || (a->Dk == 128 && a->Dv == 128)) && a->q_dec == nullptr &&
          a->k_dec == nullptr && a->mask == nullptr && a->N >= 1;
@@ -897,7 +937,7 @@ __global__ void __launch_bounds__(256) tc_merge_groups_kernel(const float* __res
                                                                int groups, int64_t rows /* B*N*H */, int N, int H, int dv,
                                                                __nv_bfloat16* y, int64_t y_stride_b, int64_t y_stride_n,
                                                                int64_t y_stride_h, float* lse_dec /* [B, H, N] or null */,
-                                                               const int32_t* lens /* [B] or null */) {
+                                                               const int32_t* lens /* [B] or null */, int* gate) {
   const int cols8 = dv >> 3;
   const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= rows * cols8) return;
@@ -912,7 +952,13 @@ __global__ void __launch_bounds__(256) tc_merge_groups_kernel(const float* __res
   }
   float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, wsum = 0.f;
   if (mx == -INFINITY) {
-    if (c8 == 0) atomicOr(&g_tc_error, 2);  // every group's weights underflowed: outside the numeric domain
+    if (c8 == 0) {  // every group's weights underflowed: outside the numeric domain
+      atomicOr(&g_tc_error, 2);
+      if (gate != nullptr) {
+        gate[0] = 1;
+        gate[1 + (row / ((int64_t)H * N)) * H + (row % H)] = 1;
+      }
+    }
   } else {
 #pragma unroll
     for (int g = 0; g < 4; ++g) {
@@ -972,7 +1018,10 @@ int launch_prefill_tc(const flare_fwd_args_t* a, const TcParams& p_in, int nseg_
     const uint64_t dims[3] = {(uint64_t)a->Dk, (uint64_t)a->M, (uint64_t)a->H};
     const int64_t str[2] = {a->q_stride_m, a->q_stride_h};
     const uint32_t box[3] = {64, 128, 1};
-    if (!make_map(&tq, a->q, 3, dims, str, box)) return FLARE_ERR_CUDA;
+    if (!make_map(&tq, a->q, 3, dims, str, box)) {
+      set_cuda_error(cudaErrorInvalidValue, "cuTensorMapEncodeTiled (latent bank)");
+      return FLARE_ERR_CUDA;
+    }
   }
   {
     const uint64_t dimk[4] = {(uint64_t)a->Dk, (uint64_t)a->H, (uint64_t)a->N, (uint64_t)a->B};
@@ -980,8 +1029,10 @@ int launch_prefill_tc(const flare_fwd_args_t* a, const TcParams& p_in, int nseg_
     const uint32_t box[4] = {64, 1, 128, 1};
     const int64_t strk[3] = {a->k_stride_h, a->k_stride_n, a->k_stride_b};
     const int64_t strv[3] = {a->v_stride_h, a->v_stride_n, a->v_stride_b};
-    if (!make_map(&tk, a->k, 4, dimk, strk, box)) return FLARE_ERR_CUDA;
-    if (!make_map(&tv, a->v, 4, dimv, strv, box)) return FLARE_ERR_CUDA;
+    if (!make_map(&tk, a->k, 4, dimk, strk, box) || !make_map(&tv, a->v, 4, dimv, strv, box)) {
+      set_cuda_error(cudaErrorInvalidValue, "cuTensorMapEncodeTiled (keys / values)");
+      return FLARE_ERR_CUDA;
+    }
   }
   const int groups = prefill_tc_latent_groups(a);
   const dim3 grid(a->B * a->H, nseg_grid, a->Dv / D * groups);
@@ -1003,7 +1054,7 @@ int launch_prefill_tc(const flare_fwd_args_t* a, const TcParams& p_in, int nseg_
   const int64_t threads = rows * (a->Dv / 8);
   tc_merge_groups_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, stream>>>(
       p.part_y, p.part_lw, groups, rows, a->N, a->H, a->Dv, reinterpret_cast<__nv_bfloat16*>(p.y), p.y_stride_b,
-      p.y_stride_n, p.y_stride_h, p.lse_dec, p.lens);
+      p.y_stride_n, p.y_stride_h, p.lse_dec, p.lens, p.gate);
   FLARE_CUDA_CHECK(cudaGetLastError());
   return FLARE_OK;
 }

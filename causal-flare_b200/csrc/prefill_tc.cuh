@@ -34,6 +34,9 @@ struct TcParams {
   void* dump_u;
   float *dump_c, *dump_d;
   int dump_nch;
+  // Optional per-call gate words (in the caller's workspace, zeroed before the launch): gate[0] is raised when any
+  // token of the call left the numeric domain of these kernels, gate[1 + lane] for the (batch, head) lane it is in.
+  int* gate;
   int* err;                  // device error word (bit 0: a wait gave up, bit 1: numeric domain exceeded)
   long long* trace;  // optional diagnostic cycle stamps of CTA (0, 0), see TC_TRACE; null in normal use
 };

@@ -136,7 +136,8 @@ __device__ __forceinline__ uint64_t make_desc_sw128(uint32_t smem_addr, uint32_t
   return d;
 }
 
-// Instruction descriptor, kind::f16, bf16 x bf16 -> fp32.
+// Instruction descriptor, kind::f16, bf16 x bf16 -> fp32.  (Both operands must have the same format: a descriptor
+// that mixes fp16 and bf16 operands is an illegal instruction on sm_100.)
 constexpr uint32_t make_idesc_bf16(int M, int N, int a_mn_major, int b_mn_major) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)a_mn_major << 15) | ((uint32_t)b_mn_major << 16) |
          ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);

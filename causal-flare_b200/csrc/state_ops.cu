@@ -25,6 +25,7 @@ __device__ __forceinline__ void merge_factors(float ma, float mb, float& mn, flo
 }
 
 __global__ void __launch_bounds__(NT) fold_kernel(const FoldParams p) {
+  if (p.gate != nullptr && *p.gate == 0) return;
   const int64_t lane_id = blockIdx.x;
   const int m = blockIdx.y * LAT_PER_CTA + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;

@@ -18,6 +18,7 @@ struct FoldParams {
   int64_t lanes;
   int M, Dv;
   int stablemax;  // the empty state has m = 0 instead of -inf
+  const int* gate;  // optional: the kernel does nothing unless *gate != 0
 };
 
 int launch_fold(const FoldParams& p, cudaStream_t stream);

@@ -22,6 +22,7 @@ template <int MM_MAX, int DD>
 __global__ void __launch_bounds__(NT, (MM_MAX * DD <= 32) ? 2 : 1) walk_exact_kernel(const WalkParams p) {
   extern __shared__ __align__(16) float smem_raw[];
   const int lane_id = blockIdx.x;  // (b, h) lane
+  if (p.gate != nullptr && p.gate[(int64_t)lane_id * p.gate_stride] == 0) return;
   const int seg = blockIdx.y;
   const int b = lane_id / p.H, h = lane_id % p.H;
   const int dvt = 32 * DD;

@@ -29,6 +29,11 @@ struct WalkParams {
   int write_y;
   float scale, power;
   int dtype, variant, block_size;
+  // Optional gate: a CTA does nothing unless gate[lane * gate_stride] != 0 (gate_stride 0: one word for the whole
+  // call, 1: one word per (batch, head) lane).  Used when these kernels stand by behind the tensor-core path and
+  // only run for calls (lanes) whose inputs left that path's numeric domain.  Null: always run.
+  const int* gate;
+  int gate_stride;
 };
 
 // grid.y = nseg_grid segments are launched (segments 0 .. nseg_grid-1)

@@ -92,10 +92,19 @@ typedef struct flare_fwd_args {
   int32_t variant;    /* flare_variant */
   int32_t block_size; /* 1: token-causal (autoregressive); > 1: block-causal (semi-autoregressive) */
   int32_t path;       /* flare_path */
+  /* Training (optional, NULL / 0 otherwise): a buffer of flare_forward_keep_bytes(args) bytes in which the tensor-core
+   * forward leaves what flare_backward needs to skip its own replay of the forward: the state before every chunk of
+   * 128 tokens (bf16 numerator, fp32 frame and denominator per latent) and the call's numeric-domain gate words.
+   * Needs y and lse_dec as well; FLARE_ERR_BAD_CONFIG when given for a problem whose keep size is 0. */
+  void* keep;
+  size_t keep_bytes;
 } flare_fwd_args_t;
 
 size_t flare_forward_workspace_bytes(const flare_fwd_args_t* args);
 int flare_forward(const flare_fwd_args_t* args, flare_stream_t stream);
+/* Size of flare_fwd_args_t::keep for this problem: 0 unless the call takes the tensor-core path with shared decode
+ * weights, no mask / lengths / carry-in state (the problems flare_backward_uses_tensor_path accepts). */
+size_t flare_forward_keep_bytes(const flare_fwd_args_t* args);
 
 /*
  * flare_forward for callers that cannot allocate device memory (no counterpart in the reference, whose wrappers
@@ -152,6 +161,12 @@ typedef struct flare_bwd_args {
   float* span_gam;        /* [B, H, M] */
   float* span_rho_first;  /* [B, H, M] */
   int32_t phase;          /* 0, 1 or 2 */
+  /* Optional, from a forward of the same problem that was given fwd.keep: its output y (strides in elements), its
+   * lse_dec [B, H, N], and the keep buffer in fwd.keep / fwd.keep_bytes.  With all three the tensor-core backward
+   * skips its replay of the forward (and asks for a smaller workspace); otherwise they are ignored. */
+  const void* y;
+  int64_t y_stride_b, y_stride_n, y_stride_h;
+  const float* lse_dec;
 } flare_bwd_args_t;
 
 size_t flare_backward_workspace_bytes(const flare_bwd_args_t* args);

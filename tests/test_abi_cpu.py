@@ -93,6 +93,11 @@ def test_workspace_plan_small_batch_is_segmented():
     few = _fake_args(B=1, N=8192, H=2, M=64, Dk=64, Dv=64)
     many = _fake_args(B=8, N=8192, H=64, M=64, Dk=64, Dv=64)
     assert lib.flare_forward_workspace_bytes(C.byref(few)) > 0
+    # many lanes: no segment states; the default path only asks for its gate words (1 + lanes ints, rounded to 256 B)
+    assert lib.flare_forward_workspace_bytes(C.byref(many)) == (4 * (1 + 8 * 64) + 255) // 256 * 256
+    many.path = _lib.PATH_TENSOR
+    assert lib.flare_forward_workspace_bytes(C.byref(many)) == 0
+    many.path = _lib.PATH_EXACT
     assert lib.flare_forward_workspace_bytes(C.byref(many)) == 0
     # too-small workspace is refused before anything is launched
     few.workspace, few.workspace_bytes = 0x2000, 16

@@ -87,10 +87,14 @@ def test_block_causal_config_messages():
 
 
 def test_semi_ar_inference_entry_points_raise():
-    with pytest.raises(NotImplementedError):
-        cf.flare_semi_autoregressive_prefill_trition()
-    with pytest.raises(NotImplementedError):
-        cf.flare_semi_autoregressive_decode_trition()
+    # same calls and messages as the reference's own tests (testing/semi_autoregressive/test_block_causal.py:260-275)
+    q, k, v = torch.randn(2, 4, 16), torch.randn(1, 8, 2, 16), torch.randn(1, 8, 2, 16)
+    with pytest.raises(NotImplementedError, match="not implemented yet"):
+        cf.flare_semi_autoregressive_prefill_trition(q, k, v)
+    with pytest.raises(NotImplementedError, match="not implemented yet"):
+        cf.flare_semi_autoregressive_decode_trition(q, k[:, 0], v[:, 0])
+    with pytest.raises(TypeError):
+        cf.flare_semi_autoregressive_prefill_trition(q, k, v, None)  # the options are keyword-only, as in the reference
 
 
 def test_stablemax_unsupported_options():

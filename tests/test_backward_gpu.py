@@ -109,7 +109,7 @@ def test_train_step_bf16_gate(variant):
     got = run_grads(fn, *to_dev(dy, q, k, v))
     for name, key in (("dq", "dQ"), ("dk", "dK"), ("dv", "dV")):
         assert got[name].dtype == torch.bfloat16
-        assert_bf16_gate(got[name], ref[key], f"{variant} {name}", max_abs=2e-2 * max(1.0, float(ref[key].abs().max())))
+        assert_bf16_gate(got[name], ref[key], f"{variant} {name}")
 
 
 @pytest.mark.parametrize("p", [1, 2, 3])
@@ -154,7 +154,7 @@ def test_semi_ar_grads_bf16_tiled_value_dim():
     fn = lambda q, k, v, qd, kd: cf.flare_semi_autoregressive_trition(q, k, v, block_size=64, chunk_size=64)  # noqa: E731
     got = run_grads(fn, *to_dev(dy, q, k, v))
     for name, key in (("dq", "dQ"), ("dk", "dK"), ("dv", "dV")):
-        assert_bf16_gate(got[name], ref[key], f"semi-AR bf16 {name}", max_abs=2e-2 * max(1.0, float(ref[key].abs().max())))
+        assert_bf16_gate(got[name], ref[key], f"semi-AR bf16 {name}")
 
 
 @pytest.mark.parametrize("N, bs", [(1024, 32), (1152, 48), (2048, 128)])

@@ -253,3 +253,33 @@ def test_semi_ar_block_granular_cached_prefill(dtype):
     assert_close(state["d"], st_full["d"], what="final state d", atol=1e-3, rtol=2e-3)
     with pytest.raises(ValueError):
         flare_semi_autoregressive_block_prefill(qc, kc[:, :40], vc[:, :40], block_size=bs)
+
+
+def test_semi_ar_token_decode_releases_outputs_block_by_block():
+    # token-by-token decoding of the block-causal operator: nothing is returned inside a block, the call that completes
+    # a block returns the whole block's outputs, which equal the full-sequence operator's
+    from causal_flare.semi_autoregressive.inference import (SemiAutoRegressiveTokenCache,
+                                                            flare_semi_autoregressive_block_prefill,
+                                                            flare_semi_autoregressive_token_decode)
+
+    B, N, H, Ml, Dl, bs = 2, 96, 2, 32, 64, 32
+    q, k, v = orc.make_inputs(B, N, H, Ml, Dl, seed0=41, dtype=torch.bfloat16)
+    ref = orc.semi_ar_forward(q, k, v, block_size=bs)[0]
+    qc, kc, vc = to_dev(q, k, v)
+    # the first block through the block-granular prefill, the rest one token at a time on top of its state
+    y0, st = flare_semi_autoregressive_block_prefill(qc, kc[:, :bs], vc[:, :bs], block_size=bs)
+    cache = SemiAutoRegressiveTokenCache(st, bs)
+    outs = [y0]
+    for t in range(bs, N):
+        y, cache = flare_semi_autoregressive_token_decode(qc, kc[:, t], vc[:, t:t + 1], cache, block_size=bs)
+        if (t + 1) % bs == 0:
+            assert y is not None and tuple(y.shape) == (B, bs, H, Dl) and cache.pending == 0
+            outs.append(y)
+        else:
+            assert y is None and cache.pending == (t + 1) % bs
+    assert_bf16_gate(torch.cat(outs, 1), ref, "token-granular block-causal decode")
+    full = cf.flare_semi_autoregressive_trition(qc, kc, vc, block_size=bs, chunk_size=16)[0]
+    assert orc.max_abs(torch.cat(outs, 1).float().cpu(), full.float().cpu()) <= 2e-2
+    with pytest.raises(ValueError):
+        flare_semi_autoregressive_token_decode(qc, kc[:, 0], vc[:, 0], cache, block_size=16)
+

@@ -85,36 +85,52 @@ def test_tensor_vs_exact_at_benchmark_size():
     assert torch.equal(y3, y_t), "tensor path must be run-to-run deterministic"
 
 
-def test_sharp_scores_are_flagged_not_silently_wrong():
-    # scores with a standard deviation of ~64 nats: outside the tensor path's domain.  Either the result still
-    # meets the gate, or the device status reports the range problem; the exact path is right in any case.
+def test_sharp_scores_forced_tensor_path_is_flagged_and_default_path_is_right():
+    # scores with a standard deviation of ~64 nats: outside the tensor kernels' numeric domain.  Forcing that path
+    # raises the device status; the default path (AUTO) reruns the flagged lanes on the exact kernels by itself.
     q, k, v = orc.make_inputs(1, 512, 2, M, D, seed0=13, dtype=torch.bfloat16)
     q, k = (q.float() * 8).bfloat16(), (k.float() * 8).bfloat16()
     ref = orc.ar_forward(q, k, v)
     qc, kc, vc = to_dev(q, k, v)
+    _ops.device_status()
     y_t, _, _, _ = _ops.forward(qc, kc, vc, scale=D ** -0.5, path=_lib.PATH_TENSOR)
     status = _ops.device_status()
     assert status in (0, 2)
     if status == 0:
         assert_bf16_gate(y_t, ref, "sharp scores, tensor path")
+    y_a = cf.flare_autoregressive_triton(qc, kc, vc)  # default environment
+    assert_bf16_gate(y_a, ref, "sharp scores, default path")
+    assert _ops.device_status() in (0, 2)  # the flag stays readable: it says that the exact kernels had to step in
     y_e, _, _, _ = _ops.forward(qc, kc, vc, scale=D ** -0.5, path=_lib.PATH_EXACT)
     assert _ops.device_status() == 0
     assert_bf16_gate(y_e, ref, "sharp scores, exact path")
-
-
-def test_checked_mode_reruns_sharp_inputs_on_the_exact_path(monkeypatch):
-    # FLARE_B200_CHECK=1: the AUTO path reads the device status after the tensor kernels and falls back by itself
-    monkeypatch.setenv("FLARE_B200_CHECK", "1")
-    q, k, v = orc.make_inputs(1, 512, 2, M, D, seed0=13, dtype=torch.bfloat16)
-    q, k = (q.float() * 8).bfloat16(), (k.float() * 8).bfloat16()
-    ref = orc.ar_forward(q, k, v)
-    y = cf.flare_autoregressive_triton(*to_dev(q, k, v))
-    assert_bf16_gate(y, ref, "sharp scores, checked AUTO path")
+    # in-domain inputs stay on the tensor kernels: same bits as the forced tensor path
+    q2, k2, v2 = to_dev(*orc.make_inputs(1, 512, 2, M, D, seed0=14, dtype=torch.bfloat16))
+    assert torch.equal(cf.flare_autoregressive_triton(q2, k2, v2),
+                       _ops.forward(q2, k2, v2, scale=D ** -0.5, path=_lib.PATH_TENSOR)[0])
     assert _ops.device_status() == 0
-    # in-domain inputs stay on the tensor path and are unchanged by the check
-    q2, k2, v2 = orc.make_inputs(1, 512, 2, M, D, seed0=14, dtype=torch.bfloat16)
-    y2 = cf.flare_autoregressive_triton(*to_dev(q2, k2, v2))
-    assert_bf16_gate(y2, orc.ar_forward(q2, k2, v2), "in-domain, checked AUTO path")
+
+
+@pytest.mark.parametrize("N", [512, 1024, 2048])
+@pytest.mark.parametrize("qk_std", [4.0, 8.0])
+def test_sharp_softmax_shapes_forward_and_backward_with_default_settings(N, qk_std):
+    # the sharp-softmax regime (B=1, H=16, M=16, D=64; q and k scaled so that the scores have a standard deviation of
+    # qk_std^2): results through the public operators with the default environment against the oracle.  The gradients
+    # grow with the score scale, so their max-abs bound is taken relative to the largest reference entry.
+    B, H, Ml, Dl = 1, 16, 16, 64
+    q, k, v, dy = orc.make_inputs(B, N, H, Ml, Dl, seed0=31, dtype=torch.bfloat16, with_dy=True)
+    q, k = (q.float() * qk_std).bfloat16(), (k.float() * qk_std).bfloat16()
+    ref_y = orc.ar_forward(q, k, v)
+    ref = orc.ar_backward_closed_form(q, k, v, dy)
+    ql, kl, vl = (t.cuda().requires_grad_(True) for t in (q, k, v))
+    y = cf.flare_autoregressive_triton(ql, kl, vl)
+    # sharp decode weights pick single values: |y| reaches 4 and more, where one bf16 output step is 3.1e-2; the
+    # max-abs bound is 1 % of the largest reference entry there
+    assert_bf16_gate(y, ref_y, f"sharp y, std {qk_std}", max_abs=max(2e-2, 1e-2 * float(ref_y.abs().max())))
+    y.backward(dy.cuda())
+    for got, key in ((ql.grad, "dQ"), (kl.grad, "dK"), (vl.grad, "dV")):
+        assert_bf16_gate(got, ref[key], f"sharp {key}, std {qk_std}", max_abs=2e-2 * max(1.0, float(ref[key].abs().max())))
+    _ops.device_status()  # clear the informational flag for the tests that follow
 
 
 @pytest.mark.parametrize("Ml", [16, 64, 96])
