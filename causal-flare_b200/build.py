@@ -17,6 +17,7 @@ LIB = os.path.join(HERE, "libflare_b200.so")
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr",
+    *os.environ.get("FLARE_B200_NVCC_FLAGS", "").split(),  # extra flags for experiments (e.g. -DNAME)
 ]
 
 # (source file, extra defines, object name)

@@ -15,7 +15,8 @@
 //   dS   = R (P - D delta_t)  +  E slope (X - Cc - sum_{t' >= t} R p)          slope = 1 | sigma'/sigma
 //   dV   = E^T G + (E^T R . vis) dY
 //   G   += R dY,  Cc += sum_t R p,  then both are rescaled by exp2(c_{i-1} - c_i) for the next chunk.
-// dS is written as a bf16 plane [lane][m][t]; a second tensor-core kernel forms dK = scale dS^T Q per chunk and
+// dS is written per token as a hi and a lo bf16 row over the latents ([lane][t][2][m], dS = hi + lo, every warp store
+// one contiguous segment); a second tensor-core kernel forms dK = scale dS^T Q per chunk and
 // dQ = scale sum_t dS K per (lane, split) (fp32 partials, summed in fixed order: no atomics, deterministic).
 //
 // Main kernel, one CTA per (lane, group of 128 latents), 14 warps: 0-7 latent group (thread = latent = TMEM lane,
@@ -54,8 +55,7 @@ struct BwdTcParams {
   float scale, power;
   const float *chunk_c, *chunk_d;  // [lanes][nch][M]
   const float *tok_l2, *tok_delta;  // [lanes][npad]
-  void* ds;      // bf16 [2][lanes][M][npad]: dS as a hi + lo pair of planes
-  int64_t ds_plane;  // elements per plane
+  void* ds;      // bf16 [lanes][npad][2][M]: dS of every token as a hi row and a lo row over the latents (dS = hi + lo)
   void* dv;      // bf16 [B, N, H, Dv] contiguous, or (more than one latent group) bf16 [groups][B][N][H][Dv]
   int groups;
   int* gate;  // per-call gate word (may be null): raised when a carry turns non-finite (inputs outside the numeric domain)
@@ -81,7 +81,10 @@ int launch_bwd_tc_unit(int mode, const CUtensorMap& tk, const CUtensorMap& tv, c
 namespace {
 
 constexpr int C = 128;
-constexpr int NT_MAIN = 448;
+constexpr int LW = 4;                           // latent warps per lane quarter
+constexpr int TOK = C / LW;                     // tokens per latent thread
+constexpr int NT_MAIN = (4 * LW + 4 + 2) * 32;  // latent warps, token warps, MMA issuer, TMA producer
+constexpr int W_TOKEN = 4 * LW, W_MMA = 4 * LW + 4, W_TMA = 4 * LW + 5;  // first token warp, issuer, producer
 constexpr float kLog2e = 1.4426950408889634f;
 
 // shared memory map of the main kernel (bytes; every operand buffer 1024-aligned for the 128B swizzle)
@@ -90,7 +93,7 @@ struct BL {
   static constexpr int OFF_KA = 0;                      // K tile [DKB][128 t][64]; later the masked A [2][128 tau][64 t]
   static constexpr int OFF_V = 32768;                   // [DVB][128 t][64]
   static constexpr int OFF_DY = OFF_V + DVB * 16384;    // [DVB][128 t][64]
-  static constexpr int OFF_UR = OFF_DY + DVB * 16384;   // U_i [DVB][128 m][64]; later the rows R p [2][128 m][64 t]
+  static constexpr int OFF_UR = OFF_DY + DVB * 16384;   // U_i [DVB][128 m][64] (the 32 KB slot keeps every buffer behind it 1024-aligned for both widths)
   static constexpr int OFF_GC = OFF_UR + 32768;         // G as bf16 [DVB][128 m][64]
   static constexpr int OFF_E = OFF_GC + DVB * 16384;    // [2 t-blocks][128 m][64 t]
   static constexpr int OFF_R = OFF_E + 32768;
@@ -103,20 +106,23 @@ struct BL {
 constexpr uint32_t T0 = 0, T1 = 128, T2 = 256, TQ = 320, TG = 384, TM_COLS = 512;
 
 struct Misc {
-  uint64_t k_full, v_full, dy_full, u_full, tok_full, q_ready;
+  uint64_t k_full, v_full, dy_full, u_full, q_ready;
   uint64_t s_ready, a_ready, px_ready, g_ready, wt_ready, dv_ready;
   uint64_t er_done, am_done, p_free, x_done, wm_done, dv_free, gc_done;
   uint64_t psum[4], prp[4];
   uint32_t tmem_base;
   volatile int abort_flag;
-  float xch[2][128];    // exchange between the two halves of a latent row: sums of E, then sums of R p
-  float tok_l2[128];    // decode log-sum-exp of the chunk's tokens, log2 units (+inf beyond the sequence)
-  float tok_delta[128];
+  float xch[LW][128];  // exchange between the token quarters of a latent row: sums of E, then sums of R p
 };
 static_assert(sizeof(Misc) <= 2560, "Misc must leave room for the alignment slack");
 
+// waits between roles are long (thousands of cycles): one quick look, then suspend
 __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, Misc* misc) {
-  return tc::wait_or_abort(bar, parity, &misc->abort_flag);
+  return tc::wait_or_abort(bar, parity, &misc->abort_flag, 1);
+}
+// exchange between the four warps of a lane quarter, which run in step: poll
+__device__ __forceinline__ bool wait_partner(uint64_t* bar, uint32_t parity, Misc* misc) {
+  return tc::wait_or_abort(bar, parity, &misc->abort_flag, 48);
 }
 
 // optional cycle trace of CTA (0, 0): [role < 4][chunk step < 8][slot < 8] clock64 stamps (diagnostic hook)
@@ -167,29 +173,28 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     mbar_init(&misc->v_full, 1);
     mbar_init(&misc->dy_full, 1);
     mbar_init(&misc->u_full, 1);
-    mbar_init(&misc->tok_full, 1);
-    mbar_init(&misc->q_ready, 8);
+    mbar_init(&misc->q_ready, 4 * LW);
     mbar_init(&misc->s_ready, 1);
     mbar_init(&misc->a_ready, 1);
     mbar_init(&misc->px_ready, 1);
     mbar_init(&misc->g_ready, 1);
     mbar_init(&misc->wt_ready, 1);
     mbar_init(&misc->dv_ready, 1);
-    mbar_init(&misc->er_done, 8);
+    mbar_init(&misc->er_done, 4 * LW);
     mbar_init(&misc->am_done, 4);
-    mbar_init(&misc->p_free, 8);
-    mbar_init(&misc->x_done, 8);
+    mbar_init(&misc->p_free, 4 * LW);
+    mbar_init(&misc->x_done, 4 * LW);
     mbar_init(&misc->wm_done, 4);
     mbar_init(&misc->dv_free, 4);
-    mbar_init(&misc->gc_done, 8);
+    mbar_init(&misc->gc_done, 4 * LW);
     for (int i = 0; i < 4; ++i) {
-      mbar_init(&misc->psum[i], 2);
-      mbar_init(&misc->prp[i], 2);
+      mbar_init(&misc->psum[i], LW);
+      mbar_init(&misc->prp[i], LW);
     }
     misc->abort_flag = 0;
     fence_barrier_init();
   }
-  if (warp == 12) {
+  if (warp == W_MMA) {
     tmem_alloc(&misc->tmem_base, TM_COLS);
     tmem_relinquish();
   }
@@ -201,15 +206,13 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
   const int rows_here = min(128, p.M - group * 128);  // latents of this group
   const int ksm = (rows_here + 15) >> 4;              // 16-latent steps of a contraction over the latents
 
-  if (warp == 13) {
+  if (warp == W_TMA) {
     // ======================================= TMA producer =======================================
     if (lane == 0) {
       prefetch_tensormap(&tm_k);
       prefetch_tensormap(&tm_v);
       prefetch_tensormap(&tm_dy);
       prefetch_tensormap(&tm_u);
-      const float* l2_row = p.tok_l2 + (int64_t)lane_id * p.npad;
-      const float* dl_row = p.tok_delta + (int64_t)lane_id * p.npad;
       for (int j = 0; ok && j < nch; ++j) {
         const int i = nch - 1 - j, t0 = i * C;
         const uint32_t pp = (j - 1) & 1;
@@ -221,13 +224,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
         mbar_arrive_expect_tx(&misc->v_full, DVB * 16384);
 #pragma unroll
         for (int vb = 0; vb < DVB; ++vb) tma_load_4d(smem + L::OFF_V + vb * 16384, &tm_v, &misc->v_full, vb * 64, h, t0, b);
-        // per-token statistics: the latent group has finished with the previous chunk's once its P pass is over
-        if (j > 0 && !(ok = wait_or_abort(&misc->p_free, pp, misc))) break;
-        mbar_arrive_expect_tx(&misc->tok_full, 1024);
-        bulk_load(misc->tok_l2, l2_row + t0, 512, &misc->tok_full);
-        bulk_load(misc->tok_delta, dl_row + t0, 512, &misc->tok_full);
-        // U_i: its buffer holds the rows R p of the previous chunk until the latent group has read them back
-        if (j > 0 && !(ok = wait_or_abort(&misc->x_done, pp, misc))) break;
+        // U_i: read by the previous chunk's P product (which has run: px_ready above)
         mbar_arrive_expect_tx(&misc->u_full, DVB * 16384);
 #pragma unroll
         for (int vb = 0; vb < DVB; ++vb)
@@ -239,7 +236,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
         for (int vb = 0; vb < DVB; ++vb) tma_load_4d(smem + L::OFF_DY + vb * 16384, &tm_dy, &misc->dy_full, vb * 64, h, t0, b);
       }
     }
-  } else if (warp == 12) {
+  } else if (warp == W_MMA) {
     // ======================================= MMA issuer =======================================
     if (lane == 0) {
       // All operands are bf16: tcgen05.mma kind::f16 wants A and B in ONE format (a descriptor that mixes fp16 and
@@ -325,165 +322,211 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
         tc_commit(&misc->dv_ready);
       }
     }
-  } else if (warp < 8) {
-    // ============ latent group: thread = (latent = TMEM lane, half of the chunk's tokens) ============
-    const int hf = warp >> 2, q = warp & 3;
+  } else if (warp < 4 * LW) {
+    // ======== latent group: thread = (latent = TMEM lane, quarter of the chunk's tokens); 4 warps per lane quarter ========
+    const int tq = warp >> 2, q = warp & 3;
     const uint32_t tl = tmem + ((uint32_t)(q * 32) << 16);
     const int m = q * 32 + lane;
     const int mg = group * 128 + m;
     const bool live = mg < p.M;
     const float sc2 = p.scale * kLog2e;
-    const int tok0 = hf * 64;
-    uint8_t* const e_row = smem + L::OFF_E + hf * 16384;
-    uint8_t* const r_row = smem + L::OFF_R + hf * 16384;
-    uint8_t* const rp_row = smem + L::OFF_UR + hf * 16384;
+    const int tok0 = tq * TOK;
+    // this thread's 32 tokens are 16-byte chunks ch0 .. ch0 + 3 of row m in t-block tq / 2 of the [2][128][64] buffers
+    const int ch0 = (tq & 1) * 4;
+    uint8_t* const e_row = smem + L::OFF_E + (tq >> 1) * 16384;
+    uint8_t* const r_row = smem + L::OFF_R + (tq >> 1) * 16384;
     {
-      // latent bank row -> tensor memory as packed bf16 (element k in column k / 2); each half writes half a row
-      const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.q) + (int64_t)h * p.q_stride_h +
-                                                        (int64_t)(live ? mg : 0) * p.q_stride_m + hf * (DKB * 32));
-      if constexpr (DKB == 2) {
-        uint32_t r[32];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const uint4 x = live ? __ldg(src + i) : make_uint4(0, 0, 0, 0);
-          r[4 * i] = x.x; r[4 * i + 1] = x.y; r[4 * i + 2] = x.z; r[4 * i + 3] = x.w;
-        }
-        tmem_st32(tl + TQ + hf * 32, r);
-      } else {
+      // latent bank row -> tensor memory as packed bf16 (element k in column k / 2); each warp of the quarter writes
+      // 32 elements of the row (Dk = 64: the first two warps)
+      if (tq * 32 < DKB * 64) {
+        const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.q) + (int64_t)h * p.q_stride_h +
+                                                          (int64_t)(live ? mg : 0) * p.q_stride_m + tq * 32);
         uint32_t r[16];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const uint4 x = live ? __ldg(src + i) : make_uint4(0, 0, 0, 0);
           r[4 * i] = x.x; r[4 * i + 1] = x.y; r[4 * i + 2] = x.z; r[4 * i + 3] = x.w;
         }
-        tmem_st16(tl + TQ + hf * 16, r);
+        tmem_st16(tl + TQ + tq * 16, r);
+        tmem_wait_st();
       }
-      tmem_wait_st();
       tc_fence_before_sync();
       warp_arrive(&misc->q_ready, lane);
     }
     float cc_carry = 0.f;  // Cc: sum over later chunks of R p, in the current chunk's frame
     const int64_t stat0 = (int64_t)lane_id * nch * p.M + mg;
-    __nv_bfloat16* const ds_row = reinterpret_cast<__nv_bfloat16*>(p.ds) + ((int64_t)lane_id * p.M + (live ? mg : 0)) * p.npad;
+    // dS rows of this lane: element (token t, part, latent) at (t * 2 + part) * M + latent; a warp's 32 latents are
+    // contiguous, so every store instruction of a warp writes one 64-byte segment
+    __nv_bfloat16* const ds_col = reinterpret_cast<__nv_bfloat16*>(p.ds) + (int64_t)lane_id * p.npad * 2 * p.M + (live ? mg : 0);
+    // value columns of G this warp rescales and repacks: a quarter of them
+    constexpr int GCOLS = DVB * 16;
+    const int gcol = tq * GCOLS;
+    uint8_t* const g_dst = smem + L::OFF_GC + (gcol >> 6) * 16384;
+    const int gch0 = (gcol & 63) >> 3;
 
-    for (int j = 0; ok && j < nch; ++j) {
-      const int i = nch - 1 - j, t0 = i * C;
-      const uint32_t par = j & 1, pp = (j - 1) & 1;
-      const int nvalid = min(C, p.N - t0);
-      const int lim = live ? nvalid - tok0 : 0;  // tokens of this thread's half that exist (may be <= 0)
-      const bool fast = __all_sync(0xffffffffu, lim >= 64);
-      const float c_i = (live && !STABLE) ? p.chunk_c[stat0 + (int64_t)i * p.M] : 0.f;
-      const float d_i = live ? p.chunk_d[stat0 + (int64_t)i * p.M] : 1.f;
-      const float c_prev = (live && !STABLE && i > 0) ? p.chunk_c[stat0 + (int64_t)(i - 1) * p.M] : c_i;
-      // E / R buffers: the previous chunk's products have read them
-      if (j > 0 && !(ok = wait_or_abort(&misc->dv_ready, pp, misc))) break;
-      if (!(ok = wait_or_abort(&misc->tok_full, par, misc))) break;
-      if (!(ok = wait_or_abort(&misc->s_ready, par, misc))) break;
-      tc_fence_after_sync();
-      if (tid == 0) BT_TRACE(0, j, 0);
-      uint32_t ra[32], rb[32];  // the 64 raw scores of this thread
-      tmem_ld32(tl + T1 + tok0, ra);
-      tmem_ld32(tl + T1 + tok0 + 32, rb);
-      tmem_wait_ld();
-      tmem_fence_regs(ra);
-      tmem_fence_regs(rb);
-      // ---- phase 1a: E rows (bf16) and their sums
-      float g16[4] = {0.f, 0.f, 0.f, 0.f};  // sums of the rounded E per 16 tokens
+    if (!__any_sync(0xffffffffu, live)) {
+      // A warp whose 32 latents all lie beyond M (M <= 96, or the ragged last group): its operand rows are zero for
+      // the whole kernel and it only keeps the barrier phases in step with the working warps.
 #pragma unroll
-      for (int ch = 0; ch < 8; ++ch) {
-        float e[8];
+      for (int ch = 0; ch < 4; ++ch) {
+        *reinterpret_cast<uint4*>(e_row + swz_chunk_off(m, ch0 + ch)) = make_uint4(0, 0, 0, 0);
+        *reinterpret_cast<uint4*>(r_row + swz_chunk_off(m, ch0 + ch)) = make_uint4(0, 0, 0, 0);
+      }
 #pragma unroll
-        for (int jj = 0; jj < 8; ++jj) {
-          const int k = ch * 8 + jj;
-          const float s = __uint_as_float(k < 32 ? ra[k] : rb[k - 32]);
-          float x = STABLE ? sigma_fast(s * p.scale, p.power) : ex2_approx(fmaf(s, sc2, -c_i));
-          if (!fast) x = k < lim ? x : 0.f;
-          e[jj] = x;
+      for (int ch = 0; ch < GCOLS / 8; ++ch)
+        *reinterpret_cast<uint4*>(g_dst + swz_chunk_off(m, gch0 + ch)) = make_uint4(0, 0, 0, 0);
+      fence_proxy_async_smem();
+      for (int j = 0; ok && j < nch; ++j) {
+        const uint32_t par = j & 1, pp = (j - 1) & 1;
+        if (j > 0 && !(ok = wait_or_abort(&misc->dv_ready, pp, misc))) break;
+        if (!(ok = wait_or_abort(&misc->s_ready, par, misc))) break;
+        warp_arrive(&misc->er_done, lane);
+        if (!(ok = wait_or_abort(&misc->px_ready, par, misc))) break;
+        warp_arrive(&misc->p_free, lane);
+        warp_arrive(&misc->x_done, lane);
+        if (j + 1 < nch) {
+          if (!(ok = wait_or_abort(&misc->dv_ready, par, misc))) break;
+          warp_arrive(&misc->gc_done, lane);
         }
-        uint4 v;
-        v.x = pack_bf16(e[0], e[1]); v.y = pack_bf16(e[2], e[3]); v.z = pack_bf16(e[4], e[5]); v.w = pack_bf16(e[6], e[7]);
-        g16[ch >> 1] += (bf16_lo(v.x) + bf16_hi(v.x)) + (bf16_lo(v.y) + bf16_hi(v.y)) + (bf16_lo(v.z) + bf16_hi(v.z)) +
-                        (bf16_lo(v.w) + bf16_hi(v.w));
-        *reinterpret_cast<uint4*>(e_row + swz_chunk_off(m, ch)) = v;
       }
-      misc->xch[hf][m] = (g16[0] + g16[1]) + (g16[2] + g16[3]);
-      warp_arrive(&misc->psum[q], lane);
-      if (!(ok = wait_or_abort(&misc->psum[q], par, misc))) break;
-      // denominator before this thread's first token
-      const float base_run = d_i + (hf ? misc->xch[0][m] : 0.f);
-      float dend[4], invg[4];  // block-causal: denominator at the end of the block of each 16-token group
-      if constexpr (BLOCK) {
-        const float p0 = base_run + g16[0], p1 = p0 + g16[1], p2 = p1 + g16[2], p3 = p2 + g16[3];
-        const int bs = p.block;
-        if (bs == 16) { dend[0] = p0; dend[1] = p1; dend[2] = p2; dend[3] = p3; }
-        else if (bs == 32) { dend[0] = dend[1] = p1; dend[2] = dend[3] = p3; }
-        else if (bs == 64) { dend[0] = dend[1] = dend[2] = dend[3] = p3; }
-        else { dend[0] = dend[1] = dend[2] = dend[3] = d_i + (misc->xch[0][m] + misc->xch[1][m]); }
+    } else {
+      // Per-chunk statistics of this thread's latent and per-token statistics of this warp's 32 tokens (lane l keeps
+      // token tok0 + l; the loops broadcast them with shuffles), all fetched one chunk ahead so that the global-memory
+      // latency never sits between two phases.
+      const float* const l2_row = p.tok_l2 + (int64_t)lane_id * p.npad + tok0 + lane;
+      const float* const dl_row = p.tok_delta + (int64_t)lane_id * p.npad + tok0 + lane;
+      float c_cur = (live && !STABLE) ? __ldg(p.chunk_c + stat0 + (int64_t)(nch - 1) * p.M) : 0.f;
+      float d_cur = live ? __ldg(p.chunk_d + stat0 + (int64_t)(nch - 1) * p.M) : 1.f;
+      float c_nxt = (live && !STABLE && nch > 1) ? __ldg(p.chunk_c + stat0 + (int64_t)(nch - 2) * p.M) : c_cur;
+      float l2_cur = __ldg(l2_row + (int64_t)(nch - 1) * C), dl_cur = __ldg(dl_row + (int64_t)(nch - 1) * C);
+
+      for (int j = 0; ok && j < nch; ++j) {
+        const int i = nch - 1 - j, t0 = i * C;
+        const uint32_t par = j & 1, pp = (j - 1) & 1;
+        const int nvalid = min(C, p.N - t0);
+        const int lim = live ? nvalid - tok0 : 0;  // tokens of this thread's quarter that exist (may be <= 0)
+        const bool fast = __all_sync(0xffffffffu, lim >= TOK);
+        const float c_i = c_cur, d_i = d_cur;
+        const float c_prev = i > 0 ? c_nxt : c_i;
+        const float l2_mine = l2_cur, dl_mine = dl_cur;
+        // the next chunk's (i - 1) values, used one iteration from now
+        if (tid == 0) BT_TRACE(3, j, 0);
+        const float d_pre = (live && i > 0) ? ldg_pinned(p.chunk_d + stat0 + (int64_t)(i - 1) * p.M) : 1.f;
+        const float c_pre = (live && !STABLE && i > 1) ? ldg_pinned(p.chunk_c + stat0 + (int64_t)(i - 2) * p.M) : c_nxt;
+        const float l2_pre = i > 0 ? ldg_pinned(l2_row + (int64_t)(i - 1) * C) : 0.f;
+        const float dl_pre = i > 0 ? ldg_pinned(dl_row + (int64_t)(i - 1) * C) : 0.f;
+        // E / R buffers: the previous chunk's products have read them
+        if (j > 0 && !(ok = wait_or_abort(&misc->dv_ready, pp, misc))) break;
+        if (!(ok = wait_or_abort(&misc->s_ready, par, misc))) break;
+        tc_fence_after_sync();
+        if (tid == 0) BT_TRACE(0, j, 0);
+        uint32_t rs[32];  // the 32 raw scores of this thread
+        tmem_ld32(tl + T1 + tok0, rs);
+        tmem_wait_ld();
+        tmem_fence_regs(rs);
+        if (tid == 0) BT_TRACE(3, j, 1);
+        // ---- phase 1a: E rows (bf16) and their sums
+        float g16[2] = {0.f, 0.f};  // sums of the rounded E per 16 tokens
 #pragma unroll
-        for (int g = 0; g < 4; ++g) invg[g] = rcp_approx(dend[g]);
-      }
-      // ---- phase 1b: R = g / D rows (bf16)
-      {
-        float run = base_run;
-#pragma unroll
-        for (int ch = 0; ch < 8; ++ch) {
-          const uint4 ev = *reinterpret_cast<const uint4*>(e_row + swz_chunk_off(m, ch));
-          const float4 la = *reinterpret_cast<const float4*>(&misc->tok_l2[tok0 + ch * 8]);
-          const float4 lb = *reinterpret_cast<const float4*>(&misc->tok_l2[tok0 + ch * 8 + 4]);
-          const float l2[8] = {la.x, la.y, la.z, la.w, lb.x, lb.y, lb.z, lb.w};
-          float r[8];
+        for (int ch = 0; ch < 4; ++ch) {
+          float e[8];
 #pragma unroll
           for (int jj = 0; jj < 8; ++jj) {
             const int k = ch * 8 + jj;
-            const float s = __uint_as_float(k < 32 ? ra[k] : rb[k - 32]);
-            const float g = ex2_approx(fmaf(s, sc2, -l2[jj]));
-            float inv;
-            if constexpr (BLOCK) {
-              inv = invg[ch >> 1];
-            } else {
-              run += unpack8(ev, jj);
-              inv = rcp_approx(run);
-            }
-            float x = g * inv;
+            const float sv = __uint_as_float(rs[k]);
+            float x = STABLE ? sigma_fast(sv * p.scale, p.power) : ex2_approx(fmaf(sv, sc2, -c_i));
             if (!fast) x = k < lim ? x : 0.f;
-            r[jj] = x;
+            e[jj] = x;
           }
-          *reinterpret_cast<uint4*>(r_row + swz_chunk_off(m, ch)) =
-              make_uint4(pack_bf16(r[0], r[1]), pack_bf16(r[2], r[3]), pack_bf16(r[4], r[5]), pack_bf16(r[6], r[7]));
+          uint4 v;
+          v.x = pack_bf16(e[0], e[1]); v.y = pack_bf16(e[2], e[3]); v.z = pack_bf16(e[4], e[5]); v.w = pack_bf16(e[6], e[7]);
+          g16[ch >> 1] += (bf16_lo(v.x) + bf16_hi(v.x)) + (bf16_lo(v.y) + bf16_hi(v.y)) + (bf16_lo(v.z) + bf16_hi(v.z)) +
+                          (bf16_lo(v.w) + bf16_hi(v.w));
+          *reinterpret_cast<uint4*>(e_row + swz_chunk_off(m, ch0 + ch)) = v;
         }
-      }
-      fence_proxy_async_smem();
-      tc_fence_before_sync();
-      warp_arrive(&misc->er_done, lane);
-      if (tid == 0) BT_TRACE(0, j, 1);
-
-      // ---- phase 2a (ascending): p = P / D, rows R p, decode part of dS
-      if (!(ok = wait_or_abort(&misc->px_ready, par, misc))) break;
-      tc_fence_after_sync();
-      if (tid == 0) BT_TRACE(0, j, 2);
-      float dec[64];  // decode-side dS of the 64 tokens (fp32: what does not fit in registers lives in local memory)
-      float rg16[4] = {0.f, 0.f, 0.f, 0.f};  // sums of the rounded R p per 16 tokens
-      {
-        float run = base_run;
+        misc->xch[tq][m] = g16[0] + g16[1];
+        warp_arrive(&misc->psum[q], lane);
+        if (tid == 0) BT_TRACE(3, j, 2);
+        if (!(ok = wait_partner(&misc->psum[q], par, misc))) break;
+        if (tid == 0) BT_TRACE(3, j, 3);
+        // denominator before this thread's first token
+        float base_run = d_i;
 #pragma unroll
-        for (int blk = 0; blk < 2; ++blk) {
-          uint32_t pr[32];
-          tmem_ld32(tl + T0 + tok0 + blk * 32, pr);
-          tmem_wait_ld();
-          tmem_fence_regs(pr);
+        for (int t = 0; t < LW - 1; ++t) base_run += t < tq ? misc->xch[t][m] : 0.f;
+        float dend[2], invg[2];  // block-causal: denominator at the end of the block of each 16-token group
+        if constexpr (BLOCK) {
+          const int bs = p.block;
+          const float p0 = base_run + g16[0], p1 = p0 + g16[1];
+          if (bs == 16) { dend[0] = p0; dend[1] = p1; }
+          else if (bs == 32) { dend[0] = dend[1] = p1; }
+          else {
+            // blocks of 64 or 128 tokens end in a later quarter: add the quarters up to the block's last one
+            const int last = bs == 64 ? (tq | 1) : LW - 1;
+            float tot = p1;
 #pragma unroll
-          for (int c4 = 0; c4 < 4; ++c4) {
-            const int ch = blk * 4 + c4;
-            const uint4 ev = *reinterpret_cast<const uint4*>(e_row + swz_chunk_off(m, ch));
-            const uint4 rv = *reinterpret_cast<const uint4*>(r_row + swz_chunk_off(m, ch));
-            const float4 da = *reinterpret_cast<const float4*>(&misc->tok_delta[tok0 + ch * 8]);
-            const float4 db = *reinterpret_cast<const float4*>(&misc->tok_delta[tok0 + ch * 8 + 4]);
-            const float dl[8] = {da.x, da.y, da.z, da.w, db.x, db.y, db.z, db.w};
-            float rp[8], dd[8];
+            for (int t = 1; t < LW; ++t) tot += (t > tq && t <= last) ? misc->xch[t][m] : 0.f;
+            dend[0] = dend[1] = tot;
+          }
+          invg[0] = rcp_approx(dend[0]);
+          invg[1] = rcp_approx(dend[1]);
+        }
+        // ---- phase 1b: R = g / D rows (bf16)
+        {
+          float run = base_run;
+#pragma unroll
+          for (int ch = 0; ch < 4; ++ch) {
+            const uint4 ev = *reinterpret_cast<const uint4*>(e_row + swz_chunk_off(m, ch0 + ch));
+            float r[8];
 #pragma unroll
             for (int jj = 0; jj < 8; ++jj) {
-              const float pacc = __uint_as_float(pr[c4 * 8 + jj]);
+              const int k = ch * 8 + jj;
+              const float l2 = __shfl_sync(0xffffffffu, l2_mine, k);
+              const float g = ex2_approx(fmaf(__uint_as_float(rs[k]), sc2, -l2));
+              float inv;
+              if constexpr (BLOCK) {
+                inv = invg[ch >> 1];
+              } else {
+                run += unpack8(ev, jj);
+                inv = rcp_approx(run);
+              }
+              float x = g * inv;
+              if (!fast) x = k < lim ? x : 0.f;
+              r[jj] = x;
+            }
+            *reinterpret_cast<uint4*>(r_row + swz_chunk_off(m, ch0 + ch)) =
+                make_uint4(pack_bf16(r[0], r[1]), pack_bf16(r[2], r[3]), pack_bf16(r[4], r[5]), pack_bf16(r[6], r[7]));
+          }
+        }
+        fence_proxy_async_smem();
+        tc_fence_before_sync();
+        warp_arrive(&misc->er_done, lane);
+        if (tid == 0) BT_TRACE(0, j, 1);
+
+        // ---- phase 2a (ascending): p = P / D, R p, decode part of dS - everything stays in registers
+        if (!(ok = wait_or_abort(&misc->px_ready, par, misc))) break;
+        tc_fence_after_sync();
+        if (tid == 0) BT_TRACE(0, j, 2);
+        uint32_t pd[32];   // P accumulators of the 32 tokens, replaced in place by the decode-side dS (fp32)
+        uint32_t rpk[16];  // R p, packed bf16 pairs
+        float rg16[2] = {0.f, 0.f};  // sums of the rounded R p per 16 tokens
+        tmem_ld32(tl + T0 + tok0, pd);
+        tmem_wait_ld();
+        tmem_fence_regs(pd);
+        tc_fence_before_sync();
+        warp_arrive(&misc->p_free, lane);  // T0 may take E^T R
+        {
+          float run = base_run;
+#pragma unroll
+          for (int ch = 0; ch < 4; ++ch) {
+            const uint4 ev = *reinterpret_cast<const uint4*>(e_row + swz_chunk_off(m, ch0 + ch));
+            const uint4 rv = *reinterpret_cast<const uint4*>(r_row + swz_chunk_off(m, ch0 + ch));
+            float rp[8];
+#pragma unroll
+            for (int jj = 0; jj < 8; ++jj) {
+              const int k = ch * 8 + jj;
+              const float pacc = __uint_as_float(pd[k]);
               const float rbv = unpack8(rv, jj);
+              const float dl = __shfl_sync(0xffffffffu, dl_mine, k);
               float dcur, inv;
               if constexpr (BLOCK) {
                 dcur = dend[ch >> 1];
@@ -494,143 +537,167 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
                 inv = rcp_approx(run);
               }
               rp[jj] = rbv * (pacc * inv);
-              dd[jj] = rbv * fmaf(-dcur, dl[jj], pacc);
+              pd[k] = __float_as_uint(rbv * fmaf(-dcur, dl, pacc));
             }
-            uint4 v;
-            v.x = pack_bf16(rp[0], rp[1]); v.y = pack_bf16(rp[2], rp[3]); v.z = pack_bf16(rp[4], rp[5]); v.w = pack_bf16(rp[6], rp[7]);
-            rg16[ch >> 1] += (bf16_lo(v.x) + bf16_hi(v.x)) + (bf16_lo(v.y) + bf16_hi(v.y)) + (bf16_lo(v.z) + bf16_hi(v.z)) +
-                             (bf16_lo(v.w) + bf16_hi(v.w));
-            *reinterpret_cast<uint4*>(rp_row + swz_chunk_off(m, ch)) = v;
 #pragma unroll
-            for (int jj = 0; jj < 8; ++jj) dec[ch * 8 + jj] = dd[jj];
+            for (int jj = 0; jj < 8; jj += 2) {
+              const uint32_t w = pack_bf16(rp[jj], rp[jj + 1]);
+              rpk[ch * 4 + (jj >> 1)] = w;
+              rg16[ch >> 1] += bf16_lo(w) + bf16_hi(w);
+            }
           }
         }
-      }
-      tc_fence_before_sync();
-      warp_arrive(&misc->p_free, lane);  // T0 may take E^T R; the per-token statistics may be replaced
-      if (tid == 0) BT_TRACE(0, j, 3);
-      const float rp_tot = (rg16[0] + rg16[1]) + (rg16[2] + rg16[3]);
-      misc->xch[hf][m] = rp_tot;
-      warp_arrive(&misc->prp[q], lane);
-      if (!(ok = wait_or_abort(&misc->prp[q], par, misc))) break;
-      const float rp_other = misc->xch[hf ^ 1][m];
+        if (tid == 0) BT_TRACE(0, j, 3);
+        const float rp_mine = rg16[0] + rg16[1];
+        misc->xch[tq][m] = rp_mine;
+        warp_arrive(&misc->prp[q], lane);
+        if (!(ok = wait_partner(&misc->prp[q], par, misc))) break;
+        if (tid == 0) BT_TRACE(3, j, 4);
+        float rp_later = 0.f, rp_all = 0.f;  // R p of the quarters after this one, and of the whole chunk
+#pragma unroll
+        for (int t = 0; t < LW; ++t) {
+          const float x = misc->xch[t][m];
+          rp_all += x;
+          rp_later += t > tq ? x : 0.f;
+        }
 
-      // ---- phase 2b: encoder part, dS rows to global memory
-      {
-        float ccg[4];  // block-causal: Cc + sum of R p from the start of the group's block on
-        float cc = cc_carry + (hf == 0 ? rp_other : 0.f);
-        if constexpr (BLOCK) {
-          const int bs = p.block;
-          const float s3 = rg16[3], s2 = s3 + rg16[2], s1 = s2 + rg16[1], s0 = s1 + rg16[0];
-          if (bs == 16) { ccg[0] = cc + s0; ccg[1] = cc + s1; ccg[2] = cc + s2; ccg[3] = cc + s3; }
-          else if (bs == 32) { ccg[0] = ccg[1] = cc + s0; ccg[2] = ccg[3] = cc + s2; }
-          else if (bs == 64) { ccg[0] = ccg[1] = ccg[2] = ccg[3] = cc + s0; }
-          else { ccg[0] = ccg[1] = ccg[2] = ccg[3] = cc_carry + (rp_tot + rp_other); }
-        }
-        uint4* const dst_hi = reinterpret_cast<uint4*>(ds_row + t0 + tok0);
-        uint4* const dst_lo = reinterpret_cast<uint4*>(ds_row + p.ds_plane + t0 + tok0);
+        // ---- phase 2b (descending): encoder part, dS rows to global memory as a hi + lo pair
+        {
+          float ccg[2];  // block-causal: Cc + sum of R p from the start of the group's block on
+          float cc = cc_carry + rp_later;
+          if constexpr (BLOCK) {
+            const int bs = p.block;
+            if (bs == 16) { ccg[1] = cc + rg16[1]; ccg[0] = ccg[1] + rg16[0]; }
+            else if (bs == 32) { ccg[0] = ccg[1] = cc + rp_mine; }
+            else {
+              // the block starts in an earlier (or this) quarter: add the quarters from its first one on
+              const int first = bs == 64 ? (tq & ~1) : 0;
+              float tot = cc + rp_mine;
 #pragma unroll
-        for (int blk = 1; blk >= 0; --blk) {
-          uint32_t xr[32];
-          tmem_ld32(tl + T1 + tok0 + blk * 32, xr);
-          tmem_wait_ld();
-          tmem_fence_regs(xr);
+              for (int t = 0; t < LW - 1; ++t) tot += (t >= first && t < tq) ? misc->xch[t][m] : 0.f;
+              ccg[0] = ccg[1] = tot;
+            }
+          }
+          __nv_bfloat16* const dst = ds_col + (int64_t)(t0 + tok0) * 2 * p.M;
+          const int64_t tstride = 2 * (int64_t)p.M;
 #pragma unroll
-          for (int c4 = 3; c4 >= 0; --c4) {
-            const int ch = blk * 4 + c4;
-            const uint4 ev = *reinterpret_cast<const uint4*>(e_row + swz_chunk_off(m, ch));
-            const uint4 pv = *reinterpret_cast<const uint4*>(rp_row + swz_chunk_off(m, ch));
-            float ds[8];
+          for (int blk = 1; blk >= 0; --blk) {
+            uint32_t xr[16];
+            tmem_ld16(tl + T1 + tok0 + blk * 16, xr);
+            tmem_wait_ld();
+            tmem_fence_regs16(xr);
 #pragma unroll
-            for (int jj = 7; jj >= 0; --jj) {
-              const float x = __uint_as_float(xr[c4 * 8 + jj]);
-              const float eb = unpack8(ev, jj);
-              float csub;
-              if constexpr (BLOCK) {
-                csub = ccg[ch >> 1];
-              } else {
-                cc += unpack8(pv, jj);
-                csub = cc;
+            for (int c2 = 1; c2 >= 0; --c2) {
+              const int ch = blk * 2 + c2;
+              const uint4 ev = *reinterpret_cast<const uint4*>(e_row + swz_chunk_off(m, ch0 + ch));
+              float ds[8];
+#pragma unroll
+              for (int jj = 7; jj >= 0; --jj) {
+                const int k = ch * 8 + jj;
+                const float x = __uint_as_float(xr[c2 * 8 + jj]);
+                const float eb = unpack8(ev, jj);
+                float csub;
+                if constexpr (BLOCK) {
+                  csub = ccg[ch >> 1];
+                } else {
+                  const uint32_t w = rpk[k >> 1];
+                  cc += (k & 1) ? bf16_hi(w) : bf16_lo(w);
+                  csub = cc;
+                }
+                float enc = eb * (x - csub);
+                if constexpr (STABLE) enc *= slope_from_sigma(eb, p.power);
+                ds[jj] = __uint_as_float(pd[k]) + ((STABLE && eb == 0.f) ? 0.f : enc);
               }
-              float enc = eb * (x - csub);
-              if constexpr (STABLE) enc *= slope_from_sigma(eb, p.power);
-              ds[jj] = dec[ch * 8 + jj] + ((STABLE && eb == 0.f) ? 0.f : enc);
-            }
-            // dS = hi + lo, two bf16 values: the dK / dQ products then see it with 16 mantissa bits
-            uint4 hi, lo;
-            hi.x = pack_bf16(ds[0], ds[1]); hi.y = pack_bf16(ds[2], ds[3]); hi.z = pack_bf16(ds[4], ds[5]); hi.w = pack_bf16(ds[6], ds[7]);
-            lo.x = pack_bf16(ds[0] - bf16_lo(hi.x), ds[1] - bf16_hi(hi.x));
-            lo.y = pack_bf16(ds[2] - bf16_lo(hi.y), ds[3] - bf16_hi(hi.y));
-            lo.z = pack_bf16(ds[4] - bf16_lo(hi.z), ds[5] - bf16_hi(hi.z));
-            lo.w = pack_bf16(ds[6] - bf16_lo(hi.w), ds[7] - bf16_hi(hi.w));
-            if (live) {
-              dst_hi[ch] = hi;
-              dst_lo[ch] = lo;
+              // dS = hi + lo, two bf16 values: the dK / dQ products then see it with 16 mantissa bits
+              if (live) {
+#pragma unroll
+                for (int jj = 0; jj < 8; ++jj) {
+                  const __nv_bfloat16 hi = __float2bfloat16_rn(ds[jj]);
+                  const __nv_bfloat16 lo = __float2bfloat16_rn(ds[jj] - __bfloat162float(hi));
+                  __nv_bfloat16* d = dst + (int64_t)(ch * 8 + jj) * tstride;
+                  d[0] = hi;
+                  d[p.M] = lo;
+                }
+              }
             }
           }
         }
-      }
-      fence_proxy_async_smem();  // the rows R p were read with generic loads; the next write of the buffer is a TMA copy
-      tc_fence_before_sync();
-      warp_arrive(&misc->x_done, lane);
-      if (tid == 0) BT_TRACE(0, j, 4);
-      // carries into the previous chunk's frame
-      const float phi = STABLE ? 1.0f : ex2_approx(c_prev - c_i);
-      cc_carry = (cc_carry + (rp_tot + rp_other)) * phi;
-      if (!(fabsf(cc_carry) < INFINITY)) {
-        // an overflow or 0 / 0 upstream (score spreads beyond what these frames hold) has reached the carries: the
-        // results of this call are invalid; the exact kernels standing by behind this pass redo it
-        atomicOr(p.err, 2);
-        if (p.gate != nullptr) p.gate[0] = 1;
-      }
-      if (i > 0) {
-        // G has taken this chunk's R dY: rescale it in tensor memory and pack it as bf16.  The shared-memory copy is
-        // still read by this chunk's dV product, so the packed rows wait in registers until that product has run.
-        if (!(ok = wait_or_abort(&misc->g_ready, par, misc))) break;
-        tc_fence_after_sync();
-        if (tid == 0) BT_TRACE(0, j, 5);
-        const bool need = __any_sync(0xffffffffu, phi != 1.0f);
-        uint4 gv[DVB * 4];
-#pragma unroll
-        for (int b32 = 0; b32 < DVB; ++b32) {
-          const int col = hf * (DVB * 32) + b32 * 32;  // first value column of this batch
-          uint32_t r[32];
-          tmem_ld32(tl + TG + col, r);
-          tmem_wait_ld();
-          tmem_fence_regs(r);
-          if (need) {
-#pragma unroll
-            for (int k = 0; k < 32; ++k) r[k] = __float_as_uint(__uint_as_float(r[k]) * phi);
-            tmem_st32(tl + TG + col, r);
-          }
-#pragma unroll
-          for (int ch = 0; ch < 4; ++ch) {
-            gv[b32 * 4 + ch].x = pack_bf16(__uint_as_float(r[ch * 8 + 0]), __uint_as_float(r[ch * 8 + 1]));
-            gv[b32 * 4 + ch].y = pack_bf16(__uint_as_float(r[ch * 8 + 2]), __uint_as_float(r[ch * 8 + 3]));
-            gv[b32 * 4 + ch].z = pack_bf16(__uint_as_float(r[ch * 8 + 4]), __uint_as_float(r[ch * 8 + 5]));
-            gv[b32 * 4 + ch].w = pack_bf16(__uint_as_float(r[ch * 8 + 6]), __uint_as_float(r[ch * 8 + 7]));
-          }
-        }
-        if (need) tmem_wait_st();
-        if (!(ok = wait_or_abort(&misc->dv_ready, par, misc))) break;
-        if (tid == 0) BT_TRACE(0, j, 6);
-#pragma unroll
-        for (int b32 = 0; b32 < DVB; ++b32) {
-          const int col = hf * (DVB * 32) + b32 * 32;
-          uint8_t* g_blk = smem + L::OFF_GC + (col >> 6) * 16384;
-#pragma unroll
-          for (int ch = 0; ch < 4; ++ch)
-            *reinterpret_cast<uint4*>(g_blk + swz_chunk_off(m, ((col & 63) >> 3) + ch)) = gv[b32 * 4 + ch];
-        }
-        fence_proxy_async_smem();
+        if (tid == 0) BT_TRACE(3, j, 5);
         tc_fence_before_sync();
-        warp_arrive(&misc->gc_done, lane);
-        if (tid == 0) BT_TRACE(0, j, 7);
+        warp_arrive(&misc->x_done, lane);
+        if (tid == 0) BT_TRACE(0, j, 4);
+        // carries into the previous chunk's frame
+        const float phi = STABLE ? 1.0f : ex2_approx(c_prev - c_i);
+        cc_carry = (cc_carry + rp_all) * phi;
+        if (!(fabsf(cc_carry) < INFINITY)) {
+          // an overflow or 0 / 0 upstream (score spreads beyond what these frames hold) has reached the carries: the
+          // results of this call are invalid; the exact kernels standing by behind this pass redo it
+          atomicOr(p.err, 2);
+          if (p.gate != nullptr) p.gate[0] = 1;
+        }
+        if (i > 0) {
+          // G has taken this chunk's R dY: rescale this warp's value columns in tensor memory and pack them as bf16.
+          // The shared-memory copy is still read by this chunk's dV product, so the packed rows wait in registers
+          // until that product has run.
+          if (!(ok = wait_or_abort(&misc->g_ready, par, misc))) break;
+          tc_fence_after_sync();
+          if (tid == 0) BT_TRACE(0, j, 5);
+          const bool need = __any_sync(0xffffffffu, phi != 1.0f);
+          uint4 gv[GCOLS / 8];
+          if constexpr (DVB == 2) {
+            uint32_t r[32];
+            tmem_ld32(tl + TG + gcol, r);
+            tmem_wait_ld();
+            tmem_fence_regs(r);
+            if (need) {
+#pragma unroll
+              for (int k = 0; k < 32; ++k) r[k] = __float_as_uint(__uint_as_float(r[k]) * phi);
+              tmem_st32(tl + TG + gcol, r);
+            }
+#pragma unroll
+            for (int ch = 0; ch < 4; ++ch)
+              gv[ch] = make_uint4(pack_bf16(__uint_as_float(r[ch * 8 + 0]), __uint_as_float(r[ch * 8 + 1])),
+                                  pack_bf16(__uint_as_float(r[ch * 8 + 2]), __uint_as_float(r[ch * 8 + 3])),
+                                  pack_bf16(__uint_as_float(r[ch * 8 + 4]), __uint_as_float(r[ch * 8 + 5])),
+                                  pack_bf16(__uint_as_float(r[ch * 8 + 6]), __uint_as_float(r[ch * 8 + 7])));
+          } else {
+            uint32_t r[16];
+            tmem_ld16(tl + TG + gcol, r);
+            tmem_wait_ld();
+            tmem_fence_regs16(r);
+            if (need) {
+#pragma unroll
+              for (int k = 0; k < 16; ++k) r[k] = __float_as_uint(__uint_as_float(r[k]) * phi);
+              tmem_st16(tl + TG + gcol, r);
+            }
+#pragma unroll
+            for (int ch = 0; ch < 2; ++ch)
+              gv[ch] = make_uint4(pack_bf16(__uint_as_float(r[ch * 8 + 0]), __uint_as_float(r[ch * 8 + 1])),
+                                  pack_bf16(__uint_as_float(r[ch * 8 + 2]), __uint_as_float(r[ch * 8 + 3])),
+                                  pack_bf16(__uint_as_float(r[ch * 8 + 4]), __uint_as_float(r[ch * 8 + 5])),
+                                  pack_bf16(__uint_as_float(r[ch * 8 + 6]), __uint_as_float(r[ch * 8 + 7])));
+          }
+          if (need) tmem_wait_st();
+          if (tid == 0) BT_TRACE(3, j, 6);
+          if (!(ok = wait_or_abort(&misc->dv_ready, par, misc))) break;
+          if (tid == 0) BT_TRACE(0, j, 6);
+#pragma unroll
+          for (int ch = 0; ch < GCOLS / 8; ++ch) *reinterpret_cast<uint4*>(g_dst + swz_chunk_off(m, gch0 + ch)) = gv[ch];
+          fence_proxy_async_smem();
+          tc_fence_before_sync();
+          warp_arrive(&misc->gc_done, lane);
+          if (tid == 0) BT_TRACE(0, j, 7);
+        }
+        c_cur = c_prev;
+        d_cur = d_pre;
+        c_nxt = c_pre;
+        l2_cur = l2_pre;
+        dl_cur = dl_pre;
       }
-    }
+    }  // working warp
   } else {
     // ============================ token group: thread = token of the chunk = TMEM lane ============================
-    const int wq = warp - 8;
+    const int wq = warp - W_TOKEN;
     const uint32_t tl = tmem + ((uint32_t)(wq * 32) << 16);
     const int tt = wq * 32 + lane;
     const int lo = BLOCK ? (tt & ~(p.block - 1)) : tt;  // first column (token) this row keeps
@@ -648,7 +715,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
       // masked A (bf16) into the K tile's buffer
       if (!(ok = wait_or_abort(&misc->a_ready, par, misc))) break;
       tc_fence_after_sync();
-      if (tid == 256) BT_TRACE(1, j, 0);
+      if (tid == W_TOKEN * 32) BT_TRACE(1, j, 0);
 #pragma unroll 1
       for (int jb = 0; jb < 4; ++jb) {
         uint32_t wp[16];
@@ -679,11 +746,11 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
       fence_proxy_async_smem();
       tc_fence_before_sync();
       warp_arrive(&misc->am_done, lane);
-      if (tid == 256) BT_TRACE(1, j, 1);
+      if (tid == W_TOKEN * 32) BT_TRACE(1, j, 1);
       // masked E^T R (bf16) into tensor memory
       if (!(ok = wait_or_abort(&misc->wt_ready, par, misc))) break;
       tc_fence_after_sync();
-      if (tid == 256) BT_TRACE(1, j, 2);
+      if (tid == W_TOKEN * 32) BT_TRACE(1, j, 2);
 #pragma unroll 1
       for (int jb = 0; jb < 4; ++jb) {
         uint32_t wp[16];
@@ -710,11 +777,11 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
       tmem_wait_st();
       tc_fence_before_sync();
       warp_arrive(&misc->wm_done, lane);
-      if (tid == 256) BT_TRACE(1, j, 3);
+      if (tid == W_TOKEN * 32) BT_TRACE(1, j, 3);
       // dV rows
       if (!(ok = wait_or_abort(&misc->dv_ready, par, misc))) break;
       tc_fence_after_sync();
-      if (tid == 256) BT_TRACE(1, j, 4);
+      if (tid == W_TOKEN * 32) BT_TRACE(1, j, 4);
 #pragma unroll
       for (int half = 0; half < DV / 32; ++half) {
         uint32_t r[32];
@@ -736,7 +803,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
       }
       tc_fence_before_sync();
       warp_arrive(&misc->dv_free, lane);
-      if (tid == 256) BT_TRACE(1, j, 5);
+      if (tid == W_TOKEN * 32) BT_TRACE(1, j, 5);
     }
   }
   if (!ok) {
@@ -745,7 +812,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
   }
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 12) tmem_dealloc(tmem, TM_COLS);
+  if (warp == W_MMA) tmem_dealloc(tmem, TM_COLS);
 }
 
 namespace {
@@ -853,7 +920,7 @@ constexpr int GRAD_MAXG = 4;
 
 template <int DKB>
 struct GL {
-  static constexpr int OFF_DS = 0;                         // 2 stages x [2 t-blocks][128 m][64 t]
+  static constexpr int OFF_DS = 0;                         // 2 stages x [2 m-blocks][128 t][64 m]
   static constexpr int OFF_K = 65536;                      // 2 stages x [DKB][128 t][64]
   static constexpr int OFF_Q = OFF_K + 2 * DKB * 16384;    // groups x [DKB][128 m][64]
   static constexpr int off_misc(int groups) { return OFF_Q + groups * DKB * 16384; }
@@ -908,7 +975,7 @@ bwd_tc_grads_kernel(const __grid_constant__ CUtensorMap tm_ds, const __grid_cons
   tc_fence_after_sync();
   const uint32_t tmem = misc->tmem_base;
   bool ok = true;
-  auto wait = [&](uint64_t* bar, uint32_t parity) { return tc::wait_or_abort(bar, parity, &misc->abort_flag); };
+  auto wait = [&](uint64_t* bar, uint32_t parity) { return tc::wait_or_abort(bar, parity, &misc->abort_flag, 1); };
 
   if (warp == 0) {
     if (lane == 0) {
@@ -931,16 +998,16 @@ bwd_tc_grads_kernel(const __grid_constant__ CUtensorMap tm_ds, const __grid_cons
           const int s = it & 1;
           if (it >= 2 && !(ok = wait(&misc->ds_empty[s], ((it - 2) >> 1) & 1))) break;
           mbar_arrive_expect_tx(&misc->ds_full[s], 32768);
-          for (int tb = 0; tb < 2; ++tb)
-            tma_load_3d(smem + L::OFF_DS + s * 32768 + tb * 16384, &tm_ds, &misc->ds_full[s], t0 + tb * 64, g * 128,
-                        part * (int)gridDim.x + lane_id);
+          for (int mb = 0; mb < 2; ++mb)
+            tma_load_4d(smem + L::OFF_DS + s * 32768 + mb * 16384, &tm_ds, &misc->ds_full[s], g * 128 + mb * 64, part, t0,
+                        lane_id);
         }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t ID_DK = make_idesc_bf16(128, DK, 1, 1);  // dS (MN-major: rows m, tokens contiguous) x Q (MN-major)
-      constexpr uint32_t ID_DQ = make_idesc_bf16(128, DK, 0, 1);  // dS (K-major) x K tile (MN-major)
+      constexpr uint32_t ID_DK = make_idesc_bf16(128, DK, 0, 1);  // dS (K-major: rows = tokens, latents contiguous) x Q (MN-major)
+      constexpr uint32_t ID_DQ = make_idesc_bf16(128, DK, 1, 1);  // dS (MN-major) x K tile (MN-major)
       ok = wait(&misc->q_full, 0);
       int it = 0;
       for (int cc = 0; ok && cc < ncs; ++cc) {
@@ -959,11 +1026,11 @@ bwd_tc_grads_kernel(const __grid_constant__ CUtensorMap tm_ds, const __grid_cons
           const uint64_t d_q_mn = make_desc_sw128(smem_u32(smem + L::OFF_Q + g * DKB * 16384), 16384, 1024);
           const int rows = min(128, p.M - g * 128);
           const int ksm = (rows + 15) >> 4;
-          for (int st = 0; st < ksm; ++st)
-            mma_ss(tmem + L::TM_DK + kb * DK, mnmaj_step(d_ds_mn, st), mnmaj_step(d_q_mn, st), ID_DK, (gp > 0 || st > 0) ? 1u : 0u);
+          for (int st = 0; st < ksm; ++st)  // contraction over the latents of the group
+            mma_ss(tmem + L::TM_DK + kb * DK, kmaj_step(d_ds_k, st), mnmaj_step(d_q_mn, st), ID_DK, (gp > 0 || st > 0) ? 1u : 0u);
 #pragma unroll
-          for (int st = 0; st < 8; ++st)
-            mma_ss(tmem + L::TM_DQ + g * DK, kmaj_step(d_ds_k, st), mnmaj_step(d_k_mn, st), ID_DQ,
+          for (int st = 0; st < 8; ++st)  // contraction over the tokens of the chunk
+            mma_ss(tmem + L::TM_DQ + g * DK, mnmaj_step(d_ds_mn, st), mnmaj_step(d_k_mn, st), ID_DQ,
                    (cc > 0 || (gp & 1) || st > 0) ? 1u : 0u);
           tc_commit(&misc->ds_empty[s]);
         }
@@ -1103,7 +1170,7 @@ TcBwdPlan plan_tc(const flare_bwd_args_t& a) {
   pl.off_cu = saved ? 0 : take((size_t)lanes * pl.nch * f.M * f.Dv * 2);
   pl.off_cc = saved ? 0 : take((size_t)lanes * pl.nch * f.M * 4);
   pl.off_cd = saved ? 0 : take((size_t)lanes * pl.nch * f.M * 4);
-  pl.off_ds = take((size_t)2 * lanes * f.M * pl.npad * 2);  // hi and lo planes
+  pl.off_ds = take((size_t)2 * lanes * f.M * pl.npad * 2);  // a hi and a lo row per token
   pl.off_dqp = take((size_t)f.B * pl.nsplit * f.H * f.M * f.Dk * 4);
   pl.off_dvp = pl.groups > 1 ? take((size_t)pl.groups * f.B * f.N * f.H * f.Dv * 2) : 0;
   pl.total = off;
@@ -1248,15 +1315,15 @@ int bwd_tc(const flare_bwd_args_t& a, cudaStream_t stream) {
     const uint64_t dimu[4] = {(uint64_t)f.Dv, (uint64_t)f.M, (uint64_t)pl.nch, (uint64_t)lanes};
     const int64_t stru[3] = {f.Dv, (int64_t)f.M * f.Dv, (int64_t)pl.nch * f.M * f.Dv};
     const uint32_t boxu[4] = {64, 128, 1, 1};
-    const uint64_t dims[3] = {(uint64_t)pl.npad, (uint64_t)f.M, (uint64_t)(2 * lanes)};
-    const int64_t strs[2] = {pl.npad, (int64_t)f.M * pl.npad};
-    const uint32_t boxs[3] = {64, 128, 1};
+    const uint64_t dims[4] = {(uint64_t)f.M, 2, (uint64_t)pl.npad, (uint64_t)lanes};
+    const int64_t strs[3] = {f.M, 2 * (int64_t)f.M, 2 * (int64_t)f.M * pl.npad};
+    const uint32_t boxs[4] = {64, 1, 128, 1};
     const uint64_t dimq[3] = {(uint64_t)f.Dk, (uint64_t)f.M, (uint64_t)f.H};
     const int64_t strq[2] = {f.q_stride_m, f.q_stride_h};
     const uint32_t boxq[3] = {64, 128, 1};
     if (!tc::make_map_bf16(&tk, f.k, 4, dimk, strk, box) || !tc::make_map_bf16(&tv, f.v, 4, dimv, strv, box) ||
         !tc::make_map_bf16(&tdy, a.dy, 4, dimv, strd, box) || !tc::make_map_bf16(&tu, keep.u, 4, dimu, stru, boxu) ||
-        !tc::make_map_bf16(&tds, ws + pl.off_ds, 3, dims, strs, boxs) || !tc::make_map_bf16(&tq, f.q, 3, dimq, strq, boxq)) {
+        !tc::make_map_bf16(&tds, ws + pl.off_ds, 4, dims, strs, boxs) || !tc::make_map_bf16(&tq, f.q, 3, dimq, strq, boxq)) {
       set_cuda_error(cudaErrorInvalidValue, "cuTensorMapEncodeTiled (backward operands)");
       return FLARE_ERR_CUDA;
     }
@@ -1269,7 +1336,6 @@ int bwd_tc(const flare_bwd_args_t& a, cudaStream_t stream) {
     p.scale = f.scale; p.power = f.power;
     p.chunk_c = keep.c; p.chunk_d = keep.d; p.tok_l2 = tok_l2; p.tok_delta = tok_delta;
     p.ds = ws + pl.off_ds;
-    p.ds_plane = lanes * f.M * pl.npad;
     p.groups = pl.groups;
     p.dv = pl.groups > 1 ? static_cast<void*>(ws + pl.off_dvp) : a.dv;
     p.err = err;

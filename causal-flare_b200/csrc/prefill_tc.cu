@@ -36,6 +36,11 @@
 #include "sm100_ptx.cuh"
 #include "tc_device.cuh"
 
+// polling rounds of every wait of the prefill kernel before it suspends (see tc::wait_or_abort)
+#ifndef FLARE_TC_FWD_POLLS
+#define FLARE_TC_FWD_POLLS 24
+#endif
+
 namespace flare {
 
 using namespace sm100;
@@ -98,7 +103,7 @@ using tc::sigma_fast;
 
 // bounded wait that also gives up as soon as another role of the CTA has given up
 __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, Misc* misc) {
-  return tc::wait_or_abort(bar, parity, &misc->abort_flag);
+  return tc::wait_or_abort(bar, parity, &misc->abort_flag, FLARE_TC_FWD_POLLS);
 }
 
 // grid.z = latent group * DKB + value slice.  First value column of this CTA's slice (a compile-time zero when there
@@ -132,7 +137,9 @@ int launch_prefill_tc_unit(bool padded, int mode, const CUtensorMap& tq, const C
 //        (E = sigma(s), D = plain running sum, the state is never rescaled); the decode weights stay a softmax over
 //        the latents, whose numerator exp2(s - c) a_m is formed with the same running-max machinery as before.
 // DVB = Dv / 64 = number of value slices (grid.z); Dv may differ from Dk (Dk = 64 with Dv = 128)
-template <bool PADDED, int DKB, int DVB, bool SPLIT, int MODE>
+// KEEP: training forward that leaves the per-chunk prefix states for the backward pass (a separate instance: the
+//       extra live values cost the register-capped latent group about 5 % when the code is merely present)
+template <bool PADDED, int DKB, int DVB, bool SPLIT, int MODE, bool KEEP>
 __global__ void __launch_bounds__(NTHREADS, 1)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                   const __grid_constant__ CUtensorMap tm_v, const TcParams p) {
@@ -661,7 +668,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             v.w = pack_bf16(__uint_as_float(r[ch * 8 + 6]), __uint_as_float(r[ch * 8 + 7]));
             *reinterpret_cast<uint4*>(smem + OFF_U + swz_chunk_off(m, hf * 4 + ch)) = v;
           }
-          if (p.dump_u != nullptr) {
+          if constexpr (KEEP) {
             // Training: the state before this chunk is kept for the backward pass, in the EXACT running-max frame
             // through this chunk (= the frame the next chunk will use), so that the backward's encoder weights of
             // the chunk never exceed 1.  Both halves' maxima of this chunk are published once its psum phase completed.
@@ -859,14 +866,21 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 
 namespace {
 
-template <bool PADDED, int DKB, int DVB, bool SPLIT, int MODE>
-int launch_instance(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const TcParams& p, dim3 grid,
-                    cudaStream_t stream) {
-  auto kern = prefill_tc_kernel<PADDED, DKB, DVB, SPLIT, MODE>;
+template <bool PADDED, int DKB, int DVB, bool SPLIT, int MODE, bool KEEP>
+int launch_keep(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const TcParams& p, dim3 grid,
+                cudaStream_t stream) {
+  auto kern = prefill_tc_kernel<PADDED, DKB, DVB, SPLIT, MODE, KEEP>;
   FLARE_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Lay<DKB>::SMEM_BYTES));
   kern<<<grid, NTHREADS, Lay<DKB>::SMEM_BYTES, stream>>>(tq, tk, tv, p);
   FLARE_CUDA_CHECK(cudaGetLastError());
   return FLARE_OK;
+}
+
+template <bool PADDED, int DKB, int DVB, bool SPLIT, int MODE>
+int launch_instance(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const TcParams& p, dim3 grid,
+                    cudaStream_t stream) {
+  return p.dump_u != nullptr ? launch_keep<PADDED, DKB, DVB, SPLIT, MODE, true>(tq, tk, tv, p, grid, stream)
+                             : launch_keep<PADDED, DKB, DVB, SPLIT, MODE, false>(tq, tk, tv, p, grid, stream);
 }
 
 }  // namespace

@@ -220,6 +220,14 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
       : "memory");
 }
 
+// Read-only global load that the compiler may not move: issued exactly where it is written, so a value needed one
+// loop iteration later is in flight during the whole iteration (a plain load gets sunk to its first use).
+__device__ __forceinline__ float ldg_pinned(const float* p) {
+  float x;
+  asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(x) : "l"(p));
+  return x;
+}
+
 // three-input maximum (one instruction on sm_100)
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
   float r;

@@ -21,17 +21,24 @@ __device__ __forceinline__ void warp_arrive(uint64_t* bar, int lane) {
   if (lane == 0) mbar_arrive(bar);
 }
 
-// bounded wait that also gives up as soon as another role of the CTA has given up (`abort_flag` set)
-__device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-  // short waits (partner warp a few hundred cycles behind) are polled; longer ones suspend in hardware
+// Bounded wait that also gives up as soon as another role of the CTA has given up (`abort_flag` set).  The wait
+// suspends in hardware in slices of at most kWaitSliceNs and wakes on completion.  The bound is a count of slices (kWaitSlices x kWaitSliceNs = 2 s when every slice runs its
+// full length) rather than a wall-clock reading: reading %globaltimer on this path cost about a microsecond per wait.
+constexpr uint32_t kWaitSliceNs = 20000u;
+constexpr uint32_t kWaitSlices = 100000u;
+// `polls`: how many cheap test-and-branch rounds come before the first suspension.  Every round is a handful of
+// instructions issued on the waiting warp's scheduler, where they compete with the working warps: use a few dozen only
+// where the partner is known to be at most a few hundred cycles behind, 1-2 where the wait is expected to be long.
+__device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int polls) {
 #pragma unroll 1
-  for (int spin = 0; spin < 24; ++spin)
+  for (int spin = 0; spin < polls; ++spin)
     if (mbar_test_wait(bar, parity)) return true;
-  const uint64_t t0 = global_timer_ns();
-  while (true) {
-    if (mbar_try_wait(bar, parity, 50000u)) return true;  // sleeps in hardware, wakes on completion
-    if (*abort_flag != 0 || global_timer_ns() - t0 > kWaitLimitNs) return false;
+#pragma unroll 1
+  for (uint32_t slice = 0; slice < kWaitSlices; ++slice) {
+    if (mbar_try_wait(bar, parity, kWaitSliceNs)) return true;  // sleeps in hardware, wakes on completion
+    if (*abort_flag != 0) return false;
   }
+  return false;
 }
 
 // stablemax encoder weight with approximate reciprocal; powers 1..4 by multiplication
