@@ -522,6 +522,37 @@ def cpu_reference_sample(threads=None):
                        f"({', '.join(f'{k_}: {v_:.1f} s' for k_, v_ in times.items())})")
 
 
+def gpu_reference_leg():
+    """The reference's own GPU (Triton) kernels on this box, when its package can be imported from the directory named
+    by FLARE_REFERENCE_PATH: C2 forward under the same events.  Baseline only; nothing in the product imports it.  The
+    reference checkout does not travel to the benchmark box and its sources are not part of this repository, so the
+    usual answer is `unavailable`."""
+    path = os.environ.get("FLARE_REFERENCE_PATH", "")
+    if not path or not os.path.isdir(path):
+        return {"unavailable": "the reference package is not present on this box (set FLARE_REFERENCE_PATH to a checkout)"}
+    import subprocess as sp
+
+    code = (
+        "import sys, json, torch; sys.path.insert(0, sys.argv[1]); import causal_flare as ref;"
+        "g = torch.Generator(device='cuda').manual_seed(1234);"
+        "q = torch.randn(16, 128, 64, generator=g, device='cuda').bfloat16();"
+        "k = torch.randn(8, 8192, 16, 64, generator=g, device='cuda').bfloat16();"
+        "v = torch.randn(8, 8192, 16, 64, generator=g, device='cuda').bfloat16();"
+        "f = lambda: ref.flare_autoregressive_triton(q, k, v);"
+        "[f() for _ in range(3)]; torch.cuda.synchronize();"
+        "a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True);"
+        "a.record(); [f() for _ in range(10)]; b.record(); torch.cuda.synchronize();"
+        "print(json.dumps({'C2_forward_ms': a.elapsed_time(b) / 10}))"
+    )
+    try:  # a separate interpreter: the reference package has the same import name as this one
+        out = sp.run([sys.executable, "-c", code, path], capture_output=True, text=True, timeout=600)
+        if out.returncode != 0:
+            return {"unavailable": (out.stderr.strip().splitlines() or ["failed"])[-1][:300]}
+        return json.loads(out.stdout.strip().splitlines()[-1])
+    except Exception as exc:  # noqa: BLE001
+        return {"unavailable": f"{type(exc).__name__}: {exc}"[:300]}
+
+
 def config_block(world):
     c = C2
     return {"workload": f"C2 chunked causal prefill forward B={c['B']} N={c['N']} H={c['H']} M={c['M']} D={c['Dk']} "
@@ -616,6 +647,7 @@ def main():
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config_block(world),
             "roofline": pre["roofline"], "cpu_baseline": cpu, "e2e": pre["e2e"], "gpu_launches": pre["gpu_launches"],
             "clocks": pre["clocks"], "decode": dec, "other_shapes": other, "strong": strong, "seqpar": seqpar,
+            "gpu_reference": gpu_reference_leg() if (world == 1 and args.only == "all" and not args.skip_other) else None,
         }
         print(json.dumps(line))
     if world > 1:

@@ -52,16 +52,36 @@ def _check_finite(name: str, tensor: torch.Tensor) -> None:
 
 
 def _timed(device, timings, name, fn):
-    """Run fn(); when ``timings`` is a dict, bracket it with CUDA events and record milliseconds."""
+    """Run fn(); when ``timings`` is a dict, record one entry per kernel launch (milliseconds of device time, summed
+    over repeated launches of the same kernel) and, under ``name + " (launch gaps, memsets)"``, what the CUDA events
+    around the whole call measured beyond the kernels, so that the entries add up to the call's device time."""
     if timings is None:
         return fn()
+    import ctypes as C
+
+    from . import _lib
+
+    lib = _lib.load()
     start = torch.cuda.Event(enable_timing=True)
     end = torch.cuda.Event(enable_timing=True)
+    lib.flare_profile_enable(1)
     start.record(torch.cuda.current_stream(device))
-    out = fn()
+    try:
+        out = fn()
+    finally:
+        lib.flare_profile_enable(0)
     end.record(torch.cuda.current_stream(device))
     end.synchronize()
-    timings[name] = timings.get(name, 0.0) + start.elapsed_time(end)
+    total = start.elapsed_time(end)
+    kernels = 0.0
+    kname, ms = C.c_char_p(), C.c_float()
+    for i in range(lib.flare_profile_count()):
+        if lib.flare_profile_entry(i, C.byref(kname), C.byref(ms)) == 0:
+            key = kname.value.decode()
+            timings[key] = timings.get(key, 0.0) + ms.value
+            kernels += ms.value
+    rest = name + " (launch gaps, memsets)"
+    timings[rest] = timings.get(rest, 0.0) + max(0.0, total - kernels)
     return out
 
 

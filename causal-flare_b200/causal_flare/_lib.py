@@ -80,6 +80,7 @@ EXPORTS = (
     "flare_abi_version", "flare_abi_sizeof", "flare_set_kernel_events", "flare_last_launch_count",
     "flare_forward_uses_tensor_path", "flare_backward_uses_tensor_path", "flare_device_status", "flare_set_trace_buffer",
     "flare_forward_noalloc", "flare_noalloc_scratch_capacity",
+    "flare_profile_enable", "flare_profile_count", "flare_profile_entry",
 )
 
 _lib = None
@@ -126,6 +127,11 @@ def load() -> C.CDLL:
     lib.flare_forward_noalloc.restype = C.c_int
     lib.flare_forward_noalloc.argtypes = [C.POINTER(FwdArgs), C.c_void_p]
     lib.flare_noalloc_scratch_capacity.restype = C.c_size_t
+    lib.flare_profile_enable.restype = None
+    lib.flare_profile_enable.argtypes = [C.c_int]
+    lib.flare_profile_count.restype = C.c_int
+    lib.flare_profile_entry.restype = C.c_int
+    lib.flare_profile_entry.argtypes = [C.c_int, C.POINTER(C.c_char_p), C.POINTER(C.c_float)]
     lib.flare_set_trace_buffer.restype = None
     lib.flare_set_trace_buffer.argtypes = [C.c_void_p]
     lib.flare_device_status.argtypes = [C.c_int]

@@ -934,10 +934,12 @@ static int launch_bwd_one(const BwdParams& p, dim3 grid, size_t smem1, size_t sm
   if (stage == 0) {
     auto k1 = bwd_replay_kernel<MM_MAX, DD>;
     FLARE_CUDA_CHECK(cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem1));
+    LaunchTimer timer("bwd_replay_kernel", stream);
     k1<<<grid, NT, smem1, stream>>>(p);
   } else {
     auto k2 = bwd_reverse_kernel<MM_MAX, DD>;
     FLARE_CUDA_CHECK(cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2));
+    LaunchTimer timer("bwd_reverse_kernel", stream);
     k2<<<grid, NT, smem2, stream>>>(p);
   }
   FLARE_CUDA_CHECK(cudaGetLastError());
@@ -1170,6 +1172,7 @@ int bwd_exact(const flare_bwd_args_t& a, cudaStream_t stream, const int* gate) {
   };
   const int64_t nscan = lanes * f.M * (f.Dv + 1);
   auto scan = [&](bool write_slots, bool with_carry, bool summary) -> int {
+    LaunchTimer timer("bwd_seg_scan_kernel", stream);
     bwd_seg_scan_kernel<<<(unsigned)((nscan + 255) / 256), 256, 0, stream>>>(
         p.seg_b, p.seg_c, p.seg_gam, pl.nseg, pl.seg_len, lanes, f.N, f.M, f.Dv, p.E, p.RHO, f.block_size,
         with_carry ? a.carry_b : nullptr, with_carry ? a.carry_c : nullptr, with_carry ? a.carry_rho : nullptr,
@@ -1191,6 +1194,7 @@ int bwd_exact(const flare_bwd_args_t& a, cudaStream_t stream, const int* gate) {
       // carries of every segment for a zero carry-in, as products over the planes
       const int mt = (f.M + LM - 1) / LM;
       dim3 g((unsigned)(lanes * mt), pl.nseg, (f.Dv + LDK - 1) / LDK);
+      LaunchTimer timer("bwd_seg_carry_kernel", stream);
       bwd_seg_carry_kernel<<<g, NT, 0, stream>>>(p.X, p.P, pl.DT, pl.plane, a.dy, f.dtype, a.dy_stride_b, a.dy_stride_n,
                                                  a.dy_stride_h, p.seg_b, p.seg_c, p.seg_gam, pl.nseg, pl.seg_len, f.N,
                                                  f.H, f.M, f.Dv, gate);
@@ -1214,6 +1218,7 @@ int bwd_exact(const flare_bwd_args_t& a, cudaStream_t stream, const int* gate) {
     r.plane = pl.plane; r.B = f.B; r.N = f.N; r.H = f.H; r.M = f.M; r.Dk = f.Dk; r.dtype = f.dtype; r.scale = f.scale;
     r.gate = gate;
     dim3 g(f.B * f.H, (f.N + RT - 1) / RT, (f.Dk + RC - 1) / RC);
+    LaunchTimer timer("bwd_rows_kernel", stream);
     bwd_rows_kernel<<<g, NT, 0, stream>>>(r);
     FLARE_CUDA_CHECK(cudaGetLastError());
     return FLARE_OK;
@@ -1252,8 +1257,12 @@ int bwd_exact(const flare_bwd_args_t& a, cudaStream_t stream, const int* gate) {
     l.gate = gate;
     l.rows_per_split = pl.rows_per_split; l.splits = pl.splits; l.partial = partial;
     dim3 g(f.H * mt, pl.splits, dkc);
-    bwd_lat_kernel<<<g, NT, 0, stream>>>(l);
+    {
+      LaunchTimer timer("bwd_lat_kernel", stream);
+      bwd_lat_kernel<<<g, NT, 0, stream>>>(l);
+    }
     FLARE_CUDA_CHECK(cudaGetLastError());
+    LaunchTimer timer("bwd_sum_splits_kernel", stream);
     bwd_sum_splits_kernel<<<(unsigned)((lat_n + 255) / 256), 256, 0, stream>>>(out, partial, lat_n, pl.splits, gate);
     FLARE_CUDA_CHECK(cudaGetLastError());
     return FLARE_OK;

@@ -822,6 +822,7 @@ int launch_main(const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap&
                 const BwdTcParams& p, dim3 grid, cudaStream_t stream) {
   auto kern = bwd_tc_kernel<DKB, DVB, MODE>;
   FLARE_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, BL<DVB>::SMEM_BYTES));
+  LaunchTimer timer("bwd_tc_kernel", stream);
   kern<<<grid, NT_MAIN, BL<DVB>::SMEM_BYTES, stream>>>(tk, tv, tdy, tu, p);
   FLARE_CUDA_CHECK(cudaGetLastError());
   return FLARE_OK;
@@ -1114,6 +1115,7 @@ int launch_grads(const CUtensorMap& tds, const CUtensorMap& tk, const CUtensorMa
   auto kern = bwd_tc_grads_kernel<DKB>;
   const int smem = GL<DKB>::smem_bytes(p.groups);
   FLARE_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  LaunchTimer timer("bwd_tc_grads_kernel", stream);
   kern<<<grid, NT_GRAD, smem, stream>>>(tds, tk, tq, p);
   FLARE_CUDA_CHECK(cudaGetLastError());
   return FLARE_OK;
@@ -1291,6 +1293,7 @@ int bwd_tc(const flare_bwd_args_t& a, cudaStream_t stream) {
   {
     const int64_t rows = (int64_t)f.B * pl.npad * f.H;
     const int rows_per_block = 256 / (f.Dv / 8);
+    LaunchTimer timer("bwd_tc_token_stats_kernel", stream);
     bwd_tc_token_stats_kernel<<<(unsigned)((rows + rows_per_block - 1) / rows_per_block), 256, 0, stream>>>(
         reinterpret_cast<const __nv_bfloat16*>(a.dy), a.dy_stride_b, a.dy_stride_n, a.dy_stride_h,
         reinterpret_cast<const __nv_bfloat16*>(y), y_sb, y_sn, y_sh, lse, f.B, f.N,
@@ -1351,6 +1354,7 @@ int bwd_tc(const flare_bwd_args_t& a, cudaStream_t stream) {
     count_launches(1);
     if (pl.groups > 1) {
       const int64_t n8 = (int64_t)f.B * f.N * f.H * f.Dv / 8;
+      LaunchTimer timer("bwd_tc_sum_groups_kernel", stream);
       bwd_tc_sum_groups_kernel<<<(unsigned)((n8 + 255) / 256), 256, 0, stream>>>(
           reinterpret_cast<const __nv_bfloat16*>(ws + pl.off_dvp), pl.groups, n8, reinterpret_cast<__nv_bfloat16*>(a.dv));
       FLARE_CUDA_CHECK(cudaGetLastError());
@@ -1369,6 +1373,7 @@ int bwd_tc(const flare_bwd_args_t& a, cudaStream_t stream) {
     const int rc = f.Dk == 128 ? launch_grads<2>(tds, tk, tq, g, grid, stream) : launch_grads<1>(tds, tk, tq, g, grid, stream);
     if (rc != FLARE_OK) return rc;
     const int64_t n4 = (int64_t)f.H * f.M * f.Dk / 4;
+    LaunchTimer timer("bwd_tc_sum_dq_kernel", stream);
     bwd_tc_sum_dq_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, stream>>>(g.dq_part, f.B * pl.nsplit, n4, a.dq);
     FLARE_CUDA_CHECK(cudaGetLastError());
     count_launches(2);

@@ -193,6 +193,7 @@ template <int PRE, int UNR, int MINB>
 static int launch_variant(const DecodeParams& p, size_t smem, cudaStream_t stream) {
   auto kern = decode_step_kernel<PRE, UNR, MINB>;
   if (smem > 48 * 1024) FLARE_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  LaunchTimer timer("decode_step_kernel", stream);
   kern<<<p.B * p.H, NT, smem, stream>>>(p);
   FLARE_CUDA_CHECK(cudaGetLastError());
   return FLARE_OK;

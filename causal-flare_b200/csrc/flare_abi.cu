@@ -45,6 +45,42 @@ static thread_local ChunkStates g_keep = {nullptr, nullptr, nullptr, 0};
 static thread_local int* g_gate = nullptr;
 
 void count_launches(int n) { g_last_launches += n; }
+
+// ---- per-kernel profile records of this thread -----------------------------------------------------------
+namespace {
+struct ProfileRecord {
+  const char* name;
+  cudaEvent_t begin, end;
+};
+constexpr int kMaxProfileRecords = 256;
+thread_local ProfileRecord g_prof[kMaxProfileRecords];
+thread_local int g_prof_count = 0;
+thread_local bool g_prof_on = false;
+
+void profile_clear() {
+  for (int i = 0; i < g_prof_count; ++i) {
+    cudaEventDestroy(g_prof[i].begin);
+    cudaEventDestroy(g_prof[i].end);
+  }
+  g_prof_count = 0;
+}
+}  // namespace
+
+LaunchTimer::LaunchTimer(const char* name, cudaStream_t s) : slot(-1), stream(s) {
+  if (!g_prof_on || g_prof_count >= kMaxProfileRecords) return;
+  ProfileRecord& r = g_prof[g_prof_count];
+  r.name = name;
+  if (cudaEventCreate(&r.begin) != cudaSuccess) return;
+  if (cudaEventCreate(&r.end) != cudaSuccess) {
+    cudaEventDestroy(r.begin);
+    return;
+  }
+  slot = g_prof_count++;
+  cudaEventRecord(r.begin, stream);
+}
+LaunchTimer::~LaunchTimer() {
+  if (slot >= 0) cudaEventRecord(g_prof[slot].end, stream);
+}
 long long* trace_buffer() { return g_trace; }
 
 namespace {
@@ -493,7 +529,20 @@ const char* flare_status_string(int status) {
 
 const char* flare_last_cuda_error(void) { return g_cuda_error; }
 
-int flare_abi_version(void) { return 1; }
+int flare_abi_version(void) { return 2; }
+
+void flare_profile_enable(int on) {
+  if (on) profile_clear();
+  g_prof_on = on != 0;
+}
+int flare_profile_count(void) { return g_prof_count; }
+int flare_profile_entry(int i, const char** name, float* ms) {
+  if (i < 0 || i >= g_prof_count || name == nullptr || ms == nullptr) return FLARE_ERR_BAD_POINTER;
+  FLARE_CUDA_CHECK(cudaEventSynchronize(g_prof[i].end));
+  FLARE_CUDA_CHECK(cudaEventElapsedTime(ms, g_prof[i].begin, g_prof[i].end));
+  *name = g_prof[i].name;
+  return FLARE_OK;
+}
 
 void flare_set_kernel_events(void* begin_event, void* end_event) {
   g_ev_begin = static_cast<cudaEvent_t>(begin_event);

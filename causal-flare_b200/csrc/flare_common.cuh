@@ -29,6 +29,16 @@ void set_cuda_error(cudaError_t e, const char* where);
 
 int sm_count();
 
+// Per-kernel timing for callers that ask for a profile (the reference's profile=True returns one entry per kernel
+// launch, causal_flare/autoregressive/training.py:4-50).  While switched on (flare_profile_enable) every launch site
+// brackets its kernel with a pair of CUDA events on the launch stream; flare_profile_entry reads them back.
+struct LaunchTimer {
+  LaunchTimer(const char* name, cudaStream_t stream);
+  ~LaunchTimer();
+  int slot;
+  cudaStream_t stream;
+};
+
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 inline int dtype_size(int dtype) { return dtype == FLARE_F32 ? 4 : 2; }

@@ -871,6 +871,7 @@ int launch_keep(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap&
                 cudaStream_t stream) {
   auto kern = prefill_tc_kernel<PADDED, DKB, DVB, SPLIT, MODE, KEEP>;
   FLARE_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Lay<DKB>::SMEM_BYTES));
+  LaunchTimer timer(p.y != nullptr ? "prefill_tc_kernel" : "prefill_tc_kernel (state only)", stream);
   kern<<<grid, NTHREADS, Lay<DKB>::SMEM_BYTES, stream>>>(tq, tk, tv, p);
   FLARE_CUDA_CHECK(cudaGetLastError());
   return FLARE_OK;
@@ -1066,6 +1067,7 @@ int launch_prefill_tc(const flare_fwd_args_t* a, const TcParams& p_in, int nseg_
   if (rc != FLARE_OK || groups == 1 || p.y == nullptr) return rc;
   const int64_t rows = (int64_t)a->B * a->N * a->H;
   const int64_t threads = rows * (a->Dv / 8);
+  LaunchTimer timer("tc_merge_groups_kernel", stream);
   tc_merge_groups_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, stream>>>(
       p.part_y, p.part_lw, groups, rows, a->N, a->H, a->Dv, reinterpret_cast<__nv_bfloat16*>(p.y), p.y_stride_b,
       p.y_stride_n, p.y_stride_h, p.lse_dec, p.lens, p.gate);

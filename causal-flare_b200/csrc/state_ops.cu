@@ -96,6 +96,7 @@ __global__ void __launch_bounds__(NT) fold_kernel(const FoldParams p) {
 int launch_fold(const FoldParams& p, cudaStream_t stream) {
   if (p.lanes <= 0 || p.count <= 0) return FLARE_OK;
   dim3 grid((unsigned)p.lanes, (p.M + LAT_PER_CTA - 1) / LAT_PER_CTA);
+  LaunchTimer timer("fold_kernel", stream);
   fold_kernel<<<grid, NT, 0, stream>>>(p);
   FLARE_CUDA_CHECK(cudaGetLastError());
   return FLARE_OK;

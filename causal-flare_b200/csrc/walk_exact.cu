@@ -269,6 +269,7 @@ template <int MM_MAX, int DD>
 static int launch_one(const WalkParams& p, dim3 grid, size_t smem, cudaStream_t stream) {
   auto kern = walk_exact_kernel<MM_MAX, DD>;
   FLARE_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  LaunchTimer timer(p.gate != nullptr ? "walk_exact_kernel (standby)" : "walk_exact_kernel", stream);
   kern<<<grid, NT, smem, stream>>>(p);
   FLARE_CUDA_CHECK(cudaGetLastError());
   return FLARE_OK;

@@ -217,6 +217,14 @@ int flare_abi_version(void);
  * stream they launch on.  flare_last_launch_count: kernels launched by this thread's last forward/backward. */
 void flare_set_kernel_events(void* begin_event, void* end_event);
 int flare_last_launch_count(void);
+/* Per-kernel timings (the reference's profile=True returns one entry per kernel launch,
+ * causal_flare/autoregressive/training.py:4-50).  flare_profile_enable(1) clears this thread's records and makes every
+ * later launch of this thread record a pair of CUDA events around its kernel; flare_profile_enable(0) stops recording.
+ * flare_profile_entry(i, &name, &ms) synchronises on record i (0 <= i < flare_profile_count()) and returns its kernel
+ * name and device time. */
+void flare_profile_enable(int on);
+int flare_profile_count(void);
+int flare_profile_entry(int i, const char** name, float* ms);
 /* Diagnostic: device buffer of 3 x 16 x 8 int64 that the tensor-core prefill kernel fills with clock64 stamps of
  * the phases of its first CTA (roles: latent group, token group, MMA issuer; first 16 chunks).  NULL disables. */
 void flare_set_trace_buffer(void* device_buffer);

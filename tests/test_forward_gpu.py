@@ -226,8 +226,19 @@ def test_profile_returns_timings(golden):
     q, k, v = to_dev(g["q"], g["k"], g["v"])
     y, prof = cf.flare_autoregressive_triton(q, k, v, profile=True)
     assert "forward" in prof and prof["forward_total_ms"] > 0 and "backward" in prof
+    # one entry per kernel, as in the reference's profile dict; the entries add up to the total
+    assert any(name.startswith("walk_exact_kernel") for name in prof["forward"]), prof["forward"]
+    assert abs(sum(prof["forward"].values()) - prof["forward_total_ms"]) < 1e-6
     (y2, st), prof2 = cf.flare_autoregressive_prefill_triton(q, k, v, profile=True)
     assert prof2["forward_total_ms"] > 0
+    # bf16 on the tensor path: the tcgen05 kernels show up by name, forward and backward
+    qb, kb, vb = (t.bfloat16().requires_grad_(True) for t in (torch.randn(2, 64, 64, device="cuda"),
+                                                                torch.randn(1, 256, 2, 64, device="cuda"),
+                                                                torch.randn(1, 256, 2, 64, device="cuda")))
+    yb, pb = cf.flare_autoregressive_triton(qb, kb, vb, profile=True)
+    assert "prefill_tc_kernel" in pb["forward"]
+    yb.backward(torch.ones_like(yb))
+    assert {"bwd_tc_kernel", "bwd_tc_grads_kernel"} <= set(pb["backward"]) and pb["backward_total_ms"] > 0
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
