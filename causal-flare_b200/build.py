@@ -28,7 +28,7 @@ UNITS = [
     ("decode_step.cu", [], "decode_step"),
     ("state_ops.cu", [], "state_ops"),
     ("prefill_tc.cu", [], "prefill_tc_host"),
-    *[("prefill_tc.cu", [f"-DFLARE_TC_UNIT={u}"], f"prefill_tc_unit{u}") for u in range(6)],
+    *[("prefill_tc.cu", [f"-DFLARE_TC_UNIT={u}"], f"prefill_tc_unit{u}") for u in range(8)],
     ("noalloc.cu", [], "noalloc"),
     ("bwd_tc.cu", [], "bwd_tc_host"),
     *[("bwd_tc.cu", [f"-DFLARE_BT_UNIT={u}"], f"bwd_tc_unit{u}") for u in range(3)],

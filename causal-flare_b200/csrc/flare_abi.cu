@@ -224,8 +224,8 @@ int launch_walk(const flare_fwd_args_t* a, const FwdPlan& pl, const WalkParams& 
   t.out_lane_stride = w.out_lane_stride; t.out_seg_stride = w.out_seg_stride;
   t.out_mode = w.out_mode; t.nseg_total = w.nseg_total;
   if (pl.part_bytes > 0 && t.y != nullptr) {
-    t.part_y = reinterpret_cast<float*>(reinterpret_cast<char*>(a->workspace) + pl.part_off);
-    t.part_lw = t.part_y + (size_t)prefill_tc_partial_bytes(a) / sizeof(float) / (a->Dv + 1) * a->Dv;
+    t.part_y = reinterpret_cast<char*>(a->workspace) + pl.part_off;
+    t.part_lw = reinterpret_cast<float*>(reinterpret_cast<char*>(t.part_y) + prefill_tc_partial_lw_offset(a));
   }
   t.trace = g_trace;
   t.gate = g_gate;

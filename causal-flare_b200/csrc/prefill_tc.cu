@@ -4,8 +4,10 @@
 // token-causal; optional per-row lengths (right padding).
 //
 // One CTA owns a (batch, head, sequence segment, slice of 64 value columns, group of 128 latents) and walks its chunks
-// of C = 128 tokens in order.  With more than one latent group every CTA emits a partial read-out (normalised over its
-// own latents, fp32) and the log2 of its weight mass per token; a small kernel merges the groups.  The CTA carries the
+// of C = 128 tokens in order ((128, 128) heads on a grid that would not fit the SMs at once: one CTA for all 128
+// value columns, the "wide" instance below).  With more than one latent group every CTA emits a partial read-out
+// (normalised over its own latents, fp16) and the log2 of its weight mass per token; a small kernel merges the
+// groups.  Read-out rows leave the CTA as tiled bulk stores of 32 x 32 tiles staged in shared memory.  The CTA carries the
 // latent state on chip: U [128 latents x 64] fp32 in tensor memory, the latent bank Q in shared memory (Dk = 64) or
 // as packed bf16 in tensor memory (Dk = 128; A operand of the score MMA), running max c and denominator d per latent
 // in registers of the thread that owns the latent (TMEM lane = thread).  Per chunk, with the frame c_m = running
@@ -31,6 +33,7 @@
 #include "prefill_tc.cuh"
 
 #include <cuda.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include "sm100_ptx.cuh"
@@ -56,24 +59,34 @@ constexpr float kLn2 = 0.6931471805599453f;
 
 // shared memory map (bytes, every operand buffer 1024-aligned for the 128B swizzle)
 // DKB = Dk / 64 = number of 64-wide key blocks
-template <int DKB>
+// WIDE: one CTA handles both 64-column value blocks of Dv = 128 (Dk = 128 only), see the kernel's comment
+template <int DKB, bool WIDE = false>
 struct Lay {
+  static_assert(!WIDE || DKB == 2, "the wide instance is the (128, 128) head shape");
   // Dk = 64: the latent bank stays in shared memory (TMA-loaded); Dk = 128 has no room for it there and keeps it in
   // tensor memory as the A operand of the score MMA
   static constexpr bool Q_SMEM = DKB == 1;
+  static constexpr int E_BUFS = WIDE ? 1 : 2;              // the wide instance has room for one E buffer only
   static constexpr int OFF_Q = 0;                          // [128 m][64] bf16, K-major                 16 KB or 0
   static constexpr int OFF_K = Q_SMEM ? 16384 : 0;         // DKB x [128 t][64] bf16                    16 KB each
-  static constexpr int OFF_V = OFF_K + DKB * 16384;        // 2 stages x [128 t][64] bf16               32 KB
-  static constexpr int OFF_E = OFF_V + 2 * 16384;          // 2 x [2 t-blocks][128 m][64 t] bf16        64 KB
-  static constexpr int OFF_R = OFF_E + 2 * 32768;          // 2 x [2 t-blocks][128 m][64 t] bf16        64 KB
-  static constexpr int OFF_U = OFF_R + 2 * 32768;          // [128 m][64 dv] bf16                       16 KB
-  static constexpr int OFF_B16 = OFF_U + 16384;            // [2 m-blocks][16 n][64 m] bf16              4 KB
-  static constexpr int OFF_MISC = OFF_B16 + 4096;          // barriers, tmem slot, reductions
-  static constexpr int SMEM_BYTES = OFF_MISC + 4608 + 1024;  // + slack for manual 1024-byte alignment
+  static constexpr int OFF_V = OFF_K + DKB * 16384;        // 2 stages x [128 t][64] bf16, or (wide) one stage of
+                                                           // [2 value blocks][128 t][64]               32 KB
+  static constexpr int OFF_E = OFF_V + 2 * 16384;          // E_BUFS x [2 t-blocks][128 m][64 t] bf16   32 KB each
+  static constexpr int OFF_R = OFF_E + E_BUFS * 32768;     // 2 x [2 t-blocks][128 m][64 t] bf16        64 KB
+  static constexpr int OFF_U = OFF_R + 2 * 32768;          // [128 m][64 dv] bf16 per value block       16 / 32 KB
+  static constexpr int OFF_B16 = OFF_U + (WIDE ? 2 : 1) * 16384;  // [2 m-blocks][16 n][64 m] bf16       4 KB
+  static constexpr int OFF_MISC = OFF_B16 + 4096;          // barriers, tmem slot, reductions          4608 B
+  static constexpr int OFF_STAGE = OFF_MISC + 4608;        // 4 token warps x [32 t][32 columns] 16-bit: source of the
+                                                           // read-out's bulk stores (64-byte swizzle)     8 KB
+  static constexpr int SMEM_BYTES = OFF_STAGE + 8192 + 1024;  // + slack for manual 1024-byte alignment
+  static_assert(SMEM_BYTES <= 232448, "shared memory");
   // tensor-memory columns.  The Y / Den accumulators are double-buffered when the columns allow it (Dk = 64).
+  // Wide: U takes 128 columns, Y is one 64-column buffer used for the two value blocks in turn, and the
+  // denominator column lands in the upper half of the W columns, which are free once W has been packed to bf16.
   static constexpr int YB = DKB == 1 ? 2 : 1;
-  static constexpr uint32_t TM_S = 0, TM_W = 128, TM_U = 256, TM_Y = 320, TM_DEN = TM_Y + YB * 64,
-                            TM_Q = TM_DEN + YB * 16 /* Dk / 2 columns of packed bf16 (Dk = 128 only) */;
+  static constexpr uint32_t TM_S = 0, TM_W = 128, TM_U = 256, TM_Y = WIDE ? 384 : 320,
+                            TM_DEN = WIDE ? TM_W + 64 : TM_Y + YB * 64,
+                            TM_Q = WIDE ? 448 : TM_DEN + YB * 16 /* Dk / 2 columns of packed bf16 (Dk = 128 only) */;
   static_assert(TM_Q + (Q_SMEM ? 0 : DKB * 32) <= 512, "tensor memory columns");
 };
 constexpr uint32_t TM_COLS = 512;
@@ -81,6 +94,7 @@ constexpr uint32_t TM_COLS = 512;
 struct Misc {
   uint64_t q_full, k_full, k_empty, v_full[2], v_empty[2];
   uint64_t s_ready, s_free, kap_done, p1_done, u_done, w_ready, p2_done, y_ready, y_free;
+  uint64_t tail_done;  // wide instance: every read-out MMA of a chunk has run
   uint64_t pmax[4], psum[4];  // pair barriers of the two latent half-groups, one per lane quarter
   uint32_t tmem_base;
   volatile int abort_flag;
@@ -123,7 +137,7 @@ __device__ __forceinline__ int latent0() {
 // with the latent-group split) to keep build times short; the unit without FLARE_TC_UNIT holds the host side.
 template <int UNIT>
 int launch_prefill_tc_unit(bool padded, int mode, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
-                           const TcParams& p, dim3 grid, cudaStream_t stream);
+                           const CUtensorMap& ty, const TcParams& p, dim3 grid, cudaStream_t stream);
 
 #ifdef FLARE_TC_UNIT
 
@@ -139,14 +153,23 @@ int launch_prefill_tc_unit(bool padded, int mode, const CUtensorMap& tq, const C
 // DVB = Dv / 64 = number of value slices (grid.z); Dv may differ from Dk (Dk = 64 with Dv = 128)
 // KEEP: training forward that leaves the per-chunk prefix states for the backward pass (a separate instance: the
 //       extra live values cost the register-capped latent group about 5 % when the code is merely present)
-template <bool PADDED, int DKB, int DVB, bool SPLIT, int MODE, bool KEEP>
+// WIDE: (Dk, Dv) = (128, 128) with ONE CTA per (lane, latent group) that carries all 128 value columns, instead of two
+//       CTAs that each repeat the score / E / R work for 64 of them.  Used when the two-slice grid would not fit the
+//       SMs in one wave.  Tensor memory and shared memory are both full in this instance: E is single-buffered (the
+//       latent group waits for the state update of the previous chunk before it writes E), V has one stage, Y is one
+//       64-column accumulator that takes the two value blocks in turn, and every read-out MMA of a chunk (Den0, Y0,
+//       tril(W) V) is issued after the token group packed W; the latent group waits for those (tail_done) before it
+//       replaces the bf16 state operand.
+template <bool PADDED, int DKB, int DVB, bool SPLIT, int MODE, bool KEEP, bool WIDE>
 __global__ void __launch_bounds__(NTHREADS, 1)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                  const __grid_constant__ CUtensorMap tm_v, const TcParams p) {
-  using L = Lay<DKB>;
+                  const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_y, const TcParams p) {
+  using L = Lay<DKB, WIDE>;
+  static_assert(!WIDE || (DVB == 2 && !KEEP && !PADDED), "wide instance");
+  constexpr int ZS = WIDE ? 1 : DVB;  // value slices on grid.z
   constexpr bool BLOCK = MODE == 1, STABLE = MODE == 2;
   constexpr int OFF_K = L::OFF_K, OFF_V = L::OFF_V, OFF_E = L::OFF_E, OFF_R = L::OFF_R, OFF_U = L::OFF_U,
-                OFF_B16 = L::OFF_B16, OFF_Q = L::OFF_Q, OFF_MISC = L::OFF_MISC, YB = L::YB;
+                OFF_B16 = L::OFF_B16, OFF_Q = L::OFF_Q, OFF_MISC = L::OFF_MISC, YB = L::YB, E_BUFS = L::E_BUFS;
   constexpr bool Q_SMEM = L::Q_SMEM;
   constexpr uint32_t TM_S = L::TM_S, TM_W = L::TM_W, TM_U = L::TM_U, TM_Y = L::TM_Y, TM_DEN = L::TM_DEN, TM_Q = L::TM_Q;
   extern __shared__ uint8_t smem_dyn[];
@@ -186,6 +209,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     mbar_init(&misc->p2_done, 4);
     mbar_init(&misc->y_ready, 1);
     mbar_init(&misc->y_free, 4);
+    mbar_init(&misc->tail_done, 1);
     misc->abort_flag = 0;
     fence_barrier_init();
   }
@@ -212,21 +236,39 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       prefetch_tensormap(&tm_v);
       if (Q_SMEM) {
         mbar_arrive_expect_tx(&misc->q_full, 16384);
-        tma_load_3d(smem + OFF_Q, &tm_q, &misc->q_full, 0, latent0<DVB, SPLIT>(), h);  // rows beyond M read as zero
+        tma_load_3d(smem + OFF_Q, &tm_q, &misc->q_full, 0, latent0<ZS, SPLIT>(), h);  // rows beyond M read as zero
       }
-      const int vc0 = value_col0<DVB, SPLIT>();
-      for (int i = 0; ok && i < nchunks; ++i) {
-        const int t0 = seg_begin + i * C;
-        // K tile: free once the score MMA of the previous chunk has run
-        if (i > 0 && !(ok = wait_or_abort(&misc->k_empty, (i - 1) & 1, misc))) break;
+      const int vc0 = value_col0<ZS, SPLIT>();
+      auto load_k = [&](int i) {
         mbar_arrive_expect_tx(&misc->k_full, DKB * 16384);
 #pragma unroll
-        for (int kb = 0; kb < DKB; ++kb) tma_load_4d(smem + OFF_K + kb * 16384, &tm_k, &misc->k_full, kb * 64, h, t0, b);
-        // V tile: stage i & 1, free once chunk i - 2 has been folded into Y
-        const int st = i & 1;
-        if (i >= 2 && !(ok = wait_or_abort(&misc->v_empty[st], ((i - 2) >> 1) & 1, misc))) break;
-        mbar_arrive_expect_tx(&misc->v_full[st], 16384);
-        tma_load_4d(smem + OFF_V + st * 16384, &tm_v, &misc->v_full[st], vc0, h, t0, b);
+        for (int kb = 0; kb < DKB; ++kb)
+          tma_load_4d(smem + OFF_K + kb * 16384, &tm_k, &misc->k_full, kb * 64, h, seg_begin + i * C, b);
+      };
+      if (WIDE && nchunks > 0) load_k(0);
+      for (int i = 0; ok && i < nchunks; ++i) {
+        const int t0 = seg_begin + i * C;
+        if constexpr (WIDE) {
+          // The single V stage (both value blocks) is free only when chunk i - 1 has been folded into Y, late in the
+          // chunk period; the K tile of the NEXT chunk is requested first so that it never queues behind that wait.
+          if (i + 1 < nchunks) {
+            if (!(ok = wait_or_abort(&misc->k_empty, i & 1, misc))) break;
+            load_k(i + 1);
+          }
+          if (i >= 1 && !(ok = wait_or_abort(&misc->v_empty[0], (i - 1) & 1, misc))) break;
+          mbar_arrive_expect_tx(&misc->v_full[0], 32768);
+          tma_load_4d(smem + OFF_V, &tm_v, &misc->v_full[0], 0, h, t0, b);
+          tma_load_4d(smem + OFF_V + 16384, &tm_v, &misc->v_full[0], 64, h, t0, b);
+        } else {
+          // K tile: free once the score MMA of the previous chunk has run
+          if (i > 0 && !(ok = wait_or_abort(&misc->k_empty, (i - 1) & 1, misc))) break;
+          load_k(i);
+          // V tile: stage i & 1, free once chunk i - 2 has been folded into Y
+          const int st = i & 1;
+          if (i >= 2 && !(ok = wait_or_abort(&misc->v_empty[st], ((i - 2) >> 1) & 1, misc))) break;
+          mbar_arrive_expect_tx(&misc->v_full[st], 16384);
+          tma_load_4d(smem + OFF_V + st * 16384, &tm_v, &misc->v_full[st], vc0, h, t0, b);
+        }
       }
     }
   } else if (warp == 12) {
@@ -235,7 +277,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       const uint32_t k_addr = smem_u32(smem + OFF_K);
       const uint32_t u_addr = smem_u32(smem + OFF_U), b16_addr = smem_u32(smem + OFF_B16);
       constexpr uint32_t ID_S = make_idesc_bf16(128, 128, 0, 0);   // Q (TMEM) x K_c (K-major)
-      constexpr uint32_t ID_U = make_idesc_bf16(128, 64, 0, 1);    // E (K-major) x V (MN-major)
+      constexpr uint32_t ID_U = make_idesc_bf16(128, WIDE ? 128 : 64, 0, 1);  // E (K-major) x V (MN-major)
       constexpr uint32_t ID_Y0 = make_idesc_bf16(128, 64, 1, 1);   // R (MN-major) x U_bf16 (MN-major)
       constexpr uint32_t ID_DEN = make_idesc_bf16(128, 16, 1, 0);  // R (MN-major) x d tile (K-major)
       constexpr uint32_t ID_W = make_idesc_bf16(128, 128, 1, 1);   // R (MN-major) x E (MN-major)
@@ -249,7 +291,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       const uint64_t de_k0 = make_desc_sw128(smem_u32(smem + OFF_E), 16, 1024);
       const uint64_t de_mn0 = make_desc_sw128(smem_u32(smem + OFF_E), 16384, 1024);
       const uint64_t dr_mn0 = make_desc_sw128(smem_u32(smem + OFF_R), 16384, 1024);
-      const uint64_t dv_mn0 = make_desc_sw128(smem_u32(smem + OFF_V), 1024, 1024);
+      // (wide: the two 64-column value blocks are 16384 bytes apart, the leading-dimension stride of the N = 128 operand)
+      const uint64_t dv_mn0 = make_desc_sw128(smem_u32(smem + OFF_V), WIDE ? 16384 : 1024, 1024);
 
       auto issue_scores = [&](int i) -> bool {  // S^T of chunk i; K tile and the S columns must be free
         if (!wait_or_abort(&misc->k_full, i & 1, misc)) return false;
@@ -267,6 +310,30 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       auto issue_tail = [&](int i) -> bool {  // Y += tril(W) V of chunk i, after the token group masked W
         if (!wait_or_abort(&misc->p2_done, i & 1, misc)) return false;
         tc_fence_after_sync();
+        if constexpr (WIDE) {
+          // the rest of the chunk's read-out (Y0 of the first value block was issued with W): Den0 into the freed
+          // upper W columns and tril(W) V of the first block; then, through the same accumulator once the token
+          // group has taken the first block, the second block
+          const uint64_t drm = dr_mn0 + (uint64_t)((i & 1) * (32768 >> 4));
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            mma_ss(tmem + TM_DEN, drm + (j * 2048 >> 4), db16 + (((j >> 2) * 2048 + (j & 3) * 32) >> 4), ID_DEN, j > 0);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) mma_ts(tmem + TM_Y, tmem + TM_W + j * 8, dv_mn0 + (j * 2048 >> 4), ID_Y1, 1);
+          tc_commit(&misc->y_ready);
+          if (!wait_or_abort(&misc->y_free, 0, misc)) return false;
+          tc_fence_after_sync();
+          TC_TRACE(2, i + 1, 7);
+          const uint64_t dub = du + (uint64_t)(16384 >> 4), dvb = dv_mn0 + (uint64_t)(16384 >> 4);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) mma_ss(tmem + TM_Y, drm + (j * 2048 >> 4), dub + (j * 2048 >> 4), ID_Y0, j > 0);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) mma_ts(tmem + TM_Y, tmem + TM_W + j * 8, dvb + (j * 2048 >> 4), ID_Y1, 1);
+          tc_commit(&misc->y_ready);
+          tc_commit(&misc->v_empty[0]);
+          tc_commit(&misc->tail_done);
+          return true;
+        }
         const uint64_t dv = dv_mn0 + (uint64_t)((i & 1) * (16384 >> 4));
 #pragma unroll
         for (int j = 0; j < 8; ++j)
@@ -291,12 +358,13 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         }
         TC_TRACE(2, i, 2);
         if (!(ok = wait_or_abort(&misc->p1_done, par, misc))) break;
-        if (!(ok = wait_or_abort(&misc->v_full[i & 1], (i >> 1) & 1, misc))) break;
+        // (wide: the values arrive late, see the producer; W and Y0 do not need them)
+        if (!WIDE && !(ok = wait_or_abort(&misc->v_full[i & 1], (i >> 1) & 1, misc))) break;
         tc_fence_after_sync();
         TC_TRACE(2, i, 3);
         const uint64_t eoff = (uint64_t)((i & 1) * (32768 >> 4));
-        const uint64_t dek = de_k0 + eoff, dem = de_mn0 + eoff, drm = dr_mn0 + eoff;
-        const uint64_t dv = dv_mn0 + (uint64_t)((i & 1) * (16384 >> 4));
+        const uint64_t dek = de_k0 + (E_BUFS == 2 ? eoff : 0), dem = de_mn0 + (E_BUFS == 2 ? eoff : 0), drm = dr_mn0 + eoff;
+        const uint64_t dv = dv_mn0 + (uint64_t)(WIDE ? 0 : (i & 1) * (16384 >> 4));
         if (!state_only) {
           // W = R^T E  (k = latents, 8 steps of 16 rows = 2048 bytes)
 #pragma unroll
@@ -304,24 +372,32 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           tc_commit(&misc->w_ready);
           TC_TRACE(2, i, 5);
           // Y = R^T U_bf16, Den0 = R^T d.  Single-buffered accumulators: the token group must have read chunk i - 1.
+          // (wide: Y0 of the first value block only; the accumulator is free once the token group has taken the
+          // second block of chunk i - 1, the second of two accumulator phases per chunk.  Den0 and the second block
+          // are issued with the rest of the read-out, see issue_tail.)
           if (YB == 1 && i >= 1) {
-            if (!(ok = wait_or_abort(&misc->y_free, (i - 1) & 1, misc))) break;
+            if (!(ok = wait_or_abort(&misc->y_free, WIDE ? 1 : (i - 1) & 1, misc))) break;
             tc_fence_after_sync();
           }
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
             mma_ss(tmem + TM_Y + (i & (YB - 1)) * 64, drm + (j * 2048 >> 4), du + (j * 2048 >> 4), ID_Y0, j > 0);
-            mma_ss(tmem + TM_DEN + (i & (YB - 1)) * 16, drm + (j * 2048 >> 4),
-                   db16 + (((j >> 2) * 2048 + (j & 3) * 32) >> 4), ID_DEN, j > 0);
+            if (!WIDE)
+              mma_ss(tmem + TM_DEN + (i & (YB - 1)) * 16, drm + (j * 2048 >> 4),
+                     db16 + (((j >> 2) * 2048 + (j & 3) * 32) >> 4), ID_DEN, j > 0);
           }
           TC_TRACE(2, i, 6);
         }
         // U += E V_c  (k = tokens of the chunk)
+        if (WIDE) {
+          if (!(ok = wait_or_abort(&misc->v_full[0], i & 1, misc))) break;
+          tc_fence_after_sync();
+        }
 #pragma unroll
         for (int j = 0; j < 8; ++j)
           mma_ss(tmem + TM_U, dek + (((j >> 2) * 16384 + (j & 3) * 32) >> 4), dv + (j * 2048 >> 4), ID_U, 1);
         tc_commit(&misc->u_done);
-        if (state_only) tc_commit(&misc->v_empty[i & 1]);  // no read-out MMA will read this V stage
+        if (state_only) tc_commit(&misc->v_empty[WIDE ? 0 : (i & 1)]);  // no read-out MMA will read this V stage
         TC_TRACE(2, i, 4);
       }
       if (!state_only && ok && nchunks > 0) ok = issue_tail(nchunks - 1);
@@ -338,15 +414,15 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     const int64_t st_idx = (int64_t)lane_id * p.in_lane_stride + (int64_t)seg * p.in_seg_stride;
     // Fewer than 128 latents: the missing rows are padding (zero rows of Q).  A padding latent gets the frame +inf,
     // so its E = exp2(0 - inf) is exactly zero without any predicate in the element loops, and a denominator of 1.
-    const bool live = !PADDED || latent0<DVB, SPLIT>() + m < p.M;
+    const bool live = !PADDED || latent0<ZS, SPLIT>() + m < p.M;
     float c2 = -INFINITY, dsum = 0.f;  // running max (log2 units) and the denominator in that frame
     if (!live) {
       c2 = 0.f;
       dsum = 1.f;
     } else if (p.in_m != nullptr) {
       // (stablemax: the carried m is a constant zero and not a frame; the decode frame starts empty)
-      if (!STABLE) c2 = p.in_m[st_idx * p.M + latent0<DVB, SPLIT>() + m] * kLog2e;
-      dsum = p.in_d[st_idx * p.M + latent0<DVB, SPLIT>() + m];
+      if (!STABLE) c2 = p.in_m[st_idx * p.M + latent0<ZS, SPLIT>() + m] * kLog2e;
+      dsum = p.in_d[st_idx * p.M + latent0<ZS, SPLIT>() + m];
     }
     float d_prev = 0.f;                                  // denominator before the chunk in flight, in its frame
     if constexpr (!Q_SMEM) {
@@ -355,7 +431,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       uint32_t r[DKB * 16];
       const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.q) +
                                                         (int64_t)h * p.q_stride_h +
-                                                        (int64_t)(live ? latent0<DVB, SPLIT>() + m : 0) * p.q_stride_m +
+                                                        (int64_t)(live ? latent0<ZS, SPLIT>() + m : 0) * p.q_stride_m +
                                                         hf * (DKB * 32));
 #pragma unroll
       for (int i = 0; i < DKB * 4; ++i) {
@@ -368,15 +444,18 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       tc_fence_before_sync();
       warp_arrive(&misc->q_full, lane);
     }
-    {
-      // carry-in numerator -> tensor memory, 32 value columns per half
+    // columns of the numerator each half-group thread looks after: 32 of the CTA's 64, or (wide) 64 of its 128
+    constexpr int UW = WIDE ? 64 : 32;
+#pragma unroll
+    for (int c0 = 0; c0 < UW; c0 += 32) {
+      // carry-in numerator -> tensor memory
       uint32_t r[32];
 #pragma unroll
       for (int i = 0; i < 32; ++i)
-        r[i] = (p.in_u && live) ? __float_as_uint(p.in_u[(st_idx * p.M + latent0<DVB, SPLIT>() + m) * DV +
-                                                         value_col0<DVB, SPLIT>() + hf * 32 + i])
+        r[i] = (p.in_u && live) ? __float_as_uint(p.in_u[(st_idx * p.M + latent0<ZS, SPLIT>() + m) * DV +
+                                                         value_col0<ZS, SPLIT>() + hf * UW + c0 + i])
                                 : 0u;
-      tmem_st32(tl + TM_U + hf * 32, r);
+      tmem_st32(tl + TM_U + hf * UW + c0, r);
       tmem_wait_st();
     }
 
@@ -384,7 +463,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       const uint32_t par = i & 1;
       const int nvalid = min(C, seg_end - (seg_begin + i * C));
       const int tok0 = hf * 64;
-      uint8_t* e_row = smem + OFF_E + (i & 1) * 32768 + hf * 16384;  // t-block hf of the chunk's operand buffers
+      uint8_t* e_row = smem + OFF_E + (E_BUFS == 2 ? (i & 1) * 32768 : 0) + hf * 16384;  // t-block hf of the operand buffers
       uint8_t* r_row = smem + OFF_R + (i & 1) * 32768 + hf * 16384;
       if (!(ok = wait_or_abort(&misc->s_ready, par, misc))) break;
       tc_fence_after_sync();
@@ -463,6 +542,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       // phase a: E for the 64 tokens of this half (in place of the scores), their sum, E operand rows
       float tot0 = 0.f, tot1 = 0.f;
       float g16[4] = {0.f, 0.f, 0.f, 0.f};  // BLOCK: sums of the four groups of 16 tokens of this half
+      // single E buffer: the products that read the previous chunk's E (W, state update) must have run
+      if (E_BUFS == 1 && STABLE && i > 0 && !(ok = wait_or_abort(&misc->u_done, (i - 1) & 1, misc))) break;
       if constexpr (STABLE) {
         // encoder weights sigma(s): packed and stored 8 tokens at a time; the raw scores stay in ra / rb for phase b
 #pragma unroll
@@ -523,6 +604,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         }
       }
       warp_arrive(&misc->psum[q], lane);
+      if (E_BUFS == 1 && !STABLE && i > 0 && !(ok = wait_or_abort(&misc->u_done, (i - 1) & 1, misc))) break;
       if constexpr (!STABLE)
 #pragma unroll
       for (int ch = 0; ch < 4; ++ch) {
@@ -612,9 +694,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           }
         }
         // log normaliser after each block that ends in this half (natural log, exact-frame independent)
-        if (p.lse_enc != nullptr && live && value_col0<DVB, SPLIT>() == 0) {
+        if (p.lse_enc != nullptr && live && value_col0<ZS, SPLIT>() == 0) {
           const int t_half = seg_begin + i * C + tok0;  // first token of this half in the sequence
-          float* dst = p.lse_enc + ((int64_t)lane_id * (p.N / bs)) * p.M + latent0<DVB, SPLIT>() + m;
+          float* dst = p.lse_enc + ((int64_t)lane_id * (p.N / bs)) * p.M + latent0<ZS, SPLIT>() + m;
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
             const int t_end = t_half + g * 16 + 15;            // last token of the group
@@ -644,10 +726,42 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       if (i > 0 && !(ok = wait_or_abort(&misc->u_done, (i - 1) & 1, misc))) break;
       tc_fence_after_sync();
       if (tid == 0) TC_TRACE(0, i, 4);
-      if (hf == 0 && !state_only)
+      if (!WIDE && hf == 0 && !state_only)
         *reinterpret_cast<__nv_bfloat16*>(smem + OFF_B16 + (m >> 6) * 2048 + ((m & 63) >> 3) * 16 + (m & 7) * 2) =
             __float2bfloat16_rn(d_carry);
       const bool need = __any_sync(0xffffffffu, alpha != 1.0f);
+      if constexpr (WIDE) {
+        // 64 value columns per thread = value block hf.  The tensor-memory side runs first; the bf16 operand rows
+        // are held packed in registers until the previous chunk's read-out products have read the operand buffer.
+        if (!state_only || need) {
+          uint32_t pk[32];
+#pragma unroll
+          for (int c0 = 0; c0 < 64; c0 += 32) {
+            uint32_t r[32];
+            tmem_ld32(tl + TM_U + hf * 64 + c0, r);
+            tmem_wait_ld();
+            tmem_fence_regs(r);
+            if (need) {
+#pragma unroll
+              for (int k = 0; k < 32; ++k) r[k] = __float_as_uint(__uint_as_float(r[k]) * alpha);
+              tmem_st32(tl + TM_U + hf * 64 + c0, r);
+            }
+#pragma unroll
+            for (int k = 0; k < 16; ++k)
+              pk[(c0 >> 1) + k] = pack_bf16(__uint_as_float(r[2 * k]), __uint_as_float(r[2 * k + 1]));
+          }
+          if (!state_only) {
+            if (tid == 0) TC_TRACE(0, i, 6);
+            if (i > 0 && !(ok = wait_or_abort(&misc->tail_done, (i - 1) & 1, misc))) break;
+            if (tid == 0) TC_TRACE(0, i, 7);
+#pragma unroll
+            for (int ch = 0; ch < 8; ++ch)
+              *reinterpret_cast<uint4*>(smem + OFF_U + hf * 16384 + swz_chunk_off(m, ch)) =
+                  make_uint4(pk[ch * 4], pk[ch * 4 + 1], pk[ch * 4 + 2], pk[ch * 4 + 3]);
+          }
+          if (need) tmem_wait_st();
+        }
+      } else
       if (!state_only || need) {
         uint32_t r[32];
         tmem_ld32(tl + TM_U + hf * 32, r);
@@ -679,9 +793,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
               fin = ex2_approx(c2 - c_true);
             }
             if (live) {
-              const int64_t o = ((int64_t)lane_id * p.dump_nch + (seg_begin / C + i)) * p.M + latent0<DVB, SPLIT>() + m;
+              const int64_t o = ((int64_t)lane_id * p.dump_nch + (seg_begin / C + i)) * p.M + latent0<ZS, SPLIT>() + m;
               uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.dump_u) + o * DV +
-                                                    value_col0<DVB, SPLIT>() + hf * 32);
+                                                    value_col0<ZS, SPLIT>() + hf * 32);
 #pragma unroll
               for (int ch = 0; ch < 4; ++ch) {
                 uint4 v;
@@ -691,7 +805,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 v.w = pack_bf16(__uint_as_float(r[ch * 8 + 6]) * fin, __uint_as_float(r[ch * 8 + 7]) * fin);
                 dst[ch] = v;
               }
-              if (hf == 0 && value_col0<DVB, SPLIT>() == 0) {
+              if (hf == 0 && value_col0<ZS, SPLIT>() == 0) {
                 p.dump_c[o] = c_true;          // log2 units (unused for the stablemax encoder)
                 p.dump_d[o] = d_carry * fin;   // denominator before the chunk in that frame
               }
@@ -700,6 +814,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         }
         if (need) tmem_wait_st();
       }
+      if (WIDE && hf == 0 && !state_only)  // (after the wait for the previous chunk's read-out products above)
+        *reinterpret_cast<__nv_bfloat16*>(smem + OFF_B16 + (m >> 6) * 2048 + ((m & 63) >> 3) * 16 + (m & 7) * 2) =
+            __float2bfloat16_rn(d_carry);
       fence_proxy_async_smem();
       tc_fence_before_sync();
       warp_arrive(&misc->p1_done, lane);
@@ -723,21 +840,24 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       tc_fence_after_sync();
       if (ok) {
         const int64_t so = (int64_t)lane_id * p.out_lane_stride + (int64_t)seg * p.out_seg_stride;
-        const int mg = latent0<DVB, SPLIT>() + m;  // latent index in the whole bank
-        if (hf == 0 && live && value_col0<DVB, SPLIT>() == 0) {
+        const int mg = latent0<ZS, SPLIT>() + m;  // latent index in the whole bank
+        if (hf == 0 && live && value_col0<ZS, SPLIT>() == 0) {
           p.out_m[so * p.M + mg] = STABLE ? 0.f : c2 * kLn2;
           p.out_d[so * p.M + mg] = dsum * fin;
         }
-        uint32_t r[32];
-        tmem_ld32(tl + TM_U + hf * 32, r);
-        tmem_wait_ld();
-        tmem_fence_regs(r);
-        float4* dst =
-            reinterpret_cast<float4*>(p.out_u + (so * p.M + (live ? mg : 0)) * DV + value_col0<DVB, SPLIT>() + hf * 32);
 #pragma unroll
-        for (int k = 0; k < 8; ++k)
-          if (live) dst[k] = make_float4(__uint_as_float(r[4 * k]) * fin, __uint_as_float(r[4 * k + 1]) * fin,
-                               __uint_as_float(r[4 * k + 2]) * fin, __uint_as_float(r[4 * k + 3]) * fin);
+        for (int c0 = 0; c0 < UW; c0 += 32) {
+          uint32_t r[32];
+          tmem_ld32(tl + TM_U + hf * UW + c0, r);
+          tmem_wait_ld();
+          tmem_fence_regs(r);
+          float4* dst = reinterpret_cast<float4*>(p.out_u + (so * p.M + (live ? mg : 0)) * DV +
+                                                  value_col0<ZS, SPLIT>() + hf * UW + c0);
+#pragma unroll
+          for (int k = 0; k < 8; ++k)
+            if (live) dst[k] = make_float4(__uint_as_float(r[4 * k]) * fin, __uint_as_float(r[4 * k + 1]) * fin,
+                                 __uint_as_float(r[4 * k + 2]) * fin, __uint_as_float(r[4 * k + 3]) * fin);
+        }
       }
     }
   } else {
@@ -745,10 +865,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     const int wq = warp - 8;  // lane quarter
     const uint32_t tl = tmem + ((uint32_t)(wq * 32) << 16);
     const int tt = wq * 32 + lane;  // token index inside the chunk
-    __nv_bfloat16* const y_lane = reinterpret_cast<__nv_bfloat16*>(p.y) + (int64_t)b * p.y_stride_b +
-                                  (int64_t)h * p.y_stride_h + value_col0<DVB, SPLIT>();
-    // latent-group split: dense fp32 partials [group][B][N][H][DV] and log2 weight masses [group][B][N][H]
-    const int64_t part_row0 = SPLIT ? (((int64_t)(blockIdx.z / DVB) * (gridDim.x / p.H) + b) * p.N) : 0;
+    uint8_t* const stage = smem + L::OFF_STAGE + wq * 2048;
+    // latent-group split: dense fp16 partials [group][B][N][H][DV] and log2 weight masses [group][B][N][H]
+    const int64_t part_row0 = SPLIT ? (((int64_t)(blockIdx.z / ZS) * (gridDim.x / p.H) + b) * p.N) : 0;
     for (int i = 0; !state_only && ok && i < nchunks; ++i) {
       const uint32_t par = i & 1;
       const int t0 = seg_begin + i * C;
@@ -796,8 +915,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       warp_arrive(&misc->p2_done, lane);
       if (tid == 256) TC_TRACE(1, i, 1);
 
-      // normalise and store
-      if (!(ok = wait_or_abort(&misc->y_ready, par, misc))) break;
+      // normalise and store (wide: the first of the two value blocks; two accumulator phases per chunk)
+      if (!(ok = wait_or_abort(&misc->y_ready, WIDE ? 0 : par, misc))) break;
       tc_fence_after_sync();
       if (tid == 256) TC_TRACE(1, i, 2);
       uint32_t den0;
@@ -815,43 +934,85 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           p.gate[1 + lane_id] = 1;
         }
       }
-      const float inv = (SPLIT && !den_ok) ? 0.f : 1.0f / den;
-      if (SPLIT && p.part_y != nullptr && tt < nvalid && value_col0<DVB, SPLIT>() == 0)
+      const float inv = (SPLIT && !den_ok) ? 0.f : rcp_approx(den);  // (a true division compiles to a call here)
+      if (SPLIT && p.part_y != nullptr && tt < nvalid && value_col0<ZS, SPLIT>() == 0)
         p.part_lw[(part_row0 + t0 + tt) * p.H + h] = den_ok ? misc->kap[par] + __log2f(den) : -INFINITY;
       // log-sum-exp of the token's decode scores = log of the decode weights' mass in the frame kappa
-      if (!SPLIT && p.lse_dec != nullptr && tt < nvalid && value_col0<DVB, SPLIT>() == 0)
+      if (!SPLIT && p.lse_dec != nullptr && tt < nvalid && value_col0<ZS, SPLIT>() == 0)
         p.lse_dec[(int64_t)lane_id * p.N + t0 + tt] = (misc->kap[par] + __log2f(den)) * kLn2;
+      // The accumulator goes back to the MMA issuer as soon as its 64 columns are in registers (single-buffered
+      // instances); scaling and the stores follow.  Wide: two value blocks per chunk through the one accumulator.
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        uint32_t r[32];
-        tmem_ld32(tl + TM_Y + (i & (YB - 1)) * 64 + half * 32, r);
+      for (int vb = 0; vb < (WIDE ? 2 : 1); ++vb) {
+        if (vb == 1) {
+          if (tid == 256) TC_TRACE(1, i, 4);
+          if (!(ok = wait_or_abort(&misc->y_ready, 1, misc))) break;
+          tc_fence_after_sync();
+          if (tid == 256) TC_TRACE(1, i, 5);
+        }
+        uint32_t ra[32], rb[32];
+        tmem_ld32(tl + TM_Y + (i & (YB - 1)) * 64, ra);
+        tmem_ld32(tl + TM_Y + (i & (YB - 1)) * 64 + 32, rb);
         tmem_wait_ld();
-        if (SPLIT) {
-          if (p.part_y != nullptr && tt < nvalid) {
-            float4* dst = reinterpret_cast<float4*>(p.part_y + ((part_row0 + t0 + tt) * p.H + h) * DV +
-                                                    value_col0<DVB, SPLIT>() + half * 32);
+        if (YB == 1) {
+          tc_fence_before_sync();
+          warp_arrive(&misc->y_free, lane);
+        }
 #pragma unroll
-            for (int k = 0; k < 8; ++k)
-              dst[k] = make_float4(__uint_as_float(r[4 * k]) * inv, __uint_as_float(r[4 * k + 1]) * inv,
-                                   __uint_as_float(r[4 * k + 2]) * inv, __uint_as_float(r[4 * k + 3]) * inv);
-          }
-        } else if (p.y != nullptr && tt < nvalid) {
-          uint4* dst = reinterpret_cast<uint4*>(y_lane + (int64_t)(t0 + tt) * p.y_stride_n + half * 32);
+        for (int half = 0; half < 2; ++half) {
+          const uint32_t(&r)[32] = half ? rb : ra;
+          const int col = value_col0<ZS, SPLIT>() + vb * 64 + half * 32;
+          // 32 columns of this thread's row as 16-bit values: bf16 of y, or fp16 of a latent group's partial
+          uint4 v[4];
 #pragma unroll
           for (int ch = 0; ch < 4; ++ch) {
-            uint4 v;
-            v.x = pack_bf16(__uint_as_float(r[ch * 8 + 0]) * inv, __uint_as_float(r[ch * 8 + 1]) * inv);
-            v.y = pack_bf16(__uint_as_float(r[ch * 8 + 2]) * inv, __uint_as_float(r[ch * 8 + 3]) * inv);
-            v.z = pack_bf16(__uint_as_float(r[ch * 8 + 4]) * inv, __uint_as_float(r[ch * 8 + 5]) * inv);
-            v.w = pack_bf16(__uint_as_float(r[ch * 8 + 6]) * inv, __uint_as_float(r[ch * 8 + 7]) * inv);
-            dst[ch] = v;
+            if (SPLIT) {
+              v[ch].x = pack_f16(__uint_as_float(r[ch * 8 + 0]) * inv, __uint_as_float(r[ch * 8 + 1]) * inv);
+              v[ch].y = pack_f16(__uint_as_float(r[ch * 8 + 2]) * inv, __uint_as_float(r[ch * 8 + 3]) * inv);
+              v[ch].z = pack_f16(__uint_as_float(r[ch * 8 + 4]) * inv, __uint_as_float(r[ch * 8 + 5]) * inv);
+              v[ch].w = pack_f16(__uint_as_float(r[ch * 8 + 6]) * inv, __uint_as_float(r[ch * 8 + 7]) * inv);
+            } else {
+              v[ch].x = pack_bf16(__uint_as_float(r[ch * 8 + 0]) * inv, __uint_as_float(r[ch * 8 + 1]) * inv);
+              v[ch].y = pack_bf16(__uint_as_float(r[ch * 8 + 2]) * inv, __uint_as_float(r[ch * 8 + 3]) * inv);
+              v[ch].z = pack_bf16(__uint_as_float(r[ch * 8 + 4]) * inv, __uint_as_float(r[ch * 8 + 5]) * inv);
+              v[ch].w = pack_bf16(__uint_as_float(r[ch * 8 + 6]) * inv, __uint_as_float(r[ch * 8 + 7]) * inv);
+            }
+          }
+          if (p.y_tma) {
+            // One tiled bulk store per warp and 32 x 32 tile.  A thread storing its own row straight to global
+            // memory costs 32 separate 16-byte transactions per instruction; the latent warps' operand stores to
+            // shared memory queued behind those and the whole kernel ran 12 % slower.  Rows beyond the sequence end
+            // are clipped by the copy.
+            if (lane == 0) bulk_wait_group_read0();  // the previous tile has left the staging buffer
+            __syncwarp();
+#pragma unroll
+            for (int ch = 0; ch < 4; ++ch)  // 64-byte swizzle: 16-byte piece index ^ (row / 2) % 4
+              *reinterpret_cast<uint4*>(stage + lane * 64 + ((ch ^ ((lane >> 1) & 3)) << 4)) = v[ch];
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_4d(&tm_y, stage, col, h, t0 + wq * 32, SPLIT ? (int)(blockIdx.z / ZS) * (int)(gridDim.x / p.H) + b : b);
+              bulk_commit_group();
+            }
+          } else if (SPLIT) {
+            if (p.part_y != nullptr && tt < nvalid) {
+              uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__half*>(p.part_y) +
+                                                    ((part_row0 + t0 + tt) * p.H + h) * DV + col);
+#pragma unroll
+              for (int ch = 0; ch < 4; ++ch) dst[ch] = v[ch];
+            }
+          } else if (p.y != nullptr && tt < nvalid) {
+            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.y) + (int64_t)b * p.y_stride_b +
+                                                  (int64_t)h * p.y_stride_h + (int64_t)(t0 + tt) * p.y_stride_n + col);
+#pragma unroll
+            for (int ch = 0; ch < 4; ++ch) dst[ch] = v[ch];
           }
         }
       }
-      tc_fence_before_sync();
-      if (YB == 1) warp_arrive(&misc->y_free, lane);
+      if (!ok) break;
       if (tid == 256) TC_TRACE(1, i, 3);
     }
+    if (lane == 0) bulk_wait_group0();  // the bulk stores of this warp are complete
   }
   if (!ok) {
     misc->abort_flag = 1;
@@ -866,54 +1027,67 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 
 namespace {
 
-template <bool PADDED, int DKB, int DVB, bool SPLIT, int MODE, bool KEEP>
-int launch_keep(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const TcParams& p, dim3 grid,
-                cudaStream_t stream) {
-  auto kern = prefill_tc_kernel<PADDED, DKB, DVB, SPLIT, MODE, KEEP>;
-  FLARE_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Lay<DKB>::SMEM_BYTES));
-  LaunchTimer timer(p.y != nullptr ? "prefill_tc_kernel" : "prefill_tc_kernel (state only)", stream);
-  kern<<<grid, NTHREADS, Lay<DKB>::SMEM_BYTES, stream>>>(tq, tk, tv, p);
+template <bool PADDED, int DKB, int DVB, bool SPLIT, int MODE, bool KEEP, bool WIDE = false>
+int launch_keep(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& ty,
+                const TcParams& p, dim3 grid, cudaStream_t stream) {
+  auto kern = prefill_tc_kernel<PADDED, DKB, DVB, SPLIT, MODE, KEEP, WIDE>;
+  FLARE_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Lay<DKB, WIDE>::SMEM_BYTES));
+  LaunchTimer timer(p.y == nullptr ? "prefill_tc_kernel (state only)" : (WIDE ? "prefill_tc_kernel (wide)" : "prefill_tc_kernel"),
+                    stream);
+  kern<<<grid, NTHREADS, Lay<DKB, WIDE>::SMEM_BYTES, stream>>>(tq, tk, tv, ty, p);
   FLARE_CUDA_CHECK(cudaGetLastError());
   return FLARE_OK;
 }
 
 template <bool PADDED, int DKB, int DVB, bool SPLIT, int MODE>
-int launch_instance(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const TcParams& p, dim3 grid,
-                    cudaStream_t stream) {
-  return p.dump_u != nullptr ? launch_keep<PADDED, DKB, DVB, SPLIT, MODE, true>(tq, tk, tv, p, grid, stream)
-                             : launch_keep<PADDED, DKB, DVB, SPLIT, MODE, false>(tq, tk, tv, p, grid, stream);
+int launch_instance(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& ty,
+                    const TcParams& p, dim3 grid, cudaStream_t stream) {
+  return p.dump_u != nullptr ? launch_keep<PADDED, DKB, DVB, SPLIT, MODE, true>(tq, tk, tv, ty, p, grid, stream)
+                             : launch_keep<PADDED, DKB, DVB, SPLIT, MODE, false>(tq, tk, tv, ty, p, grid, stream);
 }
 
 }  // namespace
 
 template <>
 int launch_prefill_tc_unit<FLARE_TC_UNIT>(bool padded, int mode, const CUtensorMap& tq, const CUtensorMap& tk,
-                                          const CUtensorMap& tv, const TcParams& p, dim3 grid, cudaStream_t stream) {
-  // units 0..2: (Dk, Dv) = (64, 64), (128, 128), (64, 128); units 3..5: the same with the latent-group split
+                                          const CUtensorMap& tv, const CUtensorMap& ty, const TcParams& p, dim3 grid,
+                                          cudaStream_t stream) {
+  // units 0..2: (Dk, Dv) = (64, 64), (128, 128), (64, 128); units 3..5: the same with the latent-group split;
+  // units 6, 7: the wide (128, 128) instance (one CTA for both value blocks) without / with the latent-group split
+#if FLARE_TC_UNIT >= 6
+  constexpr bool WSPLIT = FLARE_TC_UNIT == 7;
+  (void)padded;
+  if (mode == 1) return launch_keep<false, 2, 2, WSPLIT, 1, false, true>(tq, tk, tv, ty, p, grid, stream);
+  if (mode == 2) return launch_keep<false, 2, 2, WSPLIT, 2, false, true>(tq, tk, tv, ty, p, grid, stream);
+  return launch_keep<false, 2, 2, WSPLIT, 0, false, true>(tq, tk, tv, ty, p, grid, stream);
+#else
   constexpr int COMBO = FLARE_TC_UNIT % 3;
   constexpr int DKB = COMBO == 1 ? 2 : 1;
   constexpr int DVB = COMBO == 0 ? 1 : 2;
   constexpr bool SPLIT = FLARE_TC_UNIT >= 3;
   if (mode == 1)
-    return padded ? launch_instance<true, DKB, DVB, SPLIT, 1>(tq, tk, tv, p, grid, stream)
-                  : launch_instance<false, DKB, DVB, SPLIT, 1>(tq, tk, tv, p, grid, stream);
+    return padded ? launch_instance<true, DKB, DVB, SPLIT, 1>(tq, tk, tv, ty, p, grid, stream)
+                  : launch_instance<false, DKB, DVB, SPLIT, 1>(tq, tk, tv, ty, p, grid, stream);
   if (mode == 2)
-    return padded ? launch_instance<true, DKB, DVB, SPLIT, 2>(tq, tk, tv, p, grid, stream)
-                  : launch_instance<false, DKB, DVB, SPLIT, 2>(tq, tk, tv, p, grid, stream);
-  return padded ? launch_instance<true, DKB, DVB, SPLIT, 0>(tq, tk, tv, p, grid, stream)
-                : launch_instance<false, DKB, DVB, SPLIT, 0>(tq, tk, tv, p, grid, stream);
+    return padded ? launch_instance<true, DKB, DVB, SPLIT, 2>(tq, tk, tv, ty, p, grid, stream)
+                  : launch_instance<false, DKB, DVB, SPLIT, 2>(tq, tk, tv, ty, p, grid, stream);
+  return padded ? launch_instance<true, DKB, DVB, SPLIT, 0>(tq, tk, tv, ty, p, grid, stream)
+                : launch_instance<false, DKB, DVB, SPLIT, 0>(tq, tk, tv, ty, p, grid, stream);
+#endif
 }
 
 #else  // host side and the merge kernel
 
 __device__ int g_tc_error = 0;
 
-template <> int launch_prefill_tc_unit<0>(bool, int, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const TcParams&, dim3, cudaStream_t);
-template <> int launch_prefill_tc_unit<1>(bool, int, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const TcParams&, dim3, cudaStream_t);
-template <> int launch_prefill_tc_unit<2>(bool, int, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const TcParams&, dim3, cudaStream_t);
-template <> int launch_prefill_tc_unit<3>(bool, int, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const TcParams&, dim3, cudaStream_t);
-template <> int launch_prefill_tc_unit<4>(bool, int, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const TcParams&, dim3, cudaStream_t);
-template <> int launch_prefill_tc_unit<5>(bool, int, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const TcParams&, dim3, cudaStream_t);
+template <> int launch_prefill_tc_unit<0>(bool, int, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const TcParams&, dim3, cudaStream_t);
+template <> int launch_prefill_tc_unit<1>(bool, int, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const TcParams&, dim3, cudaStream_t);
+template <> int launch_prefill_tc_unit<2>(bool, int, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const TcParams&, dim3, cudaStream_t);
+template <> int launch_prefill_tc_unit<3>(bool, int, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const TcParams&, dim3, cudaStream_t);
+template <> int launch_prefill_tc_unit<4>(bool, int, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const TcParams&, dim3, cudaStream_t);
+template <> int launch_prefill_tc_unit<5>(bool, int, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const TcParams&, dim3, cudaStream_t);
+template <> int launch_prefill_tc_unit<6>(bool, int, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const TcParams&, dim3, cudaStream_t);
+template <> int launch_prefill_tc_unit<7>(bool, int, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const TcParams&, dim3, cudaStream_t);
 
 // -------------------------------------------------------------------------------------------------
 // host side
@@ -948,7 +1122,7 @@ bool prefill_tc_supported(const flare_fwd_args_t* a) {
 
 // Merge of the latent groups' partial read-outs: y = sum_g w_g y_g / sum_g w_g with w_g = exp2(lw_g - max lw).
 // One thread per (token, head, 8 value columns).
-__global__ void __launch_bounds__(256) tc_merge_groups_kernel(const float* __restrict__ part_y, const float* __restrict__ part_lw,
+__global__ void __launch_bounds__(256) tc_merge_groups_kernel(const __half* __restrict__ part_y, const float* __restrict__ part_lw,
                                                                int groups, int64_t rows /* B*N*H */, int N, int H, int dv,
                                                                __nv_bfloat16* y, int64_t y_stride_b, int64_t y_stride_n,
                                                                int64_t y_stride_h, float* lse_dec /* [B, H, N] or null */,
@@ -980,10 +1154,14 @@ __global__ void __launch_bounds__(256) tc_merge_groups_kernel(const float* __res
       if (g >= groups) break;
       const float w = exp2f(lw[g] - mx);
       wsum += w;
-      const float4* src = reinterpret_cast<const float4*>(part_y + (g * rows + row) * dv + c8 * 8);
-      const float4 a = src[0], b = src[1];
-      acc[0] += w * a.x; acc[1] += w * a.y; acc[2] += w * a.z; acc[3] += w * a.w;
-      acc[4] += w * b.x; acc[5] += w * b.y; acc[6] += w * b.z; acc[7] += w * b.w;
+      const uint4 raw = *reinterpret_cast<const uint4*>(part_y + (g * rows + row) * dv + c8 * 8);
+      const uint32_t rw[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&rw[j]));
+        acc[2 * j] += w * f.x;
+        acc[2 * j + 1] += w * f.y;
+      }
     }
   }
   const float inv = wsum > 0.f ? 1.0f / wsum : 0.f;
@@ -1005,10 +1183,16 @@ int prefill_tc_latent_groups(const flare_fwd_args_t* a) { return (a->M + M - 1) 
 
 int prefill_tc_ctas_per_lane(const flare_fwd_args_t* a) { return a->Dv / D * prefill_tc_latent_groups(a); }
 
+// fp16 partial read-outs [groups][B][N][H][Dv], then fp32 weight masses [groups][B][N][H]
+size_t prefill_tc_partial_lw_offset(const flare_fwd_args_t* a) {
+  const int groups = prefill_tc_latent_groups(a);
+  return align_up((size_t)groups * a->B * a->N * a->H * a->Dv * sizeof(__half), 256);
+}
+
 size_t prefill_tc_partial_bytes(const flare_fwd_args_t* a) {
   const int groups = prefill_tc_latent_groups(a);
   if (groups == 1) return 0;
-  return (size_t)groups * a->B * a->N * a->H * (a->Dv + 1) * sizeof(float);
+  return prefill_tc_partial_lw_offset(a) + (size_t)groups * a->B * a->N * a->H * sizeof(float);
 }
 
 int launch_prefill_tc(const flare_fwd_args_t* a, const TcParams& p_in, int nseg_grid, cudaStream_t stream) {
@@ -1050,26 +1234,57 @@ int launch_prefill_tc(const flare_fwd_args_t* a, const TcParams& p_in, int nseg_
     }
   }
   const int groups = prefill_tc_latent_groups(a);
-  const dim3 grid(a->B * a->H, nseg_grid, a->Dv / D * groups);
+  // Read-out rows leave through tiled bulk stores of 32 tokens x 32 columns (64-byte swizzle): into y, or with several
+  // latent groups into the dense fp16 partials.  Per-row lengths (rows beyond a length stay untouched) and output
+  // strides the tiled copy cannot express fall back to per-thread stores.
+  CUtensorMap ty = tk;
+  p.y_tma = 0;
+  if (p.y != nullptr && a->lengths == nullptr) {
+    const uint32_t box[4] = {32, 1, 32, 1};
+    if (groups > 1) {
+      const uint64_t dims[4] = {(uint64_t)a->Dv, (uint64_t)a->H, (uint64_t)a->N, (uint64_t)groups * a->B};
+      const int64_t str[3] = {a->Dv, (int64_t)a->H * a->Dv, (int64_t)a->N * a->H * a->Dv};
+      p.y_tma = tc::make_map_bf16(&ty, p.part_y, 4, dims, str, box, CU_TENSOR_MAP_SWIZZLE_64B) ? 1 : 0;
+    } else {
+      const int64_t str[3] = {p.y_stride_h, p.y_stride_n, p.y_stride_b};
+      bool ok = (reinterpret_cast<uintptr_t>(p.y) % 16) == 0;
+      for (int64_t st : str) ok = ok && st > 0 && (st % 8) == 0 && st < (int64_t(1) << 39);
+      const uint64_t dims[4] = {(uint64_t)a->Dv, (uint64_t)a->H, (uint64_t)a->N, (uint64_t)a->B};
+      p.y_tma = ok && tc::make_map_bf16(&ty, p.y, 4, dims, str, box, CU_TENSOR_MAP_SWIZZLE_64B) ? 1 : 0;
+    }
+  }
+  if (const char* env = getenv("FLARE_B200_ROW_STORES"))  // diagnostic: per-thread row stores instead
+    if (env[0] == '1') p.y_tma = 0;
   const bool padded = (a->M % M) != 0;
   const int mode = a->variant == FLARE_STABLEMAX ? 2 : (a->block_size > 1 ? 1 : 0);
+  // (128, 128) heads: two CTAs per (lane, group), each repeating the score / E / R work for 64 value columns, while
+  // they all fit the SMs at once; beyond that the wide instance, one CTA for all 128 columns.  (Not for the training
+  // forward that keeps its states, nor for a padded latent bank.)  FLARE_B200_WIDE=0 / 1 forces the choice.
+  bool wide = a->Dk == 128 && a->Dv == 128 && !padded && p.dump_u == nullptr &&
+              (int64_t)a->B * a->H * nseg_grid * groups * 2 > sm_count();
+  if (const char* env = getenv("FLARE_B200_WIDE"))
+    wide = a->Dk == 128 && a->Dv == 128 && !padded && p.dump_u == nullptr && env[0] == '1';
+  const dim3 grid(a->B * a->H, nseg_grid, wide ? groups : a->Dv / D * groups);
   int rc;
   const int combo = a->Dk == 128 ? 1 : (a->Dv == 128 ? 2 : 0);  // (64, 64), (128, 128), (64, 128)
-  if (combo == 0)
-    rc = groups > 1 ? launch_prefill_tc_unit<3>(padded, mode, tq, tk, tv, p, grid, stream)
-                    : launch_prefill_tc_unit<0>(padded, mode, tq, tk, tv, p, grid, stream);
+  if (wide)
+    rc = groups > 1 ? launch_prefill_tc_unit<7>(padded, mode, tq, tk, tv, ty, p, grid, stream)
+                    : launch_prefill_tc_unit<6>(padded, mode, tq, tk, tv, ty, p, grid, stream);
+  else if (combo == 0)
+    rc = groups > 1 ? launch_prefill_tc_unit<3>(padded, mode, tq, tk, tv, ty, p, grid, stream)
+                    : launch_prefill_tc_unit<0>(padded, mode, tq, tk, tv, ty, p, grid, stream);
   else if (combo == 1)
-    rc = groups > 1 ? launch_prefill_tc_unit<4>(padded, mode, tq, tk, tv, p, grid, stream)
-                    : launch_prefill_tc_unit<1>(padded, mode, tq, tk, tv, p, grid, stream);
+    rc = groups > 1 ? launch_prefill_tc_unit<4>(padded, mode, tq, tk, tv, ty, p, grid, stream)
+                    : launch_prefill_tc_unit<1>(padded, mode, tq, tk, tv, ty, p, grid, stream);
   else
-    rc = groups > 1 ? launch_prefill_tc_unit<5>(padded, mode, tq, tk, tv, p, grid, stream)
-                    : launch_prefill_tc_unit<2>(padded, mode, tq, tk, tv, p, grid, stream);
+    rc = groups > 1 ? launch_prefill_tc_unit<5>(padded, mode, tq, tk, tv, ty, p, grid, stream)
+                    : launch_prefill_tc_unit<2>(padded, mode, tq, tk, tv, ty, p, grid, stream);
   if (rc != FLARE_OK || groups == 1 || p.y == nullptr) return rc;
   const int64_t rows = (int64_t)a->B * a->N * a->H;
   const int64_t threads = rows * (a->Dv / 8);
   LaunchTimer timer("tc_merge_groups_kernel", stream);
   tc_merge_groups_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, stream>>>(
-      p.part_y, p.part_lw, groups, rows, a->N, a->H, a->Dv, reinterpret_cast<__nv_bfloat16*>(p.y), p.y_stride_b,
+      reinterpret_cast<const __half*>(p.part_y), p.part_lw, groups, rows, a->N, a->H, a->Dv, reinterpret_cast<__nv_bfloat16*>(p.y), p.y_stride_b,
       p.y_stride_n, p.y_stride_h, p.lse_dec, p.lens, p.gate);
   FLARE_CUDA_CHECK(cudaGetLastError());
   return FLARE_OK;

@@ -19,9 +19,14 @@ struct TcParams {
   int64_t in_lane_stride, in_seg_stride;
   float *out_m, *out_d, *out_u;
   int64_t out_lane_stride, out_seg_stride;
-  // more than 128 latents: per-group partial read-outs, fp32 [groups][B][N][H][Dv] and [groups][B][N][H]; the launch
-  // merges them into y afterwards
-  float *part_y, *part_lw;
+  // more than 128 latents: per-group partial read-outs (each normalised over its own latents), fp16
+  // [groups][B][N][H][Dv], and the log2 of each group's weight mass, fp32 [groups][B][N][H]; the launch merges them
+  // into y afterwards
+  void* part_y;
+  float* part_lw;
+  // the read-out rows leave through tiled bulk stores (set by the launch when the output's strides allow it and no
+  // per-row lengths are given); otherwise every thread stores its own row
+  int y_tma;
   int out_mode;  // 0: none, 1: every segment, 2: last segment only
   int nseg_total;
   const int32_t* lens;       // [B] tokens per batch row (right padding beyond), or null
@@ -44,8 +49,10 @@ struct TcParams {
 bool prefill_tc_supported(const flare_fwd_args_t* a);
 // CTAs the kernel launches per (lane, segment)
 int prefill_tc_ctas_per_lane(const flare_fwd_args_t* a);
-// scratch for the partial read-outs of the latent groups (0 for M <= 128)
+// scratch for the partial read-outs of the latent groups (0 for M <= 128), and the byte offset of the weight-mass
+// array inside it
 size_t prefill_tc_partial_bytes(const flare_fwd_args_t* a);
+size_t prefill_tc_partial_lw_offset(const flare_fwd_args_t* a);
 // launches segments 0 .. nseg_grid-1
 int launch_prefill_tc(const flare_fwd_args_t* a, const TcParams& p, int nseg_grid, cudaStream_t stream);
 // device address (current device) of the error word shared by all tensor-core kernels

@@ -82,8 +82,9 @@ inline EncodeTiledFn encode_fn() {
   return fn;
 }
 
+// (any 16-bit element type: the copies do no arithmetic)
 inline bool make_map_bf16(CUtensorMap* map, const void* base, int rank, const uint64_t* dims, const int64_t* strides_elems,
-                          const uint32_t* box) {
+                          const uint32_t* box, CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return false;
   cuuint64_t gdim[5], gstride[4];
@@ -95,7 +96,7 @@ inline bool make_map_bf16(CUtensorMap* map, const void* base, int rank, const ui
   }
   for (int i = 0; i + 1 < rank; ++i) gstride[i] = (cuuint64_t)strides_elems[i] * 2;
   return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank, const_cast<void*>(base), gdim, gstride, bx, estr,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
