@@ -337,7 +337,7 @@ def bench_seqpar(args, rank, world):
     states, fold of the lower ranks, span pass with carry-in).  One GPU: the whole sequence, no exchange."""
     from causal_flare import _ops, parallel
 
-    B, N, H, M, D, bs = 2, 65536, 32, 256, 128, 64
+    B, N, H, M, D, bs = 2, args.seqpar_tokens, 32, 256, 128, 64
     span = N // world
     g = torch.Generator(device="cuda").manual_seed(5 + rank)
     q = torch.randn(H, M, D, generator=torch.Generator(device="cuda").manual_seed(5), device="cuda").bfloat16()
@@ -575,6 +575,8 @@ def main():
                     help="profiling aid: run one section only (the JSON line then lacks the other)")
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--seqpar-backward", action="store_true", help="with --only seqpar: also time forward+backward")
+    ap.add_argument("--seqpar-tokens", type=int, default=65536,
+                    help="with --only seqpar: sequence length (the C5 shape has 65536; shorter for profiler captures)")
     ap.add_argument("--skip-other", action="store_true", help="skip the short runs of the other benchmark shapes")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup

@@ -66,27 +66,31 @@ struct Lay {
   // Dk = 64: the latent bank stays in shared memory (TMA-loaded); Dk = 128 has no room for it there and keeps it in
   // tensor memory as the A operand of the score MMA
   static constexpr bool Q_SMEM = DKB == 1;
-  static constexpr int E_BUFS = WIDE ? 1 : 2;              // the wide instance has room for one E buffer only
+  // operand buffers of E and R: two each, or (wide) one each: there every product that reads R is issued at once
+  // when the latent group has finished a chunk, so the buffers are free long before the next chunk writes them
+  static constexpr int ER_BUFS = WIDE ? 1 : 2;
+  static constexpr int VB = WIDE ? 2 : 1;                  // 64-column value blocks per CTA
   static constexpr int OFF_Q = 0;                          // [128 m][64] bf16, K-major                 16 KB or 0
   static constexpr int OFF_K = Q_SMEM ? 16384 : 0;         // DKB x [128 t][64] bf16                    16 KB each
-  static constexpr int OFF_V = OFF_K + DKB * 16384;        // 2 stages x [128 t][64] bf16, or (wide) one stage of
-                                                           // [2 value blocks][128 t][64]               32 KB
-  static constexpr int OFF_E = OFF_V + 2 * 16384;          // E_BUFS x [2 t-blocks][128 m][64 t] bf16   32 KB each
-  static constexpr int OFF_R = OFF_E + E_BUFS * 32768;     // 2 x [2 t-blocks][128 m][64 t] bf16        64 KB
-  static constexpr int OFF_U = OFF_R + 2 * 32768;          // [128 m][64 dv] bf16 per value block       16 / 32 KB
-  static constexpr int OFF_B16 = OFF_U + (WIDE ? 2 : 1) * 16384;  // [2 m-blocks][16 n][64 m] bf16       4 KB
+  static constexpr int OFF_V = OFF_K + DKB * 16384;        // 2 stages x [VB value blocks][128 t][64]   16 KB each
+  static constexpr int OFF_E = OFF_V + 2 * VB * 16384;     // ER_BUFS x [2 t-blocks][128 m][64 t] bf16  32 KB each
+  // wide: the bf16 state operand follows E directly, so that one MN-major B operand of four 64-wide blocks
+  // [E t-block 0 | E t-block 1 | U value block 0 | U value block 1] feeds the merged product [W | Y0]
+  static constexpr int OFF_U = WIDE ? OFF_E + 32768 : OFF_E + 4 * 32768;  // [VB][128 m][64 dv] bf16    16 KB each
+  static constexpr int OFF_R = WIDE ? OFF_U + 32768 : OFF_E + 2 * 32768;  // ER_BUFS x [2 t-blocks][128 m][64 t]
+  static constexpr int OFF_B16 = WIDE ? OFF_R + 32768 : OFF_U + 16384;    // [2 m-blocks][16 n][64 m] bf16  4 KB
   static constexpr int OFF_MISC = OFF_B16 + 4096;          // barriers, tmem slot, reductions          4608 B
   static constexpr int OFF_STAGE = OFF_MISC + 4608;        // 4 token warps x [32 t][32 columns] 16-bit: source of the
                                                            // read-out's bulk stores (64-byte swizzle)     8 KB
   static constexpr int SMEM_BYTES = OFF_STAGE + 8192 + 1024;  // + slack for manual 1024-byte alignment
   static_assert(SMEM_BYTES <= 232448, "shared memory");
   // tensor-memory columns.  The Y / Den accumulators are double-buffered when the columns allow it (Dk = 64).
-  // Wide: U takes 128 columns, Y is one 64-column buffer used for the two value blocks in turn, and the
-  // denominator column lands in the upper half of the W columns, which are free once W has been packed to bf16.
+  // Wide: W shares the columns of S (the latent group has the next chunk's scores in registers before W of this
+  // chunk is written), Y follows W directly (one product writes both) and U takes 128 columns.
   static constexpr int YB = DKB == 1 ? 2 : 1;
-  static constexpr uint32_t TM_S = 0, TM_W = 128, TM_U = 256, TM_Y = WIDE ? 384 : 320,
-                            TM_DEN = WIDE ? TM_W + 64 : TM_Y + YB * 64,
-                            TM_Q = WIDE ? 448 : TM_DEN + YB * 16 /* Dk / 2 columns of packed bf16 (Dk = 128 only) */;
+  static constexpr uint32_t TM_S = 0, TM_W = WIDE ? 0 : 128, TM_U = 256, TM_Y = WIDE ? 128 : 320,
+                            TM_DEN = WIDE ? 384 : TM_Y + YB * 64,
+                            TM_Q = TM_DEN + YB * 16 /* Dk / 2 columns of packed bf16 (Dk = 128 only) */;
   static_assert(TM_Q + (Q_SMEM ? 0 : DKB * 32) <= 512, "tensor memory columns");
 };
 constexpr uint32_t TM_COLS = 512;
@@ -94,7 +98,6 @@ constexpr uint32_t TM_COLS = 512;
 struct Misc {
   uint64_t q_full, k_full, k_empty, v_full[2], v_empty[2];
   uint64_t s_ready, s_free, kap_done, p1_done, u_done, w_ready, p2_done, y_ready, y_free;
-  uint64_t tail_done;  // wide instance: every read-out MMA of a chunk has run
   uint64_t pmax[4], psum[4];  // pair barriers of the two latent half-groups, one per lane quarter
   uint32_t tmem_base;
   volatile int abort_flag;
@@ -155,11 +158,9 @@ int launch_prefill_tc_unit(bool padded, int mode, const CUtensorMap& tq, const C
 //       extra live values cost the register-capped latent group about 5 % when the code is merely present)
 // WIDE: (Dk, Dv) = (128, 128) with ONE CTA per (lane, latent group) that carries all 128 value columns, instead of two
 //       CTAs that each repeat the score / E / R work for 64 of them.  Used when the two-slice grid would not fit the
-//       SMs in one wave.  Tensor memory and shared memory are both full in this instance: E is single-buffered (the
-//       latent group waits for the state update of the previous chunk before it writes E), V has one stage, Y is one
-//       64-column accumulator that takes the two value blocks in turn, and every read-out MMA of a chunk (Den0, Y0,
-//       tril(W) V) is issued after the token group packed W; the latent group waits for those (tail_done) before it
-//       replaces the bf16 state operand.
+//       SMs in one wave.  Differences: U and Y are 128 columns wide; W and Y0 = R^T U_bf16 come out of ONE product of
+//       width 256 ([E | U_bf16] as one B operand, [W | Y] adjacent in tensor memory), so R is read once for both; W
+//       shares the columns of S; E and R are single-buffered.
 template <bool PADDED, int DKB, int DVB, bool SPLIT, int MODE, bool KEEP, bool WIDE>
 __global__ void __launch_bounds__(NTHREADS, 1)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
@@ -169,7 +170,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   constexpr int ZS = WIDE ? 1 : DVB;  // value slices on grid.z
   constexpr bool BLOCK = MODE == 1, STABLE = MODE == 2;
   constexpr int OFF_K = L::OFF_K, OFF_V = L::OFF_V, OFF_E = L::OFF_E, OFF_R = L::OFF_R, OFF_U = L::OFF_U,
-                OFF_B16 = L::OFF_B16, OFF_Q = L::OFF_Q, OFF_MISC = L::OFF_MISC, YB = L::YB, E_BUFS = L::E_BUFS;
+                OFF_B16 = L::OFF_B16, OFF_Q = L::OFF_Q, OFF_MISC = L::OFF_MISC, YB = L::YB, ER_BUFS = L::ER_BUFS,
+                VB = L::VB;
   constexpr bool Q_SMEM = L::Q_SMEM;
   constexpr uint32_t TM_S = L::TM_S, TM_W = L::TM_W, TM_U = L::TM_U, TM_Y = L::TM_Y, TM_DEN = L::TM_DEN, TM_Q = L::TM_Q;
   extern __shared__ uint8_t smem_dyn[];
@@ -209,7 +211,6 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     mbar_init(&misc->p2_done, 4);
     mbar_init(&misc->y_ready, 1);
     mbar_init(&misc->y_free, 4);
-    mbar_init(&misc->tail_done, 1);
     misc->abort_flag = 0;
     fence_barrier_init();
   }
@@ -239,36 +240,20 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         tma_load_3d(smem + OFF_Q, &tm_q, &misc->q_full, 0, latent0<ZS, SPLIT>(), h);  // rows beyond M read as zero
       }
       const int vc0 = value_col0<ZS, SPLIT>();
-      auto load_k = [&](int i) {
-        mbar_arrive_expect_tx(&misc->k_full, DKB * 16384);
-#pragma unroll
-        for (int kb = 0; kb < DKB; ++kb)
-          tma_load_4d(smem + OFF_K + kb * 16384, &tm_k, &misc->k_full, kb * 64, h, seg_begin + i * C, b);
-      };
-      if (WIDE && nchunks > 0) load_k(0);
       for (int i = 0; ok && i < nchunks; ++i) {
         const int t0 = seg_begin + i * C;
-        if constexpr (WIDE) {
-          // The single V stage (both value blocks) is free only when chunk i - 1 has been folded into Y, late in the
-          // chunk period; the K tile of the NEXT chunk is requested first so that it never queues behind that wait.
-          if (i + 1 < nchunks) {
-            if (!(ok = wait_or_abort(&misc->k_empty, i & 1, misc))) break;
-            load_k(i + 1);
-          }
-          if (i >= 1 && !(ok = wait_or_abort(&misc->v_empty[0], (i - 1) & 1, misc))) break;
-          mbar_arrive_expect_tx(&misc->v_full[0], 32768);
-          tma_load_4d(smem + OFF_V, &tm_v, &misc->v_full[0], 0, h, t0, b);
-          tma_load_4d(smem + OFF_V + 16384, &tm_v, &misc->v_full[0], 64, h, t0, b);
-        } else {
-          // K tile: free once the score MMA of the previous chunk has run
-          if (i > 0 && !(ok = wait_or_abort(&misc->k_empty, (i - 1) & 1, misc))) break;
-          load_k(i);
-          // V tile: stage i & 1, free once chunk i - 2 has been folded into Y
-          const int st = i & 1;
-          if (i >= 2 && !(ok = wait_or_abort(&misc->v_empty[st], ((i - 2) >> 1) & 1, misc))) break;
-          mbar_arrive_expect_tx(&misc->v_full[st], 16384);
-          tma_load_4d(smem + OFF_V + st * 16384, &tm_v, &misc->v_full[st], vc0, h, t0, b);
-        }
+        // K tile: free once the score MMA of the previous chunk has run
+        if (i > 0 && !(ok = wait_or_abort(&misc->k_empty, (i - 1) & 1, misc))) break;
+        mbar_arrive_expect_tx(&misc->k_full, DKB * 16384);
+#pragma unroll
+        for (int kb = 0; kb < DKB; ++kb) tma_load_4d(smem + OFF_K + kb * 16384, &tm_k, &misc->k_full, kb * 64, h, t0, b);
+        // V tile: stage i & 1, free once chunk i - 2 has been folded into Y
+        const int st = i & 1;
+        if (i >= 2 && !(ok = wait_or_abort(&misc->v_empty[st], ((i - 2) >> 1) & 1, misc))) break;
+        mbar_arrive_expect_tx(&misc->v_full[st], VB * 16384);
+#pragma unroll
+        for (int vb = 0; vb < VB; ++vb)
+          tma_load_4d(smem + OFF_V + (st * VB + vb) * 16384, &tm_v, &misc->v_full[st], vc0 + vb * 64, h, t0, b);
       }
     }
   } else if (warp == 12) {
@@ -281,7 +266,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       constexpr uint32_t ID_Y0 = make_idesc_bf16(128, 64, 1, 1);   // R (MN-major) x U_bf16 (MN-major)
       constexpr uint32_t ID_DEN = make_idesc_bf16(128, 16, 1, 0);  // R (MN-major) x d tile (K-major)
       constexpr uint32_t ID_W = make_idesc_bf16(128, 128, 1, 1);   // R (MN-major) x E (MN-major)
-      constexpr uint32_t ID_Y1 = make_idesc_bf16(128, 64, 0, 1);   // tril(W) (TMEM) x V (MN-major)
+      constexpr uint32_t ID_Y1 = make_idesc_bf16(128, WIDE ? 128 : 64, 0, 1);  // tril(W) (TMEM) x V (MN-major)
+      constexpr uint32_t ID_WY = make_idesc_bf16(128, 256, 1, 1);  // wide: R (MN-major) x [E | U_bf16] (MN-major)
 
       // descriptors are built once; inside the loops only the start-address field (units of 16 bytes) advances
       const uint64_t dk = make_desc_sw128(k_addr, 16, 1024);
@@ -293,6 +279,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       const uint64_t dr_mn0 = make_desc_sw128(smem_u32(smem + OFF_R), 16384, 1024);
       // (wide: the two 64-column value blocks are 16384 bytes apart, the leading-dimension stride of the N = 128 operand)
       const uint64_t dv_mn0 = make_desc_sw128(smem_u32(smem + OFF_V), WIDE ? 16384 : 1024, 1024);
+      constexpr int V_STAGE = VB * 16384;
 
       auto issue_scores = [&](int i) -> bool {  // S^T of chunk i; K tile and the S columns must be free
         if (!wait_or_abort(&misc->k_full, i & 1, misc)) return false;
@@ -310,31 +297,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       auto issue_tail = [&](int i) -> bool {  // Y += tril(W) V of chunk i, after the token group masked W
         if (!wait_or_abort(&misc->p2_done, i & 1, misc)) return false;
         tc_fence_after_sync();
-        if constexpr (WIDE) {
-          // the rest of the chunk's read-out (Y0 of the first value block was issued with W): Den0 into the freed
-          // upper W columns and tril(W) V of the first block; then, through the same accumulator once the token
-          // group has taken the first block, the second block
-          const uint64_t drm = dr_mn0 + (uint64_t)((i & 1) * (32768 >> 4));
-#pragma unroll
-          for (int j = 0; j < 8; ++j)
-            mma_ss(tmem + TM_DEN, drm + (j * 2048 >> 4), db16 + (((j >> 2) * 2048 + (j & 3) * 32) >> 4), ID_DEN, j > 0);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) mma_ts(tmem + TM_Y, tmem + TM_W + j * 8, dv_mn0 + (j * 2048 >> 4), ID_Y1, 1);
-          tc_commit(&misc->y_ready);
-          if (!wait_or_abort(&misc->y_free, 0, misc)) return false;
-          tc_fence_after_sync();
-          TC_TRACE(2, i + 1, 7);
-          const uint64_t dub = du + (uint64_t)(16384 >> 4), dvb = dv_mn0 + (uint64_t)(16384 >> 4);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) mma_ss(tmem + TM_Y, drm + (j * 2048 >> 4), dub + (j * 2048 >> 4), ID_Y0, j > 0);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) mma_ts(tmem + TM_Y, tmem + TM_W + j * 8, dvb + (j * 2048 >> 4), ID_Y1, 1);
-          tc_commit(&misc->y_ready);
-          tc_commit(&misc->v_empty[0]);
-          tc_commit(&misc->tail_done);
-          return true;
-        }
-        const uint64_t dv = dv_mn0 + (uint64_t)((i & 1) * (16384 >> 4));
+        const uint64_t dv = dv_mn0 + (uint64_t)((i & 1) * (V_STAGE >> 4));
 #pragma unroll
         for (int j = 0; j < 8; ++j)
           mma_ts(tmem + TM_Y + (i & (YB - 1)) * 64, tmem + TM_W + j * 8, dv + (j * 2048 >> 4), ID_Y1, 1);
@@ -358,46 +321,55 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         }
         TC_TRACE(2, i, 2);
         if (!(ok = wait_or_abort(&misc->p1_done, par, misc))) break;
-        // (wide: the values arrive late, see the producer; W and Y0 do not need them)
-        if (!WIDE && !(ok = wait_or_abort(&misc->v_full[i & 1], (i >> 1) & 1, misc))) break;
+        if (!(ok = wait_or_abort(&misc->v_full[i & 1], (i >> 1) & 1, misc))) break;
         tc_fence_after_sync();
         TC_TRACE(2, i, 3);
-        const uint64_t eoff = (uint64_t)((i & 1) * (32768 >> 4));
-        const uint64_t dek = de_k0 + (E_BUFS == 2 ? eoff : 0), dem = de_mn0 + (E_BUFS == 2 ? eoff : 0), drm = dr_mn0 + eoff;
-        const uint64_t dv = dv_mn0 + (uint64_t)(WIDE ? 0 : (i & 1) * (16384 >> 4));
+        const uint64_t eoff = (uint64_t)(ER_BUFS == 2 ? (i & 1) * (32768 >> 4) : 0);
+        const uint64_t dek = de_k0 + eoff, dem = de_mn0 + eoff, drm = dr_mn0 + eoff;
+        const uint64_t dv = dv_mn0 + (uint64_t)((i & 1) * (V_STAGE >> 4));
         if (!state_only) {
-          // W = R^T E  (k = latents, 8 steps of 16 rows = 2048 bytes)
-#pragma unroll
-          for (int j = 0; j < 8; ++j) mma_ss(tmem + TM_W, drm + (j * 2048 >> 4), dem + (j * 2048 >> 4), ID_W, j > 0);
-          tc_commit(&misc->w_ready);
-          TC_TRACE(2, i, 5);
-          // Y = R^T U_bf16, Den0 = R^T d.  Single-buffered accumulators: the token group must have read chunk i - 1.
-          // (wide: Y0 of the first value block only; the accumulator is free once the token group has taken the
-          // second block of chunk i - 1, the second of two accumulator phases per chunk.  Den0 and the second block
-          // are issued with the rest of the read-out, see issue_tail.)
+          // Single-buffered accumulators: the token group must have taken Y of chunk i - 1.
           if (YB == 1 && i >= 1) {
-            if (!(ok = wait_or_abort(&misc->y_free, WIDE ? 1 : (i - 1) & 1, misc))) break;
+            if (!(ok = wait_or_abort(&misc->y_free, (i - 1) & 1, misc))) break;
             tc_fence_after_sync();
           }
+          if constexpr (WIDE) {
+            // W shares the columns of S: the latent group must have taken the next chunk's scores
+            if (i + 1 < nchunks) {
+              if (!(ok = wait_or_abort(&misc->s_free, (i + 1) & 1, misc))) break;
+              tc_fence_after_sync();
+            }
+            // [W | Y0] = R^T [E | U_bf16]: one product of width 256 (k = latents); the B operand's four 64-wide blocks
+            // lie 16384 bytes apart (E t-blocks, then the two value blocks of the bf16 state)
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            mma_ss(tmem + TM_Y + (i & (YB - 1)) * 64, drm + (j * 2048 >> 4), du + (j * 2048 >> 4), ID_Y0, j > 0);
-            if (!WIDE)
+            for (int j = 0; j < 8; ++j) mma_ss(tmem + TM_W, drm + (j * 2048 >> 4), dem + (j * 2048 >> 4), ID_WY, j > 0);
+            tc_commit(&misc->w_ready);
+            TC_TRACE(2, i, 5);
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              mma_ss(tmem + TM_DEN, drm + (j * 2048 >> 4), db16 + (((j >> 2) * 2048 + (j & 3) * 32) >> 4), ID_DEN, j > 0);
+          } else {
+            // W = R^T E  (k = latents, 8 steps of 16 rows = 2048 bytes)
+#pragma unroll
+            for (int j = 0; j < 8; ++j) mma_ss(tmem + TM_W, drm + (j * 2048 >> 4), dem + (j * 2048 >> 4), ID_W, j > 0);
+            tc_commit(&misc->w_ready);
+            TC_TRACE(2, i, 5);
+            // Y = R^T U_bf16, Den0 = R^T d
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              mma_ss(tmem + TM_Y + (i & (YB - 1)) * 64, drm + (j * 2048 >> 4), du + (j * 2048 >> 4), ID_Y0, j > 0);
               mma_ss(tmem + TM_DEN + (i & (YB - 1)) * 16, drm + (j * 2048 >> 4),
                      db16 + (((j >> 2) * 2048 + (j & 3) * 32) >> 4), ID_DEN, j > 0);
+            }
           }
           TC_TRACE(2, i, 6);
         }
         // U += E V_c  (k = tokens of the chunk)
-        if (WIDE) {
-          if (!(ok = wait_or_abort(&misc->v_full[0], i & 1, misc))) break;
-          tc_fence_after_sync();
-        }
 #pragma unroll
         for (int j = 0; j < 8; ++j)
           mma_ss(tmem + TM_U, dek + (((j >> 2) * 16384 + (j & 3) * 32) >> 4), dv + (j * 2048 >> 4), ID_U, 1);
         tc_commit(&misc->u_done);
-        if (state_only) tc_commit(&misc->v_empty[WIDE ? 0 : (i & 1)]);  // no read-out MMA will read this V stage
+        if (state_only) tc_commit(&misc->v_empty[i & 1]);  // no read-out MMA will read this V stage
         TC_TRACE(2, i, 4);
       }
       if (!state_only && ok && nchunks > 0) ok = issue_tail(nchunks - 1);
@@ -463,8 +435,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       const uint32_t par = i & 1;
       const int nvalid = min(C, seg_end - (seg_begin + i * C));
       const int tok0 = hf * 64;
-      uint8_t* e_row = smem + OFF_E + (E_BUFS == 2 ? (i & 1) * 32768 : 0) + hf * 16384;  // t-block hf of the operand buffers
-      uint8_t* r_row = smem + OFF_R + (i & 1) * 32768 + hf * 16384;
+      uint8_t* e_row = smem + OFF_E + (ER_BUFS == 2 ? (i & 1) * 32768 : 0) + hf * 16384;  // t-block hf of the operand buffers
+      uint8_t* r_row = smem + OFF_R + (ER_BUFS == 2 ? (i & 1) * 32768 : 0) + hf * 16384;
       if (!(ok = wait_or_abort(&misc->s_ready, par, misc))) break;
       tc_fence_after_sync();
       if (tid == 0) TC_TRACE(0, i, 0);
@@ -542,8 +514,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       // phase a: E for the 64 tokens of this half (in place of the scores), their sum, E operand rows
       float tot0 = 0.f, tot1 = 0.f;
       float g16[4] = {0.f, 0.f, 0.f, 0.f};  // BLOCK: sums of the four groups of 16 tokens of this half
-      // single E buffer: the products that read the previous chunk's E (W, state update) must have run
-      if (E_BUFS == 1 && STABLE && i > 0 && !(ok = wait_or_abort(&misc->u_done, (i - 1) & 1, misc))) break;
+      // single E / R buffers: the products that read the previous chunk's E and R (they are all issued together and
+      // the state update comes last) must have run
+      if (ER_BUFS == 1 && STABLE && i > 0 && !(ok = wait_or_abort(&misc->u_done, (i - 1) & 1, misc))) break;
       if constexpr (STABLE) {
         // encoder weights sigma(s): packed and stored 8 tokens at a time; the raw scores stay in ra / rb for phase b
 #pragma unroll
@@ -604,7 +577,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         }
       }
       warp_arrive(&misc->psum[q], lane);
-      if (E_BUFS == 1 && !STABLE && i > 0 && !(ok = wait_or_abort(&misc->u_done, (i - 1) & 1, misc))) break;
+      if (ER_BUFS == 1 && !STABLE && i > 0 && !(ok = wait_or_abort(&misc->u_done, (i - 1) & 1, misc))) break;
       if constexpr (!STABLE)
 #pragma unroll
       for (int ch = 0; ch < 4; ++ch) {
@@ -726,15 +699,14 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       if (i > 0 && !(ok = wait_or_abort(&misc->u_done, (i - 1) & 1, misc))) break;
       tc_fence_after_sync();
       if (tid == 0) TC_TRACE(0, i, 4);
-      if (!WIDE && hf == 0 && !state_only)
+      if (hf == 0 && !state_only)
         *reinterpret_cast<__nv_bfloat16*>(smem + OFF_B16 + (m >> 6) * 2048 + ((m & 63) >> 3) * 16 + (m & 7) * 2) =
             __float2bfloat16_rn(d_carry);
       const bool need = __any_sync(0xffffffffu, alpha != 1.0f);
       if constexpr (WIDE) {
-        // 64 value columns per thread = value block hf.  The tensor-memory side runs first; the bf16 operand rows
-        // are held packed in registers until the previous chunk's read-out products have read the operand buffer.
+        // 64 value columns per thread = value block hf of the bf16 state operand (free: the products that read it
+        // were issued before the state update this thread has just waited for)
         if (!state_only || need) {
-          uint32_t pk[32];
 #pragma unroll
           for (int c0 = 0; c0 < 64; c0 += 32) {
             uint32_t r[32];
@@ -746,18 +718,17 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
               for (int k = 0; k < 32; ++k) r[k] = __float_as_uint(__uint_as_float(r[k]) * alpha);
               tmem_st32(tl + TM_U + hf * 64 + c0, r);
             }
+            if (!state_only) {
 #pragma unroll
-            for (int k = 0; k < 16; ++k)
-              pk[(c0 >> 1) + k] = pack_bf16(__uint_as_float(r[2 * k]), __uint_as_float(r[2 * k + 1]));
-          }
-          if (!state_only) {
-            if (tid == 0) TC_TRACE(0, i, 6);
-            if (i > 0 && !(ok = wait_or_abort(&misc->tail_done, (i - 1) & 1, misc))) break;
-            if (tid == 0) TC_TRACE(0, i, 7);
-#pragma unroll
-            for (int ch = 0; ch < 8; ++ch)
-              *reinterpret_cast<uint4*>(smem + OFF_U + hf * 16384 + swz_chunk_off(m, ch)) =
-                  make_uint4(pk[ch * 4], pk[ch * 4 + 1], pk[ch * 4 + 2], pk[ch * 4 + 3]);
+              for (int ch = 0; ch < 4; ++ch) {
+                uint4 v;
+                v.x = pack_bf16(__uint_as_float(r[ch * 8 + 0]), __uint_as_float(r[ch * 8 + 1]));
+                v.y = pack_bf16(__uint_as_float(r[ch * 8 + 2]), __uint_as_float(r[ch * 8 + 3]));
+                v.z = pack_bf16(__uint_as_float(r[ch * 8 + 4]), __uint_as_float(r[ch * 8 + 5]));
+                v.w = pack_bf16(__uint_as_float(r[ch * 8 + 6]), __uint_as_float(r[ch * 8 + 7]));
+                *reinterpret_cast<uint4*>(smem + OFF_U + hf * 16384 + swz_chunk_off(m, (c0 >> 3) + ch)) = v;
+              }
+            }
           }
           if (need) tmem_wait_st();
         }
@@ -814,9 +785,6 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         }
         if (need) tmem_wait_st();
       }
-      if (WIDE && hf == 0 && !state_only)  // (after the wait for the previous chunk's read-out products above)
-        *reinterpret_cast<__nv_bfloat16*>(smem + OFF_B16 + (m >> 6) * 2048 + ((m & 63) >> 3) * 16 + (m & 7) * 2) =
-            __float2bfloat16_rn(d_carry);
       fence_proxy_async_smem();
       tc_fence_before_sync();
       warp_arrive(&misc->p1_done, lane);
@@ -916,7 +884,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       if (tid == 256) TC_TRACE(1, i, 1);
 
       // normalise and store (wide: the first of the two value blocks; two accumulator phases per chunk)
-      if (!(ok = wait_or_abort(&misc->y_ready, WIDE ? 0 : par, misc))) break;
+      if (!(ok = wait_or_abort(&misc->y_ready, par, misc))) break;
       tc_fence_after_sync();
       if (tid == 256) TC_TRACE(1, i, 2);
       uint32_t den0;
@@ -940,21 +908,15 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       // log-sum-exp of the token's decode scores = log of the decode weights' mass in the frame kappa
       if (!SPLIT && p.lse_dec != nullptr && tt < nvalid && value_col0<ZS, SPLIT>() == 0)
         p.lse_dec[(int64_t)lane_id * p.N + t0 + tt] = (misc->kap[par] + __log2f(den)) * kLn2;
-      // The accumulator goes back to the MMA issuer as soon as its 64 columns are in registers (single-buffered
-      // instances); scaling and the stores follow.  Wide: two value blocks per chunk through the one accumulator.
+      // The accumulator goes back to the MMA issuer as soon as its columns are in registers (single-buffered
+      // instances); scaling and the stores follow.  Wide: two value blocks of 64 columns, handed back after the second.
 #pragma unroll
-      for (int vb = 0; vb < (WIDE ? 2 : 1); ++vb) {
-        if (vb == 1) {
-          if (tid == 256) TC_TRACE(1, i, 4);
-          if (!(ok = wait_or_abort(&misc->y_ready, 1, misc))) break;
-          tc_fence_after_sync();
-          if (tid == 256) TC_TRACE(1, i, 5);
-        }
+      for (int vb = 0; vb < VB; ++vb) {
         uint32_t ra[32], rb[32];
-        tmem_ld32(tl + TM_Y + (i & (YB - 1)) * 64, ra);
-        tmem_ld32(tl + TM_Y + (i & (YB - 1)) * 64 + 32, rb);
+        tmem_ld32(tl + TM_Y + (i & (YB - 1)) * 64 + vb * 64, ra);
+        tmem_ld32(tl + TM_Y + (i & (YB - 1)) * 64 + vb * 64 + 32, rb);
         tmem_wait_ld();
-        if (YB == 1) {
+        if (YB == 1 && vb == VB - 1) {
           tc_fence_before_sync();
           warp_arrive(&misc->y_free, lane);
         }
