@@ -82,7 +82,10 @@ struct Lay {
   static constexpr int OFF_MISC = OFF_B16 + 4096;          // barriers, tmem slot, reductions          4608 B
   static constexpr int OFF_STAGE = OFF_MISC + 4608;        // 4 token warps x [32 t][32 columns] 16-bit: source of the
                                                            // read-out's bulk stores (64-byte swizzle)     8 KB
-  static constexpr int SMEM_BYTES = OFF_STAGE + 8192 + 1024;  // + slack for manual 1024-byte alignment
+  // wide, two latent groups merged on chip: the partner CTA's normalised partial rows of the value block this CTA
+  // finalises, [128 t][64] fp16 (16-byte pieces swizzled by row), and the log2 weight mass per row
+  static constexpr int OFF_XCH = OFF_STAGE + 8192;         //                                          16 KB + 512 B
+  static constexpr int SMEM_BYTES = OFF_XCH + (WIDE ? 16384 + 512 : 0) + 1024;  // + slack for manual 1024-byte alignment
   static_assert(SMEM_BYTES <= 232448, "shared memory");
   // tensor-memory columns.  The Y / Den accumulators are double-buffered when the columns allow it (Dk = 64).
   // Wide: W shares the columns of S (the latent group has the next chunk's scores in registers before W of this
@@ -99,6 +102,8 @@ struct Misc {
   uint64_t q_full, k_full, k_empty, v_full[2], v_empty[2];
   uint64_t s_ready, s_free, kap_done, p1_done, u_done, w_ready, p2_done, y_ready, y_free;
   uint64_t pmax[4], psum[4];  // pair barriers of the two latent half-groups, one per lane quarter
+  uint64_t xfull[4], xfree[4];  // on-chip merge of two latent groups, per token warp: the partner's rows have arrived /
+                                // the partner has read the rows this CTA sent
   uint32_t tmem_base;
   volatile int abort_flag;
   float wmax[2][4];
@@ -110,7 +115,7 @@ struct Misc {
 // optional cycle trace of CTA (0, 0): [role][chunk < 16][slot < 8] clock64 stamps (diagnostic hook, null in normal use)
 #define TC_TRACE(role, chunk, slot)                                                                   \
   do {                                                                                                \
-    if (p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && (chunk) < 16)                     \
+    if (p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (chunk) < 16)                   \
       p.trace[((role) * 16 + (chunk)) * 8 + (slot)] = clock64();                                      \
   } while (0)
 
@@ -211,6 +216,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     mbar_init(&misc->p2_done, 4);
     mbar_init(&misc->y_ready, 1);
     mbar_init(&misc->y_free, 4);
+    for (int i = 0; i < 4; ++i) {
+      mbar_init(&misc->xfull[i], 1);
+      mbar_init(&misc->xfree[i], 32);
+    }
     misc->abort_flag = 0;
     fence_barrier_init();
   }
@@ -224,6 +233,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
+  // on-chip merge: the partner CTA arrives on this CTA's barriers, which must be initialised first
+  const bool xmerge = WIDE && SPLIT && p.cluster_merge != 0;
+  if (xmerge) cluster_sync_all();
   const uint32_t tmem = misc->tmem_base;
   bool ok = true;
   // No read-out wanted (segment states for a scan, prefix states): only E and U += E V are computed; R, W, the
@@ -903,11 +915,120 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         }
       }
       const float inv = (SPLIT && !den_ok) ? 0.f : rcp_approx(den);  // (a true division compiles to a call here)
-      if (SPLIT && p.part_y != nullptr && tt < nvalid && value_col0<ZS, SPLIT>() == 0)
+      if (SPLIT && !xmerge && p.part_y != nullptr && tt < nvalid && value_col0<ZS, SPLIT>() == 0)
         p.part_lw[(part_row0 + t0 + tt) * p.H + h] = den_ok ? misc->kap[par] + __log2f(den) : -INFINITY;
       // log-sum-exp of the token's decode scores = log of the decode weights' mass in the frame kappa
       if (!SPLIT && p.lse_dec != nullptr && tt < nvalid && value_col0<ZS, SPLIT>() == 0)
         p.lse_dec[(int64_t)lane_id * p.N + t0 + tt] = (misc->kap[par] + __log2f(den)) * kLn2;
+      if constexpr (WIDE && SPLIT) {
+        if (xmerge) {
+          // Two latent groups = two CTAs of a cluster.  CTA r finalises value block r: it sends its normalised
+          // partial of the OTHER block (fp16) and the log2 of its weight mass into the partner's shared memory,
+          // takes the partner's rows for its own block, and stores y = sum_g w_g y_g / sum_g w_g.
+          const uint32_t rank = cluster_ctarank(), peer = rank ^ 1u;
+          const float lw_own = den_ok ? misc->kap[par] + __log2f(den) : -INFINITY;
+          uint32_t ra[32], rb[32], pk[32];
+          // The exchange tile was the source of the previous chunk's bulk stores: once they have read it the partner
+          // may send this chunk's rows (32 rows x 128 bytes and 32 weight masses per warp), which the barrier counts.
+          if (lane == 0) {
+            bulk_wait_group_read0();
+            mbar_arrive_expect_tx(&misc->xfull[wq], 4096 + 128);
+          }
+          __syncwarp();
+          if (i > 0) mbar_arrive_cluster_relaxed(mapa_shared(smem_u32(&misc->xfree[wq]), peer));
+          // the partner's block, normalised, as fp16 pairs; then this CTA's block; the accumulator is free again
+          tmem_ld32(tl + TM_Y + peer * 64, ra);
+          tmem_ld32(tl + TM_Y + peer * 64 + 32, rb);
+          tmem_wait_ld();
+#pragma unroll
+          for (int k = 0; k < 16; ++k) {
+            pk[k] = pack_f16(__uint_as_float(ra[2 * k]) * inv, __uint_as_float(ra[2 * k + 1]) * inv);
+            pk[16 + k] = pack_f16(__uint_as_float(rb[2 * k]) * inv, __uint_as_float(rb[2 * k + 1]) * inv);
+          }
+          tmem_ld32(tl + TM_Y + rank * 64, ra);
+          tmem_ld32(tl + TM_Y + rank * 64 + 32, rb);
+          tmem_wait_ld();
+          tc_fence_before_sync();
+          warp_arrive(&misc->y_free, lane);
+          // (1) send: the rows sent for chunk i - 1 must have been read by the partner.  The stores are asynchronous and
+          // count their bytes on the partner's barrier: plain remote stores followed by a releasing arrive cost 1600
+          // cycles per chunk here.  Every thread sends the eight 16-byte pieces of its row, in the tile's layout.
+          if (i > 0 && !(ok = tc::wait_or_abort_cluster(&misc->xfree[wq], (i - 1) & 1, &misc->abort_flag))) break;
+          {
+            const uint32_t xw = mapa_shared(smem_u32(smem + L::OFF_XCH + wq * 4096), peer);
+            const uint32_t xbar = mapa_shared(smem_u32(&misc->xfull[wq]), peer);
+#pragma unroll
+            for (int half = 0; half < 2; ++half)
+#pragma unroll
+              for (int ch = 0; ch < 4; ++ch)
+                st_async_v4(xw + half * 2048 + lane * 64 + ((ch ^ ((lane >> 1) & 3)) << 4),
+                            make_uint4(pk[half * 16 + ch * 4], pk[half * 16 + ch * 4 + 1], pk[half * 16 + ch * 4 + 2],
+                                       pk[half * 16 + ch * 4 + 3]), xbar);
+            st_async_b32(mapa_shared(smem_u32(smem + L::OFF_XCH + 16384 + tt * 4), peer), __float_as_uint(lw_own), xbar);
+          }
+          if (tid == 256) TC_TRACE(1, i, 4);
+          // (2) receive the partner's rows of this CTA's block
+          if (!(ok = tc::wait_or_abort_cluster(&misc->xfull[wq], par, &misc->abort_flag))) break;
+          if (tid == 256) TC_TRACE(1, i, 5);
+          const float lw_p = *reinterpret_cast<const float*>(smem + L::OFF_XCH + 16384 + tt * 4);
+          uint4 xp[8];
+#pragma unroll
+          for (int ch = 0; ch < 8; ++ch)  // [warp][32-column half][32 rows x 64 bytes, 16-byte pieces swizzled as in the staging tile]
+            xp[ch] = *reinterpret_cast<const uint4*>(smem + L::OFF_XCH + wq * 4096 + (ch >> 2) * 2048 + lane * 64 +
+                                                     (((ch & 3) ^ ((lane >> 1) & 3)) << 4));
+          const float mx = fmaxf(lw_own, lw_p);
+          float ca = 0.f, cb = 0.f;  // coefficients of the raw accumulator values and of the partner's normalised rows
+          if (mx == -INFINITY) {
+            // every group's weights underflowed: outside the numeric domain of this path
+            if (rank == 0 && tt < nvalid) {
+              atomicOr(p.err, 2);
+              if (p.gate != nullptr) {
+                p.gate[0] = 1;
+                p.gate[1 + lane_id] = 1;
+              }
+            }
+          } else {
+            const float wa = ex2_approx(lw_own - mx), wb = ex2_approx(lw_p - mx);
+            const float iw = rcp_approx(wa + wb);
+            ca = wa * iw * inv;
+            cb = wb * iw;
+            if (rank == 0 && p.lse_dec != nullptr && tt < nvalid)
+              p.lse_dec[(int64_t)lane_id * p.N + t0 + tt] = (mx + __log2f(wa + wb)) * kLn2;
+          }
+          // The merged rows go out from the exchange tile itself (its layout is the bulk store's 64-byte swizzle and
+          // the partner's rows are in registers by now): both 32-column tiles are stored without waiting on each other.
+          uint8_t* const xt = smem + L::OFF_XCH + wq * 4096;
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            const uint32_t(&r)[32] = half ? rb : ra;
+#pragma unroll
+            for (int ch = 0; ch < 4; ++ch) {
+              const uint4 x = xp[half * 4 + ch];
+              const uint32_t xw[4] = {x.x, x.y, x.z, x.w};
+              uint32_t o[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&xw[j]));
+                o[j] = pack_bf16(__uint_as_float(r[ch * 8 + 2 * j]) * ca + f.x * cb,
+                                 __uint_as_float(r[ch * 8 + 2 * j + 1]) * ca + f.y * cb);
+              }
+              *reinterpret_cast<uint4*>(xt + half * 2048 + lane * 64 + ((ch ^ ((lane >> 1) & 3)) << 4)) =
+                  make_uint4(o[0], o[1], o[2], o[3]);
+            }
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_4d(&tm_y, xt, (int)rank * 64, h, t0 + wq * 32, b);
+            tma_store_4d(&tm_y, xt + 2048, (int)rank * 64 + 32, h, t0 + wq * 32, b);
+            bulk_commit_group();
+          }
+          // (the partner learns that the tile is free when the next chunk's epilogue begins, see above: by then the
+          // stores have long read it; it does not send before its own next epilogue anyway)
+          if (tid == 256) TC_TRACE(1, i, 3);
+          continue;
+        }
+      }
       // The accumulator goes back to the MMA issuer as soon as its columns are in registers (single-buffered
       // instances); scaling and the stores follow.  Wide: two value blocks of 64 columns, handed back after the second.
 #pragma unroll
@@ -982,6 +1103,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   }
   tc_fence_before_sync();
   __syncthreads();
+  // the partner may still write to this CTA's shared memory or arrive on its barriers until it is done as well
+  if (xmerge) cluster_sync_all();
   if (warp == 12) tmem_dealloc(tmem, TM_COLS);
 }
 
@@ -996,7 +1119,24 @@ int launch_keep(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap&
   FLARE_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Lay<DKB, WIDE>::SMEM_BYTES));
   LaunchTimer timer(p.y == nullptr ? "prefill_tc_kernel (state only)" : (WIDE ? "prefill_tc_kernel (wide)" : "prefill_tc_kernel"),
                     stream);
-  kern<<<grid, NTHREADS, Lay<DKB, WIDE>::SMEM_BYTES, stream>>>(tq, tk, tv, ty, p);
+  if (WIDE && SPLIT && p.cluster_merge) {
+    // the two latent-group CTAs of a lane (adjacent in grid.z) as one thread-block cluster
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(NTHREADS);
+    cfg.dynamicSmemBytes = Lay<DKB, WIDE>::SMEM_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 1;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 2;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    FLARE_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kern, tq, tk, tv, ty, p));
+  } else {
+    kern<<<grid, NTHREADS, Lay<DKB, WIDE>::SMEM_BYTES, stream>>>(tq, tk, tv, ty, p);
+  }
   FLARE_CUDA_CHECK(cudaGetLastError());
   return FLARE_OK;
 }
@@ -1196,27 +1336,6 @@ int launch_prefill_tc(const flare_fwd_args_t* a, const TcParams& p_in, int nseg_
     }
   }
   const int groups = prefill_tc_latent_groups(a);
-  // Read-out rows leave through tiled bulk stores of 32 tokens x 32 columns (64-byte swizzle): into y, or with several
-  // latent groups into the dense fp16 partials.  Per-row lengths (rows beyond a length stay untouched) and output
-  // strides the tiled copy cannot express fall back to per-thread stores.
-  CUtensorMap ty = tk;
-  p.y_tma = 0;
-  if (p.y != nullptr && a->lengths == nullptr) {
-    const uint32_t box[4] = {32, 1, 32, 1};
-    if (groups > 1) {
-      const uint64_t dims[4] = {(uint64_t)a->Dv, (uint64_t)a->H, (uint64_t)a->N, (uint64_t)groups * a->B};
-      const int64_t str[3] = {a->Dv, (int64_t)a->H * a->Dv, (int64_t)a->N * a->H * a->Dv};
-      p.y_tma = tc::make_map_bf16(&ty, p.part_y, 4, dims, str, box, CU_TENSOR_MAP_SWIZZLE_64B) ? 1 : 0;
-    } else {
-      const int64_t str[3] = {p.y_stride_h, p.y_stride_n, p.y_stride_b};
-      bool ok = (reinterpret_cast<uintptr_t>(p.y) % 16) == 0;
-      for (int64_t st : str) ok = ok && st > 0 && (st % 8) == 0 && st < (int64_t(1) << 39);
-      const uint64_t dims[4] = {(uint64_t)a->Dv, (uint64_t)a->H, (uint64_t)a->N, (uint64_t)a->B};
-      p.y_tma = ok && tc::make_map_bf16(&ty, p.y, 4, dims, str, box, CU_TENSOR_MAP_SWIZZLE_64B) ? 1 : 0;
-    }
-  }
-  if (const char* env = getenv("FLARE_B200_ROW_STORES"))  // diagnostic: per-thread row stores instead
-    if (env[0] == '1') p.y_tma = 0;
   const bool padded = (a->M % M) != 0;
   const int mode = a->variant == FLARE_STABLEMAX ? 2 : (a->block_size > 1 ? 1 : 0);
   // (128, 128) heads: two CTAs per (lane, group), each repeating the score / E / R work for 64 value columns, while
@@ -1226,6 +1345,36 @@ int launch_prefill_tc(const flare_fwd_args_t* a, const TcParams& p_in, int nseg_
               (int64_t)a->B * a->H * nseg_grid * groups * 2 > sm_count();
   if (const char* env = getenv("FLARE_B200_WIDE"))
     wide = a->Dk == 128 && a->Dv == 128 && !padded && p.dump_u == nullptr && env[0] == '1';
+  // Read-out rows leave through tiled bulk stores of 32 tokens x 32 columns (64-byte swizzle): into y, or with several
+  // latent groups into the dense fp16 partials.  Per-row lengths (rows beyond a length stay untouched) and output
+  // strides the tiled copy cannot express fall back to per-thread stores.
+  CUtensorMap ty = tk;
+  p.y_tma = 0;
+  p.cluster_merge = 0;
+  if (p.y != nullptr && a->lengths == nullptr) {
+    const uint32_t box[4] = {32, 1, 32, 1};
+    const int64_t str[3] = {p.y_stride_h, p.y_stride_n, p.y_stride_b};
+    bool y_ok = (reinterpret_cast<uintptr_t>(p.y) % 16) == 0;
+    for (int64_t st : str) y_ok = y_ok && st > 0 && (st % 8) == 0 && st < (int64_t(1) << 39);
+    const uint64_t ydims[4] = {(uint64_t)a->Dv, (uint64_t)a->H, (uint64_t)a->N, (uint64_t)a->B};
+    // wide instance with exactly two latent groups: the two CTAs of a lane merge on chip (thread-block cluster) and
+    // store y themselves.  FLARE_B200_CLUSTER=0 keeps the partials in global memory and the merge kernel.
+    bool cluster = wide && groups == 2 && y_ok;
+    if (const char* env = getenv("FLARE_B200_CLUSTER"))
+      if (env[0] == '0') cluster = false;
+    if (cluster && tc::make_map_bf16(&ty, p.y, 4, ydims, str, box, CU_TENSOR_MAP_SWIZZLE_64B)) {
+      p.y_tma = 1;
+      p.cluster_merge = 1;
+    } else if (groups > 1) {
+      const uint64_t dims[4] = {(uint64_t)a->Dv, (uint64_t)a->H, (uint64_t)a->N, (uint64_t)groups * a->B};
+      const int64_t pstr[3] = {a->Dv, (int64_t)a->H * a->Dv, (int64_t)a->N * a->H * a->Dv};
+      p.y_tma = tc::make_map_bf16(&ty, p.part_y, 4, dims, pstr, box, CU_TENSOR_MAP_SWIZZLE_64B) ? 1 : 0;
+    } else {
+      p.y_tma = y_ok && tc::make_map_bf16(&ty, p.y, 4, ydims, str, box, CU_TENSOR_MAP_SWIZZLE_64B) ? 1 : 0;
+    }
+  }
+  if (const char* env = getenv("FLARE_B200_ROW_STORES"))  // diagnostic: per-thread row stores instead
+    if (env[0] == '1' && !p.cluster_merge) p.y_tma = 0;
   const dim3 grid(a->B * a->H, nseg_grid, wide ? groups : a->Dv / D * groups);
   int rc;
   const int combo = a->Dk == 128 ? 1 : (a->Dv == 128 ? 2 : 0);  // (64, 64), (128, 128), (64, 128)
@@ -1241,7 +1390,7 @@ int launch_prefill_tc(const flare_fwd_args_t* a, const TcParams& p_in, int nseg_
   else
     rc = groups > 1 ? launch_prefill_tc_unit<5>(padded, mode, tq, tk, tv, ty, p, grid, stream)
                     : launch_prefill_tc_unit<2>(padded, mode, tq, tk, tv, ty, p, grid, stream);
-  if (rc != FLARE_OK || groups == 1 || p.y == nullptr) return rc;
+  if (rc != FLARE_OK || groups == 1 || p.y == nullptr || p.cluster_merge) return rc;
   const int64_t rows = (int64_t)a->B * a->N * a->H;
   const int64_t threads = rows * (a->Dv / 8);
   LaunchTimer timer("tc_merge_groups_kernel", stream);

@@ -27,6 +27,10 @@ struct TcParams {
   // the read-out rows leave through tiled bulk stores (set by the launch when the output's strides allow it and no
   // per-row lengths are given); otherwise every thread stores its own row
   int y_tma;
+  // Two latent groups on the wide instance: the two CTAs of a lane form a thread-block cluster and merge their
+  // partial read-outs on chip (each finalises one 64-column value block); no partials in global memory, no merge
+  // kernel.  Set by the launch.
+  int cluster_merge;
   int out_mode;  // 0: none, 1: every segment, 2: last segment only
   int nseg_total;
   const int32_t* lens;       // [B] tokens per batch row (right padding beyond), or null

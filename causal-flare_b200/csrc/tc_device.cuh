@@ -41,6 +41,16 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, vo
   return false;
 }
 
+// the same for a barrier that threads of the partner CTA of a cluster arrive on
+__device__ __forceinline__ bool wait_or_abort_cluster(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+#pragma unroll 1
+  for (uint32_t slice = 0; slice < kWaitSlices; ++slice) {
+    if (mbar_try_wait_cluster(bar, parity, kWaitSliceNs)) return true;
+    if (*abort_flag != 0) return false;
+  }
+  return false;
+}
+
 // stablemax encoder weight with approximate reciprocal; powers 1..4 by multiplication
 __device__ __forceinline__ float sigma_fast(float x, float p) {
   const float base = 1.0f + fabsf(x);

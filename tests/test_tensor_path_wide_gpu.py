@@ -20,9 +20,13 @@ def run(q, k, v, **kw):
     return out
 
 
-@pytest.fixture
-def wide(monkeypatch):
+@pytest.fixture(params=["on-chip merge", "merge kernel"])
+def wide(monkeypatch, request):
+    # two latent groups (M = 256): the two CTAs of a lane merge on chip as a thread-block cluster by default;
+    # FLARE_B200_CLUSTER=0 keeps the partials in global memory and the merge kernel (the path M = 384 / 512 always take)
     monkeypatch.setenv("FLARE_B200_WIDE", "1")
+    if request.param == "merge kernel":
+        monkeypatch.setenv("FLARE_B200_CLUSTER", "0")
     return monkeypatch
 
 
