@@ -17,19 +17,26 @@
 //   E[m,t]   = exp(s[m,t] - c_m)           one exp per element, thread m scans its row
 //   D[m,t]   = d_m + cumsum_t E[m,t]       (d_m already rescaled into the new frame)
 //   R[m,t]   = E[m,t] exp(c_m - kappa) / D[m,t]        = softmax-numerator / encoder denominator
-//   W    = R^T E   (tokens x tokens)       MMA4  -> causal mask + bf16, written back to TMEM
-//   Y    = R^T U_bf16   ,  Den0 = R^T d    MMA3  (+ a 16-column MMA for the denominator column)
-//   U   += E V_c                           MMA2
-//   Y   += tril(W) V_c                     MMA5  (A operand from TMEM)
+//   [W | Y | Den0] = R^T [E | U_bf16 | d]   MMA2  ONE product of width 208 (256 with two value blocks, Den0 separate):
+//                                                  W = R^T E (tokens x tokens), Y = R^T U_bf16, Den0 = R^T d
+//   W -> causal mask + bf16, written back to TMEM (token group)
+//   U   += E V_c                           MMA3
+//   Y   += tril(W) V_c                     MMA4  (A operand from TMEM)
 //   y_t  = Y[t,:] / (Den0[t] + rowsum tril(W)[t,:])
 //
 // Operands E, R (written by the latent threads row-wise) feed MMAs both K-major and MN-major from the same
-// 128-byte-swizzled buffers, so no transposition pass exists.
+// 128-byte-swizzled buffers, so no transposition pass exists.  E, the bf16 copy of the state and the block whose
+// column 0 is d lie behind one another in shared memory, so that they form ONE MN-major B operand and R is read once
+// for all three products (28 MMA instructions per chunk at Dk = 64 instead of 44: every instruction costs 100-190
+// cycles from issue to issue in this kernel whatever its width, 49-130 cycles alone).
 //
 // Warp roles (14 warps): 0-7 "latent group" (two warps per lane quarter, each half of the chunk's tokens): scores ->
 // E, R, state rescale (chunk i+1);  8-11 "token group": causal mask of W, normalisation and store of Y (chunk i);
-// 12: MMA issuer (one thread);  13: TMA producer (one thread).  The three stages work on consecutive chunks concurrently: E/R operand buffers and the Y / Den
-// accumulators are double-buffered, K is single-buffered (free as soon as its score MMA has run), V has two stages.
+// 12: MMA issuer (one thread);  13: TMA producer (one thread).  The three stages work on consecutive chunks
+// concurrently.  E and R have one buffer each (every product that reads them is issued when the latent group has
+// finished the chunk; the latent group waits for the state update of the previous chunk before it writes E), the
+// accumulators [W | Y | Den0] are single and go back to the MMA issuer as soon as the token group has them in
+// registers, K is single-buffered (free as soon as its score MMA has run), V has two stages.
 #include "prefill_tc.cuh"
 
 #include <cuda.h>
@@ -66,20 +73,23 @@ struct Lay {
   // Dk = 64: the latent bank stays in shared memory (TMA-loaded); Dk = 128 has no room for it there and keeps it in
   // tensor memory as the A operand of the score MMA
   static constexpr bool Q_SMEM = DKB == 1;
-  // operand buffers of E and R: two each, or (wide) one each: there every product that reads R is issued at once
-  // when the latent group has finished a chunk, so the buffers are free long before the next chunk writes them
-  static constexpr int ER_BUFS = WIDE ? 1 : 2;
+  // Every product that reads R (W, Y0, Den0) is ONE tcgen05.mma sequence over a B operand of adjacent 64-wide
+  // MN-major blocks [E t-block 0 | E t-block 1 | U_bf16 ... | d], issued when the latent group has finished a chunk:
+  // R is read once, and E and R need one buffer each (free long before the next chunk writes them).
   static constexpr int VB = WIDE ? 2 : 1;                  // 64-column value blocks per CTA
   static constexpr int OFF_Q = 0;                          // [128 m][64] bf16, K-major                 16 KB or 0
   static constexpr int OFF_K = Q_SMEM ? 16384 : 0;         // DKB x [128 t][64] bf16                    16 KB each
   static constexpr int OFF_V = OFF_K + DKB * 16384;        // 2 stages x [VB value blocks][128 t][64]   16 KB each
-  static constexpr int OFF_E = OFF_V + 2 * VB * 16384;     // ER_BUFS x [2 t-blocks][128 m][64 t] bf16  32 KB each
-  // wide: the bf16 state operand follows E directly, so that one MN-major B operand of four 64-wide blocks
-  // [E t-block 0 | E t-block 1 | U value block 0 | U value block 1] feeds the merged product [W | Y0]
-  static constexpr int OFF_U = WIDE ? OFF_E + 32768 : OFF_E + 4 * 32768;  // [VB][128 m][64 dv] bf16    16 KB each
-  static constexpr int OFF_R = WIDE ? OFF_U + 32768 : OFF_E + 2 * 32768;  // ER_BUFS x [2 t-blocks][128 m][64 t]
-  static constexpr int OFF_B16 = WIDE ? OFF_R + 32768 : OFF_U + 16384;    // [2 m-blocks][16 n][64 m] bf16  4 KB
-  static constexpr int OFF_MISC = OFF_B16 + 4096;          // barriers, tmem slot, reductions          4608 B
+  static constexpr int OFF_E = OFF_V + 2 * VB * 16384;     // [2 t-blocks][128 m][64 t] bf16            32 KB
+  // merged product: the bf16 state operand follows E directly; with one value block the denominator follows as a
+  // fourth MN-major block [128 m][64] of which column 0 holds d (product width 128 + 64 + 16 = 208); with two value
+  // blocks the width is 256 already and Den0 stays a product of its own over the small K-major d tile
+  static constexpr int OFF_U = OFF_E + 32768;              // [VB][128 m][64 dv] bf16                    16 KB each
+  static constexpr int OFF_B16 = OFF_U + VB * 16384;       // d: MN-major block 16 KB, or (wide) the K-major tile
+                                                           // [2 m-blocks][16 n][64 m] 4 KB
+  static constexpr int D_BYTES = WIDE ? 4096 : 16384;
+  static constexpr int OFF_R = OFF_B16 + D_BYTES;          // [2 t-blocks][128 m][64 t] bf16              32 KB
+  static constexpr int OFF_MISC = OFF_R + 32768;           // barriers, tmem slot, reductions          4608 B
   static constexpr int OFF_STAGE = OFF_MISC + 4608;        // 4 token warps x [32 t][32 columns] 16-bit: source of the
                                                            // read-out's bulk stores (64-byte swizzle)     8 KB
   // wide, two latent groups merged on chip: the partner CTA's normalised partial rows of the value block this CTA
@@ -87,13 +97,11 @@ struct Lay {
   static constexpr int OFF_XCH = OFF_STAGE + 8192;         //                                          16 KB + 512 B
   static constexpr int SMEM_BYTES = OFF_XCH + (WIDE ? 16384 + 512 : 0) + 1024;  // + slack for manual 1024-byte alignment
   static_assert(SMEM_BYTES <= 232448, "shared memory");
-  // tensor-memory columns.  The Y / Den accumulators are double-buffered when the columns allow it (Dk = 64).
-  // Wide: W shares the columns of S (the latent group has the next chunk's scores in registers before W of this
-  // chunk is written), Y follows W directly (one product writes both) and U takes 128 columns.
-  static constexpr int YB = DKB == 1 ? 2 : 1;
-  static constexpr uint32_t TM_S = 0, TM_W = WIDE ? 0 : 128, TM_U = 256, TM_Y = WIDE ? 128 : 320,
-                            TM_DEN = WIDE ? 384 : TM_Y + YB * 64,
-                            TM_Q = TM_DEN + YB * 16 /* Dk / 2 columns of packed bf16 (Dk = 128 only) */;
+  // tensor-memory columns.  [W | Y | Den] are adjacent (one product writes them); single accumulators, handed back by
+  // the token group as soon as it has them in registers.  Wide: W shares the columns of S (the latent group has the
+  // next chunk's scores in registers before W of this chunk is written) and U takes 128 columns.
+  static constexpr uint32_t TM_S = 0, TM_W = WIDE ? 0 : 128, TM_Y = TM_W + 128, TM_DEN = WIDE ? 384 : TM_Y + 64,
+                            TM_U = WIDE ? 256 : TM_DEN + 16, TM_Q = WIDE ? 400 : TM_U + 64 /* packed bf16 (Dk = 128 only) */;
   static_assert(TM_Q + (Q_SMEM ? 0 : DKB * 32) <= 512, "tensor memory columns");
 };
 constexpr uint32_t TM_COLS = 512;
@@ -175,8 +183,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   constexpr int ZS = WIDE ? 1 : DVB;  // value slices on grid.z
   constexpr bool BLOCK = MODE == 1, STABLE = MODE == 2;
   constexpr int OFF_K = L::OFF_K, OFF_V = L::OFF_V, OFF_E = L::OFF_E, OFF_R = L::OFF_R, OFF_U = L::OFF_U,
-                OFF_B16 = L::OFF_B16, OFF_Q = L::OFF_Q, OFF_MISC = L::OFF_MISC, YB = L::YB, ER_BUFS = L::ER_BUFS,
-                VB = L::VB;
+                OFF_B16 = L::OFF_B16, OFF_Q = L::OFF_Q, OFF_MISC = L::OFF_MISC, VB = L::VB, D_BYTES = L::D_BYTES;
   constexpr bool Q_SMEM = L::Q_SMEM;
   constexpr uint32_t TM_S = L::TM_S, TM_W = L::TM_W, TM_U = L::TM_U, TM_Y = L::TM_Y, TM_DEN = L::TM_DEN, TM_Q = L::TM_Q;
   extern __shared__ uint8_t smem_dyn[];
@@ -224,7 +231,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     fence_barrier_init();
   }
   // zero the denominator operand tile once (rows 1..15 stay zero for the whole kernel)
-  for (int i = tid; i < 4096 / 16; i += NTHREADS) reinterpret_cast<uint4*>(smem + OFF_B16)[i] = make_uint4(0, 0, 0, 0);
+  for (int i = tid; i < D_BYTES / 16; i += NTHREADS) reinterpret_cast<uint4*>(smem + OFF_B16)[i] = make_uint4(0, 0, 0, 0);
 
   if (warp == 12) {
     tmem_alloc(&misc->tmem_base, TM_COLS);
@@ -272,19 +279,18 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     // ======================================= MMA issuer =======================================
     if (lane == 0) {
       const uint32_t k_addr = smem_u32(smem + OFF_K);
-      const uint32_t u_addr = smem_u32(smem + OFF_U), b16_addr = smem_u32(smem + OFF_B16);
+      const uint32_t b16_addr = smem_u32(smem + OFF_B16);
       constexpr uint32_t ID_S = make_idesc_bf16(128, 128, 0, 0);   // Q (TMEM) x K_c (K-major)
       constexpr uint32_t ID_U = make_idesc_bf16(128, WIDE ? 128 : 64, 0, 1);  // E (K-major) x V (MN-major)
-      constexpr uint32_t ID_Y0 = make_idesc_bf16(128, 64, 1, 1);   // R (MN-major) x U_bf16 (MN-major)
       constexpr uint32_t ID_DEN = make_idesc_bf16(128, 16, 1, 0);  // R (MN-major) x d tile (K-major)
-      constexpr uint32_t ID_W = make_idesc_bf16(128, 128, 1, 1);   // R (MN-major) x E (MN-major)
       constexpr uint32_t ID_Y1 = make_idesc_bf16(128, WIDE ? 128 : 64, 0, 1);  // tril(W) (TMEM) x V (MN-major)
-      constexpr uint32_t ID_WY = make_idesc_bf16(128, 256, 1, 1);  // wide: R (MN-major) x [E | U_bf16] (MN-major)
+      // merged: R (MN-major) x [E | U_bf16 (| d)] (MN-major), width 256 with two value blocks, 208 with one
+      constexpr uint32_t ID_WY = make_idesc_bf16(128, WIDE ? 256 : 208, 1, 1);
 
       // descriptors are built once; inside the loops only the start-address field (units of 16 bytes) advances
       const uint64_t dk = make_desc_sw128(k_addr, 16, 1024);
       const uint64_t dq = make_desc_sw128(smem_u32(smem + OFF_Q), 16, 1024);
-      const uint64_t du = make_desc_sw128(u_addr, 1024, 1024), db16 = make_desc_sw128(b16_addr, 16, 1024);
+      const uint64_t db16 = make_desc_sw128(b16_addr, 16, 1024);
       // second buffer of a double-buffered operand = first + its byte distance (in 16-byte units)
       const uint64_t de_k0 = make_desc_sw128(smem_u32(smem + OFF_E), 16, 1024);
       const uint64_t de_mn0 = make_desc_sw128(smem_u32(smem + OFF_E), 16384, 1024);
@@ -312,7 +318,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         const uint64_t dv = dv_mn0 + (uint64_t)((i & 1) * (V_STAGE >> 4));
 #pragma unroll
         for (int j = 0; j < 8; ++j)
-          mma_ts(tmem + TM_Y + (i & (YB - 1)) * 64, tmem + TM_W + j * 8, dv + (j * 2048 >> 4), ID_Y1, 1);
+          mma_ts(tmem + TM_Y, tmem + TM_W + j * 8, dv + (j * 2048 >> 4), ID_Y1, 1);
         tc_commit(&misc->y_ready);
         tc_commit(&misc->v_empty[i & 1]);
         return true;
@@ -336,42 +342,31 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         if (!(ok = wait_or_abort(&misc->v_full[i & 1], (i >> 1) & 1, misc))) break;
         tc_fence_after_sync();
         TC_TRACE(2, i, 3);
-        const uint64_t eoff = (uint64_t)(ER_BUFS == 2 ? (i & 1) * (32768 >> 4) : 0);
-        const uint64_t dek = de_k0 + eoff, dem = de_mn0 + eoff, drm = dr_mn0 + eoff;
+        const uint64_t dek = de_k0, dem = de_mn0, drm = dr_mn0;
         const uint64_t dv = dv_mn0 + (uint64_t)((i & 1) * (V_STAGE >> 4));
         if (!state_only) {
           // Single-buffered accumulators: the token group must have taken Y of chunk i - 1.
-          if (YB == 1 && i >= 1) {
+          if (i >= 1) {
             if (!(ok = wait_or_abort(&misc->y_free, (i - 1) & 1, misc))) break;
             tc_fence_after_sync();
           }
-          if constexpr (WIDE) {
-            // W shares the columns of S: the latent group must have taken the next chunk's scores
-            if (i + 1 < nchunks) {
+          {
+            // wide: W shares the columns of S: the latent group must have taken the next chunk's scores
+            if (WIDE && i + 1 < nchunks) {
               if (!(ok = wait_or_abort(&misc->s_free, (i + 1) & 1, misc))) break;
               tc_fence_after_sync();
             }
-            // [W | Y0] = R^T [E | U_bf16]: one product of width 256 (k = latents); the B operand's four 64-wide blocks
-            // lie 16384 bytes apart (E t-blocks, then the two value blocks of the bf16 state)
+            // [W | Y0 (| Den0)] = R^T [E | U_bf16 (| d)]: one product (k = latents); the B operand's four 64-wide blocks
+            // lie 16384 bytes apart: the E t-blocks, then the two value blocks of the bf16 state, or its one value
+            // block and the block whose column 0 is d
 #pragma unroll
             for (int j = 0; j < 8; ++j) mma_ss(tmem + TM_W, drm + (j * 2048 >> 4), dem + (j * 2048 >> 4), ID_WY, j > 0);
             tc_commit(&misc->w_ready);
             TC_TRACE(2, i, 5);
+            if constexpr (WIDE) {
 #pragma unroll
-            for (int j = 0; j < 8; ++j)
-              mma_ss(tmem + TM_DEN, drm + (j * 2048 >> 4), db16 + (((j >> 2) * 2048 + (j & 3) * 32) >> 4), ID_DEN, j > 0);
-          } else {
-            // W = R^T E  (k = latents, 8 steps of 16 rows = 2048 bytes)
-#pragma unroll
-            for (int j = 0; j < 8; ++j) mma_ss(tmem + TM_W, drm + (j * 2048 >> 4), dem + (j * 2048 >> 4), ID_W, j > 0);
-            tc_commit(&misc->w_ready);
-            TC_TRACE(2, i, 5);
-            // Y = R^T U_bf16, Den0 = R^T d
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              mma_ss(tmem + TM_Y + (i & (YB - 1)) * 64, drm + (j * 2048 >> 4), du + (j * 2048 >> 4), ID_Y0, j > 0);
-              mma_ss(tmem + TM_DEN + (i & (YB - 1)) * 16, drm + (j * 2048 >> 4),
-                     db16 + (((j >> 2) * 2048 + (j & 3) * 32) >> 4), ID_DEN, j > 0);
+              for (int j = 0; j < 8; ++j)
+                mma_ss(tmem + TM_DEN, drm + (j * 2048 >> 4), db16 + (((j >> 2) * 2048 + (j & 3) * 32) >> 4), ID_DEN, j > 0);
             }
           }
           TC_TRACE(2, i, 6);
@@ -447,8 +442,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       const uint32_t par = i & 1;
       const int nvalid = min(C, seg_end - (seg_begin + i * C));
       const int tok0 = hf * 64;
-      uint8_t* e_row = smem + OFF_E + (ER_BUFS == 2 ? (i & 1) * 32768 : 0) + hf * 16384;  // t-block hf of the operand buffers
-      uint8_t* r_row = smem + OFF_R + (ER_BUFS == 2 ? (i & 1) * 32768 : 0) + hf * 16384;
+      uint8_t* e_row = smem + OFF_E + hf * 16384;  // t-block hf of the operand buffers
+      uint8_t* r_row = smem + OFF_R + hf * 16384;
       if (!(ok = wait_or_abort(&misc->s_ready, par, misc))) break;
       tc_fence_after_sync();
       if (tid == 0) TC_TRACE(0, i, 0);
@@ -528,7 +523,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       float g16[4] = {0.f, 0.f, 0.f, 0.f};  // BLOCK: sums of the four groups of 16 tokens of this half
       // single E / R buffers: the products that read the previous chunk's E and R (they are all issued together and
       // the state update comes last) must have run
-      if (ER_BUFS == 1 && STABLE && i > 0 && !(ok = wait_or_abort(&misc->u_done, (i - 1) & 1, misc))) break;
+      if (STABLE && i > 0 && !(ok = wait_or_abort(&misc->u_done, (i - 1) & 1, misc))) break;
       if constexpr (STABLE) {
         // encoder weights sigma(s): packed and stored 8 tokens at a time; the raw scores stay in ra / rb for phase b
 #pragma unroll
@@ -589,7 +584,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         }
       }
       warp_arrive(&misc->psum[q], lane);
-      if (ER_BUFS == 1 && !STABLE && i > 0 && !(ok = wait_or_abort(&misc->u_done, (i - 1) & 1, misc))) break;
+      if (!STABLE && i > 0 && !(ok = wait_or_abort(&misc->u_done, (i - 1) & 1, misc))) break;
       if constexpr (!STABLE)
 #pragma unroll
       for (int ch = 0; ch < 4; ++ch) {
@@ -711,9 +706,15 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       if (i > 0 && !(ok = wait_or_abort(&misc->u_done, (i - 1) & 1, misc))) break;
       tc_fence_after_sync();
       if (tid == 0) TC_TRACE(0, i, 4);
-      if (hf == 0 && !state_only)
-        *reinterpret_cast<__nv_bfloat16*>(smem + OFF_B16 + (m >> 6) * 2048 + ((m & 63) >> 3) * 16 + (m & 7) * 2) =
-            __float2bfloat16_rn(d_carry);
+      if (hf == 0 && !state_only) {
+        // d of the carried state: column 0 of row m of the MN-major block (merged product with one value block), or
+        // element m of row 0 of the small K-major tile
+        if (!WIDE)
+          *reinterpret_cast<__nv_bfloat16*>(smem + OFF_B16 + swz_chunk_off(m, 0)) = __float2bfloat16_rn(d_carry);
+        else
+          *reinterpret_cast<__nv_bfloat16*>(smem + OFF_B16 + (m >> 6) * 2048 + ((m & 63) >> 3) * 16 + (m & 7) * 2) =
+              __float2bfloat16_rn(d_carry);
+      }
       const bool need = __any_sync(0xffffffffu, alpha != 1.0f);
       if constexpr (WIDE) {
         // 64 value columns per thread = value block hf of the bf16 state operand (free: the products that read it
@@ -900,7 +901,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       tc_fence_after_sync();
       if (tid == 256) TC_TRACE(1, i, 2);
       uint32_t den0;
-      tmem_ld1(tl + TM_DEN + (i & (YB - 1)) * 16, den0);
+      tmem_ld1(tl + TM_DEN, den0);
       tmem_wait_ld();
       const float den = __uint_as_float(den0) + rowsum;
       const bool den_ok = den > 0.f && den < INFINITY;
@@ -1034,10 +1035,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 #pragma unroll
       for (int vb = 0; vb < VB; ++vb) {
         uint32_t ra[32], rb[32];
-        tmem_ld32(tl + TM_Y + (i & (YB - 1)) * 64 + vb * 64, ra);
-        tmem_ld32(tl + TM_Y + (i & (YB - 1)) * 64 + vb * 64 + 32, rb);
+        tmem_ld32(tl + TM_Y + vb * 64, ra);
+        tmem_ld32(tl + TM_Y + vb * 64 + 32, rb);
         tmem_wait_ld();
-        if (YB == 1 && vb == VB - 1) {
+        if (vb == VB - 1) {
           tc_fence_before_sync();
           warp_arrive(&misc->y_free, lane);
         }
