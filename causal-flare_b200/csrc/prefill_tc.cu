@@ -330,14 +330,21 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       for (int i = 0; ok && i < nchunks; ++i) {
         const uint32_t par = i & 1;
         TC_TRACE(2, i, 0);
-        if (!state_only && i >= 1 && !(ok = issue_tail(i - 1))) break;
-        TC_TRACE(2, i, 1);
-        if (i + 1 < nchunks) {
-          // the latent group has read S of chunk i: the columns can take the next chunk's scores
+        // Next chunk's scores first: the latent group took S of chunk i long ago, while the token group is still
+        // masking W of chunk i - 1, which the read-out product below waits for.  (Wide: the scores go into the columns
+        // that hold the packed W of chunk i - 1 until that product has read them, so they come second there.)
+        if (!WIDE && i + 1 < nchunks) {
           if (!(ok = wait_or_abort(&misc->s_free, par, misc))) break;
           if (!(ok = issue_scores(i + 1))) break;
         }
         TC_TRACE(2, i, 2);
+        if (!state_only && i >= 1 && !(ok = issue_tail(i - 1))) break;
+        TC_TRACE(2, i, 1);
+        if (WIDE && i + 1 < nchunks) {
+          // the latent group has read S of chunk i: the columns can take the next chunk's scores
+          if (!(ok = wait_or_abort(&misc->s_free, par, misc))) break;
+          if (!(ok = issue_scores(i + 1))) break;
+        }
         if (!(ok = wait_or_abort(&misc->p1_done, par, misc))) break;
         if (!(ok = wait_or_abort(&misc->v_full[i & 1], (i >> 1) & 1, misc))) break;
         tc_fence_after_sync();
@@ -451,51 +458,41 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       uint32_t ra[32], rb[32];
       tmem_ld32(tl + TM_S + tok0, ra);
       tmem_ld32(tl + TM_S + tok0 + 32, rb);
-      tmem_wait_ld();
-      tmem_fence_regs(ra);
-      tmem_fence_regs(rb);
-      tc_fence_before_sync();
-      warp_arrive(&misc->s_free, lane);  // the S columns may take the next chunk's scores
-      // row maximum over the valid tokens of this half
-      float cm0 = -INFINITY, cm1 = -INFINITY, cm2 = -INFINITY, cm3 = -INFINITY;
-      if (nvalid == C && sc2 >= 0.f) {
-        // the scale is monotone: take the maximum of the raw scores and scale once
-#pragma unroll
-        for (int k = 0; k < 32; k += 4) {
-          cm0 = fmax3(cm0, __uint_as_float(ra[k]), __uint_as_float(ra[k + 1]));
-          cm1 = fmax3(cm1, __uint_as_float(ra[k + 2]), __uint_as_float(ra[k + 3]));
-          cm2 = fmax3(cm2, __uint_as_float(rb[k]), __uint_as_float(rb[k + 1]));
-          cm3 = fmax3(cm3, __uint_as_float(rb[k + 2]), __uint_as_float(rb[k + 3]));
-        }
-        cm0 = fmaxf(fmaxf(cm0, cm1), fmaxf(cm2, cm3)) * sc2;
-        cm1 = cm2 = cm3 = cm0;
-      } else {
-#pragma unroll
-        for (int k = 0; k < 32; ++k) {
-          if (tok0 + k < nvalid) cm0 = fmaxf(cm0, __uint_as_float(ra[k]) * sc2);
-          if (tok0 + 32 + k < nvalid) cm2 = fmaxf(cm2, __uint_as_float(rb[k]) * sc2);
-        }
-      }
-      misc->xmax[par][hf][m] = live ? fmaxf(fmaxf(cm0, cm1), fmaxf(cm2, cm3)) : -INFINITY;
       // Frame of this chunk.  Chunk 0 exchanges the two halves' maxima synchronously (the carried frame may be
-      // empty).  Later chunks use the running max through the PREVIOUS chunk, known without waiting; E may then
-      // exceed 1 by the growth of the max inside one chunk, which fp32 / bf16 hold easily, and the maxima published
-      // above enter the next chunk's frame.  The state is put into the exact running-max frame when it is written out.
-      float c_new;
-      if (i == 0) {
-        warp_arrive(&misc->pmax[q], lane);
-        if (!(ok = wait_or_abort(&misc->pmax[q], 0, misc))) break;
-        c_new = fmaxf(c2, fmaxf(misc->xmax[0][0][m], misc->xmax[0][1][m]));
-      } else {
+      // empty).  Later chunks use the running max through the PREVIOUS chunk, known without waiting (this bookkeeping
+      // runs while the scores are on their way out of tensor memory); E may then exceed 1 by the growth of the max
+      // inside one chunk, which fp32 / bf16 hold easily.  This chunk's own row maximum is taken along with the E pass
+      // and enters the next chunk's frame.  The state is put into the exact running-max frame when it is written out.
+      float c_new = c2;
+      if (i > 0) {
         // bookkeeping of chunk i - 1: both halves' sums and maxima are published once its psum phase completed
         if (!(ok = wait_or_abort(&misc->psum[q], (i - 1) & 1, misc))) break;
         dsum = d_prev + (misc->xsum[par ^ 1][0][m] + misc->xsum[par ^ 1][1][m]);
         c_new = fmaxf(c2, fmaxf(misc->xmax[par ^ 1][0][m], misc->xmax[par ^ 1][1][m]));
       }
+      tmem_wait_ld();
+      tmem_fence_regs(ra);
+      tmem_fence_regs(rb);
+      tc_fence_before_sync();
+      warp_arrive(&misc->s_free, lane);  // the S columns may take the next chunk's scores
+      if (i == 0) {
+        // row maximum over the valid tokens of this half, exchanged with the other half
+        float cm0 = -INFINITY, cm2 = -INFINITY;
+#pragma unroll
+        for (int k = 0; k < 32; ++k) {
+          if (tok0 + k < nvalid) cm0 = fmaxf(cm0, __uint_as_float(ra[k]) * sc2);
+          if (tok0 + 32 + k < nvalid) cm2 = fmaxf(cm2, __uint_as_float(rb[k]) * sc2);
+        }
+        misc->xmax[0][hf][m] = live ? fmaxf(cm0, cm2) : -INFINITY;
+        warp_arrive(&misc->pmax[q], lane);
+        if (!(ok = wait_or_abort(&misc->pmax[q], 0, misc))) break;
+        c_new = fmaxf(c2, fmaxf(misc->xmax[0][0][m], misc->xmax[0][1][m]));
+      }
       float alpha = STABLE ? 1.0f : ex2_approx(c2 - c_new);  // 0 when the old state is empty
       // kappa: common frame of the decode weights = max over latents of the running max.  Chunk 0 synchronises;
       // later chunks use the value published during the previous chunk (one chunk stale, which only changes a
-      // per-token scale that cancels in y).
+      // per-token scale that cancels in y).  (Publishing behind the E pass and reading the value of two chunks before,
+      // to take the warp reduction off the start of the chunk, measured 3 % slower: the E pass grew by more.)
       float wm = live ? c_new : -INFINITY;
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) wm = fmaxf(wm, __shfl_xor_sync(0xffffffffu, wm, o));
@@ -521,9 +518,14 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       // phase a: E for the 64 tokens of this half (in place of the scores), their sum, E operand rows
       float tot0 = 0.f, tot1 = 0.f;
       float g16[4] = {0.f, 0.f, 0.f, 0.f};  // BLOCK: sums of the four groups of 16 tokens of this half
+      // this half's row maximum of s - c_new (log2 units), taken along with the pass
+      float cma = -INFINITY, cmb = -INFINITY;
       // single E / R buffers: the products that read the previous chunk's E and R (they are all issued together and
       // the state update comes last) must have run
-      if (STABLE && i > 0 && !(ok = wait_or_abort(&misc->u_done, (i - 1) & 1, misc))) break;
+      if (STABLE && i > 0) {
+        if (!(ok = wait_or_abort(&misc->u_done, (i - 1) & 1, misc))) break;
+        tc_fence_after_sync();
+      }
       if constexpr (STABLE) {
         // encoder weights sigma(s): packed and stored 8 tokens at a time; the raw scores stay in ra / rb for phase b
 #pragma unroll
@@ -532,6 +534,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
             const float raw = __uint_as_float(ch < 4 ? ra[ch * 8 + j] : rb[(ch - 4) * 8 + j]);
+            if (tok0 + ch * 8 + j < nvalid) cma = fmaxf(cma, raw * sc2 - c_new);
             sg[j] = (tok0 + ch * 8 + j < nvalid) ? sigma_fast(raw * p.scale, p.power) : 0.f;
             tot0 += sg[j];
           }
@@ -541,8 +544,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       } else if (nvalid == C) {
 #pragma unroll
         for (int k = 0; k < 32; ++k) {
-          const float e0 = ex2_approx(__uint_as_float(ra[k]) * sc2 - c_new);
-          const float e1 = ex2_approx(__uint_as_float(rb[k]) * sc2 - c_new);
+          const float x0 = __uint_as_float(ra[k]) * sc2 - c_new, x1 = __uint_as_float(rb[k]) * sc2 - c_new;
+          if (k & 1) cmb = fmax3(cmb, x0, x1);
+          else cma = fmax3(cma, x0, x1);
+          const float e0 = ex2_approx(x0);
+          const float e1 = ex2_approx(x1);
           ra[k] = __float_as_uint(e0);
           rb[k] = __float_as_uint(e1);
           if (BLOCK) {
@@ -556,8 +562,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       } else {
 #pragma unroll
         for (int k = 0; k < 32; ++k) {
-          const float e0 = (tok0 + k < nvalid) ? ex2_approx(__uint_as_float(ra[k]) * sc2 - c_new) : 0.f;
-          const float e1 = (tok0 + 32 + k < nvalid) ? ex2_approx(__uint_as_float(rb[k]) * sc2 - c_new) : 0.f;
+          const float x0 = __uint_as_float(ra[k]) * sc2 - c_new, x1 = __uint_as_float(rb[k]) * sc2 - c_new;
+          if (tok0 + k < nvalid) cma = fmaxf(cma, x0);
+          if (tok0 + 32 + k < nvalid) cmb = fmaxf(cmb, x1);
+          const float e0 = (tok0 + k < nvalid) ? ex2_approx(x0) : 0.f;
+          const float e1 = (tok0 + 32 + k < nvalid) ? ex2_approx(x1) : 0.f;
           ra[k] = __float_as_uint(e0);
           rb[k] = __float_as_uint(e1);
           if (BLOCK) {
@@ -574,6 +583,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         tot1 = g16[2] + g16[3];
       }
       misc->xsum[par][hf][m] = tot0 + tot1;
+      // (chunk 0 published its maximum before the pass; an empty half stays at -inf)
+      if (i > 0) misc->xmax[par][hf][m] = live ? fmaxf(cma, cmb) + c_new : -INFINITY;
       if (!(tot0 + tot1 < INFINITY)) {
         // an encoder weight overflowed (the running max grew by more than fp32 holds inside one chunk): outside the
         // numeric domain of this path
@@ -584,7 +595,12 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         }
       }
       warp_arrive(&misc->psum[q], lane);
-      if (!STABLE && i > 0 && !(ok = wait_or_abort(&misc->u_done, (i - 1) & 1, misc))) break;
+      // E has one buffer: the products that read the previous chunk's E and R (issued together, the state update last)
+      // must have run.  (Storing inside the pass would need this wait before it, where it is not yet satisfied.)
+      if (!STABLE && i > 0) {
+        if (!(ok = wait_or_abort(&misc->u_done, (i - 1) & 1, misc))) break;
+        tc_fence_after_sync();
+      }
       if constexpr (!STABLE)
 #pragma unroll
       for (int ch = 0; ch < 4; ++ch) {
@@ -702,9 +718,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         }
       }
       if (tid == 0) TC_TRACE(0, i, 3);
-      // state part: needs the numerator update of the previous chunk to have landed
-      if (i > 0 && !(ok = wait_or_abort(&misc->u_done, (i - 1) & 1, misc))) break;
-      tc_fence_after_sync();
+      // state part: needs the numerator update of the previous chunk to have landed (waited for before the E rows
+      // were written)
       if (tid == 0) TC_TRACE(0, i, 4);
       if (hf == 0 && !state_only) {
         // d of the carried state: column 0 of row m of the MN-major block (merged product with one value block), or
