@@ -493,10 +493,12 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       // later chunks use the value published during the previous chunk (one chunk stale, which only changes a
       // per-token scale that cancels in y).  (Publishing behind the E pass and reading the value of two chunks before,
       // to take the warp reduction off the start of the chunk, measured 3 % slower: the E pass grew by more.)
-      float wm = live ? c_new : -INFINITY;
+      if (hf == 0) {  // (both half-groups hold the same frames: one of them publishes)
+        float wm = live ? c_new : -INFINITY;
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1) wm = fmaxf(wm, __shfl_xor_sync(0xffffffffu, wm, o));
-      if (hf == 0 && lane == 0) misc->wmax[par][q] = wm;
+        for (int o = 16; o > 0; o >>= 1) wm = fmaxf(wm, __shfl_xor_sync(0xffffffffu, wm, o));
+        if (lane == 0) misc->wmax[par][q] = wm;
+      }
       if (i == 0) {
         if (hf == 0 && lane == 0) mbar_arrive(&misc->kap_done);
         if (!(ok = wait_or_abort(&misc->kap_done, 0, misc))) break;
