@@ -370,6 +370,9 @@ def bench_seqpar(args, rank, world):
             if world == 1:
                 _ops.forward(q, k, v, scale=sc, block_size=bs)
                 return _ops.backward(q, k, v, dy, scale=sc, block_size=bs)[0]
+            parallel.sequence_parallel_prefill(q, k, v, scale=sc, block_size=bs)
+            if H % world == 0:  # re-sharded by heads: whole sequences on the tensor-core backward
+                return parallel.sequence_parallel_backward_by_heads(q, k, v, dy, scale=sc, block_size=bs)[0]
             _, _, prefix = parallel.sequence_parallel_prefill(q, k, v, scale=sc, block_size=bs, return_prefix=True)
             return parallel.sequence_parallel_backward(q, k, v, dy, scale=sc, prefix_state=prefix, block_size=bs)[0]
 
@@ -387,7 +390,8 @@ def bench_seqpar(args, rank, world):
             "n_gpus": world, "steps": steps, "ms_per_step": ms, "scaling": "strong", "higher_is_better": True,
             "dtype": "bf16", "data": "synthetic",
             "config": {"workload": f"C5 semi-AR B={B} N={N} H={H} M={M} D={D} block={bs}, {span} tokens per GPU",
-                       "parallelism": f"sequence parallel over {world} GPU(s), one all-gather of span states per step"}}
+                       "parallelism": f"sequence parallel over {world} GPU(s), one all-gather of span states per step; "
+                                      "backward: all-to-all to a head sharding and back"}}
 
 
 def bench_strong(args, rank, world):
@@ -630,8 +634,9 @@ def main():
     strong = seqpar = None
     if world > 1 and args.only == "all" and not args.skip_other:
         # the two multi-GPU partitions of the path: fixed workload split by heads (no collective), and the long
-        # block-causal sequence split by tokens (one all-gather of span states in the forward, one of span summaries
-        # plus an all-reduce of dQ in the backward)
+        # block-causal sequence split by tokens (one all-gather of span states in the forward; the backward re-shards
+        # K, V, dY by heads with one all-to-all, runs whole sequences on the tensor-core backward and brings dK, dV
+        # back with a second all-to-all)
         strong = bench_strong(args, rank, world)
         args.seqpar_backward = True
         sp_args = argparse.Namespace(**vars(args))

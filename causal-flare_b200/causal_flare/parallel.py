@@ -103,6 +103,62 @@ def right_carry(stacked, rank: int):
     return {"b": run_b, "c": run_c, "rho": stacked["rho_first"][rank + 1]}
 
 
+def heads_from_spans(x_local, group=None):
+    """All-to-all that turns the token sharding into a head sharding: ``x_local`` is ``[..., B, span, H, D]`` with the
+    tokens ``[rank span, (rank + 1) span)`` of every head (leading dimensions, e.g. a stack of K, V and dY, travel in the
+    same collective); the result is ``[..., B, world span, H / world, D]``: the whole sequence of the heads
+    ``[rank H / world, (rank + 1) H / world)``."""
+    world = dist.get_world_size(group)
+    *lead, B, S, H, D = x_local.shape
+    assert H % world == 0, "the head count must be a multiple of the world size"
+    hp = H // world
+    nl = len(lead)
+    # [world (head group), ..., B, S, hp, D]: block j goes to rank j
+    send = x_local.reshape(*lead, B, S, world, hp, D).movedim(nl + 2, 0).contiguous()
+    recv = torch.empty_like(send)
+    dist.all_to_all_single(recv, send, group=group)
+    # block j came from rank j: its span of this rank's heads
+    return recv.movedim(0, nl + 1).reshape(*lead, B, world * S, hp, D)
+
+
+def spans_from_heads(x_heads, group=None):
+    """Inverse of ``heads_from_spans``: ``[..., B, N, H / world, D]`` (whole sequence, this rank's heads) ->
+    ``[..., B, N / world, H, D]`` (this rank's tokens, every head)."""
+    world = dist.get_world_size(group)
+    *lead, B, N, hp, D = x_heads.shape
+    assert N % world == 0
+    S = N // world
+    nl = len(lead)
+    send = x_heads.reshape(*lead, B, world, S, hp, D).movedim(nl + 1, 0).contiguous()  # block j: span j
+    recv = torch.empty_like(send)
+    dist.all_to_all_single(recv, send, group=group)
+    # block j came from rank j: head group j of this rank's span
+    return recv.movedim(0, nl + 2).reshape(*lead, B, S, world * hp, D)
+
+
+def sequence_parallel_backward_by_heads(Q, K_local, V_local, dY_local, *, scale, group=None, block_size=1):
+    """Gradients of the sequence-parallel forward with the work re-sharded by heads: one all-to-all moves K, V and dY
+    from token spans to whole sequences of H / world heads per rank, every rank runs the ordinary single-device
+    backward on its heads (lanes are independent, so the tensor-core backward applies unchanged, including its own
+    replay of the forward), one all-to-all brings dK and dV back to the spans and an all-gather collects dQ.
+    Needs H to be a multiple of the world size.  Returns (dQ [H, M, D], dK_local, dV_local)."""
+    from . import _ops
+
+    rank, world = dist.get_rank(group), dist.get_world_size(group)
+    H = Q.shape[0]
+    hp = H // world
+    kvd = heads_from_spans(torch.stack((K_local, V_local, dY_local)), group=group)
+    qh = Q[rank * hp:(rank + 1) * hp].contiguous()
+    dq_h, dk_h, dv_h = _ops.backward(qh, kvd[0], kvd[1], kvd[2], scale=scale, block_size=block_size)[:3]
+    dkv = spans_from_heads(torch.stack((dk_h, dv_h)), group=group)
+    dq = torch.empty((world,) + tuple(dq_h.shape), device=dq_h.device, dtype=dq_h.dtype)
+    if dist.get_backend(group) == "nccl":
+        dist.all_gather_into_tensor(dq, dq_h.contiguous(), group=group)
+    else:
+        dist.all_gather(list(dq.unbind(0)), dq_h.contiguous(), group=group)
+    return dq.reshape((H,) + tuple(dq_h.shape[1:])), dkv[0], dkv[1]
+
+
 def sequence_parallel_backward(Q, K_local, V_local, dY_local, *, scale, prefix_state, group=None, block_size=1):
     """Gradients of the sequence-parallel forward.  Every rank replays its span from ``prefix_state`` (the third value
     of ``sequence_parallel_prefill(..., return_prefix=True)``), the spans' reverse-carry summaries (b, c at the span's

@@ -97,3 +97,35 @@ def test_right_carry_folds_span_summaries_like_the_token_recurrence():
         first_next = (r + 1) * span_len
         assert torch.allclose(got["b"], b[first_next]) and torch.allclose(got["c"], c[first_next])
         assert torch.equal(got["rho"], rho[first_next])
+
+
+def _reshard_worker(rank, world, port, ret):
+    for p in (ROOT, os.path.join(ROOT, "causal-flare_b200")):
+        if p not in sys.path:
+            sys.path.insert(0, p)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from causal_flare import parallel
+
+    B, N, H, D = 2, 12, 4, 3
+    full = torch.arange(2 * B * N * H * D, dtype=torch.float32).reshape(2, B, N, H, D)  # a stack of two tensors
+    span, hp = N // world, H // world
+    local = full[:, :, rank * span:(rank + 1) * span].contiguous()
+    heads = parallel.heads_from_spans(local)  # whole sequence of this rank's heads
+    ok = torch.equal(heads, full[:, :, :, rank * hp:(rank + 1) * hp])
+    back = parallel.spans_from_heads(heads)   # and back to this rank's tokens of every head
+    ok = ok and torch.equal(back, local)
+    one = parallel.heads_from_spans(local[0])  # without leading dimensions
+    ok = ok and torch.equal(one, full[0, :, :, rank * hp:(rank + 1) * hp])
+    ret[rank] = bool(ok)
+    dist.destroy_process_group()
+
+
+def test_span_to_head_resharding_world2():
+    world = 2
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    port = 31500 + (os.getpid() % 2000)
+    mp.spawn(_reshard_worker, args=(world, port, ret), nprocs=world, join=True)
+    assert len(ret) == world and all(ret[r] for r in range(world))

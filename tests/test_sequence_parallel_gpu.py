@@ -85,7 +85,10 @@ def _bwd_worker(rank, world, port, block_size, ret):
     def rel(a, b):
         return float((a.float() - b.float()).norm() / b.float().norm())
 
-    ret[rank] = (rel(dq, dq_f), rel(dk, dk_f[:, sl]), rel(dv, dv_f[:, sl]))
+    # the same gradients with the work re-sharded by heads (all-to-all, whole sequences on the single-device kernels)
+    dq2, dk2, dv2 = parallel.sequence_parallel_backward_by_heads(q, kl, vl, dyl, scale=sc, block_size=block_size)
+    ret[rank] = (rel(dq, dq_f), rel(dk, dk_f[:, sl]), rel(dv, dv_f[:, sl]),
+                 rel(dq2, dq_f), rel(dk2, dk_f[:, sl]), rel(dv2, dv_f[:, sl]))
     dist.destroy_process_group()
 
 
@@ -99,5 +102,5 @@ def test_sequence_parallel_backward_two_gpus(block_size):
     port = 29700 + (os.getpid() % 2000) + block_size
     mp.spawn(_bwd_worker, args=(world, port, block_size, ret), nprocs=world, join=True)
     for rank in range(world):
-        for name, err in zip(("dq", "dk", "dv"), ret[rank]):
+        for name, err in zip(("dq", "dk", "dv", "dq by heads", "dk by heads", "dv by heads"), ret[rank]):
             assert err < 5e-3, f"rank {rank}: {name} differs from the one-GPU backward by rel-L2 {err}"
