@@ -107,3 +107,17 @@ def test_wide_is_the_default_for_grids_beyond_one_wave():
     ref = orc.ar_forward(q, k, v, scale=D ** -0.5)
     y, _, _, _ = run(*to_dev(q, k, v))
     assert_bf16_gate(y, ref, "wide instance by default")
+
+
+def test_wide_long_block_causal_lanes_at_full_length(wide):
+    # C5's lanes at their full length (N = 65536, M = 256, D = 128, block 64; two of the 64 lanes): every token against
+    # the oracle, 512 chunks of running frames, carried state and (by default) the on-chip merge of the two groups
+    q, k, v = orc.make_inputs(1, 65536, 2, 256, D, seed0=17, dtype=torch.bfloat16)
+    sc = D ** -0.5
+    ref, lse_dec, lse_enc = orc.semi_ar_forward(q, k, v, block_size=64, scale=sc)
+    qc, kc, vc = to_dev(q, k, v)
+    y, _, ld, le = run(qc, kc, vc, block_size=64, want_lse=True, scale=sc)
+    assert_bf16_gate(y, ref, "C5 lanes at full length, wide instance")
+    assert_bf16_gate(y[:, -4096:], ref[:, -4096:], "C5 lanes, last 4096 tokens")
+    assert_close(le, lse_enc, what="LSE_enc", atol=5e-4, rtol=5e-4)
+    assert_close(ld, lse_dec, what="LSE_dec", atol=5e-3, rtol=0)
