@@ -179,7 +179,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                   const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_y, const TcParams p) {
   using L = Lay<DKB, WIDE>;
-  static_assert(!WIDE || (DVB == 2 && !KEEP && !PADDED), "wide instance");
+  static_assert(!WIDE || (DVB == 2 && !PADDED), "wide instance");
   constexpr int ZS = WIDE ? 1 : DVB;  // value slices on grid.z
   constexpr bool BLOCK = MODE == 1, STABLE = MODE == 2;
   constexpr int OFF_K = L::OFF_K, OFF_V = L::OFF_V, OFF_E = L::OFF_E, OFF_R = L::OFF_R, OFF_U = L::OFF_U,
@@ -758,8 +758,33 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 v.w = pack_bf16(__uint_as_float(r[ch * 8 + 6]), __uint_as_float(r[ch * 8 + 7]));
                 *reinterpret_cast<uint4*>(smem + OFF_U + hf * 16384 + swz_chunk_off(m, (c0 >> 3) + ch)) = v;
               }
+              if constexpr (KEEP) {
+                // training: the state before this chunk in the exact running-max frame through it (see below)
+                if (c0 == 0 && !(ok = wait_or_abort(&misc->psum[q], par, misc))) break;
+                float fin = 1.0f, c_true = c2;
+                if (!STABLE) {
+                  c_true = fmaxf(c2, fmaxf(misc->xmax[par][0][m], misc->xmax[par][1][m]));
+                  fin = ex2_approx(c2 - c_true);
+                }
+                const int64_t o = ((int64_t)lane_id * p.dump_nch + (seg_begin / C + i)) * p.M + latent0<ZS, SPLIT>() + m;
+                uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.dump_u) + o * DV + hf * 64 + c0);
+#pragma unroll
+                for (int ch = 0; ch < 4; ++ch) {
+                  uint4 v;
+                  v.x = pack_bf16(__uint_as_float(r[ch * 8 + 0]) * fin, __uint_as_float(r[ch * 8 + 1]) * fin);
+                  v.y = pack_bf16(__uint_as_float(r[ch * 8 + 2]) * fin, __uint_as_float(r[ch * 8 + 3]) * fin);
+                  v.z = pack_bf16(__uint_as_float(r[ch * 8 + 4]) * fin, __uint_as_float(r[ch * 8 + 5]) * fin);
+                  v.w = pack_bf16(__uint_as_float(r[ch * 8 + 6]) * fin, __uint_as_float(r[ch * 8 + 7]) * fin);
+                  dst[ch] = v;
+                }
+                if (hf == 0 && c0 == 0) {
+                  p.dump_c[o] = c_true;
+                  p.dump_d[o] = d_carry * fin;
+                }
+              }
             }
           }
+          if (!ok) break;
           if (need) tmem_wait_st();
         }
       } else
@@ -1177,6 +1202,11 @@ int launch_prefill_tc_unit<FLARE_TC_UNIT>(bool padded, int mode, const CUtensorM
 #if FLARE_TC_UNIT >= 6
   constexpr bool WSPLIT = FLARE_TC_UNIT == 7;
   (void)padded;
+  if (p.dump_u != nullptr) {  // training forward that keeps its per-chunk states
+    if (mode == 1) return launch_keep<false, 2, 2, WSPLIT, 1, true, true>(tq, tk, tv, ty, p, grid, stream);
+    if (mode == 2) return launch_keep<false, 2, 2, WSPLIT, 2, true, true>(tq, tk, tv, ty, p, grid, stream);
+    return launch_keep<false, 2, 2, WSPLIT, 0, true, true>(tq, tk, tv, ty, p, grid, stream);
+  }
   if (mode == 1) return launch_keep<false, 2, 2, WSPLIT, 1, false, true>(tq, tk, tv, ty, p, grid, stream);
   if (mode == 2) return launch_keep<false, 2, 2, WSPLIT, 2, false, true>(tq, tk, tv, ty, p, grid, stream);
   return launch_keep<false, 2, 2, WSPLIT, 0, false, true>(tq, tk, tv, ty, p, grid, stream);
@@ -1357,12 +1387,10 @@ int launch_prefill_tc(const flare_fwd_args_t* a, const TcParams& p_in, int nseg_
   const bool padded = (a->M % M) != 0;
   const int mode = a->variant == FLARE_STABLEMAX ? 2 : (a->block_size > 1 ? 1 : 0);
   // (128, 128) heads: two CTAs per (lane, group), each repeating the score / E / R work for 64 value columns, while
-  // they all fit the SMs at once; beyond that the wide instance, one CTA for all 128 columns.  (Not for the training
-  // forward that keeps its states, nor for a padded latent bank.)  FLARE_B200_WIDE=0 / 1 forces the choice.
-  bool wide = a->Dk == 128 && a->Dv == 128 && !padded && p.dump_u == nullptr &&
-              (int64_t)a->B * a->H * nseg_grid * groups * 2 > sm_count();
-  if (const char* env = getenv("FLARE_B200_WIDE"))
-    wide = a->Dk == 128 && a->Dv == 128 && !padded && p.dump_u == nullptr && env[0] == '1';
+  // they all fit the SMs at once; beyond that the wide instance, one CTA for all 128 columns.  (Not for a padded
+  // latent bank.)  FLARE_B200_WIDE=0 / 1 forces the choice.
+  bool wide = a->Dk == 128 && a->Dv == 128 && !padded && (int64_t)a->B * a->H * nseg_grid * groups * 2 > sm_count();
+  if (const char* env = getenv("FLARE_B200_WIDE")) wide = a->Dk == 128 && a->Dv == 128 && !padded && env[0] == '1';
   // Read-out rows leave through tiled bulk stores of 32 tokens x 32 columns (64-byte swizzle): into y, or with several
   // latent groups into the dense fp16 partials.  Per-row lengths (rows beyond a length stay untouched) and output
   // strides the tiled copy cannot express fall back to per-thread stores.

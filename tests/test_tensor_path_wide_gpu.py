@@ -121,3 +121,25 @@ def test_wide_long_block_causal_lanes_at_full_length(wide):
     assert_bf16_gate(y[:, -4096:], ref[:, -4096:], "C5 lanes, last 4096 tokens")
     assert_close(le, lse_enc, what="LSE_enc", atol=5e-4, rtol=5e-4)
     assert_close(ld, lse_dec, what="LSE_dec", atol=5e-3, rtol=0)
+
+
+@pytest.mark.parametrize("bs, Ml", [(1, 128), (1, 256), (64, 256)])
+def test_wide_training_forward_keeps_the_same_states_as_the_two_slice_instance(wide, bs, Ml):
+    # the training forward leaves the per-chunk prefix states for the backward: gradients from the states kept by the
+    # wide instance equal those from the two-slice instance's and pass the oracle's closed form
+    q, k, v, dy = orc.make_inputs(2, 640, 2, Ml, D, seed0=18, dtype=torch.bfloat16, with_dy=True)
+    sc = D ** -0.5
+    qc, kc, vc, dyc = to_dev(q, k, v, dy)
+    out = {}
+    for w in ("1", "0"):
+        wide.setenv("FLARE_B200_WIDE", w)
+        kept = {}
+        y, _, _, _ = _ops.forward(qc, kc, vc, scale=sc, block_size=bs, keep_for_backward=kept)
+        out[w] = (y, _ops.backward(qc, kc, vc, dyc, scale=sc, block_size=bs, saved=kept)[:3])
+        assert _ops.device_status() == 0
+    assert_bf16_gate(out["1"][0], out["0"][0].float(), "y of the training forward, wide vs two-slice")
+    for name, a, b in zip(("dQ", "dK", "dV"), out["1"][1], out["0"][1]):
+        assert orc.rel_l2(a.float().cpu(), b.float().cpu()) < 2e-3, name
+    ref = orc.ar_backward_closed_form(q, k, v, dy, scale=sc, block_size=bs)
+    for name, got in zip(("dQ", "dK", "dV"), out["1"][1]):
+        assert orc.rel_l2(got.float().cpu(), ref[name]) <= 6.5e-3, name
