@@ -544,22 +544,38 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
               make_uint4(pack_bf16(sg[0], sg[1]), pack_bf16(sg[2], sg[3]), pack_bf16(sg[4], sg[5]), pack_bf16(sg[6], sg[7]));
         }
       } else if (nvalid == C) {
+        // two tokens per FMA / add instruction (packed fp32 pairs): the passes are bound by instruction issue
+        const uint64_t sc2p = f2_pack(sc2, sc2), cnp = f2_pack(-c_new, -c_new);
+        uint64_t sa[2] = {f2_pack(0.f, 0.f), f2_pack(0.f, 0.f)}, sb[2] = {f2_pack(0.f, 0.f), f2_pack(0.f, 0.f)};
 #pragma unroll
-        for (int k = 0; k < 32; ++k) {
-          const float x0 = __uint_as_float(ra[k]) * sc2 - c_new, x1 = __uint_as_float(rb[k]) * sc2 - c_new;
-          if (k & 1) cmb = fmax3(cmb, x0, x1);
-          else cma = fmax3(cma, x0, x1);
-          const float e0 = ex2_approx(x0);
-          const float e1 = ex2_approx(x1);
-          ra[k] = __float_as_uint(e0);
-          rb[k] = __float_as_uint(e1);
-          if (BLOCK) {
-            g16[k >> 4] += e0;
-            g16[2 + (k >> 4)] += e1;
-          } else {
-            tot0 += e0;
-            tot1 += e1;
+        for (int k = 0; k < 32; k += 2) {
+          float xa0, xa1, xb0, xb1;
+          f2_unpack(f2_fma(f2_pack(__uint_as_float(ra[k]), __uint_as_float(ra[k + 1])), sc2p, cnp), xa0, xa1);
+          f2_unpack(f2_fma(f2_pack(__uint_as_float(rb[k]), __uint_as_float(rb[k + 1])), sc2p, cnp), xb0, xb1);
+          cma = fmax3(cma, xa0, xa1);
+          cmb = fmax3(cmb, xb0, xb1);
+          const float ea0 = ex2_approx(xa0), ea1 = ex2_approx(xa1), eb0 = ex2_approx(xb0), eb1 = ex2_approx(xb1);
+          ra[k] = __float_as_uint(ea0);
+          ra[k + 1] = __float_as_uint(ea1);
+          rb[k] = __float_as_uint(eb0);
+          rb[k + 1] = __float_as_uint(eb1);
+          sa[BLOCK ? (k >> 4) : 0] = f2_add(sa[BLOCK ? (k >> 4) : 0], f2_pack(ea0, ea1));
+          sb[BLOCK ? (k >> 4) : 0] = f2_add(sb[BLOCK ? (k >> 4) : 0], f2_pack(eb0, eb1));
+        }
+        float lo, hi;
+        if (BLOCK) {
+#pragma unroll
+          for (int g = 0; g < 2; ++g) {
+            f2_unpack(sa[g], lo, hi);
+            g16[g] = lo + hi;
+            f2_unpack(sb[g], lo, hi);
+            g16[2 + g] = lo + hi;
           }
+        } else {
+          f2_unpack(sa[0], lo, hi);
+          tot0 = lo + hi;
+          f2_unpack(sb[0], lo, hi);
+          tot1 = lo + hi;
         }
       } else {
 #pragma unroll
@@ -662,9 +678,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             const float e0 = __uint_as_float(blk ? rb[k] : ra[k]);
             const float e1 = __uint_as_float(blk ? rb[k + 1] : ra[k + 1]);
             run += e0;
-            const float r0 = e0 * (a_m * rcp_approx(run));
+            const float i0 = rcp_approx(run);
             run += e1;
-            const float r1 = e1 * (a_m * rcp_approx(run));
+            const float i1 = rcp_approx(run);
+            float r0, r1;  // e * (a_m / D), two tokens per multiply
+            f2_unpack(f2_mul(f2_pack(e0, e1), f2_mul(f2_pack(i0, i1), f2_pack(a_m, a_m))), r0, r1);
             rp[k >> 1] = pack_bf16(r0, r1);
           }
 #pragma unroll
@@ -711,7 +729,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 #pragma unroll
           for (int k = 0; k < 32; k += 2) {
             const float w = inv[blk * 2 + (k >> 4)];
-            rp[k >> 1] = pack_bf16(__uint_as_float(blk ? rb[k] : ra[k]) * w, __uint_as_float(blk ? rb[k + 1] : ra[k + 1]) * w);
+            float r0, r1;
+            f2_unpack(f2_mul(f2_pack(__uint_as_float(blk ? rb[k] : ra[k]), __uint_as_float(blk ? rb[k + 1] : ra[k + 1])),
+                             f2_pack(w, w)), r0, r1);
+            rp[k >> 1] = pack_bf16(r0, r1);
           }
 #pragma unroll
           for (int ch = 0; ch < 4; ++ch)
@@ -745,7 +766,12 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             tmem_fence_regs(r);
             if (need) {
 #pragma unroll
-              for (int k = 0; k < 32; ++k) r[k] = __float_as_uint(__uint_as_float(r[k]) * alpha);
+              for (int k = 0; k < 32; k += 2) {
+                float u0, u1;
+                f2_unpack(f2_mul(f2_pack(__uint_as_float(r[k]), __uint_as_float(r[k + 1])), f2_pack(alpha, alpha)), u0, u1);
+                r[k] = __float_as_uint(u0);
+                r[k + 1] = __float_as_uint(u1);
+              }
               tmem_st32(tl + TM_U + hf * 64 + c0, r);
             }
             if (!state_only) {
@@ -795,7 +821,12 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         tmem_fence_regs(r);
         if (need) {
 #pragma unroll
-          for (int k = 0; k < 32; ++k) r[k] = __float_as_uint(__uint_as_float(r[k]) * alpha);
+          for (int k = 0; k < 32; k += 2) {
+            float u0, u1;
+            f2_unpack(f2_mul(f2_pack(__uint_as_float(r[k]), __uint_as_float(r[k + 1])), f2_pack(alpha, alpha)), u0, u1);
+            r[k] = __float_as_uint(u0);
+            r[k + 1] = __float_as_uint(u1);
+          }
           tmem_st32(tl + TM_U + hf * 32, r);
         }
         if (!state_only) {
@@ -1090,19 +1121,17 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           const int col = value_col0<ZS, SPLIT>() + vb * 64 + half * 32;
           // 32 columns of this thread's row as 16-bit values: bf16 of y, or fp16 of a latent group's partial
           uint4 v[4];
+          const uint64_t inv2 = f2_pack(inv, inv);
 #pragma unroll
           for (int ch = 0; ch < 4; ++ch) {
-            if (SPLIT) {
-              v[ch].x = pack_f16(__uint_as_float(r[ch * 8 + 0]) * inv, __uint_as_float(r[ch * 8 + 1]) * inv);
-              v[ch].y = pack_f16(__uint_as_float(r[ch * 8 + 2]) * inv, __uint_as_float(r[ch * 8 + 3]) * inv);
-              v[ch].z = pack_f16(__uint_as_float(r[ch * 8 + 4]) * inv, __uint_as_float(r[ch * 8 + 5]) * inv);
-              v[ch].w = pack_f16(__uint_as_float(r[ch * 8 + 6]) * inv, __uint_as_float(r[ch * 8 + 7]) * inv);
-            } else {
-              v[ch].x = pack_bf16(__uint_as_float(r[ch * 8 + 0]) * inv, __uint_as_float(r[ch * 8 + 1]) * inv);
-              v[ch].y = pack_bf16(__uint_as_float(r[ch * 8 + 2]) * inv, __uint_as_float(r[ch * 8 + 3]) * inv);
-              v[ch].z = pack_bf16(__uint_as_float(r[ch * 8 + 4]) * inv, __uint_as_float(r[ch * 8 + 5]) * inv);
-              v[ch].w = pack_bf16(__uint_as_float(r[ch * 8 + 6]) * inv, __uint_as_float(r[ch * 8 + 7]) * inv);
+            uint32_t o[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              float y0, y1;  // two columns per multiply
+              f2_unpack(f2_mul(f2_pack(__uint_as_float(r[ch * 8 + 2 * j]), __uint_as_float(r[ch * 8 + 2 * j + 1])), inv2), y0, y1);
+              o[j] = SPLIT ? pack_f16(y0, y1) : pack_bf16(y0, y1);
             }
+            v[ch] = make_uint4(o[0], o[1], o[2], o[3]);
           }
           if (p.y_tma) {
             // One tiled bulk store per warp and 32 x 32 tile.  A thread storing its own row straight to global
