@@ -115,7 +115,7 @@ struct Misc {
   uint32_t tmem_base;
   volatile int abort_flag;
   float wmax[2][4];
-  float kap[2];  // decode frame of the chunk in flight, for the token group (latent-group split only)
+  float kap[4];  // decode frame of chunk i in slot i % 4, for the token group (log-sum-exp, weight mass of a latent group)
   float xmax[2][2][128], xsum[2][2][128];  // [chunk parity][half][latent]
 };
 
@@ -506,7 +506,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       const float* wsrc = misc->wmax[i == 0 ? 0 : ((i - 1) & 1)];
       const float kappa = fmaxf(fmaxf(wsrc[0], wsrc[1]), fmaxf(wsrc[2], wsrc[3]));
       // ordered before the token group's read by the barrier chain
-      if ((SPLIT || BLOCK || p.lse_dec != nullptr) && tid == 0) misc->kap[par] = kappa;
+      if ((SPLIT || BLOCK || p.lse_dec != nullptr) && tid == 0) misc->kap[i & 3] = kappa;
       if (tid == 0) TC_TRACE(0, i, 1);
       float a_m = ex2_approx(c_new - kappa);
       float d_carry = dsum * alpha;  // denominator of the carried state in the new frame
@@ -929,6 +929,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       // causal mask of W, bf16 pack, row sums
       if (!(ok = wait_or_abort(&misc->w_ready, par, misc))) break;
       tc_fence_after_sync();
+      // This chunk's decode frame, taken now: the latent group is one to two chunks ahead and reuses the slot four
+      // chunks on (read late, in the epilogue, from a two-slot array, a slow token group saw a later chunk's frame:
+      // wrong weight masses for the merge of latent groups)
+      const float kap_i = misc->kap[i & 3];
       if (tid == 256) TC_TRACE(1, i, 0);
       float rowsum = 0.f;  // of the bf16-rounded masked W, the values the read-out MMA multiplies
       // last column (token of the chunk) this row may see: itself, or the end of its block
@@ -990,17 +994,17 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       }
       const float inv = (SPLIT && !den_ok) ? 0.f : rcp_approx(den);  // (a true division compiles to a call here)
       if (SPLIT && !xmerge && p.part_y != nullptr && tt < nvalid && value_col0<ZS, SPLIT>() == 0)
-        p.part_lw[(part_row0 + t0 + tt) * p.H + h] = den_ok ? misc->kap[par] + __log2f(den) : -INFINITY;
+        p.part_lw[(part_row0 + t0 + tt) * p.H + h] = den_ok ? kap_i + __log2f(den) : -INFINITY;
       // log-sum-exp of the token's decode scores = log of the decode weights' mass in the frame kappa
       if (!SPLIT && p.lse_dec != nullptr && tt < nvalid && value_col0<ZS, SPLIT>() == 0)
-        p.lse_dec[(int64_t)lane_id * p.N + t0 + tt] = (misc->kap[par] + __log2f(den)) * kLn2;
+        p.lse_dec[(int64_t)lane_id * p.N + t0 + tt] = (kap_i + __log2f(den)) * kLn2;
       if constexpr (WIDE && SPLIT) {
         if (xmerge) {
           // Two latent groups = two CTAs of a cluster.  CTA r finalises value block r: it sends its normalised
           // partial of the OTHER block (fp16) and the log2 of its weight mass into the partner's shared memory,
           // takes the partner's rows for its own block, and stores y = sum_g w_g y_g / sum_g w_g.
           const uint32_t rank = cluster_ctarank(), peer = rank ^ 1u;
-          const float lw_own = den_ok ? misc->kap[par] + __log2f(den) : -INFINITY;
+          const float lw_own = den_ok ? kap_i + __log2f(den) : -INFINITY;
           uint32_t ra[32], rb[32], pk[32];
           // The exchange tile was the source of the previous chunk's bulk stores: once they have read it the partner
           // may send this chunk's rows (32 rows x 128 bytes and 32 weight masses per warp), which the barrier counts.
