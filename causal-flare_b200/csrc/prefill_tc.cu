@@ -603,9 +603,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       misc->xsum[par][hf][m] = tot0 + tot1;
       // (chunk 0 published its maximum before the pass; an empty half stays at -inf)
       if (i > 0) misc->xmax[par][hf][m] = live ? fmaxf(cma, cmb) + c_new : -INFINITY;
-      if (!(tot0 + tot1 < INFINITY)) {
-        // an encoder weight overflowed (the running max grew by more than fp32 holds inside one chunk): outside the
-        // numeric domain of this path
+      if (!(tot0 + tot1 < 1.15e18f)) {
+        // the running max grew by more than 60 powers of two inside one chunk (the frame is the max through the
+        // previous chunk): the denominators of this row leave the range in which the read-out weights are safe, see
+        // the token group's check; an overflow (or a NaN) lands here as well.  Outside the numeric domain of this path.
         atomicOr(p.err, 2);
         if (p.gate != nullptr) {
           p.gate[0] = 1;
@@ -981,11 +982,15 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       tmem_ld1(tl + TM_DEN, den0);
       tmem_wait_ld();
       const float den = __uint_as_float(den0) + rowsum;
-      const bool den_ok = den > 0.f && den < INFINITY;
-      // outside the numeric domain of this path (scores of a token more than ~80 nats below the running maxima):
-      // every weight underflowed.  Flag it; the exact path has no such limit.  With a latent-group split one group
-      // may legitimately carry no weight; the merge kernel flags a token only when every group is empty.
-      if (!SPLIT && tt < nvalid && !den_ok) {
+      // Numeric domain of this path.  The read-out weight of (token, latent) is R = E a_m / D: it is flushed to zero
+      // below 2^-126, while what it stands for, R D = the token's decode weight in the frame kappa, may still matter
+      // when the whole token's weight mass is small.  With the row denominators held below 2^60 (checked by the latent
+      // group) a flushed weight is below 2^-66, so a token whose mass is at least 2^-40 loses nothing it can see in
+      // bf16; below that, or with a mass that overflowed or is not a number, the token is flagged and the exact path,
+      // which has no such limit, redoes its lane.  With several latent groups each group's own mass is held to this
+      // (the frames differ between groups, so a group that looks empty in its own frame may carry the token).
+      const bool den_ok = den >= 9.1e-13f && den < INFINITY;
+      if (tt < nvalid && !den_ok) {
         atomicOr(p.err, 2);
         if (p.gate != nullptr) {
           p.gate[0] = 1;

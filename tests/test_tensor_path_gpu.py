@@ -133,6 +133,28 @@ def test_sharp_softmax_shapes_forward_and_backward_with_default_settings(N, qk_s
     _ops.device_status()  # clear the informational flag for the tests that follow
 
 
+@pytest.mark.parametrize("B, N, H, Ml, Dl, bs", [(2, 1024, 40, 256, 128, 1), (2, 1024, 40, 256, 128, 64),
+                                                 (1, 512, 160, 128, 128, 1), (1, 1024, 16, 256, 128, 1)])
+def test_sharp_scores_on_wide_heads_and_latent_groups_with_default_settings(B, N, H, Ml, Dl, bs):
+    # Sharp scores (standard deviation 16) on the (128, 128) head shape, with one and two latent groups, on grids that
+    # take the two-slice, the wide and the cluster-merged instance.  Three things went wrong here before the numeric
+    # domain checks were tightened: a latent group whose weight mass was not a number passed as "empty" (NaN rows), a
+    # read-out weight R = E a / D flushed to zero under a denominator that had grown by 2^43 inside one chunk (one
+    # token off by 0.37), and the lane gates of such tokens were not raised.  Every entry is checked, per lane.
+    g = torch.Generator().manual_seed(4 + N + H)
+    q = (torch.randn(H, Ml, Dl, generator=g) * 4.0).bfloat16()
+    k = (torch.randn(B, N, H, Dl, generator=g) * 4.0).bfloat16()
+    v = torch.randn(B, N, H, Dl, generator=g).bfloat16()
+    sc = Dl ** -0.5
+    ref = orc.ar_forward(q, k, v, scale=sc) if bs == 1 else orc.semi_ar_forward(q, k, v, block_size=bs, scale=sc)[0]
+    y = _ops.forward(*to_dev(q, k, v), scale=sc, block_size=bs)[0]  # default path
+    assert torch.isfinite(y.float()).all()
+    assert_bf16_gate(y, ref, "sharp scores, default path", max_abs=max(2e-2, 1e-2 * float(ref.abs().max())))
+    d = y.float().cpu() - ref.float()
+    assert float(d.abs().amax(dim=(1, 3)).max()) <= max(2e-2, 1e-2 * float(ref.abs().max())), "worst lane"
+    _ops.device_status()  # clear the informational flag for the tests that follow
+
+
 @pytest.mark.parametrize("Ml", [16, 64, 96])
 def test_tensor_path_fewer_latents(Ml):
     q, k, v = orc.make_inputs(2, 333, 2, Ml, D, seed0=19, dtype=torch.bfloat16)
