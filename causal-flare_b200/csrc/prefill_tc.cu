@@ -497,6 +497,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         float wm = live ? c_new : -INFINITY;
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) wm = fmaxf(wm, __shfl_xor_sync(0xffffffffu, wm, o));
+        // (Two slots suffice: the slot written now is read by the other warps at the top of the NEXT chunk and
+        // rewritten at the top of the one after; a warp gets that far only after every warp has finished this chunk -
+        // the state update it waits for follows the product that waits for all of them - and has 3 000 cycles of passes
+        // of its own in between, while a reader needs a few hundred from the end of this chunk to its read.  Four
+        // slots indexed by chunk % 4 measured 4 % slower: one more live value in a register-capped loop.)
         if (lane == 0) misc->wmax[par][q] = wm;
       }
       if (i == 0) {
