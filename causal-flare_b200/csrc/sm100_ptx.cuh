@@ -61,13 +61,6 @@ __device__ __forceinline__ uint32_t mapa_shared(uint32_t cta_smem_addr, uint32_t
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(cta_smem_addr), "r"(rank));
   return r;
 }
-__device__ __forceinline__ void st_cluster_v4(uint32_t cluster_addr, uint4 v) {
-  asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(cluster_addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
-               : "memory");
-}
-__device__ __forceinline__ void st_cluster_f32(uint32_t cluster_addr, float v) {
-  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(cluster_addr), "f"(v) : "memory");
-}
 // Asynchronous store into another CTA's shared memory that reports its bytes to a barrier of THAT CTA when it lands
 // (both addresses in the shared::cluster window of the same CTA).  The receiver arms the barrier with expect_tx and
 // waits on it; no fence on the sending side.
@@ -86,10 +79,6 @@ __device__ __forceinline__ void st_async_b32(uint32_t cluster_addr, uint32_t v, 
 // read before)
 __device__ __forceinline__ void mbar_arrive_cluster_relaxed(uint32_t cluster_bar_addr) {
   asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar_addr) : "memory");
-}
-// arrive on a barrier of another CTA of the cluster; releases this thread's earlier writes at cluster scope
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar_addr) : "memory");
 }
 // suspending wait on a barrier of this CTA that threads of another CTA arrive on (acquire at cluster scope)
 __device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
@@ -159,14 +148,6 @@ __device__ __forceinline__ void bulk_wait_group_read0() { asm volatile("cp.async
 __device__ __forceinline__ void bulk_wait_group0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void prefetch_tensormap(const void* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
-}
-// untiled bulk copy global -> shared (both addresses 16-byte aligned, size a multiple of 16 bytes), completion on an
-// mbarrier of this CTA
-__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                   smem_u32(smem_dst)),
-               "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
-               : "memory");
 }
 
 // ---------------------------------------------------------------------------------------------
