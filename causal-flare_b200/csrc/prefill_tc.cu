@@ -940,7 +940,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       // wrong weight masses for the merge of latent groups)
       const float kap_i = misc->kap[i & 3];
       if (tid == 256) TC_TRACE(1, i, 0);
-      float rowsum = 0.f;  // of the bf16-rounded masked W, the values the read-out MMA multiplies
+      uint64_t rs2 = f2_pack(0.f, 0.f);  // row sum of the bf16-rounded masked W (the values the read-out MMA multiplies), as a pair of partial sums
       // last column (token of the chunk) this row may see: itself, or the end of its block
       const int be = BLOCK ? (tt | (p.block - 1)) : tt;
 #pragma unroll 1
@@ -956,7 +956,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             for (int k = 0; k < 32; k += 2) {
               const uint32_t pk = pack_bf16(__uint_as_float(r[k]), __uint_as_float(r[k + 1]));
               wp[k >> 1] = pk;
-              rowsum += __uint_as_float(pk << 16) + __uint_as_float(pk & 0xffff0000u);
+              rs2 = f2_add(rs2, f2_pack(__uint_as_float(pk << 16), __uint_as_float(pk & 0xffff0000u)));
             }
           } else {
 #pragma unroll
@@ -965,7 +965,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
               const float w1 = (BLOCK ? (j * 32 + k + 1 <= be) : (k + 1 <= lane)) ? __uint_as_float(r[k + 1]) : 0.f;
               const uint32_t pk = pack_bf16(w0, w1);
               wp[k >> 1] = pk;
-              rowsum += __uint_as_float(pk << 16) + __uint_as_float(pk & 0xffff0000u);
+              rs2 = f2_add(rs2, f2_pack(__uint_as_float(pk << 16), __uint_as_float(pk & 0xffff0000u)));
             }
           }
         } else {
@@ -986,7 +986,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       uint32_t den0;
       tmem_ld1(tl + TM_DEN, den0);
       tmem_wait_ld();
-      const float den = __uint_as_float(den0) + rowsum;
+      float rs_lo, rs_hi;
+      f2_unpack(rs2, rs_lo, rs_hi);
+      const float den = __uint_as_float(den0) + (rs_lo + rs_hi);
       // Numeric domain of this path.  The read-out weight of (token, latent) is R = E a_m / D: it is flushed to zero
       // below 2^-126, while what it stands for, R D = the token's decode weight in the frame kappa, may still matter
       // when the whole token's weight mass is small.  With the row denominators held below 2^60 (checked by the latent
@@ -1030,8 +1032,12 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           tmem_wait_ld();
 #pragma unroll
           for (int k = 0; k < 16; ++k) {
-            pk[k] = pack_f16(__uint_as_float(ra[2 * k]) * inv, __uint_as_float(ra[2 * k + 1]) * inv);
-            pk[16 + k] = pack_f16(__uint_as_float(rb[2 * k]) * inv, __uint_as_float(rb[2 * k + 1]) * inv);
+            const uint64_t inv2 = f2_pack(inv, inv);
+            float a0, a1, b0, b1;
+            f2_unpack(f2_mul(f2_pack(__uint_as_float(ra[2 * k]), __uint_as_float(ra[2 * k + 1])), inv2), a0, a1);
+            f2_unpack(f2_mul(f2_pack(__uint_as_float(rb[2 * k]), __uint_as_float(rb[2 * k + 1])), inv2), b0, b1);
+            pk[k] = pack_f16(a0, a1);
+            pk[16 + k] = pack_f16(b0, b1);
           }
           tmem_ld32(tl + TM_Y + rank * 64, ra);
           tmem_ld32(tl + TM_Y + rank * 64 + 32, rb);
@@ -1097,8 +1103,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 #pragma unroll
               for (int j = 0; j < 4; ++j) {
                 const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&xw[j]));
-                o[j] = pack_bf16(__uint_as_float(r[ch * 8 + 2 * j]) * ca + f.x * cb,
-                                 __uint_as_float(r[ch * 8 + 2 * j + 1]) * ca + f.y * cb);
+                float y0, y1;  // own raw values * ca + partner's normalised values * cb, two columns per instruction
+                f2_unpack(f2_fma(f2_pack(__uint_as_float(r[ch * 8 + 2 * j]), __uint_as_float(r[ch * 8 + 2 * j + 1])),
+                                 f2_pack(ca, ca), f2_mul(f2_pack(f.x, f.y), f2_pack(cb, cb))), y0, y1);
+                o[j] = pack_bf16(y0, y1);
               }
               *reinterpret_cast<uint4*>(xt + half * 2048 + lane * 64 + ((ch ^ ((lane >> 1) & 3)) << 4)) =
                   make_uint4(o[0], o[1], o[2], o[3]);
