@@ -497,6 +497,14 @@ def bench_other_shapes(which="all"):
             lambda: cf.flare_semi_autoregressive_trition(q, k, v, block_size=bs, chunk_size=64), n=3)
     out["C5"] = f"B={B} N={N} H={H} M={M} D={D} block={bs} bf16, whole sequence on one GPU"
     out["C5_roofline"] = _shape_roofline(B * N * H, M, D, D, out["C5_one_gpu_semi_ar_forward_ms"], flops_per_md=6, tensors=3)
+    del q, k, v
+    # the headline shape with fp16 inputs: bf16 copies of q, k, v in the workspace, tensor-core kernels, y back as fp16
+    c = C2
+    q = torch.randn(c["H"], c["M"], c["Dk"], generator=g, device="cuda").half()
+    k = torch.randn(c["B"], c["N"], c["H"], c["Dk"], generator=g, device="cuda").half()
+    v = torch.randn(c["B"], c["N"], c["H"], c["Dv"], generator=g, device="cuda").half()
+    with torch.no_grad():
+        out["C2_fp16_forward_ms"] = timed(lambda: cf.flare_autoregressive_triton(q, k, v))
     return out
 
 

@@ -1,5 +1,6 @@
 // extern "C" entry points of libflare_b200.so: argument validation, launch planning, dispatch.
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include "bwd_exact.cuh"
@@ -355,6 +356,81 @@ int forward_tensor_or_exact(const flare_fwd_args_t* a, const FwdPlan& pl, cudaSt
   return launch_walk(a, pl, w, pl.nseg, stream);
 }
 
+// fp16 inputs on the tensor-core kernels.  The kernels multiply bf16 operands (the tensor-core products of E, R, W
+// and the running state are bf16 whatever the inputs are), so an fp16 call is served by rounding q, k, v to bf16
+// copies in the workspace, running the bf16 forward on those, and writing y back as fp16: three streaming passes
+// around a kernel that is 40 to 60 times faster than the exact walk the call would otherwise take.  States and
+// log-sum-exps are fp32 on both sides and go straight to the caller's buffers.  Not for the training forward (no
+// state is kept for a backward) and not with separate decode weights or a mask, which the tensor kernels do not take.
+struct CastPlan {
+  bool on;
+  size_t off_q, off_k, off_v, off_y, total;
+};
+
+CastPlan plan_cast(const flare_fwd_args_t* a, flare_fwd_args_t* b) {
+  CastPlan cp{false, 0, 0, 0, 0, 0};
+  if (a->dtype != FLARE_F16 || a->path == FLARE_PATH_EXACT || a->keep != nullptr || a->q_dec != nullptr ||
+      a->k_dec != nullptr || a->mask != nullptr || a->B == 0 || a->N == 0)
+    return cp;
+  // FLARE_B200_FP16_TENSOR=0 keeps fp16 calls on the exact kernels (q, k, v at their full fp16 precision)
+  if (const char* env = getenv("FLARE_B200_FP16_TENSOR"))
+    if (env[0] == '0') return cp;
+  *b = *a;
+  b->dtype = FLARE_BF16;
+  b->q_stride_m = a->Dk; b->q_stride_h = (int64_t)a->M * a->Dk;
+  b->k_stride_h = a->Dk; b->k_stride_n = (int64_t)a->H * a->Dk; b->k_stride_b = (int64_t)a->N * b->k_stride_n;
+  b->v_stride_h = a->Dv; b->v_stride_n = (int64_t)a->H * a->Dv; b->v_stride_b = (int64_t)a->N * b->v_stride_n;
+  b->y_stride_h = a->Dv; b->y_stride_n = (int64_t)a->H * a->Dv; b->y_stride_b = (int64_t)a->N * b->y_stride_n;
+  if (!prefill_tc_supported(b)) return cp;
+  const size_t rows = (size_t)a->B * a->N * a->H;
+  cp.on = true;
+  cp.off_q = 0;
+  cp.off_k = align_up((size_t)a->H * a->M * a->Dk * 2, 256);
+  cp.off_v = cp.off_k + align_up(rows * a->Dk * 2, 256);
+  cp.off_y = cp.off_v + align_up(rows * a->Dv * 2, 256);
+  cp.total = cp.off_y + (a->y != nullptr ? align_up(rows * a->Dv * 2, 256) : 0);
+  return cp;
+}
+
+int forward_cast(const flare_fwd_args_t* a, flare_fwd_args_t& b, const CastPlan& cp, cudaStream_t stream) {
+  const size_t inner = plan_forward(&b).ws_bytes;
+  if (a->workspace == nullptr || a->workspace_bytes < cp.total + inner || !aligned16(a->workspace)) return FLARE_ERR_WORKSPACE;
+  char* ws = reinterpret_cast<char*>(a->workspace);
+  b.q = ws + cp.off_q; b.k = ws + cp.off_k; b.v = ws + cp.off_v;
+  b.y = a->y != nullptr ? ws + cp.off_y : nullptr;
+  b.workspace = inner > 0 ? ws + cp.total : nullptr;
+  b.workspace_bytes = inner > 0 ? a->workspace_bytes - cp.total : 0;
+  CastParams c;
+  memset(&c, 0, sizeof(c));
+  c.in = a->q; c.out = const_cast<void*>(b.q); c.n0 = 1; c.n1 = a->H; c.n2 = a->M; c.d = a->Dk;
+  c.is1 = a->q_stride_h; c.is2 = a->q_stride_m; c.os1 = b.q_stride_h; c.os2 = b.q_stride_m;
+  int rc = launch_cast_rows(c, stream);
+  if (rc != FLARE_OK) return rc;
+  c.in = a->k; c.out = const_cast<void*>(b.k); c.n0 = a->B; c.n1 = a->N; c.n2 = a->H; c.d = a->Dk;
+  c.is0 = a->k_stride_b; c.is1 = a->k_stride_n; c.is2 = a->k_stride_h;
+  c.os0 = b.k_stride_b; c.os1 = b.k_stride_n; c.os2 = b.k_stride_h;
+  rc = launch_cast_rows(c, stream);
+  if (rc != FLARE_OK) return rc;
+  c.in = a->v; c.out = const_cast<void*>(b.v); c.d = a->Dv;
+  c.is0 = a->v_stride_b; c.is1 = a->v_stride_n; c.is2 = a->v_stride_h;
+  c.os0 = b.v_stride_b; c.os1 = b.v_stride_n; c.os2 = b.v_stride_h;
+  rc = launch_cast_rows(c, stream);
+  if (rc != FLARE_OK) return rc;
+  rc = forward_run(&b, stream);  // with its own gate words and exact standby, on the bf16 copies
+  if (rc != FLARE_OK) return rc;
+  int casts = 3;
+  if (a->y != nullptr) {
+    c.in = b.y; c.out = a->y; c.to_f16 = 1;
+    c.is0 = b.y_stride_b; c.is1 = b.y_stride_n; c.is2 = b.y_stride_h;
+    c.os0 = a->y_stride_b; c.os1 = a->y_stride_n; c.os2 = a->y_stride_h;
+    rc = launch_cast_rows(c, stream);
+    if (rc != FLARE_OK) return rc;
+    ++casts;
+  }
+  g_last_launches += casts;
+  return FLARE_OK;
+}
+
 }  // namespace
 
 int forward_keep_states(const flare_fwd_args_t* a, const ChunkStates& keep, int* gate, cudaStream_t stream) {
@@ -414,6 +490,9 @@ extern "C" {
 
 size_t flare_forward_workspace_bytes(const flare_fwd_args_t* args) {
   if (check_forward(args) != FLARE_OK) return 0;
+  flare_fwd_args_t b;
+  const CastPlan cp = plan_cast(args, &b);
+  if (cp.on) return cp.total + plan_forward(&b).ws_bytes;
   return plan_forward(args).ws_bytes;
 }
 
@@ -442,6 +521,9 @@ int flare_forward(const flare_fwd_args_t* args, flare_stream_t stream) {
     }
     return FLARE_OK;
   }
+  flare_fwd_args_t b;
+  const CastPlan cp = plan_cast(args, &b);
+  if (cp.on) return forward_cast(args, b, cp, stream);
   return forward_run(args, stream);
 }
 
@@ -558,6 +640,8 @@ void flare_set_trace_buffer(void* device_buffer) { g_trace = static_cast<long lo
 
 int flare_forward_uses_tensor_path(const flare_fwd_args_t* args) {
   if (check_forward(args) != FLARE_OK) return 0;
+  flare_fwd_args_t b;
+  if (plan_cast(args, &b).on) return 1;
   return plan_forward(args).use_tc ? 1 : 0;
 }
 

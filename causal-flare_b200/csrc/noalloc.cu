@@ -31,7 +31,13 @@ int flare_forward_noalloc(const flare_fwd_args_t* args, flare_stream_t stream) {
   flare_fwd_args_t a = *args;
   a.workspace = nullptr;
   a.workspace_bytes = 0;
-  const size_t need = flare_forward_workspace_bytes(&a);
+  size_t need = flare_forward_workspace_bytes(&a);
+  if (need > FLARE_NOALLOC_SCRATCH_BYTES && a.dtype == FLARE_F16 && a.path != FLARE_PATH_EXACT) {
+    // the tensor-core route of an fp16 call keeps bf16 copies of k and v in the workspace; when those do not fit the
+    // built-in scratch the call runs on the exact kernels, which read fp16 directly
+    a.path = FLARE_PATH_EXACT;
+    need = flare_forward_workspace_bytes(&a);
+  }
   if (need > FLARE_NOALLOC_SCRATCH_BYTES) return FLARE_ERR_TOO_LARGE;
   // What must start at zero is cleared by flare_forward itself, on the stream (the gate words of the default path);
   // the segment pass writes every state slot before the scan and the output pass read it.  The rest of the previous

@@ -91,7 +91,54 @@ __global__ void __launch_bounds__(NT) fold_kernel(const FoldParams p) {
   }
 }
 
+template <bool TO_F16>
+__global__ void __launch_bounds__(256) cast_rows_kernel(const CastParams p) {
+  const int c8n = p.d >> 3;
+  const int64_t total = p.n0 * p.n1 * p.n2 * c8n;
+  const uint16_t* in = reinterpret_cast<const uint16_t*>(p.in);
+  uint16_t* out = reinterpret_cast<uint16_t*>(p.out);
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
+    const int c8 = (int)(idx % c8n);
+    int64_t r = idx / c8n;
+    const int64_t i2 = r % p.n2;
+    r /= p.n2;
+    const int64_t i1 = r % p.n1;
+    const int64_t i0 = r / p.n1;
+    uint4 x = *reinterpret_cast<const uint4*>(in + i0 * p.is0 + i1 * p.is1 + i2 * p.is2 + c8 * 8);
+    uint32_t w[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (TO_F16) {
+        const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[j]));
+        const __half2 h = __floats2half2_rn(f.x, f.y);
+        w[j] = *reinterpret_cast<const uint32_t*>(&h);
+      } else {
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
+        const __nv_bfloat162 h = __floats2bfloat162_rn(f.x, f.y);
+        w[j] = *reinterpret_cast<const uint32_t*>(&h);
+      }
+    }
+    *reinterpret_cast<uint4*>(out + i0 * p.os0 + i1 * p.os1 + i2 * p.os2 + c8 * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+}
+
 }  // namespace
+
+int launch_cast_rows(const CastParams& p, cudaStream_t stream) {
+  const int64_t total = p.n0 * p.n1 * p.n2 * (p.d >> 3);
+  if (total <= 0) return FLARE_OK;
+  if (p.d % 8) return FLARE_ERR_BAD_SHAPE;
+  int64_t blocks = (total + 255) / 256;
+  const int64_t cap = (int64_t)sm_count() * 16;
+  if (blocks > cap) blocks = cap;
+  LaunchTimer timer(p.to_f16 ? "cast_rows_kernel<bf16 to fp16>" : "cast_rows_kernel<fp16 to bf16>", stream);
+  if (p.to_f16)
+    cast_rows_kernel<true><<<(unsigned)blocks, 256, 0, stream>>>(p);
+  else
+    cast_rows_kernel<false><<<(unsigned)blocks, 256, 0, stream>>>(p);
+  FLARE_CUDA_CHECK(cudaGetLastError());
+  return FLARE_OK;
+}
 
 int launch_fold(const FoldParams& p, cudaStream_t stream) {
   if (p.lanes <= 0 || p.count <= 0) return FLARE_OK;

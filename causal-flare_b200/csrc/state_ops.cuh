@@ -23,4 +23,18 @@ struct FoldParams {
 
 int launch_fold(const FoldParams& p, cudaStream_t stream);
 
+// fp16 <-> bf16 copy of a tensor of rows: n0 x n1 x n2 rows of d contiguous 2-byte elements (d a multiple of 8, row
+// starts 16-byte aligned), row (i0, i1, i2) at element offset i0 * s0 + i1 * s1 + i2 * s2 on either side.
+struct CastParams {
+  const void* in;
+  void* out;
+  int64_t n0, n1, n2;
+  int d;
+  int64_t is0, is1, is2;
+  int64_t os0, os1, os2;
+  int to_f16;  // 1: bf16 -> fp16, 0: fp16 -> bf16
+};
+
+int launch_cast_rows(const CastParams& p, cudaStream_t stream);
+
 }  // namespace flare

@@ -230,7 +230,8 @@ int flare_profile_entry(int i, const char** name, float* ms);
 void flare_set_trace_buffer(void* device_buffer);
 
 /* 1 when flare_forward would take the tcgen05 tensor-core path for this problem, else 0.  That is: path AUTO or
- * TENSOR, bf16, 16 <= M <= 512 (multiple of 16), (Dk, Dv) = (64, 64), (128, 128) or (64, 128), shared decode weights (q_dec = k_dec = NULL),
+ * TENSOR, bf16 (or fp16 without args->keep: q, k, v are rounded to bf16 copies in the workspace, the kernels run on
+ * those and y is written back as fp16; flare_forward_workspace_bytes includes the copies), 16 <= M <= 512 (multiple of 16), (Dk, Dv) = (64, 64), (128, 128) or (64, 128), shared decode weights (q_dec = k_dec = NULL),
  * mask = NULL, and either the softmax encoder with block_size 1 / 16 / 32 / 64 / 128 (N a multiple of it) or the
  * stablemax encoder with block_size 1; lse_enc only with block_size > 1; lengths only with block_size 1. */
 int flare_forward_uses_tensor_path(const flare_fwd_args_t* args);

@@ -104,6 +104,26 @@ def test_workspace_plan_small_batch_is_segmented():
     assert lib.flare_forward(C.byref(few), None) == 4
 
 
+def test_fp16_plan_takes_the_tensor_path_through_bf16_copies():
+    lib = _lib.load()
+    B, N, H, M, D = 8, 8192, 64, 64, 64
+    bf = _fake_args(B=B, N=N, H=H, M=M, Dk=D, Dv=D, path=_lib.PATH_TENSOR)
+    hf = _fake_args(B=B, N=N, H=H, M=M, Dk=D, Dv=D, path=_lib.PATH_TENSOR, dtype=_lib.F16)
+    assert lib.flare_forward_uses_tensor_path(C.byref(bf)) == 1
+    assert lib.flare_forward_uses_tensor_path(C.byref(hf)) == 1
+    # bf16 copies of q, k, v and a bf16 y (each rounded up to 256 bytes) on top of the bf16 plan
+    copies = (H * M * D * 2 + 255) // 256 * 256 + 3 * (B * N * H * D * 2)
+    assert lib.flare_forward_workspace_bytes(C.byref(hf)) == lib.flare_forward_workspace_bytes(C.byref(bf)) + copies
+    hf.workspace, hf.workspace_bytes = 0x2000, copies - 256
+    assert lib.flare_forward(C.byref(hf), None) == 4  # too small: refused before any launch
+    # the exact kernels read fp16 directly; the training forward and separate decode weights stay on them
+    assert lib.flare_forward_keep_bytes(C.byref(hf)) == 0
+    for kw in (dict(path=_lib.PATH_EXACT), dict(q_dec=0x1000, qd_stride_b=N * H * D, qd_stride_n=H * D, qd_stride_h=D),
+               dict(Dk=32, Dv=32)):
+        other = _fake_args(B=B, N=N, H=H, M=M, **{"Dk": D, "Dv": D, "dtype": _lib.F16, **kw})
+        assert lib.flare_forward_uses_tensor_path(C.byref(other)) == 0
+
+
 def test_decode_and_merge_reject_bad_problems():
     lib = _lib.load()
     d = _lib.DecodeArgs()
