@@ -505,6 +505,13 @@ def bench_other_shapes(which="all"):
     v = torch.randn(c["B"], c["N"], c["H"], c["Dv"], generator=g, device="cuda").half()
     with torch.no_grad():
         out["C2_fp16_forward_ms"] = timed(lambda: cf.flare_autoregressive_triton(q, k, v))
+    del q, k, v
+    B, N, H, M, D = 4, 4096, 16, 64, 128  # the training shape with fp16 tensors
+    q = torch.randn(H, M, D, generator=g, device="cuda").half().requires_grad_()
+    k = torch.randn(B, N, H, D, generator=g, device="cuda").half().requires_grad_()
+    v = torch.randn(B, N, H, D, generator=g, device="cuda").half().requires_grad_()
+    dy = torch.randn(B, N, H, D, generator=g, device="cuda").half()
+    out["C4_fp16_fwd_bwd_softmax_ms"] = timed(lambda: train_step(cf.flare_autoregressive_triton), n=3)
     return out
 
 

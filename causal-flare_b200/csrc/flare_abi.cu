@@ -544,8 +544,106 @@ static int check_backward(const flare_bwd_args_t* args) {
   return FLARE_OK;
 }
 
+// fp16 gradients on the tensor-core backward, the same way as the fp16 forward: bf16 copies of q, k, v and dY in the
+// workspace, the bf16 backward (with its own replay of the forward, gate and exact standby) on those, dK and dV
+// written back as fp16; dQ is fp32 on both sides.
+namespace {
+struct BwdCastPlan {
+  bool on;
+  size_t off_q, off_k, off_v, off_dy, off_dk, off_dv, total;
+};
+
+BwdCastPlan plan_bwd_cast(const flare_bwd_args_t* a, flare_bwd_args_t* b) {
+  BwdCastPlan cp;
+  memset(&cp, 0, sizeof(cp));
+  const flare_fwd_args_t& f = a->fwd;
+  if (f.dtype != FLARE_F16 || f.path == FLARE_PATH_EXACT || f.q_dec != nullptr || f.k_dec != nullptr || f.B == 0 || f.N == 0)
+    return cp;
+  if (const char* env = getenv("FLARE_B200_FP16_TENSOR"))
+    if (env[0] == '0') return cp;
+  *b = *a;
+  flare_fwd_args_t& g = b->fwd;
+  g.dtype = FLARE_BF16;
+  g.q_stride_m = f.Dk; g.q_stride_h = (int64_t)f.M * f.Dk;
+  g.k_stride_h = f.Dk; g.k_stride_n = (int64_t)f.H * f.Dk; g.k_stride_b = (int64_t)f.N * g.k_stride_n;
+  g.v_stride_h = f.Dv; g.v_stride_n = (int64_t)f.H * f.Dv; g.v_stride_b = (int64_t)f.N * g.v_stride_n;
+  b->dy_stride_h = f.Dv; b->dy_stride_n = (int64_t)f.H * f.Dv; b->dy_stride_b = (int64_t)f.N * b->dy_stride_n;
+  g.keep = nullptr; g.keep_bytes = 0;  // an fp16 forward keeps nothing: the backward replays it
+  b->y = nullptr; b->lse_dec = nullptr;
+  if (!bwd_tc_supported(*b)) return cp;
+  const size_t rows = (size_t)f.B * f.N * f.H;
+  size_t off = 0;
+  auto take = [&](size_t bytes) {
+    const size_t o = off;
+    off += align_up(bytes, 256);
+    return o;
+  };
+  cp.on = true;
+  cp.off_q = take((size_t)f.H * f.M * f.Dk * 2);
+  cp.off_k = take(rows * f.Dk * 2);
+  cp.off_v = take(rows * f.Dv * 2);
+  cp.off_dy = take(rows * f.Dv * 2);
+  cp.off_dk = take(rows * f.Dk * 2);
+  cp.off_dv = take(rows * f.Dv * 2);
+  cp.total = off;
+  return cp;
+}
+
+int backward_cast(const flare_bwd_args_t* a, flare_bwd_args_t& b, const BwdCastPlan& cp, cudaStream_t stream) {
+  const flare_fwd_args_t& f = a->fwd;
+  const size_t inner = bwd_tc_workspace_bytes(b);
+  if (f.workspace == nullptr || f.workspace_bytes < cp.total + inner || (reinterpret_cast<uintptr_t>(f.workspace) & 255u))
+    return FLARE_ERR_WORKSPACE;
+  char* ws = reinterpret_cast<char*>(f.workspace);
+  flare_fwd_args_t& g = b.fwd;
+  g.q = ws + cp.off_q; g.k = ws + cp.off_k; g.v = ws + cp.off_v;
+  b.dy = ws + cp.off_dy; b.dk = ws + cp.off_dk; b.dv = ws + cp.off_dv;
+  g.workspace = ws + cp.total;
+  g.workspace_bytes = f.workspace_bytes - cp.total;
+  CastParams c;
+  memset(&c, 0, sizeof(c));
+  c.in = f.q; c.out = const_cast<void*>(g.q); c.n0 = 1; c.n1 = f.H; c.n2 = f.M; c.d = f.Dk;
+  c.is1 = f.q_stride_h; c.is2 = f.q_stride_m; c.os1 = g.q_stride_h; c.os2 = g.q_stride_m;
+  int rc = launch_cast_rows(c, stream);
+  if (rc != FLARE_OK) return rc;
+  c.in = f.k; c.out = const_cast<void*>(g.k); c.n0 = f.B; c.n1 = f.N; c.n2 = f.H; c.d = f.Dk;
+  c.is0 = f.k_stride_b; c.is1 = f.k_stride_n; c.is2 = f.k_stride_h;
+  c.os0 = g.k_stride_b; c.os1 = g.k_stride_n; c.os2 = g.k_stride_h;
+  rc = launch_cast_rows(c, stream);
+  if (rc != FLARE_OK) return rc;
+  c.in = f.v; c.out = const_cast<void*>(g.v); c.d = f.Dv;
+  c.is0 = f.v_stride_b; c.is1 = f.v_stride_n; c.is2 = f.v_stride_h;
+  c.os0 = g.v_stride_b; c.os1 = g.v_stride_n; c.os2 = g.v_stride_h;
+  rc = launch_cast_rows(c, stream);
+  if (rc != FLARE_OK) return rc;
+  c.in = a->dy; c.out = const_cast<void*>(b.dy);
+  c.is0 = a->dy_stride_b; c.is1 = a->dy_stride_n; c.is2 = a->dy_stride_h;
+  c.os0 = b.dy_stride_b; c.os1 = b.dy_stride_n; c.os2 = b.dy_stride_h;
+  rc = launch_cast_rows(c, stream);
+  if (rc != FLARE_OK) return rc;
+  rc = bwd_tc(b, stream);
+  if (rc != FLARE_OK) return rc;
+  c.to_f16 = 1;
+  c.in = b.dv; c.out = a->dv;
+  c.is0 = c.os0 = b.dy_stride_b; c.is1 = c.os1 = b.dy_stride_n; c.is2 = c.os2 = b.dy_stride_h;
+  rc = launch_cast_rows(c, stream);
+  if (rc != FLARE_OK) return rc;
+  c.in = b.dk; c.out = a->dk; c.d = f.Dk;
+  c.is0 = c.os0 = g.k_stride_b; c.is1 = c.os1 = g.k_stride_n; c.is2 = c.os2 = g.k_stride_h;
+  rc = launch_cast_rows(c, stream);
+  if (rc != FLARE_OK) return rc;
+  g_last_launches += 6;
+  return FLARE_OK;
+}
+}  // namespace
+
 size_t flare_backward_workspace_bytes(const flare_bwd_args_t* args) {
   if (check_backward(args) != FLARE_OK) return 0;
+  {
+    flare_bwd_args_t b;
+    const BwdCastPlan cp = plan_bwd_cast(args, &b);
+    if (cp.on) return cp.total + bwd_tc_workspace_bytes(b);
+  }
   if (bwd_tc_supported(*args)) return bwd_tc_workspace_bytes(*args);
   return bwd_exact_workspace_bytes(*args);
 }
@@ -554,6 +652,11 @@ int flare_backward(const flare_bwd_args_t* args, flare_stream_t stream) {
   const int rc = check_backward(args);
   if (rc != FLARE_OK) return rc;
   g_last_launches = 0;
+  {
+    flare_bwd_args_t b;
+    const BwdCastPlan cp = plan_bwd_cast(args, &b);
+    if (cp.on) return backward_cast(args, b, cp, stream);
+  }
   if (bwd_tc_supported(*args)) return bwd_tc(*args, stream);
   return bwd_exact(*args, stream);
 }
@@ -647,6 +750,8 @@ int flare_forward_uses_tensor_path(const flare_fwd_args_t* args) {
 
 int flare_backward_uses_tensor_path(const flare_bwd_args_t* args) {
   if (check_backward(args) != FLARE_OK) return 0;
+  flare_bwd_args_t b;
+  if (plan_bwd_cast(args, &b).on) return 1;
   return bwd_tc_supported(*args) ? 1 : 0;
 }
 

@@ -115,3 +115,52 @@ def test_fp16_masked_rows_and_sharp_scores_keep_the_default_path_correct():
     assert ysh.dtype == F16
     assert_bf16_gate(ysh, ref.float(), "fp16 sharp scores on the default path",
                      max_abs=max(2e-2, 1e-2 * float(ref.float().abs().max())))
+
+
+@pytest.mark.parametrize("B, N, H, M, Dk, Dv, bs, variant", [
+    (2, 512, 2, 64, 128, 128, 1, "softmax"), (1, 300, 2, 64, 64, 64, 1, "softmax"), (1, 640, 2, 256, 128, 128, 64, "softmax"),
+    (1, 384, 1, 48, 64, 128, 1, "stablemax")])
+def test_fp16_backward_on_the_tensor_kernels(B, N, H, M, Dk, Dv, bs, variant):
+    # gradients of fp16 inputs: bf16 copies of q, k, v, dY, the tensor-core backward, dK / dV back as fp16.  Against the
+    # oracle on the bf16-rounded inputs the bound is the one of the bf16 shape sweep; against the oracle on the fp16
+    # inputs the rounding of the four inputs adds to it.
+    q, k, v, dy = orc.make_inputs(B, N, H, M, Dk, Dv, seed0=55, dtype=F16, with_dy=True)
+    sc = Dk ** -0.5
+    var = _lib.SOFTMAX if variant == "softmax" else _lib.STABLEMAX
+    qc, kc, vc, dyc = to_dev(q, k, v, dy)
+    a = _lib.BwdArgs()
+    a.fwd = _lib.make_fwd_args(qc, kc, vc, None, None, None, scale=sc, variant=var, block_size=bs)
+    a.dy = dyc.data_ptr()
+    a.dy_stride_b, a.dy_stride_n, a.dy_stride_h = dyc.stride(0), dyc.stride(1), dyc.stride(2)
+    dq0, dk0, dv0 = torch.empty(qc.shape, device="cuda"), torch.empty_like(kc), torch.empty_like(vc)
+    a.dq, a.dk, a.dv = dq0.data_ptr(), dk0.data_ptr(), dv0.data_ptr()
+    assert _lib.load().flare_backward_uses_tensor_path(C.byref(a)) == 1
+    dq, dk, dv, _, _ = _ops.backward(qc, kc, vc, dyc, scale=sc, variant=var, power=2.0, block_size=bs)
+    assert _ops.device_status() == 0
+    assert dq.dtype == torch.float32 and dk.dtype == F16 and dv.dtype == F16
+    got = dict(dQ=dq, dK=dk, dV=dv)
+    kw = dict(scale=sc, block_size=bs, variant=variant, power=2.0)
+    ref_b = orc.ar_backward_closed_form(q.bfloat16(), k.bfloat16(), v.bfloat16(), dy.bfloat16(), **kw)
+    ref_h = orc.ar_backward_closed_form(q, k, v, dy, **kw)
+    for key in ("dQ", "dK", "dV"):
+        peak = float(ref_h[key].abs().max())
+        assert_bf16_gate(got[key], ref_b[key], f"fp16 {key} vs oracle on the bf16 copies", max_abs=max(2e-2, peak * 2.0 ** -7),
+                         rel_l2=6.5e-3)
+        assert_bf16_gate(got[key], ref_h[key], f"fp16 {key} vs oracle on the fp16 inputs", max_abs=max(2e-2, peak * 2.0 ** -7),
+                         rel_l2=8e-3)
+
+
+def test_fp16_training_step_through_autograd():
+    B, N, H, M, D = 2, 512, 2, 64, 64
+    q, k, v, dy = orc.make_inputs(B, N, H, M, D, seed0=56, dtype=F16, with_dy=True)
+    ref = orc.ar_backward_closed_form(q, k, v, dy)
+    ql, kl, vl = (t.cuda().requires_grad_(True) for t in (q, k, v))
+    y = cf.flare_autoregressive_triton(ql, kl, vl)
+    assert y.dtype == F16
+    assert_bf16_gate(y, orc.ar_forward(q, k, v), "fp16 y of the training forward")
+    y.backward(dy.cuda())
+    assert _ops.device_status() == 0
+    for got, key in ((ql.grad, "dQ"), (kl.grad, "dK"), (vl.grad, "dV")):
+        assert got.dtype == F16
+        assert_bf16_gate(got, ref[key], f"fp16 autograd {key}", max_abs=max(2e-2, float(ref[key].abs().max()) * 2.0 ** -7),
+                         rel_l2=8e-3)
