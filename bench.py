@@ -45,7 +45,12 @@ def peaks():
 
 
 class ClockSampler:
-    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clock and throttle reasons with nvidia-smi while the GPU runs the timed workload.
+
+    nvidia-smi takes a while to come up and its start-up holds driver locks that stall kernel launches, so the sampler
+    is started - and has delivered its first sample - before the warm-up; ``begin()`` marks the start of the timed
+    region, and ``hold_load()`` keeps the same (untimed) workload running after it until a few samples have been taken
+    under that load (the timed region itself is a few milliseconds, the sampling period 20 ms)."""
 
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
@@ -53,7 +58,9 @@ class ClockSampler:
     def __init__(self, index: int):
         self.index = index
         self.samples = []
+        self.first = 0  # samples before this index were taken before the timed region
         self.proc = None
+        self.up = threading.Event()
 
     def __enter__(self):
         try:
@@ -62,6 +69,7 @@ class ClockSampler:
                  "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
+            self.up.wait(timeout=3.0)
         except OSError:
             self.proc = None
         return self
@@ -71,10 +79,23 @@ class ClockSampler:
             parts = [x.strip() for x in line.split(",")]
             if len(parts) >= 6:
                 self.samples.append(parts)
+                self.up.set()
+
+    def begin(self):
+        self.first = len(self.samples)
+
+    def hold_load(self, fn, min_samples=4, max_seconds=0.5):
+        """Run ``fn`` (the timed step, now untimed) until ``min_samples`` samples have been taken since ``begin()``."""
+        if self.proc is None or not self.up.is_set():
+            return
+        end = time.monotonic() + max_seconds
+        while len(self.samples) - self.first < min_samples and time.monotonic() < end:
+            for _ in range(8):
+                fn()
+            torch.cuda.current_stream().synchronize()
 
     def __exit__(self, *exc):
         if self.proc is not None:
-            time.sleep(0.15)
             self.proc.terminate()
             try:
                 self.proc.wait(timeout=2)
@@ -82,14 +103,15 @@ class ClockSampler:
                 self.proc.kill()
 
     def summary(self):
-        if not self.samples:
+        rows = self.samples[self.first:] or self.samples
+        if not rows:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        sm = [float(s[0]) for s in self.samples if s[0].replace(".", "").isdigit()]
-        mx = [float(s[1]) for s in self.samples if s[1].replace(".", "").isdigit()]
+        sm = [float(s[0]) for s in rows if s[0].replace(".", "").isdigit()]
+        mx = [float(s[1]) for s in rows if s[1].replace(".", "").isdigit()]
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        reasons = [n for i, n in enumerate(names) if any(s[2 + i].lower().startswith("active") for s in self.samples)]
+        reasons = [n for i, n in enumerate(names) if any(s[2 + i].lower().startswith("active") for s in rows)]
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": reasons, "samples": len(self.samples)}
+                "reasons": reasons, "samples": len(rows)}
 
 
 def dist_setup(n_gpus: int):
@@ -148,12 +170,13 @@ def bench_prefill(args, rank, world):
     ev_e = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
     for e in ev_b + ev_e:
         e.record()  # materialise the handles
-    for _ in range(args.warmup):
-        fn()
-    barrier(world)
     t0 = torch.cuda.Event(enable_timing=True)
     t1 = torch.cuda.Event(enable_timing=True)
     with ClockSampler(torch.cuda.current_device()) as clk:
+        for _ in range(args.warmup):
+            fn()
+        barrier(world)
+        clk.begin()
         t0.record()
         for i in range(args.steps):
             lib.flare_set_kernel_events(ev_b[i].cuda_event, ev_e[i].cuda_event)
@@ -161,6 +184,7 @@ def bench_prefill(args, rank, world):
         t1.record()
         lib.flare_set_kernel_events(None, None)
         barrier(world)
+        clk.hold_load(fn)  # the same workload, untimed, until nvidia-smi has sampled it a few times
     launches = lib.flare_last_launch_count() * args.steps
     ms = t0.elapsed_time(t1)
     ms = max_over_ranks(ms, world)
