@@ -50,23 +50,29 @@ class ClockSampler:
     nvidia-smi takes a while to come up and its start-up holds driver locks that stall kernel launches, so the sampler
     is started - and has delivered its first sample - before the warm-up; ``begin()`` marks the start of the timed
     region, and ``hold_load()`` keeps the same (untimed) workload running after it until a few samples have been taken
-    under that load (the timed region itself is a few milliseconds, the sampling period 20 ms)."""
+    under that load (the timed region itself is a few milliseconds).  One process, on rank 0, samples all GPUs of the
+    job: every query takes driver locks that delay launches on every GPU of the node, and eight pollers at 20 ms cost
+    the slowest of eight ranks 0.7 ms of a 10 ms timed region."""
 
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, index: int):
-        self.index = index
+    def __init__(self, indices, active: bool = True):
+        self.indices = list(indices)
+        self.active = active
         self.samples = []
         self.first = 0  # samples before this index were taken before the timed region
         self.proc = None
         self.up = threading.Event()
 
     def __enter__(self):
+        if not self.active:
+            return self
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                ["nvidia-smi", "-i", ",".join(str(i) for i in self.indices), f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "20" if len(self.indices) == 1 else "50"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
             self.up.wait(timeout=3.0)
@@ -84,12 +90,14 @@ class ClockSampler:
     def begin(self):
         self.first = len(self.samples)
 
-    def hold_load(self, fn, min_samples=4, max_seconds=0.5):
-        """Run ``fn`` (the timed step, now untimed) until ``min_samples`` samples have been taken since ``begin()``."""
-        if self.proc is None or not self.up.is_set():
+    def hold_load(self, fn, polls=4, max_seconds=0.5):
+        """Run ``fn`` (the timed step, now untimed) until ``polls`` queries have been answered since ``begin()``; ranks
+        without the sampler keep their GPU under the same load for as long as that takes at most."""
+        if self.active and (self.proc is None or not self.up.is_set()):
             return
-        end = time.monotonic() + max_seconds
-        while len(self.samples) - self.first < min_samples and time.monotonic() < end:
+        end = time.monotonic() + (max_seconds if self.active else 0.3)
+        want = polls * len(self.indices)
+        while (not self.active or len(self.samples) - self.first < want) and time.monotonic() < end:
             for _ in range(8):
                 fn()
             torch.cuda.current_stream().synchronize()
@@ -172,7 +180,7 @@ def bench_prefill(args, rank, world):
         e.record()  # materialise the handles
     t0 = torch.cuda.Event(enable_timing=True)
     t1 = torch.cuda.Event(enable_timing=True)
-    with ClockSampler(torch.cuda.current_device()) as clk:
+    with ClockSampler(range(world), active=rank == 0) as clk:
         for _ in range(args.warmup):
             fn()
         barrier(world)
