@@ -164,3 +164,22 @@ def test_fp16_training_step_through_autograd():
         assert got.dtype == F16
         assert_bf16_gate(got, ref[key], f"fp16 autograd {key}", max_abs=max(2e-2, float(ref[key].abs().max()) * 2.0 ** -7),
                          rel_l2=8e-3)
+
+
+def test_fp16_through_the_entry_point_that_allocates_nothing():
+    # the bf16 copies live in the library's built-in scratch when they fit it (same bits as flare_forward with a
+    # workspace); when they do not, the call runs on the exact kernels, which read fp16 directly
+    lib = _lib.load()
+    cap = lib.flare_noalloc_scratch_capacity()
+    stream = torch.cuda.current_stream().cuda_stream
+    for (B, N, H, M, D), fits in (((1, 1024, 2, 64, 64), True), ((2, 8192, 8, 64, 64), False)):
+        q, k, v = to_dev(*orc.make_inputs(B, N, H, M, D, seed0=57, dtype=F16))
+        y = torch.full_like(v, float("nan"))
+        args = _lib.make_fwd_args(q, k, v, None, None, y, scale=D ** -0.5)
+        need = lib.flare_forward_workspace_bytes(C.byref(args))
+        assert (need <= cap) == fits
+        assert lib.flare_forward_noalloc(C.byref(args), stream) == 0
+        torch.cuda.synchronize()
+        want = _ops.forward(q, k, v, scale=D ** -0.5, path=_lib.PATH_AUTO if fits else _lib.PATH_EXACT)[0]
+        assert torch.equal(y, want)
+    assert _ops.device_status() == 0
