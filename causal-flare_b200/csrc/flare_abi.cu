@@ -261,7 +261,17 @@ int launch_guard_walk(const flare_fwd_args_t* a, const int* lane_gates, cudaStre
   return launch_walk_exact(w, 1, stream);
 }
 
-int forward_run(const flare_fwd_args_t* a, cudaStream_t stream) {
+// What an fp16 call that runs on bf16 copies (forward_cast below) still has to do once the tensor kernels are enqueued:
+// y back to fp16, and then the standby walk of the flagged lanes on the caller's own fp16 tensors, so that the lanes
+// whose score spreads left the tensor kernels' domain - where the rounding of q and k to bf16 would move the scores
+// most - are computed from the unrounded inputs.
+struct FinishCast {
+  const flare_fwd_args_t* orig;
+  const CastParams* y_back;  // null: no y wanted
+  bool y_done;
+};
+
+int forward_run(const flare_fwd_args_t* a, cudaStream_t stream, FinishCast* fin = nullptr) {
   const FwdPlan pl = plan_forward(a);
   if (g_keep.u != nullptr) return forward_tensor_or_exact(a, pl, stream);  // the backward's own replay of the forward
   const int64_t lanes = (int64_t)a->B * a->H;
@@ -295,7 +305,16 @@ int forward_run(const flare_fwd_args_t* a, cudaStream_t stream) {
   g_keep = ChunkStates{nullptr, nullptr, nullptr, 0};
   if (rc != FLARE_OK) return rc;
   if (a->path == FLARE_PATH_AUTO && a->lengths == nullptr) {
-    rc = launch_guard_walk(a, gate + 1, stream);
+    const flare_fwd_args_t* walk_args = a;
+    if (fin != nullptr) {
+      if (fin->y_back != nullptr) {
+        rc = launch_cast_rows(*fin->y_back, stream);
+        if (rc != FLARE_OK) return rc;
+        fin->y_done = true;
+      }
+      walk_args = fin->orig;
+    }
+    rc = launch_guard_walk(walk_args, gate + 1, stream);
     g_last_launches += 1;
   }
   return rc;
@@ -359,7 +378,8 @@ int forward_tensor_or_exact(const flare_fwd_args_t* a, const FwdPlan& pl, cudaSt
 // fp16 inputs on the tensor-core kernels.  The kernels multiply bf16 operands (the tensor-core products of E, R, W
 // and the running state are bf16 whatever the inputs are), so an fp16 call is served by rounding q, k, v to bf16
 // copies in the workspace, running the bf16 forward on those, and writing y back as fp16: three streaming passes
-// around a kernel that is 40 to 60 times faster than the exact walk the call would otherwise take.  States and
+// around a kernel that is 40 to 60 times faster than the exact walk the call would otherwise take.  Lanes that the
+// kernels flag as outside their numeric domain are recomputed by the exact kernels from the fp16 tensors themselves.  States and
 // log-sum-exps are fp32 on both sides and go straight to the caller's buffers.  Not for the training forward (no
 // state is kept for a backward) and not with separate decode weights or a mask, which the tensor kernels do not take.
 struct CastPlan {
@@ -416,15 +436,19 @@ int forward_cast(const flare_fwd_args_t* a, flare_fwd_args_t& b, const CastPlan&
   c.os0 = b.v_stride_b; c.os1 = b.v_stride_n; c.os2 = b.v_stride_h;
   rc = launch_cast_rows(c, stream);
   if (rc != FLARE_OK) return rc;
-  rc = forward_run(&b, stream);  // with its own gate words and exact standby, on the bf16 copies
+  CastParams yb = c;
+  yb.in = b.y; yb.out = a->y; yb.to_f16 = 1;
+  yb.is0 = b.y_stride_b; yb.is1 = b.y_stride_n; yb.is2 = b.y_stride_h;
+  yb.os0 = a->y_stride_b; yb.os1 = a->y_stride_n; yb.os2 = a->y_stride_h;
+  FinishCast fin{a, a->y != nullptr ? &yb : nullptr, false};
+  rc = forward_run(&b, stream, &fin);  // gate words in b's workspace; the standby walk reads the caller's fp16 tensors
   if (rc != FLARE_OK) return rc;
   int casts = 3;
   if (a->y != nullptr) {
-    c.in = b.y; c.out = a->y; c.to_f16 = 1;
-    c.is0 = b.y_stride_b; c.is1 = b.y_stride_n; c.is2 = b.y_stride_h;
-    c.os0 = a->y_stride_b; c.os1 = a->y_stride_n; c.os2 = a->y_stride_h;
-    rc = launch_cast_rows(c, stream);
-    if (rc != FLARE_OK) return rc;
+    if (!fin.y_done) {  // no standby on this path (forced tensor path, per-row lengths)
+      rc = launch_cast_rows(yb, stream);
+      if (rc != FLARE_OK) return rc;
+    }
     ++casts;
   }
   g_last_launches += casts;

@@ -107,14 +107,27 @@ def test_fp16_masked_rows_and_sharp_scores_keep_the_default_path_correct():
         ref = orc.ar_forward(q, k[b:b + 1, :n], v[b:b + 1, :n], scale=D ** -0.5)
         assert_bf16_gate(y[b:b + 1, :n], ref, f"fp16 masked row {b}")
         assert float(y[b, n:].abs().max()) == 0.0
-    # score spreads of hundreds of nats: the kernels flag the lanes, the exact kernels finish them (on the bf16 copies)
+    # score spreads of hundreds of nats: the kernels flag the lanes and the exact kernels recompute them from the fp16
+    # tensors themselves (rounding q and k to bf16 would move such scores by more than a nat); a lane that stayed in
+    # the kernels' domain is held to the oracle on the bf16 copies instead
     qs, ks = (q.float() * 8).to(F16), (k.float() * 8).to(F16)
-    ref = orc.ar_forward(qs.bfloat16(), ks.bfloat16(), v.bfloat16(), scale=D ** -0.5)
+    ref_h = orc.ar_forward(qs, ks, v, scale=D ** -0.5).float()
+    ref_b = orc.ar_forward(qs.bfloat16(), ks.bfloat16(), v.bfloat16(), scale=D ** -0.5).float()
     ysh, _, _, _ = _ops.forward(qs.cuda(), ks.cuda(), vc, scale=D ** -0.5)
-    assert _ops.device_status() in (0, 2)  # 2: the exact kernels had to step in (informational)
+    status = _ops.device_status()
+    assert status in (0, 2)  # 2: the exact kernels had to step in (informational)
     assert ysh.dtype == F16
-    assert_bf16_gate(ysh, ref.float(), "fp16 sharp scores on the default path",
-                     max_abs=max(2e-2, 1e-2 * float(ref.float().abs().max())))
+    from_fp16 = 0
+    for b in range(B):
+        for h in range(H):
+            got = ysh[b:b + 1, :, h:h + 1]
+            bound = max(2e-2, 1e-2 * float(ref_h.abs().max()))
+            try:
+                assert_bf16_gate(got, ref_h[b:b + 1, :, h:h + 1], f"fp16 sharp scores, lane ({b}, {h})", max_abs=bound)
+                from_fp16 += 1
+            except AssertionError:
+                assert_bf16_gate(got, ref_b[b:b + 1, :, h:h + 1], f"fp16 sharp scores, lane ({b}, {h}), bf16 copies", max_abs=bound)
+    assert status == 0 or from_fp16 > 0, "flagged lanes must come from the fp16 tensors"
 
 
 @pytest.mark.parametrize("B, N, H, M, Dk, Dv, bs, variant", [
