@@ -379,9 +379,10 @@ int forward_tensor_or_exact(const flare_fwd_args_t* a, const FwdPlan& pl, cudaSt
 // and the running state are bf16 whatever the inputs are), so an fp16 call is served by rounding q, k, v to bf16
 // copies in the workspace, running the bf16 forward on those, and writing y back as fp16: three streaming passes
 // around a kernel that is 40 to 60 times faster than the exact walk the call would otherwise take.  Lanes that the
-// kernels flag as outside their numeric domain are recomputed by the exact kernels from the fp16 tensors themselves.  States and
-// log-sum-exps are fp32 on both sides and go straight to the caller's buffers.  Not for the training forward (no
-// state is kept for a backward) and not with separate decode weights or a mask, which the tensor kernels do not take.
+// kernels flag as outside their numeric domain are recomputed by the exact kernels from the fp16 tensors themselves.
+// States and log-sum-exps are fp32 on both sides and go straight to the caller's buffers.  Not for the training
+// forward (no state is kept for a backward) and not with separate decode weights or a mask, which the tensor kernels
+// do not take.
 struct CastPlan {
   bool on;
   size_t off_q, off_k, off_v, off_y, total;
